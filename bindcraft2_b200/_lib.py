@@ -1,0 +1,51 @@
+"""ctypes binding of the C ABI declared in ``include/bc2_b200.h``."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+_LIB = None
+
+_vp, _i64, _i32, _cp = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_char_p
+
+# name -> (restype, argtypes); one entry per function the header declares
+PROTOTYPES = {
+    'bc2_evoformer_fwd': (_i32, [_vp] * 6 + [_i64] * 8 + [_cp] + [_vp] * 4),
+    'bc2_evoformer_bwd': (_i32, [_vp] * 8 + [_i64] * 7 + [_cp] + [_vp] * 2),
+    'native_stack_prealloc': (_i32, [_i32, _i32, _i32, _cp, _i32, _i32, _i32]),
+    'native_save_slots_probe': (_i32, [_i32, _i32]),
+    'bc2_release_all': (None, []),
+    'bc2_last_error': (_cp, []),
+    'bc2_device_status': (_i32, []),
+    'bc2_launch_count': (_i64, []),
+    'bc2_test_gemm': (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i64, _i32, _i32]),
+    'bc2_test_attention': (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _i32]),
+}
+
+
+def lib_path() -> str:
+    return os.environ.get('BC2_NATIVE_LIB', _build.LIB)  # same override variable as the reference (native.py:57)
+
+
+def load() -> ctypes.CDLL:
+    """Loads the library; raises if it has not been built.  There is deliberately no fallback."""
+    global _LIB
+    if _LIB is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise RuntimeError(f'no kernel library at {path}: build it with `python -m bindcraft2_b200.build` '
+                               '(needs nvcc; the kernels are sm_100a only)')
+        lib = ctypes.CDLL(path)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = lib
+    return _LIB
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise RuntimeError('bc2_b200: ' + load().bc2_last_error().decode())

@@ -1,0 +1,39 @@
+"""Builds ``libbc2_b200.so`` in-tree with nvcc for sm_100a (cross-compiles without a GPU)."""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB = os.path.join(HERE, 'libbc2_b200.so')
+SOURCES = [os.path.join(HERE, 'csrc', 'abi.cu')]
+
+
+def _newest_source() -> float:
+    t = 0.0
+    for root in (os.path.join(HERE, 'csrc'), os.path.join(os.path.dirname(HERE), 'include')):
+        for f in os.listdir(root):
+            if f.endswith(('.cu', '.cuh', '.h')):
+                t = max(t, os.path.getmtime(os.path.join(root, f)))
+    return t
+
+
+def stale() -> bool:
+    """True when the library is missing or older than a source file (the reference refuses such a library,
+    bindcraft/af/native.py:60-98)."""
+    return not os.path.exists(LIB) or os.path.getmtime(LIB) < _newest_source()
+
+
+def build(force: bool = False, extra_flags=()) -> str:
+    if not force and not stale():
+        return LIB
+    nvcc = shutil.which('nvcc') or '/usr/local/cuda/bin/nvcc'
+    cmd = [nvcc, '-gencode', 'arch=compute_100a,code=sm_100a', '-std=c++17', '-O3', '-lineinfo',
+           '-Xcompiler', '-fPIC', '-shared', *extra_flags, *SOURCES, '-o', LIB, '-lcudart']
+    subprocess.run(cmd, check=True)
+    return LIB
+
+
+if __name__ == '__main__':
+    print(build(force=True))

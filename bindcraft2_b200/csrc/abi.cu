@@ -1,0 +1,193 @@
+// extern "C" surface of the library (declared in include/bc2_b200.h): the bodies of the reference's FFI handlers for
+// the Evoformer stack (native/ffi.cu:183-371) on top of EvoStack, the trace-time entry points, and small bring-up
+// calls used by the unit tests.
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "../../include/bc2_b200.h"
+#include "stack.cuh"
+
+namespace {
+
+using namespace bc2;
+
+thread_local std::string t_error;
+
+int fail(const std::exception& e) {
+  t_error = e.what();
+  fprintf(stderr, "native: error: %s\n", e.what());
+  return 1;
+}
+
+// Stack objects are cached per (shape, depth, flags, weights_dir), as the reference does (ffi.cu:125-175), behind
+// one process-wide mutex (ffi.cu:79-86): a background thread may build the next length while the main one runs.
+std::recursive_mutex g_mu;
+using Key = std::tuple<int, int, int, int, int, int, std::string>;
+std::map<Key, std::unique_ptr<EvoStack>> g_stacks;
+
+EvoStack* get_stack(int N, int S, int depth, const std::string& dir, bool pair_only, bool opm_first) {
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  Key k{dev, N, S, depth, pair_only ? 1 : 0, opm_first ? 1 : 0, dir};
+  auto it = g_stacks.find(k);
+  if (it != g_stacks.end()) return it->second.get();
+  StackConfig c;
+  c.N = N;
+  c.S = S;
+  c.depth = depth;
+  c.pair_only = pair_only;
+  c.opm_first = opm_first;
+  auto s = std::make_unique<EvoStack>(c, dir);
+  EvoStack* p = s.get();
+  g_stacks.emplace(k, std::move(s));
+  return p;
+}
+
+}  // namespace
+
+extern "C" {
+
+int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
+                      const uint32_t* /*seed*/, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t pair_only,
+                      int64_t /*own_save*/, int64_t opm_first, int64_t /*dropout*/, const char* weights_dir,
+                      float* pair_out, float* msa_out, uint16_t* psave, float* msave) {
+  try {
+    BC2_CHECK(pair && msa && pair_mask && msa_mask && pair_out && msa_out && weights_dir, "null operand");
+    BC2_CHECK(!save || (psave && msave), "save != 0 needs psave and msave");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
+    s->forward(pair, msa, pair_mask, msa_mask, pair_out, msa_out, save ? reinterpret_cast<bf16*>(psave) : nullptr,
+               save ? msave : nullptr, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
+                      const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* /*seed*/,
+                      int64_t N, int64_t S, int64_t depth, int64_t pair_only, int64_t /*own_save*/, int64_t opm_first,
+                      int64_t /*dropout*/, const char* weights_dir, float* dpair, float* dmsa) {
+  try {
+    BC2_CHECK(ct_pair && ct_msa && pair_mask && msa_mask && psave && msave && dpair && dmsa && weights_dir, "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
+    s->backward(ct_pair, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave), msave, dpair, dmsa,
+                (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int native_stack_prealloc(int N, int S, int depth, const char* weights_dir, int pair_only, int opm_first, int /*dropout*/) {
+  try {
+    size_t f0 = 0, f1 = 0, tot = 0;
+    BC2_CUDA(cudaMemGetInfo(&f0, &tot));
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    get_stack(N, S, depth, weights_dir, pair_only != 0, opm_first != 0);
+    BC2_CUDA(cudaMemGetInfo(&f1, &tot));
+    fprintf(stderr, "native: prealloc N=%d S=%d depth=%d pair_only=%d took %.2f GB (%.2f of %.2f GB free after)\n", N, S,
+            depth, pair_only, (f0 - f1) / 1e9, f1 / 1e9, tot / 1e9);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int native_save_slots_probe(int depth, int /*n*/) { return depth; }
+
+void bc2_release_all(void) {
+  std::lock_guard<std::recursive_mutex> lock(g_mu);
+  g_stacks.clear();
+}
+
+const char* bc2_last_error(void) { return t_error.c_str(); }
+
+int bc2_device_status(void) {
+  unsigned h[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(h, g_dev_status, sizeof(h)) != cudaSuccess) return -1;
+  if (h[0]) {
+    unsigned z[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_dev_status, z, sizeof(z));
+    fprintf(stderr, "native: a bounded wait gave up at site %u (block %u)\n", h[0], h[1]);
+  }
+  return (int)h[0];
+}
+
+int64_t bc2_launch_count(void) { return launch_counter().load(); }
+
+int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, int a_mn, const uint16_t* b, int64_t ldb,
+                  int64_t b_bs, int b_mn, uint16_t* d, int64_t M, int64_t N, int64_t K, int64_t batch, int bn,
+                  int use_ref) {
+  try {
+    Operand oa{reinterpret_cast<const bf16*>(a), (long)lda, (long)a_bs, a_mn != 0};
+    Operand ob{reinterpret_cast<const bf16*>(b), (long)ldb, (long)b_bs, b_mn != 0};
+    GemmPlan p = make_gemm(oa, ob, (int)M, (int)N, (int)K, (int)batch, bn, use_ref != 0);
+    EpiStore e;
+    e.out = reinterpret_cast<bf16*>(d);
+    e.ldo = N;
+    e.bso = M * N;
+    e.M = (int)M;
+    e.N = (int)N;
+    run_gemm(p, e, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, const uint16_t* d_og,
+                       int64_t B, int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og, uint16_t* d_qkvg,
+                       float* d_bias, int use_ref) {
+  try {
+    cudaStream_t st = (cudaStream_t)stream;
+    DeviceArena A;
+    const int HD = (int)(H * D);
+    const long rows = B * N;
+    BC2_CHECK(!transposed || B == N, "transposed orientation needs a square [N,N] batch");
+    AttnPlan plan;
+    AttnArgs& a = plan.args;
+    a.qkvg = reinterpret_cast<const bf16*>(qkvg);
+    a.ld = 4 * HD;
+    a.row_b = transposed ? 1 : N;
+    a.row_p = transposed ? N : 1;
+    a.B = (int)B; a.N = (int)N; a.H = (int)H; a.D = (int)D;
+    a.bias = bias;
+    a.mask = mask;
+    a.mask_b = transposed ? 1 : N;
+    a.mask_k = transposed ? N : 1;
+    bf16* o = A.alloc<bf16>(rows * HD);
+    bf16* d_o = A.alloc<bf16>(rows * HD);
+    a.o = o;
+    a.og = reinterpret_cast<bf16*>(og);
+    a.lse = A.alloc<float>(B * H * N);
+    float* delta = A.alloc<float>(B * H * N);
+    a.d_o = d_o;
+    a.delta = delta;
+    a.d_qkv = reinterpret_cast<bf16*>(d_qkvg);
+    a.d_bias = d_bias;
+    a.dq_acc = A.alloc<float>(rows * HD);
+    plan.rows = rows;
+    plan.ref_dkv = A.alloc<float>(rows * 2 * HD);
+    attn_prepare(plan, use_ref != 0);
+    attn_fwd(plan, st);
+    AttnBwdPrepArgs p{reinterpret_cast<const bf16*>(d_og), o, a.qkvg, 4L * HD, d_o, a.d_qkv, delta, rows, a.row_b, a.row_p,
+                      (int)N, (int)H, (int)D};
+    attn_bwd_prep(p, st);
+    BC2_CUDA(cudaMemsetAsync(d_bias, 0, (size_t)H * N * N * 4, st));
+    attn_bwd(plan, st);
+    BC2_CUDA(cudaStreamSynchronize(st));
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,713 @@
+// Gated multi-head attention with a shared (non-batched) pair bias and a key mask: triangle attention around the
+// starting/ending node and MSA row attention (reference arithmetic: bindcraft/af/alphafold/model/modules.py:313-400
+// with bindcraft/af/accel.py:13-22: logits = q.k + 1e9(mask-1) + bias, clipped to +-1e8, softmax over keys).
+//
+// Operands live in one fused projection buffer  qkvg[row][4*H*D]  (q | k | v | sigmoid gate), q already scaled by
+// D^-1/2 through the packed weight.  Row of (batch b, position p) = b*row_b + p*row_p, so the ending-node variant
+// (attention along columns) is the same kernel with the two strides swapped and a transposed bias; nothing is
+// transposed in memory.
+//
+// Forward, one CTA per (128-query tile, head, batch row), flash style on tcgen05:
+//   TMA loads Q, all K and all V of the (b,h) into swizzled shared memory;
+//   S = Q K^T for a 128-key block is one tcgen05.mma chain into TMEM; 128 softmax threads (one query row each)
+//   read it back with tcgen05.ld, add bias and mask, keep the running max/sum in registers (online softmax, base 2),
+//   write P as a bf16 K-major swizzled operand; O_blk = P V is a second MMA; the running output is rescaled in
+//   registers.  Outputs: o (ungated), og = o*gate, and the base-2 log-sum-exp per row for the backward.
+//
+// Backward, one CTA per (head, batch row) (<= 256 keys per CTA; larger N splits keys over CTAs and accumulates dQ
+// with fp32 atomics): recomputes S and P from the saved log-sum-exp, forms dP = dO V^T, dS = P (dP - delta) and the
+// three gradient MMAs dV += P^T dO, dK += dS^T Q, dQ += dS K reusing the same shared-memory tiles as K-major or
+// MN-major operands.  The bias gradient (a sum over batch rows) is accumulated with vector fp32 atomics.
+#pragma once
+#include "common.cuh"
+#include "gemm.cuh"
+
+namespace bc2 {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kClip = 1e8f;
+
+// Clipped logit (natural-log units) of one (query, key) pair; keys beyond N (tile padding) are -inf so they get
+// zero weight even when every real key of the row is masked (the reference then attends uniformly to the N keys).
+__device__ __forceinline__ float attn_logit(float s, float mk, const float* brow, int k, int N) {
+  if (k >= N) return -INFINITY;
+  float t = s + mk;
+  if (brow) t += brow[k];
+  return fminf(fmaxf(t, -kClip), kClip);
+}
+
+struct AttnArgs {
+  // fused projections
+  const bf16* qkvg = nullptr;
+  long ld = 0;          // row length of qkvg (= 4*H*D)
+  long row_b = 0, row_p = 0;
+  int B = 0, N = 0, H = 0, D = 0;
+  const float* bias = nullptr;  // [H][N][N] (query, key) or null
+  const float* mask = nullptr;  // key mask, element (b, k) at mask[b*mask_b + k*mask_k]
+  long mask_b = 0, mask_k = 0;
+  bf16* o = nullptr;    // [rows][H*D] ungated output
+  bf16* og = nullptr;   // [rows][H*D] gated output
+  float* lse = nullptr; // [B][H][N] base-2 log-sum-exp
+  // backward only
+  const bf16* d_o = nullptr;   // [rows][H*D] gradient wrt the ungated output
+  const float* delta = nullptr; // [B][H][N] rowsum(dO * O)
+  bf16* d_qkv = nullptr;       // [rows][ld]: dq | dk | dv written into the first 3*H*D columns
+  float* d_bias = nullptr;     // [H][N][N], accumulated atomically (must be zeroed by the caller)
+  float* dq_acc = nullptr;     // [rows][H*D] fp32, only when keys are split over several CTAs
+};
+
+struct AttnMaps {
+  CUtensorMap qkvg;  // box {D, 128 positions, 1 batch}
+  CUtensorMap d_o;   // same box over d_o (backward)
+  bool ready = false;
+};
+
+inline CUtensorMap attn_tmap(const bf16* base, long ld, long row_b, long row_p, int B, int N, int D) {
+  uint64_t d[3] = {(uint64_t)ld, (uint64_t)N, (uint64_t)B};
+  uint64_t s[3] = {1, (uint64_t)(row_p * ld), (uint64_t)(row_b * ld)};
+  uint32_t b[3] = {(uint32_t)D, 128, 1};
+  return make_tmap(base, 3, d, s, b, 2 * D);
+}
+
+// Descriptor helpers for [rows][D] bf16 tiles whose rows are exactly one swizzle span (2*D bytes: 64B or 32B).
+// K-major view: operand rows = tile rows, reduction along D.  8-row groups are 16*D bytes apart.
+template <int D>
+__device__ __forceinline__ uint64_t desc_rows_kmajor(uint32_t saddr, int k16) {
+  return umma_desc(saddr + k16 * 32, 16, 16 * D, D == 32 ? 4 : 6);
+}
+// MN-major view of the same memory: operand rows (N or M of the MMA) = D, reduction along tile rows.
+// 8 reduction rows form one 16*D-byte atom; a K=16 step covers two atoms.
+template <int D>
+__device__ __forceinline__ uint64_t desc_rows_mnmajor(uint32_t saddr, int k16) {
+  return umma_desc(saddr + k16 * 32 * D, 16 * D, 16 * D, D == 32 ? 4 : 6);
+}
+// P / dS tiles: [128 rows][128 cols] bf16 as two 64-column 128B-swizzled blocks of 16 KB.
+// K-major view (rows = MMA M, reduction along columns): k16 in 0..7.
+__device__ __forceinline__ uint64_t desc_p_kmajor(uint32_t saddr, int k16) {
+  return umma_desc(saddr + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024, 2);
+}
+// MN-major view (columns = MMA M, reduction along rows): 128 M = two 64-wide blocks 16 KB apart (LBO);
+// 8 reduction rows per 1024-byte atom (SBO), a K=16 step covers two atoms.
+__device__ __forceinline__ uint64_t desc_p_mnmajor(uint32_t saddr, int k16) {
+  return umma_desc(saddr + k16 * 2048, 16384, 1024, 2);
+}
+
+// ------------------------------------------------------------------------------------------- forward (tcgen05)
+template <int D>
+__global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int nkb = cdiv(a.N, 128);
+  constexpr int TILE = 128 * D * 2;  // bytes of a [128][D] tile
+  uint8_t* sP = smem;                 // 32 KB
+  uint8_t* sQ = sP + 32768;
+  uint8_t* sK = sQ + TILE;
+  uint8_t* sV = sK + nkb * TILE;
+  float* sMask = reinterpret_cast<float*>(sV + nkb * TILE);  // [nkb*128] additive key mask (natural-log units)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + nkb * 128);
+  uint64_t* b_load = bars;       // Q, K, V landed
+  uint64_t* b_s = bars + 1;      // S block ready in TMEM
+  uint64_t* b_p = bars + 2;      // P block written to smem (128 arrivals)
+  uint64_t* b_o = bars + 3;      // O block ready in TMEM
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * 128, h = blockIdx.y, b = blockIdx.z;
+  const int HD = a.H * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_load, 1);
+    mbar_init(b_s, 1);
+    mbar_init(b_p, 128);
+    mbar_init(b_o, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm);
+  }
+  if (warp == 1) tmem_alloc(tslot, 256);
+  for (int k = threadIdx.x; k < nkb * 128; k += blockDim.x) {
+    float mk = 0.f;
+    if (k < a.N && a.mask) mk = 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
+    sMask[k] = mk;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tslot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(b_load, TILE * (1 + 2 * nkb));
+      tma_load_3d(sQ, &tm, b_load, h * D, q0, b);
+      for (int j = 0; j < nkb; ++j) {
+        tma_load_3d(sK + j * TILE, &tm, b_load, HD + h * D, j * 128, b);
+        tma_load_3d(sV + j * TILE, &tm, b_load, 2 * HD + h * D, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idS = umma_idesc(128, 128, 0, 0);
+      constexpr uint32_t idO = umma_idesc(128, D, 0, 1);
+      bool ok = mbar_wait(b_load, 0, SITE_ATTN);
+      tc_fence_after();
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      auto issue_s = [&](int j) {
+        const uint32_t aK = smem_u32(sK + j * TILE);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_ss(tS, desc_rows_kmajor<D>(aQ, k), desc_rows_kmajor<D>(aK, k), idS, k > 0 ? 1u : 0u);
+        umma_commit(b_s);
+      };
+      if (ok) issue_s(0);
+      for (int j = 0; j < nkb && ok; ++j) {
+        ok = mbar_wait(b_p, j & 1, SITE_ATTN);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + j * TILE);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_ss(tO, desc_p_kmajor(aP, k), desc_rows_mnmajor<D>(aV, k), idO, k > 0 ? 1u : 0u);
+        umma_commit(b_o);
+        if (j + 1 < nkb) issue_s(j + 1);
+      }
+    }
+  } else {
+    // softmax threads: warps 2..5, TMEM lane quarter = warp & 3
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const int q = q0 + r;
+    const bool qin = q < a.N;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const float* brow = (a.bias && qin) ? a.bias + ((long)h * a.N + q) * a.N : nullptr;
+    float mrun = -INFINITY, lrun = 0.f;
+    float acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    float alpha_prev = 1.f;
+    bool ok = true;
+    for (int j = 0; j < nkb && ok; ++j) {
+      ok = mbar_wait(b_s, j & 1, SITE_ATTN);
+      if (!ok) break;
+      tc_fence_after();
+      // pass 1: block max (base-2 units)
+      float mblk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float s[32];
+        tmem_ld32(tS + lane_off + c * 32, s);
+        tmem_ld_wait();
+        const int k0 = j * 128 + c * 32;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mblk = fmaxf(mblk, attn_logit(s[i], sMask[k0 + i], brow, k0 + i, a.N));
+      }
+      const float mnew = fmaxf(mrun, mblk * kLog2e);
+      const float alpha = exp2f(mrun - mnew);  // 0 on the first block (mrun = -inf)
+      // fold the previous block's output in before P is overwritten (its MMA has finished once b_o flips)
+      if (j > 0) {
+        ok = mbar_wait(b_o, (j - 1) & 1, SITE_ATTN);
+        if (!ok) break;
+        tc_fence_after();
+        float ob[32];
+        tmem_ld32(tO + lane_off, ob);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < D; ++i) acc[i] = acc[i] * alpha_prev + ob[i];
+      }
+      // pass 2: probabilities, row sum, P tile
+      float lblk = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float s[32];
+        tmem_ld32(tS + lane_off + c * 32, s);
+        tmem_ld_wait();
+        const int k0 = j * 128 + c * 32;
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float t0 = attn_logit(s[i], sMask[k0 + i], brow, k0 + i, a.N);
+          const float t1 = attn_logit(s[i + 1], sMask[k0 + i + 1], brow, k0 + i + 1, a.N);
+          const float p0 = exp2f(t0 * kLog2e - mnew), p1 = exp2f(t1 * kLog2e - mnew);
+          lblk += p0 + p1;
+          pk[i >> 1] = pack_bf16(p0, p1);
+        }
+        // 32 keys = 4 chunks of 16 bytes; key column inside the 128-wide tile = c*32
+        uint8_t* blk = sP + (c >> 1) * 16384;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int chunk = (c & 1) * 4 + i;
+          *reinterpret_cast<uint4*>(blk + sw128_off(r, chunk)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+        }
+      }
+      lrun = lrun * alpha + lblk;
+      mrun = mnew;
+      alpha_prev = 1.f;  // acc is rescaled by `alpha` lazily: remember it for when this block's output arrives
+      // acc currently holds blocks < j at scale of the previous max; bring it to the new max now
+#pragma unroll
+      for (int i = 0; i < D; ++i) acc[i] *= alpha;
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(b_p);
+    }
+    if (ok) ok = mbar_wait(b_o, (nkb - 1) & 1, SITE_ATTN);
+    if (ok) {
+      tc_fence_after();
+      float ob[32];
+      tmem_ld32(tO + lane_off, ob);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < D; ++i) acc[i] += ob[i];
+      if (qin) {
+        const float inv = 1.f / lrun;
+        const long row = (long)b * a.row_b + (long)q * a.row_p;
+        const bf16* gp = a.qkvg + row * a.ld + 3 * HD + h * D;
+        bf16* op = a.o + row * HD + h * D;
+        bf16* ogp = a.og + row * HD + h * D;
+#pragma unroll
+        for (int i = 0; i < D; i += 8) {
+          uint4 g4 = *reinterpret_cast<const uint4*>(gp + i);
+          const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
+          uint32_t ow[4], ogw[4];
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float o0 = acc[i + 2 * t] * inv, o1 = acc[i + 2 * t + 1] * inv;
+            const float2 g = unpack_bf16(gw[t]);
+            ow[t] = pack_bf16(o0, o1);
+            ogw[t] = pack_bf16(o0 * g.x, o1 * g.y);
+          }
+          *reinterpret_cast<uint4*>(op + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          *reinterpret_cast<uint4*>(ogp + i) = make_uint4(ogw[0], ogw[1], ogw[2], ogw[3]);
+        }
+        a.lse[((long)b * a.H + h) * a.N + q] = mrun + log2f(lrun);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+inline int attn_fwd_smem(int N, int D) {
+  const int nkb = cdiv(N, 128);
+  return 1024 + 32768 + 128 * D * 2 * (1 + 2 * nkb) + nkb * 128 * 4 + 128;
+}
+
+// ------------------------------------------------------------------------------------------- backward (tcgen05)
+// One CTA per (key group of <=256 keys, head, batch row).  TMEM columns: S [0,128) dP [128,256) dQ [256,256+D)
+// dK [320 + jb*64, +D)  dV [352 + jb*64, +D) for the (<=2) key blocks jb of the group.
+template <int D>
+__global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm,
+                                                          const __grid_constant__ CUtensorMap tdo, AttnArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE = 128 * D * 2;
+  const int nqb = cdiv(a.N, 128);
+  const int kb0 = blockIdx.x * 2;
+  const int nkb = min(2, cdiv(a.N, 128) - kb0);
+  const bool split = gridDim.x > 1;
+  uint8_t* sP = smem;            // 32 KB  P  [128 q][128 k]
+  uint8_t* sDS = sP + 32768;     // 32 KB  dS [128 q][128 k]
+  uint8_t* sQ = sDS + 32768;     // [128][D]
+  uint8_t* sDO = sQ + TILE;      // [128][D]
+  uint8_t* sK = sDO + TILE;      // up to 2 tiles
+  uint8_t* sV = sK + 2 * TILE;   // up to 2 tiles
+  float* sMask = reinterpret_cast<float*>(sV + 2 * TILE);  // [256]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + 256);
+  uint64_t* b_kv = bars;        // K, V landed
+  uint64_t* b_q = bars + 1;     // Q, dO tile landed
+  uint64_t* b_s = bars + 2;     // S and dP ready
+  uint64_t* b_p = bars + 3;     // P and dS written (256 arrivals)
+  uint64_t* b_g = bars + 4;     // gradient MMAs of the step finished (smem tiles reusable)
+  uint64_t* b_qfree = bars + 5; // dQ read out by the epilogue threads (128 arrivals)
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 6);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int HD = a.H * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(b_kv, 1);
+    mbar_init(b_q, 1);
+    mbar_init(b_s, 1);
+    mbar_init(b_p, 256);
+    mbar_init(b_g, 1);
+    mbar_init(b_qfree, 128);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm);
+    tma_prefetch_desc(&tdo);
+  }
+  if (warp == 1) tmem_alloc(tslot, 512);
+  for (int k = threadIdx.x; k < 256; k += blockDim.x) {
+    const int kk = kb0 * 128 + k;
+    float mk = 0.f;
+    if (kk < a.N && a.mask) mk = 1e9f * (a.mask[(long)b * a.mask_b + (long)kk * a.mask_k] - 1.f);
+    sMask[k] = mk;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tslot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+  const int nsteps = nqb * nkb;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(b_kv, 2 * nkb * TILE);
+      for (int j = 0; j < nkb; ++j) {
+        tma_load_3d(sK + j * TILE, &tm, b_kv, HD + h * D, (kb0 + j) * 128, b);
+        tma_load_3d(sV + j * TILE, &tm, b_kv, 2 * HD + h * D, (kb0 + j) * 128, b);
+      }
+      bool ok = true;
+      for (int i = 0; i < nqb && ok; ++i) {
+        // the previous q tile's Q/dO are still operands of its last gradient MMAs
+        if (i > 0) ok = mbar_wait(b_g, (i * nkb - 1) & 1, SITE_ATTN_BWD);
+        if (!ok) break;
+        mbar_expect_tx(b_q, 2 * TILE);
+        tma_load_3d(sQ, &tm, b_q, h * D, i * 128, b);
+        tma_load_3d(sDO, &tdo, b_q, h * D, i * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idS = umma_idesc(128, 128, 0, 0);   // Q K^T, dO V^T : both K-major
+      constexpr uint32_t idKV = umma_idesc(128, D, 1, 1);    // P^T dO, dS^T Q : A MN-major, B MN-major
+      constexpr uint32_t idQ = umma_idesc(128, D, 0, 1);     // dS K : A K-major, B MN-major
+      bool ok = mbar_wait(b_kv, 0, SITE_ATTN_BWD);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aP = smem_u32(sP), aDS = smem_u32(sDS);
+      int step = 0;
+      for (int i = 0; i < nqb && ok; ++i) {
+        ok = mbar_wait(b_q, i & 1, SITE_ATTN_BWD);
+        for (int j = 0; j < nkb && ok; ++j, ++step) {
+          // S and dP overwrite TMEM the softmax threads read in the previous step: b_p of that step was waited on
+          // below before its gradient MMAs were issued, so the reads are complete.
+          tc_fence_after();
+          const uint32_t aK = smem_u32(sK + j * TILE), aV = smem_u32(sV + j * TILE);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_ss(tS, desc_rows_kmajor<D>(aQ, k), desc_rows_kmajor<D>(aK, k), idS, k > 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k)
+            umma_ss(tDP, desc_rows_kmajor<D>(aDO, k), desc_rows_kmajor<D>(aV, k), idS, k > 0 ? 1u : 0u);
+          umma_commit(b_s);
+          ok = mbar_wait(b_p, step & 1, SITE_ATTN_BWD);
+          if (!ok) break;
+          // dQ of the previous q tile must have been drained before the first accumulate of this one
+          if (j == 0 && i > 0) ok = mbar_wait(b_qfree, (i - 1) & 1, SITE_ATTN_BWD);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tDK = tmem + 320 + j * 64, tDV = tDK + 32;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)  // dV[key][d] += sum_q P[q][key] dO[q][d]
+            umma_ss(tDV, desc_p_mnmajor(aP, k), desc_rows_mnmajor<D>(aDO, k), idKV, (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)  // dK[key][d] += sum_q dS[q][key] Q[q][d]
+            umma_ss(tDK, desc_p_mnmajor(aDS, k), desc_rows_mnmajor<D>(aQ, k), idKV, (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)  // dQ[q][d] += sum_key dS[q][key] K[key][d]
+            umma_ss(tDQ, desc_p_kmajor(aDS, k), desc_rows_mnmajor<D>(aK, k), idQ, (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(b_g);
+        }
+      }
+    }
+  } else {
+    // 8 softmax warps: lane quarter = warp & 3, column half = (warp - 2) / 4
+    const int w = warp - 2;
+    const int qd = warp & 3, half = w >> 2;
+    const int r = qd * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    bool ok = true;
+    int step = 0;
+    for (int i = 0; i < nqb && ok; ++i) {
+      const int q = i * 128 + r;
+      const bool qin = q < a.N;
+      const long lidx = ((long)b * a.H + h) * a.N + q;
+      const float lse = qin ? a.lse[lidx] : 0.f;
+      const float dl = qin ? a.delta[lidx] : 0.f;
+      const float* brow = (a.bias && qin) ? a.bias + ((long)h * a.N + q) * a.N : nullptr;
+      float* dbrow = (a.d_bias && qin) ? a.d_bias + ((long)h * a.N + q) * a.N : nullptr;
+      for (int j = 0; j < nkb && ok; ++j, ++step) {
+        ok = mbar_wait(b_s, step & 1, SITE_ATTN_BWD);
+        if (!ok) break;
+        // P/dS tiles are operands of the previous step's gradient MMAs until b_g flips
+        if (step > 0) ok = mbar_wait(b_g, (step - 1) & 1, SITE_ATTN_BWD);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = half * 2 + cc;  // 32-key chunk inside the 128-key block
+          float s[32], dp[32];
+          tmem_ld32(tS + lane_off + c * 32, s);
+          tmem_ld32(tDP + lane_off + c * 32, dp);
+          tmem_ld_wait();
+          const int kl = j * 128 + c * 32;          // key index inside the group (mask)
+          const int k0 = (kb0 + j) * 128 + c * 32;  // global key index
+          uint32_t pk[16], dk[16];
+          float dsv[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            float t = s[e] + sMask[kl + e];
+            if (brow && k0 + e < a.N) t += brow[k0 + e];
+            const bool kin = k0 + e < a.N;
+            const bool live = qin && kin && (t >= -kClip) && (t <= kClip);
+            t = fminf(fmaxf(t, -kClip), kClip);
+            const float p = (qin && kin) ? exp2f(t * kLog2e - lse) : 0.f;
+            s[e] = p;
+            dsv[e] = live ? p * (dp[e] - dl) : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            pk[e >> 1] = pack_bf16(s[e], s[e + 1]);
+            dk[e >> 1] = pack_bf16(dsv[e], dsv[e + 1]);
+          }
+          uint8_t* pb = sP + (c >> 1) * 16384;
+          uint8_t* db = sDS + (c >> 1) * 16384;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const int chunk = (c & 1) * 4 + t;
+            *reinterpret_cast<uint4*>(pb + sw128_off(r, chunk)) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+            *reinterpret_cast<uint4*>(db + sw128_off(r, chunk)) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
+          }
+          if (dbrow) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              if (k0 + e < a.N)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dbrow + k0 + e), "f"(dsv[e]),
+                             "f"(dsv[e + 1]), "f"(dsv[e + 2]), "f"(dsv[e + 3])
+                             : "memory");
+            }
+          }
+        }
+        tc_fence_before();
+        fence_async_smem();
+        mbar_arrive(b_p);
+      }
+      // dQ of this q tile is complete once the last step's gradient MMAs finish
+      if (ok) ok = mbar_wait(b_g, (step - 1) & 1, SITE_ATTN_BWD);
+      if (ok && half == 0) {
+        tc_fence_after();
+        float dq[32];
+        tmem_ld32(tDQ + lane_off, dq);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(b_qfree);
+        if (qin) {
+          const long row = (long)b * a.row_b + (long)q * a.row_p;
+          if (!split) {
+            bf16* dst = a.d_qkv + row * a.ld + h * D;
+#pragma unroll
+            for (int e = 0; e < D; e += 8)
+              *reinterpret_cast<uint4*>(dst + e) = make_uint4(pack_bf16(dq[e], dq[e + 1]), pack_bf16(dq[e + 2], dq[e + 3]),
+                                                             pack_bf16(dq[e + 4], dq[e + 5]), pack_bf16(dq[e + 6], dq[e + 7]));
+          } else {
+            float* dst = a.dq_acc + row * HD + h * D;
+#pragma unroll
+            for (int e = 0; e < D; e += 4)
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e), "f"(dq[e]), "f"(dq[e + 1]),
+                           "f"(dq[e + 2]), "f"(dq[e + 3])
+                           : "memory");
+          }
+        }
+      }
+    }
+    // dK, dV: rows = keys; warps of column-half 0 write dK, half 1 write dV
+    if (ok) {
+      tc_fence_after();
+      for (int j = 0; j < nkb; ++j) {
+        const int key = (kb0 + j) * 128 + r;
+        float g[32];
+        tmem_ld32(tmem + 320 + j * 64 + half * 32 + lane_off, g);
+        tmem_ld_wait();
+        if (key < a.N) {
+          const long row = (long)b * a.row_b + (long)key * a.row_p;
+          bf16* dst = a.d_qkv + row * a.ld + (1 + half) * HD + h * D;
+#pragma unroll
+          for (int e = 0; e < D; e += 8)
+            *reinterpret_cast<uint4*>(dst + e) = make_uint4(pack_bf16(g[e], g[e + 1]), pack_bf16(g[e + 2], g[e + 3]),
+                                                           pack_bf16(g[e + 4], g[e + 5]), pack_bf16(g[e + 6], g[e + 7]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+template <int D>
+constexpr int attn_bwd_smem() {
+  return 1024 + 65536 + 128 * D * 2 * 6 + 256 * 4 + 128;
+}
+
+// ------------------------------------------------------------------------------------------- CUDA-core reference
+// One thread per (batch, head, query); used for bring-up and as the on-device reference in the unit tests.
+template <int D>
+__global__ void attn_fwd_ref_kernel(AttnArgs a) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long)a.B * a.H * a.N) return;
+  const int q = t % a.N, h = (t / a.N) % a.H, b = t / ((long)a.N * a.H);
+  const int HD = a.H * D;
+  const long rowq = (long)b * a.row_b + (long)q * a.row_p;
+  float qv[D];
+  for (int d = 0; d < D; ++d) qv[d] = __bfloat162float(a.qkvg[rowq * a.ld + h * D + d]);
+  float m = -INFINITY;
+  for (int k = 0; k < a.N; ++k) {
+    const long rowk = (long)b * a.row_b + (long)k * a.row_p;
+    float s = 0.f;
+    for (int d = 0; d < D; ++d) s += qv[d] * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
+    if (a.mask) s += 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
+    if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
+    s = fminf(fmaxf(s, -kClip), kClip);
+    m = fmaxf(m, s);
+  }
+  float l = 0.f, acc[D];
+  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+  for (int k = 0; k < a.N; ++k) {
+    const long rowk = (long)b * a.row_b + (long)k * a.row_p;
+    float s = 0.f;
+    for (int d = 0; d < D; ++d) s += qv[d] * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
+    if (a.mask) s += 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
+    if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
+    s = fminf(fmaxf(s, -kClip), kClip);
+    const float p = __expf(s - m);
+    l += p;
+    for (int d = 0; d < D; ++d) acc[d] += p * __bfloat162float(a.qkvg[rowk * a.ld + 2 * HD + h * D + d]);
+  }
+  for (int d = 0; d < D; ++d) {
+    const float o = acc[d] / l;
+    const float g = __bfloat162float(a.qkvg[rowq * a.ld + 3 * HD + h * D + d]);
+    a.o[rowq * HD + h * D + d] = __float2bfloat16(o);
+    a.og[rowq * HD + h * D + d] = __float2bfloat16(o * g);
+  }
+  a.lse[((long)b * a.H + h) * a.N + q] = (m + __logf(l)) * kLog2e;
+}
+
+// dq written directly; dk/dv accumulated with fp32 atomics into dkv_acc [rows][2*H*D] (zeroed by the caller).
+template <int D>
+__global__ void attn_bwd_ref_kernel(AttnArgs a, float* dkv_acc) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long)a.B * a.H * a.N) return;
+  const int q = t % a.N, h = (t / a.N) % a.H, b = t / ((long)a.N * a.H);
+  const int HD = a.H * D;
+  const long rowq = (long)b * a.row_b + (long)q * a.row_p;
+  const long lidx = ((long)b * a.H + h) * a.N + q;
+  float qv[D], dov[D], dq[D];
+  for (int d = 0; d < D; ++d) {
+    qv[d] = __bfloat162float(a.qkvg[rowq * a.ld + h * D + d]);
+    dov[d] = __bfloat162float(a.d_o[rowq * HD + h * D + d]);
+    dq[d] = 0.f;
+  }
+  const float lse = a.lse[lidx], dl = a.delta[lidx];
+  for (int k = 0; k < a.N; ++k) {
+    const long rowk = (long)b * a.row_b + (long)k * a.row_p;
+    float s = 0.f, dp = 0.f;
+    for (int d = 0; d < D; ++d) {
+      s += qv[d] * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
+      dp += dov[d] * __bfloat162float(a.qkvg[rowk * a.ld + 2 * HD + h * D + d]);
+    }
+    if (a.mask) s += 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
+    if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
+    const bool live = s >= -kClip && s <= kClip;
+    s = fminf(fmaxf(s, -kClip), kClip);
+    const float p = exp2f(s * kLog2e - lse);
+    const float ds = live ? p * (dp - dl) : 0.f;
+    if (a.d_bias) atomicAdd(a.d_bias + ((long)h * a.N + q) * a.N + k, ds);
+    for (int d = 0; d < D; ++d) {
+      dq[d] += ds * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
+      atomicAdd(dkv_acc + rowk * 2 * HD + h * D + d, ds * qv[d]);
+      atomicAdd(dkv_acc + rowk * 2 * HD + HD + h * D + d, p * dov[d]);
+    }
+  }
+  for (int d = 0; d < D; ++d) a.d_qkv[rowq * a.ld + h * D + d] = __float2bfloat16(dq[d]);
+}
+
+__global__ void attn_ref_dkv_store(const float* acc, bf16* d_qkv, long ld, long rows, int HD) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * 2 * HD) return;
+  const long row = t / (2 * HD);
+  const int c = t % (2 * HD);
+  d_qkv[row * ld + HD + c] = __float2bfloat16(acc[t]);
+}
+
+// fp32 dq accumulator -> bf16 dq columns (only when the backward split its keys over several CTAs)
+__global__ void attn_dq_store(const float* acc, bf16* d_qkv, long ld, long rows, int HD) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= rows * HD) return;
+  const long row = t / HD;
+  const int c = t % HD;
+  d_qkv[row * ld + c] = __float2bfloat16(acc[t]);
+}
+
+// ------------------------------------------------------------------------------------------- host side
+struct AttnPlan {
+  AttnArgs args;
+  CUtensorMap tm, tdo;
+  bool tc = false;
+  float* ref_dkv = nullptr;  // reference path scratch [rows][2*H*D]
+  long rows = 0;
+};
+
+inline void attn_prepare(AttnPlan& p, bool force_ref = false) {
+  const AttnArgs& a = p.args;
+  BC2_CHECK(a.D == 32 || a.D == 16, "attention head width must be 16 or 32");
+  p.tc = !kUseRefKernels && !force_ref;
+  if (p.tc) {
+    p.tm = attn_tmap(a.qkvg, a.ld, a.row_b, a.row_p, a.B, a.N, a.D);
+    if (a.d_o) p.tdo = attn_tmap(a.d_o, (long)a.H * a.D, a.row_b, a.row_p, a.B, a.N, a.D);
+  }
+}
+
+template <int D>
+inline void attn_fwd_launch(const AttnPlan& p, cudaStream_t st) {
+  const AttnArgs& a = p.args;
+  if (!p.tc) {
+    const long n = (long)a.B * a.H * a.N;
+    launch_counter()++; attn_fwd_ref_kernel<D><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(a);
+    return;
+  }
+  const int smem = attn_fwd_smem(a.N, D);
+  BC2_CHECK(smem <= 227 * 1024, "attention forward: too many keys for one CTA's shared memory");
+  static int set_for = 0;
+  if (smem > set_for) {
+    BC2_CUDA(cudaFuncSetAttribute(attn_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    set_for = smem;
+  }
+  dim3 grid(cdiv(a.N, 128), a.H, a.B);
+  launch_counter()++; attn_fwd_tc_kernel<D><<<grid, 192, smem, st>>>(p.tm, a);
+}
+
+template <int D>
+inline void attn_bwd_launch(const AttnPlan& p, cudaStream_t st) {
+  const AttnArgs& a = p.args;
+  const int HD = a.H * D;
+  if (!p.tc) {
+    BC2_CUDA(cudaMemsetAsync(p.ref_dkv, 0, (size_t)p.rows * 2 * HD * 4, st));
+    const long n = (long)a.B * a.H * a.N;
+    launch_counter()++; attn_bwd_ref_kernel<D><<<(unsigned)((n + 127) / 128), 128, 0, st>>>(a, p.ref_dkv);
+    const long m = p.rows * 2 * HD;
+    launch_counter()++; attn_ref_dkv_store<<<(unsigned)((m + 255) / 256), 256, 0, st>>>(p.ref_dkv, a.d_qkv, a.ld, p.rows, HD);
+    return;
+  }
+  constexpr int smem = attn_bwd_smem<D>();
+  static bool set = false;
+  if (!set) {
+    BC2_CUDA(cudaFuncSetAttribute(attn_bwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    set = true;
+  }
+  const int groups = cdiv(cdiv(a.N, 128), 2);
+  if (groups > 1) BC2_CUDA(cudaMemsetAsync(a.dq_acc, 0, (size_t)p.rows * HD * 4, st));
+  dim3 grid(groups, a.H, a.B);
+  launch_counter()++; attn_bwd_tc_kernel<D><<<grid, 320, smem, st>>>(p.tm, p.tdo, a);
+  if (groups > 1) {
+    const long m = p.rows * HD;
+    launch_counter()++; attn_dq_store<<<(unsigned)((m + 255) / 256), 256, 0, st>>>(a.dq_acc, a.d_qkv, a.ld, p.rows, HD);
+  }
+}
+
+inline void attn_fwd(const AttnPlan& p, cudaStream_t st) {
+  if (p.args.D == 32) attn_fwd_launch<32>(p, st);
+  else attn_fwd_launch<16>(p, st);
+}
+inline void attn_bwd(const AttnPlan& p, cudaStream_t st) {
+  if (p.args.D == 32) attn_bwd_launch<32>(p, st);
+  else attn_bwd_launch<16>(p, st);
+}
+
+}  // namespace bc2

@@ -1,0 +1,145 @@
+// Memory-bound glue kernels of the pair track: dtype conversion and the gating arithmetic of the triangle
+// multiplication and attention backward passes.  All use 64/128-bit accesses and keep reductions inside a warp.
+#pragma once
+#include "common.cuh"
+
+namespace bc2 {
+
+__global__ void __launch_bounds__(256) cvt_f32_bf16_kernel(const float4* __restrict__ in, uint2* __restrict__ out, long n4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const float4 v = in[i];
+    out[i] = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+  }
+}
+__global__ void __launch_bounds__(256) cvt_bf16_f32_kernel(const uint2* __restrict__ in, float4* __restrict__ out, long n4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const uint2 v = in[i];
+    const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y);
+    out[i] = make_float4(a.x, a.y, b.x, b.y);
+  }
+}
+inline int ew_grid(long n, int per_block) { return (int)std::min<long>((n + per_block - 1) / per_block, 148L * 16); }
+inline void cvt_f32_bf16(const float* in, bf16* out, long n, cudaStream_t st) {
+  launch_counter()++; cvt_f32_bf16_kernel<<<ew_grid(n / 4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n / 4);
+}
+inline void cvt_bf16_f32(const bf16* in, float* out, long n, cudaStream_t st) {
+  launch_counter()++; cvt_bf16_f32_kernel<<<ew_grid(n / 4, 256), 256, 0, st>>>(reinterpret_cast<const uint2*>(in), reinterpret_cast<float4*>(out), n / 4);
+}
+
+// Triangle multiplication backward, output side.  out = ob * g2 with ob = center-projection (+bias) and g2 the output
+// gate.  Given dz (fp32 cotangent of the residual):  d_ob = dz * g2  -> d_o [M,C];
+// d(gate pre-activation) = dz * ob * g2 * (1 - g2) -> columns [off, off+C) of the concatenated gradient buffer.
+__global__ void __launch_bounds__(256)
+trimul_bwd_out_kernel(const float4* __restrict__ dz, const uint2* __restrict__ ob, const uint2* __restrict__ g2,
+                      uint2* __restrict__ d_o, bf16* __restrict__ dcat, long ldd, int off, long M, int C) {
+  const int c4 = C / 4;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < M * c4; i += (long)gridDim.x * blockDim.x) {
+    const long m = i / c4;
+    const int c = (int)(i - m * c4) * 4;
+    const float4 z = dz[i];
+    const uint2 o2 = ob[i], g = g2[i];
+    const float2 o01 = unpack_bf16(o2.x), o23 = unpack_bf16(o2.y), g01 = unpack_bf16(g.x), g23 = unpack_bf16(g.y);
+    d_o[i] = make_uint2(pack_bf16(z.x * g01.x, z.y * g01.y), pack_bf16(z.z * g23.x, z.w * g23.y));
+    const float a = z.x * o01.x * g01.x * (1.f - g01.x), b = z.y * o01.y * g01.y * (1.f - g01.y);
+    const float cc = z.z * o23.x * g23.x * (1.f - g23.x), d = z.w * o23.y * g23.y * (1.f - g23.y);
+    *reinterpret_cast<uint2*>(dcat + m * ldd + off + c) = make_uint2(pack_bf16(a, b), pack_bf16(cc, d));
+  }
+}
+
+// Triangle multiplication backward, input side.  ab = mask * p * g was stored channel-major [CH][M]; its gradient
+// d_ab arrives channel-major as well.  Row-major outputs (operand of the projection backward GEMM):
+//   d_p    = d_ab * mask * g           at column (ch/128)*256 + ch%128
+//   d_gpre = d_ab * ab * (1 - g)       at that column + 128
+// which is the packing order of the fused projection|gate weight.  A block transposes a [64 ch x 64 pos] tile through
+// shared memory so both sides are coalesced.
+__global__ void __launch_bounds__(256)
+trimul_bwd_gate_kernel(const bf16* __restrict__ d_ab, const bf16* __restrict__ ab, const bf16* __restrict__ gate,
+                       const float* __restrict__ mask, bf16* __restrict__ dcat, long ldd, long M, int CH) {
+  __shared__ float sd[64][65], sa[64][65];
+  const long p0 = (long)blockIdx.x * 64;
+  const int c0 = blockIdx.y * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = warp; c < 64; c += 8) {
+    const long p = p0 + 2 * lane;
+    const float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(d_ab + (long)(c0 + c) * M + p));
+    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(ab + (long)(c0 + c) * M + p));
+    sd[c][2 * lane] = d.x; sd[c][2 * lane + 1] = d.y;
+    sa[c][2 * lane] = a.x; sa[c][2 * lane + 1] = a.y;
+  }
+  __syncthreads();
+  for (int r = warp; r < 64; r += 8) {
+    const long p = p0 + r;
+    const float mk = mask[p];
+    const int c = 2 * lane;
+    const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(gate + p * CH + c0 + c));
+    const float d0 = sd[c][r], d1 = sd[c + 1][r], a0 = sa[c][r], a1 = sa[c + 1][r];
+    const int ch = c0 + c;
+    const long col = (long)(ch / 128) * 256 + ch % 128;
+    *reinterpret_cast<uint32_t*>(dcat + p * ldd + col) = pack_bf16(d0 * mk * g.x, d1 * mk * g.y);
+    *reinterpret_cast<uint32_t*>(dcat + p * ldd + col + 128) = pack_bf16(d0 * a0 * (1.f - g.x), d1 * a1 * (1.f - g.y));
+  }
+}
+
+// Attention backward, output side.  og = o * gate.  Given d_og:
+//   d_o = d_og * gate (gradient wrt the ungated attention output), delta[b][h][q] = sum_d d_o * o,
+//   d(gate pre-activation) = d_og * o * gate * (1 - gate) -> columns [3HD, 4HD) of the projection-gradient buffer.
+// One warp per row; a head's D values sit in D/VPL adjacent lanes.
+struct AttnBwdPrepArgs {
+  const bf16* d_og; const bf16* o; const bf16* qkvg; long ld;
+  bf16* d_o; bf16* d_qkvg; float* delta;
+  long rows; long row_b, row_p; int N, H, D;
+};
+template <int HD>
+__global__ void __launch_bounds__(256) attn_bwd_prep_kernel(AttnBwdPrepArgs a) {
+  constexpr int VPL = HD / 32;
+  const int lane = threadIdx.x & 31;
+  const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (m >= a.rows) return;
+  const int c = lane * VPL;
+  float dg[VPL], ov[VPL], gv[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; i += 2) {
+    const float2 x = unpack_bf16(*reinterpret_cast<const uint32_t*>(a.d_og + m * HD + c + i));
+    const float2 y = unpack_bf16(*reinterpret_cast<const uint32_t*>(a.o + m * HD + c + i));
+    const float2 z = unpack_bf16(*reinterpret_cast<const uint32_t*>(a.qkvg + m * a.ld + 3 * HD + c + i));
+    dg[i] = x.x; dg[i + 1] = x.y; ov[i] = y.x; ov[i + 1] = y.y; gv[i] = z.x; gv[i + 1] = z.y;
+  }
+  float part = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; i += 2) {
+    const float d0 = dg[i] * gv[i], d1 = dg[i + 1] * gv[i + 1];
+    part += d0 * ov[i] + d1 * ov[i + 1];
+    *reinterpret_cast<uint32_t*>(a.d_o + m * HD + c + i) = pack_bf16(d0, d1);
+    *reinterpret_cast<uint32_t*>(a.d_qkvg + m * a.ld + 3 * HD + c + i) =
+        pack_bf16(dg[i] * ov[i] * gv[i] * (1.f - gv[i]), dg[i + 1] * ov[i + 1] * gv[i + 1] * (1.f - gv[i + 1]));
+  }
+  const int lanes_per_head = a.D / VPL;
+  for (int o = lanes_per_head >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if ((lane % lanes_per_head) == 0) {
+    const int h = c / a.D;
+    long b, q;
+    if (a.row_b > a.row_p) { b = m / a.row_b; q = (m % a.row_b) / a.row_p; }
+    else { q = m / a.row_p; b = (m % a.row_p) / a.row_b; }
+    a.delta[(b * a.H + h) * a.N + q] = part;
+  }
+}
+inline void attn_bwd_prep(const AttnBwdPrepArgs& a, cudaStream_t st) {
+  const int HD = a.H * a.D;
+  const unsigned grid = (unsigned)((a.rows + 7) / 8);
+  launch_counter()++;
+  if (HD == 128) attn_bwd_prep_kernel<128><<<grid, 256, 0, st>>>(a);
+  else if (HD == 256) attn_bwd_prep_kernel<256><<<grid, 256, 0, st>>>(a);
+  else if (HD == 64) attn_bwd_prep_kernel<64><<<grid, 256, 0, st>>>(a);
+  else throw Error("attn_bwd_prep: unsupported H*D");
+}
+
+// g_out = g_in + add (fp32), used where a gradient branch lands on an existing cotangent
+__global__ void __launch_bounds__(256) add_f32_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
+                                                      float4* __restrict__ o, long n4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const float4 x = a[i], y = b[i];
+    o[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  }
+}
+
+}  // namespace bc2

@@ -1,0 +1,474 @@
+// tcgen05 GEMM for the trunk: D[z][m][n] = sum_k A[z](m,k) * B[z](n,k), bf16 operands, fp32 accumulation in TMEM.
+//
+//   * operands arrive by TMA (cp.async.bulk.tensor, 128B swizzle) through a STAGES-deep mbarrier ring;
+//   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction); the accumulator tile
+//     [128 x BN] fp32 lives in TMEM and is read back by four epilogue warps with tcgen05.ld (one row per thread);
+//   * each operand may be K-major (k contiguous: activations [rows,K], weights packed [N,K]) or MN-major
+//     (m/n contiguous), which is what lets the triangle-multiplication contractions and their backward read the
+//     channel-major planes [c][i][k] in place with no transposes;
+//   * the epilogue is a functor fed 32 consecutive columns of one row at a time, so bias, activation, gating,
+//     masking, residual add and layout changes are fused into the store.
+//
+// A plain CUDA-core kernel with the same operand/epilogue interface (gemm_ref_kernel) exists for bring-up and as
+// the on-device reference in the unit tests; the product path never selects it unless built with -DBC2_REF_KERNELS.
+#pragma once
+#include "common.cuh"
+
+namespace bc2 {
+
+// ------------------------------------------------------------------------------------------- tensor maps
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_encodeTiled get_encode_fn() {
+  static PFN_encodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    BC2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    BC2_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled not available");
+    fn = (PFN_encodeTiled)p;
+  }
+  return fn;
+}
+
+// bf16 tensor map with up to 4 dims; dims[0] is the contiguous one; strides[i] (elements) for dims 1..n-1.
+inline CUtensorMap make_tmap(const void* base, int nd, const uint64_t* dims, const uint64_t* strides_elems,
+                             const uint32_t* box, int swizzle_bytes) {
+  CUtensorMap m;
+  cuuint64_t gd[5], gs[5];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < nd; ++i) {
+    gd[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+  }
+  for (int i = 1; i < nd; ++i) {
+    gs[i - 1] = strides_elems[i] * 2;
+    BC2_CHECK(gs[i - 1] % 16 == 0, "tensor-map stride must be a multiple of 16 bytes");
+  }
+  BC2_CHECK(((uintptr_t)base & 15) == 0, "tensor-map base must be 16-byte aligned");
+  CUtensorMapSwizzle sw = swizzle_bytes == 128  ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                          : swizzle_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = get_encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)nd, const_cast<void*>(base), gd, gs,
+                               bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  BC2_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return m;
+}
+
+// One GEMM operand: (rows, K) matrix per batch entry.  mn_major=false: element (r,k) at base[z*bs + r*ld + k];
+// mn_major=true: element (r,k) at base[z*bs + k*ld + r].
+struct Operand {
+  const bf16* base = nullptr;
+  long ld = 0, bs = 0;
+  bool mn_major = false;
+};
+
+inline CUtensorMap operand_tmap(const Operand& o, int rows, int K, int batch, int box_rows) {
+  if (!o.mn_major) {
+    uint64_t d[3] = {(uint64_t)K, (uint64_t)rows, (uint64_t)batch};
+    uint64_t s[3] = {1, (uint64_t)o.ld, (uint64_t)(batch > 1 ? o.bs : (long)rows * o.ld)};
+    uint32_t b[3] = {64, (uint32_t)box_rows, 1};
+    return make_tmap(o.base, 3, d, s, b, 128);
+  }
+  uint64_t d[3] = {(uint64_t)rows, (uint64_t)K, (uint64_t)batch};
+  uint64_t s[3] = {1, (uint64_t)o.ld, (uint64_t)(batch > 1 ? o.bs : (long)K * o.ld)};
+  uint32_t b[3] = {64, 64, 1};
+  return make_tmap(o.base, 3, d, s, b, 128);
+}
+
+// ------------------------------------------------------------------------------------------- epilogues
+// Every epilogue sees one row m of batch z and 32 consecutive columns starting at n0 (fp32 accumulators).
+
+// out = act(acc + bias) [* mul | * (mul > 0)], stored as bf16 with arbitrary leading dimension / batch stride.
+struct EpiStore {
+  bf16* out = nullptr;
+  long ldo = 0, bso = 0;
+  const float* bias = nullptr;
+  int act = 0;       // 0 none, 1 relu, 2 sigmoid
+  int act_from = 0;  // activation applies to columns >= act_from
+  const bf16* mul = nullptr;
+  long ldm = 0;
+  int mul_mode = 0;  // 1: multiply by mul, 2: multiply by (mul > 0)
+  const float* rowscale = nullptr;  // optional per-row factor applied last (row masks)
+  int M = 0, N = 0;
+  static constexpr bool kPaired = false;
+  __device__ __forceinline__ void operator()(int z, int m, int n0, const float (&v)[32]) const {
+    if (m >= M || n0 >= N) return;
+    const float rs = rowscale ? rowscale[m] : 1.f;
+    uint32_t pk[16];
+    uint4 mv[4];
+    if (mul_mode) {
+      const uint4* mp = reinterpret_cast<const uint4*>(mul + (long)m * ldm + n0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) mv[i] = mp[i];
+    }
+    const uint32_t* mw = reinterpret_cast<const uint32_t*>(mv);
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      float a = v[j], b = v[j + 1];
+      if (bias) {
+        a += bias[n0 + j];
+        b += bias[n0 + j + 1];
+      }
+      if (act == 1) {
+        a = fmaxf(a, 0.f);
+        b = fmaxf(b, 0.f);
+      } else if (act == 2 && n0 + j >= act_from) {
+        a = sigmoidf_(a);
+        b = sigmoidf_(b);
+      }
+      if (mul_mode) {
+        float2 mm = unpack_bf16(mw[j >> 1]);
+        if (mul_mode == 1) {
+          a *= mm.x;
+          b *= mm.y;
+        } else {
+          a = mm.x > 0.f ? a : 0.f;
+          b = mm.y > 0.f ? b : 0.f;
+        }
+      }
+      pk[j >> 1] = pack_bf16(a * rs, b * rs);
+    }
+    uint4* op = reinterpret_cast<uint4*>(out + (long)z * bso + (long)m * ldo + n0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) op[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+  }
+};
+
+// val = acc + bias; optionally saved (bf16); res_out = res_in + val [* mul].  The residual stream is fp32.
+struct EpiResidual {
+  const float* res_in = nullptr;
+  float* res_out = nullptr;
+  long ld = 0;
+  const float* bias = nullptr;
+  const bf16* mul = nullptr;
+  long ldm = 0;
+  bf16* save = nullptr;
+  long lds = 0;
+  int M = 0, N = 0;
+  static constexpr bool kPaired = false;
+  __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
+    if (m >= M || n0 >= N) return;
+    const float4* rp = reinterpret_cast<const float4*>(res_in + (long)m * ld + n0);
+    float4* wp = reinterpret_cast<float4*>(res_out + (long)m * ld + n0);
+    const uint4* mp = mul ? reinterpret_cast<const uint4*>(mul + (long)m * ldm + n0) : nullptr;
+    uint4* sp = save ? reinterpret_cast<uint4*>(save + (long)m * lds + n0) : nullptr;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = v[i * 8 + j] + (bias ? bias[n0 + i * 8 + j] : 0.f);
+      if (sp) sp[i] = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+      if (mp) {
+        uint4 mm = mp[i];
+        float2 a = unpack_bf16(mm.x), b = unpack_bf16(mm.y), c = unpack_bf16(mm.z), d = unpack_bf16(mm.w);
+        x[0] *= a.x; x[1] *= a.y; x[2] *= b.x; x[3] *= b.y; x[4] *= c.x; x[5] *= c.y; x[6] *= d.x; x[7] *= d.y;
+      }
+      float4 r0 = rp[2 * i], r1 = rp[2 * i + 1];
+      wp[2 * i] = make_float4(r0.x + x[0], r0.y + x[1], r0.z + x[2], r0.w + x[3]);
+      wp[2 * i + 1] = make_float4(r1.x + x[4], r1.y + x[5], r1.z + x[6], r1.w + x[7]);
+    }
+  }
+};
+
+// Triangle-multiplication projection+gate.  The packed weight puts, for each 128-channel group t, the 128
+// projection columns followed by the matching 128 gate columns, so one 256-wide accumulator tile holds both:
+//   g  = sigmoid(gate + bg)            -> gate_out [M, CH] row-major (kept for the backward)
+//   ab = mask[m] * (proj + bp) * g     -> ab_out [CH][M] channel-major planes (operand of the contraction)
+// With channels_per_tile < 128 (template stack, CH = 128 total -> one tile of 128 proj + 128 gate) the same holds.
+struct EpiProjGate {
+  const float* bias_p = nullptr;  // [CH]
+  const float* bias_g = nullptr;  // [CH]
+  const float* mask = nullptr;    // [M]
+  bf16* gate_out = nullptr;       // [M, CH]
+  bf16* ab_out = nullptr;         // [CH][M]
+  int M = 0, CH = 0;
+  static constexpr bool kPaired = true;
+  // n0 = channel index of vp[0] (already includes the tile's channel base)
+  __device__ __forceinline__ void operator()(int, int m, int n0, const float (&vp)[32], const float (&vg)[32]) const {
+    if (m >= M || n0 >= CH) return;
+    float mk = mask[m];
+    uint32_t pk[16];
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      float g0 = sigmoidf_(vg[j] + bias_g[n0 + j]), g1 = sigmoidf_(vg[j + 1] + bias_g[n0 + j + 1]);
+      pk[j >> 1] = pack_bf16(g0, g1);
+      float a0 = mk * (vp[j] + bias_p[n0 + j]) * g0, a1 = mk * (vp[j + 1] + bias_p[n0 + j + 1]) * g1;
+      ab_out[(long)(n0 + j) * M + m] = __float2bfloat16(a0);
+      ab_out[(long)(n0 + j + 1) * M + m] = __float2bfloat16(a1);
+    }
+    uint4* gp = reinterpret_cast<uint4*>(gate_out + (long)m * CH + n0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) gp[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- tcgen05 kernel
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
+
+template <int BN, int STAGES>
+constexpr int gemm_smem_bytes() {
+  return STAGES * (GEMM_A_BYTES + BN * GEMM_BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb, int K, Epi epi) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int B_BYTES = BN * GEMM_BK * 2;
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * GEMM_A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accb = empty + STAGES;
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(accb + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * BN, z = blockIdx.z;
+  const int nkb = cdiv(K, GEMM_BK);
+  constexpr uint32_t TCOLS = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accb, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&ta);
+    tma_prefetch_desc(&tb);
+  }
+  if (warp == 1) tmem_alloc(tslot, TCOLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tslot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, SITE_GEMM_EMPTY)) break;
+        mbar_expect_tx(&full[s], GEMM_A_BYTES + B_BYTES);
+        uint8_t* a = sA + s * GEMM_A_BYTES;
+        uint8_t* b = sB + s * B_BYTES;
+        if (!A_MN) {
+          tma_load_3d(a, &ta, &full[s], kb * GEMM_BK, m0, z);
+        } else {
+#pragma unroll
+          for (int h = 0; h < GEMM_BM / 64; ++h) tma_load_3d(a + h * 8192, &ta, &full[s], m0 + h * 64, kb * GEMM_BK, z);
+        }
+        if (!B_MN) {
+          tma_load_3d(b, &tb, &full[s], kb * GEMM_BK, n0, z);
+        } else {
+#pragma unroll
+          for (int h = 0; h < BN / 64; ++h) tma_load_3d(b + h * 8192, &tb, &full[s], n0 + h * 64, kb * GEMM_BK, z);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % STAGES;
+        ok = mbar_wait(&full[s], (kb / STAGES) & 1, SITE_GEMM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a = smem_u32(sA + s * GEMM_A_BYTES), b = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+        for (int k = 0; k < GEMM_BK / 16; ++k) {
+          // K-major: 8-row groups are 1024 B apart, a 16-element k step is 32 B inside the swizzled row.
+          // MN-major: each 64-wide box is [64 k][128 B]; 8 k-rows per 1024 B atom, boxes 8192 B apart.
+          const uint64_t ad = A_MN ? umma_desc(a + k * 2048, 8192, 1024, 2) : umma_desc(a + k * 32, 16, 1024, 2);
+          const uint64_t bd = B_MN ? umma_desc(b + k * 2048, 8192, 1024, 2) : umma_desc(b + k * 32, 16, 1024, 2);
+          umma_ss(tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[s]);
+      }
+      umma_commit(accb);
+    }
+  } else {
+    const bool ok = mbar_wait(accb, 0, SITE_GEMM_ACC);
+    tc_fence_after();
+    const int q = warp & 3;
+    const int m = m0 + q * 32 + lane;
+    const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16);
+    if (ok) {
+      if constexpr (Epi::kPaired) {
+        static_assert(!Epi::kPaired || BN == 256, "paired epilogue needs a 256-wide tile");
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          float vp[32], vg[32];
+          tmem_ld32(tbase + c * 32, vp);
+          tmem_ld32(tbase + 128 + c * 32, vg);
+          tmem_ld_wait();
+          epi(z, m, blockIdx.y * 128 + c * 32, vp, vg);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          float v[32];
+          tmem_ld32(tbase + c * 32, v);
+          tmem_ld_wait();
+          epi(z, m, n0 + c * 32, v);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, TCOLS);
+}
+
+// ------------------------------------------------------------------------------------------- CUDA-core reference
+// One thread per output row, 32 (or 32+32 paired) columns per thread; operands read with generic strides.
+template <class Epi>
+__global__ void __launch_bounds__(128)
+gemm_ref_kernel(const bf16* A, long a_rs, long a_ks, long a_bs, const bf16* B, long b_rs, long b_ks, long b_bs, int M,
+                int N, int K, Epi epi) {
+  __shared__ float sB[2][32][33];
+  const int m = blockIdx.x * 128 + threadIdx.x, z = blockIdx.z;
+  const int nb = blockIdx.y;  // 32-column block (paired: proj block nb and its gate block)
+  int nA, nG = 0, ep_n0;
+  if constexpr (Epi::kPaired) {
+    const int t = nb / 4, c = nb % 4;
+    nA = t * 256 + c * 32;
+    nG = nA + 128;
+    ep_n0 = t * 128 + c * 32;
+  } else {
+    nA = nb * 32;
+    ep_n0 = nA;
+  }
+  float acc[32], acc2[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) acc[j] = acc2[j] = 0.f;
+  const bf16* Ap = A + (long)z * a_bs + (long)m * a_rs;
+  const bf16* Bp = B + (long)z * b_bs;
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * 32; i += 128) {
+      const int n = i / 32, k = i % 32;
+      const bool kin = k0 + k < K;
+      sB[0][n][k] = (kin && nA + n < N) ? __bfloat162float(Bp[(long)(nA + n) * b_rs + (long)(k0 + k) * b_ks]) : 0.f;
+      if constexpr (Epi::kPaired)
+        sB[1][n][k] = (kin && nG + n < N) ? __bfloat162float(Bp[(long)(nG + n) * b_rs + (long)(k0 + k) * b_ks]) : 0.f;
+    }
+    __syncthreads();
+    if (m < M) {
+      const int kk = min(32, K - k0);
+      for (int k = 0; k < kk; ++k) {
+        const float a = __bfloat162float(Ap[(long)(k0 + k) * a_ks]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          acc[j] += a * sB[0][j][k];
+          if constexpr (Epi::kPaired) acc2[j] += a * sB[1][j][k];
+        }
+      }
+    }
+  }
+  if constexpr (Epi::kPaired) epi(z, m, ep_n0, acc, acc2);
+  else epi(z, m, ep_n0, acc);
+}
+
+// ------------------------------------------------------------------------------------------- host launcher
+#ifdef BC2_REF_KERNELS
+constexpr bool kUseRefKernels = true;
+#else
+constexpr bool kUseRefKernels = false;
+#endif
+
+// A prepared GEMM: operands, shape and (for the tensor-core path) the two tensor maps, built once per buffer.
+struct GemmPlan {
+  Operand a, b;
+  int M = 0, N = 0, K = 0, batch = 1;
+  int bn = 128;
+  CUtensorMap ta, tb;
+  bool ready = false;
+};
+
+inline GemmPlan make_gemm(Operand a, Operand b, int M, int N, int K, int batch = 1, int bn = 0, bool force_ref = false) {
+  GemmPlan p;
+  p.a = a;
+  p.b = b;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batch = batch;
+  if (bn == 0) bn = N >= 256 ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
+  p.bn = bn;
+  if (!kUseRefKernels && !force_ref) {
+    p.ta = operand_tmap(a, M, K, batch, GEMM_BM);
+    p.tb = operand_tmap(b, N, K, batch, bn);
+    p.ready = true;
+  }
+  return p;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+inline void launch_tc(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
+  constexpr int smem = gemm_smem_bytes<BN, STAGES>();
+  static bool attr_set = false;
+  auto kern = gemm_tc_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  if (!attr_set) {
+    BC2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  dim3 grid(cdiv(p.M, GEMM_BM), cdiv(p.N, BN), p.batch);
+  launch_counter()++; kern<<<grid, 192, smem, st>>>(p.ta, p.tb, p.K, epi);
+}
+
+template <class Epi>
+inline void launch_ref(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
+  const long a_rs = p.a.mn_major ? 1 : p.a.ld, a_ks = p.a.mn_major ? p.a.ld : 1;
+  const long b_rs = p.b.mn_major ? 1 : p.b.ld, b_ks = p.b.mn_major ? p.b.ld : 1;
+  const int nblocks = Epi::kPaired ? cdiv(p.N, 256) * 4 : cdiv(p.N, 32);
+  dim3 grid(cdiv(p.M, 128), nblocks, p.batch);
+  launch_counter()++; gemm_ref_kernel<Epi><<<grid, 128, 0, st>>>(p.a.base, a_rs, a_ks, p.a.bs, p.b.base, b_rs, b_ks, p.b.bs, p.M, p.N, p.K,
+                                             epi);
+}
+
+template <int BN, bool A_MN, bool B_MN, class Epi>
+inline void launch_tc_stages(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
+  const int nkb = cdiv(p.K, GEMM_BK);
+  if (nkb <= 2) launch_tc<BN, 2, A_MN, B_MN, Epi>(p, epi, st);
+  else launch_tc<BN, 4, A_MN, B_MN, Epi>(p, epi, st);
+}
+
+// Dispatch on tile width and operand majorness.  Only the combinations the trunk uses are instantiated.
+template <class Epi>
+inline void run_gemm(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
+  if (!p.ready) {
+    launch_ref(p, epi, st);
+    return;
+  }
+  const bool am = p.a.mn_major, bm = p.b.mn_major;
+  if constexpr (Epi::kPaired) {
+    BC2_CHECK(p.bn == 256 && !am && !bm, "paired epilogue: 256-wide K-major tiles only");
+    launch_tc_stages<256, false, false, Epi>(p, epi, st);
+  } else {
+    if (am || bm) {
+      BC2_CHECK(p.bn == 128, "MN-major operands use 128-wide tiles");
+      if (am && bm) launch_tc_stages<128, true, true, Epi>(p, epi, st);
+      else if (am) launch_tc_stages<128, true, false, Epi>(p, epi, st);
+      else launch_tc_stages<128, false, true, Epi>(p, epi, st);
+    } else {
+      switch (p.bn) {
+        case 256: launch_tc_stages<256, false, false, Epi>(p, epi, st); break;
+        case 128: launch_tc_stages<128, false, false, Epi>(p, epi, st); break;
+        case 64: launch_tc_stages<64, false, false, Epi>(p, epi, st); break;
+        default: launch_tc_stages<32, false, false, Epi>(p, epi, st); break;
+      }
+    }
+  }
+}
+
+}  // namespace bc2

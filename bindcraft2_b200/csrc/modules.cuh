@@ -1,0 +1,595 @@
+// The residual modules of an Evoformer / template pair block, forward and input-gradient backward, as sequences of
+// the kernels in gemm.cuh, attn.cuh, norm.cuh, ew.cuh and msa.cuh.  Weights are frozen (design optimises the
+// sequence), so every backward is dX only: dY . W^T GEMMs plus the element-wise / normalisation / attention adjoints.
+//
+// Conventions: the residual streams (pair [N,N,Cz], msa [S,N,Cm]) and their cotangents are fp32; everything between
+// a LayerNorm and the residual add is bf16 with fp32 accumulation.  `forward(in, out)` writes out = in + module(in) to
+// a different buffer; `backward(in, g)` updates the cotangent g in place: g += J(in)^T g.  Tensors a backward needs
+// (gates, attention operands, log-sum-exp, ReLU inputs) are kept in per-module buffers filled by the forward.
+#pragma once
+#include "attn.cuh"
+#include "ew.cuh"
+#include "gemm.cuh"
+#include "msa.cuh"
+#include "norm.cuh"
+#include "weights.cuh"
+
+namespace bc2 {
+
+template <int... Cs>
+struct CList {};
+
+inline void ln_fwd_c(int C, const LnArgs& a, cudaStream_t st) {
+  switch (C) {
+    case 64: ln_fwd<64>(a, st); break;
+    case 128: ln_fwd<128>(a, st); break;
+    case 256: ln_fwd<256>(a, st); break;
+    case 384: ln_fwd<384>(a, st); break;
+    default: throw Error("LayerNorm width " + std::to_string(C) + " not instantiated");
+  }
+}
+inline void ln_bwd_c(int C, const LnBwdArgs& a, cudaStream_t st) {
+  switch (C) {
+    case 64: ln_bwd<64>(a, st); break;
+    case 128: ln_bwd<128>(a, st); break;
+    case 256: ln_bwd<256>(a, st); break;
+    case 384: ln_bwd<384>(a, st); break;
+    default: throw Error("LayerNorm width " + std::to_string(C) + " not instantiated");
+  }
+}
+
+// Temporaries shared by all modules working on one residual stream of `rows` x `C`.
+struct Scratch {
+  long rows = 0;
+  int C = 0, wide = 0;
+  bf16 *x = nullptr, *y = nullptr, *dx = nullptr, *dy = nullptr, *d_o = nullptr;
+  bf16* big = nullptr;  // [rows][wide]
+  bf16 *dt = nullptr, *dab = nullptr;  // channel-major planes (pair stream only)
+  float *delta = nullptr, *dnb = nullptr, *dq_acc = nullptr, *ref_dkv = nullptr;
+  void init(DeviceArena& A, long rows_, int C_, int wide_, bool pair, int n_res, int max_heads) {
+    rows = rows_; C = C_; wide = wide_;
+    x = A.alloc<bf16>(rows * C); y = A.alloc<bf16>(rows * C); dx = A.alloc<bf16>(rows * C);
+    dy = A.alloc<bf16>(rows * C); d_o = A.alloc<bf16>(rows * C);
+    big = A.alloc<bf16>(rows * wide);
+    if (pair) { dt = A.alloc<bf16>(rows * C); dab = A.alloc<bf16>(rows * 2 * C); }
+    delta = A.alloc<float>(rows * max_heads);
+    dnb = A.alloc<float>((long)max_heads * n_res * n_res);
+    if (n_res > 256) dq_acc = A.alloc<float>(rows * C);
+    if (kUseRefKernels) ref_dkv = A.alloc<float>(rows * 2 * C);
+  }
+};
+
+struct LnW {
+  float *scale = nullptr, *offset = nullptr;
+  void load(DeviceArena& A, const Manifest& m, const std::string& p) {
+    scale = A.upload(m.get(p + "/scale").data);
+    offset = A.upload(m.get(p + "/offset").data);
+  }
+};
+
+inline Operand kmaj(const bf16* p, long ld) { return Operand{p, ld, 0, false}; }
+
+// ------------------------------------------------------------------------------------------- Transition
+// modules.Transition (bindcraft/af/alphafold/model/modules.py:252-304): LN -> Linear C->F*C -> ReLU -> Linear -> C.
+struct Transition {
+  int C = 0, F = 0;
+  long rows = 0;
+  struct W {
+    LnW ln;
+    bf16 *w1 = nullptr, *w2 = nullptr, *w1b = nullptr, *w2b = nullptr;
+    float *b1 = nullptr, *b2 = nullptr;
+    GemmPlan g1, g2, gb2, gb1;
+  };
+  std::vector<W> w;
+  bf16* h = nullptr;  // [rows][F*C] ReLU output, kept for the backward's mask
+  Scratch* S = nullptr;
+
+  void init(DeviceArena& A, Scratch* s, long rows_, int C_, int F_) {
+    S = s; rows = rows_; C = C_; F = F_;
+    h = A.alloc<bf16>(rows * C * F);
+  }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.ln.load(A, m, p + "/input_layer_norm");
+    const auto& W1 = m.get(p + "/transition1/weights");
+    const auto& W2 = m.get(p + "/transition2/weights");
+    BC2_CHECK(W1.shape.size() == 2 && W1.shape[0] == C && W1.shape[1] == C * F, p + ": transition1 shape");
+    b.w1 = A.upload_bf16(transpose_io(W1.data, C, C * F));
+    b.w1b = A.upload_bf16(W1.data);
+    b.w2 = A.upload_bf16(transpose_io(W2.data, C * F, C));
+    b.w2b = A.upload_bf16(W2.data);
+    b.b1 = A.upload(m.get(p + "/transition1/bias").data);
+    b.b2 = A.upload(m.get(p + "/transition2/bias").data);
+    const int M = (int)rows, FC = F * C;
+    b.g1 = make_gemm(kmaj(S->x, C), kmaj(b.w1, C), M, FC, C);
+    b.g2 = make_gemm(kmaj(h, FC), kmaj(b.w2, FC), M, C, FC);
+    b.gb2 = make_gemm(kmaj(S->dy, C), kmaj(b.w2b, C), M, FC, C);
+    b.gb1 = make_gemm(kmaj(S->big, FC), kmaj(b.w1b, FC), M, C, FC);
+    w.push_back(b);
+  }
+  void forward(int blk, const float* in, float* out, cudaStream_t st) {
+    W& b = w[blk];
+    const int M = (int)rows, FC = F * C;
+    LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = M;
+    ln_fwd_c(C, l, st);
+    EpiStore e1; e1.out = h; e1.ldo = FC; e1.bias = b.b1; e1.act = 1; e1.M = M; e1.N = FC;
+    run_gemm(b.g1, e1, st);
+    EpiResidual e2; e2.res_in = in; e2.res_out = out; e2.ld = C; e2.bias = b.b2; e2.M = M; e2.N = C;
+    run_gemm(b.g2, e2, st);
+  }
+  void backward(int blk, const float* in, float* g, cudaStream_t st) {
+    W& b = w[blk];
+    const int M = (int)rows, FC = F * C;
+    cvt_f32_bf16(g, S->dy, rows * C, st);
+    EpiStore e2; e2.out = S->big; e2.ldo = FC; e2.mul = h; e2.ldm = FC; e2.mul_mode = 2; e2.M = M; e2.N = FC;
+    run_gemm(b.gb2, e2, st);
+    EpiStore e1; e1.out = S->dx; e1.ldo = C; e1.M = M; e1.N = C;
+    run_gemm(b.gb1, e1, st);
+    LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.g_in = g; l.g_out = g; l.M = M;
+    ln_bwd_c(C, l, st);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- Triangle multiplication
+// modules.TriangleMultiplication._fused_triangle_multiplication (modules.py:1043-1088).
+struct TriMul {
+  int n = 0, C = 0, Hc = 0;
+  bool outgoing = true;
+  long M = 0;
+  struct W {
+    LnW ln, cn;
+    bf16 *wpg = nullptr, *wg2 = nullptr, *wo = nullptr, *wo_b = nullptr, *wcat_b = nullptr;
+    float *bp = nullptr, *bg = nullptr, *bo = nullptr, *bg2 = nullptr;
+    GemmPlan g_pg, g_g2, g_o, gb_o, gb_cat;
+  };
+  std::vector<W> w;
+  GemmPlan g_con, gb_da, gb_db;  // activation x activation: shared by all blocks
+  bf16 *gate = nullptr, *ab = nullptr, *t = nullptr, *ob = nullptr, *g2 = nullptr;
+  Scratch* S = nullptr;
+
+  void init(DeviceArena& A, Scratch* s, int n_, int C_, int Hc_, bool outgoing_) {
+    S = s; n = n_; C = C_; Hc = Hc_; outgoing = outgoing_;
+    M = (long)n * n;
+    gate = A.alloc<bf16>(M * 2 * Hc);
+    ab = A.alloc<bf16>(M * 2 * Hc);
+    t = A.alloc<bf16>(M * Hc);
+    ob = A.alloc<bf16>(M * C);
+    g2 = A.alloc<bf16>(M * C);
+    const bf16 *a = ab, *bq = ab + (long)Hc * M;           // left planes, right planes
+    const bf16 *da = S->dab, *db = S->dab + (long)Hc * M;  // their gradients
+    (void)da; (void)db;
+    auto K = [&](const bf16* p) { return Operand{p, n, M, false}; };
+    auto T = [&](const bf16* p) { return Operand{p, n, M, true}; };
+    if (outgoing) {
+      // t[i,j] = sum_k a[i,k] b[j,k];  da[i,k] = sum_j dt[i,j] b[j,k];  db[j,k] = sum_i dt[i,j] a[i,k]
+      g_con = make_gemm(K(a), K(bq), n, n, n, Hc, 128);
+      gb_da = make_gemm(K(S->dt), T(bq), n, n, n, Hc, 128);
+      gb_db = make_gemm(T(S->dt), T(a), n, n, n, Hc, 128);
+    } else {
+      // t[i,j] = sum_k r[k,i] l[k,j];  dr[k,i] = sum_j l[k,j] dt[i,j];  dl[k,j] = sum_i r[k,i] dt[i,j]   (l = a, r = b)
+      g_con = make_gemm(T(bq), T(a), n, n, n, Hc, 128);
+      gb_db = make_gemm(K(a), K(S->dt), n, n, n, Hc, 128);
+      gb_da = make_gemm(K(bq), T(S->dt), n, n, n, Hc, 128);
+    }
+  }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.ln.load(A, m, p + "/left_norm_input");
+    b.cn.load(A, m, p + "/center_norm");
+    const auto& Wp = m.get(p + "/projection/weights");
+    const auto& Wg = m.get(p + "/gate/weights");
+    const auto& Wo = m.get(p + "/output_projection/weights");
+    const auto& Wl = m.get(p + "/gating_linear/weights");
+    const int CH = 2 * Hc;
+    BC2_CHECK(Wp.shape.size() == 2 && Wp.shape[0] == C && Wp.shape[1] == CH, p + ": projection shape");
+    BC2_CHECK(CH % 128 == 0, "triangle multiplication: 2*hidden must be a multiple of 128");
+    // packed [n][k]: per 128-channel group, 128 projection rows then the 128 matching gate rows
+    const int NP = 2 * CH;
+    std::vector<float> pg((size_t)NP * C);
+    for (int ch = 0; ch < CH; ++ch) {
+      const int rp = (ch / 128) * 256 + ch % 128, rg = rp + 128;
+      for (int k = 0; k < C; ++k) {
+        pg[(size_t)rp * C + k] = Wp.data[(size_t)k * CH + ch];
+        pg[(size_t)rg * C + k] = Wg.data[(size_t)k * CH + ch];
+      }
+    }
+    b.wpg = A.upload_bf16(pg);
+    b.wg2 = A.upload_bf16(transpose_io(Wl.data, C, C));
+    b.wo = A.upload_bf16(transpose_io(Wo.data, Hc, C));
+    b.wo_b = A.upload_bf16(Wo.data);  // [Hc][C]: B operand of d_y = d_o . Wo^T
+    // backward of the two input-side projections in one GEMM: d_x[c_in] = sum_n d_pg[n] wpg[n][c_in] + sum_c d_g2[c] Wl[c_in][c]
+    const int KC = NP + C;
+    std::vector<float> cat((size_t)C * KC);
+    for (int ci = 0; ci < C; ++ci) {
+      for (int nn = 0; nn < NP; ++nn) cat[(size_t)ci * KC + nn] = pg[(size_t)nn * C + ci];
+      for (int c = 0; c < C; ++c) cat[(size_t)ci * KC + NP + c] = Wl.data[(size_t)ci * C + c];
+    }
+    b.wcat_b = A.upload_bf16(cat);
+    b.bp = A.upload(m.get(p + "/projection/bias").data);
+    b.bg = A.upload(m.get(p + "/gate/bias").data);
+    b.bo = A.upload(m.get(p + "/output_projection/bias").data);
+    b.bg2 = A.upload(m.get(p + "/gating_linear/bias").data);
+    const int Mi = (int)M;
+    b.g_pg = make_gemm(kmaj(S->x, C), kmaj(b.wpg, C), Mi, NP, C, 1, 256);
+    b.g_g2 = make_gemm(kmaj(S->x, C), kmaj(b.wg2, C), Mi, C, C);
+    b.g_o = make_gemm(kmaj(S->y, Hc), kmaj(b.wo, Hc), Mi, C, Hc);
+    b.gb_o = make_gemm(kmaj(S->d_o, C), kmaj(b.wo_b, C), Mi, Hc, C);
+    b.gb_cat = make_gemm(kmaj(S->big, KC), kmaj(b.wcat_b, KC), Mi, C, KC);
+    w.push_back(b);
+  }
+  void cln_fwd_c(const bf16* tt, const LnW& l, bf16* y, cudaStream_t st) {
+    const unsigned grid = (unsigned)(M / 64);
+    launch_counter()++;
+    if (Hc == 128) cln_fwd_kernel<128><<<grid, 256, 0, st>>>(tt, l.scale, l.offset, y, (int)M);
+    else if (Hc == 64) cln_fwd_kernel<64><<<grid, 256, 0, st>>>(tt, l.scale, l.offset, y, (int)M);
+    else throw Error("centre norm width not instantiated");
+  }
+  void cln_bwd_c(const bf16* tt, const LnW& l, const bf16* dy, bf16* dtt, cudaStream_t st) {
+    const unsigned grid = (unsigned)(M / 64);
+    launch_counter()++;
+    if (Hc == 128) cln_bwd_kernel<128><<<grid, 256, 0, st>>>(tt, l.scale, dy, dtt, (int)M);
+    else if (Hc == 64) cln_bwd_kernel<64><<<grid, 256, 0, st>>>(tt, l.scale, dy, dtt, (int)M);
+    else throw Error("centre norm width not instantiated");
+  }
+  void forward(int blk, const float* in, float* out, const float* mask, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)M, CH = 2 * Hc;
+    LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = Mi;
+    ln_fwd_c(C, l, st);
+    EpiProjGate ep; ep.bias_p = b.bp; ep.bias_g = b.bg; ep.mask = mask; ep.gate_out = gate; ep.ab_out = ab; ep.M = Mi; ep.CH = CH;
+    run_gemm(b.g_pg, ep, st);
+    EpiStore ec; ec.out = t; ec.ldo = n; ec.bso = M; ec.M = n; ec.N = n;
+    run_gemm(g_con, ec, st);
+    cln_fwd_c(t, b.cn, S->y, st);
+    EpiStore eg; eg.out = g2; eg.ldo = C; eg.bias = b.bg2; eg.act = 2; eg.act_from = 0; eg.M = Mi; eg.N = C;
+    run_gemm(b.g_g2, eg, st);
+    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.bo; er.mul = g2; er.ldm = C; er.save = ob; er.lds = C; er.M = Mi; er.N = C;
+    run_gemm(b.g_o, er, st);
+  }
+  void backward(int blk, const float* in, float* g, const float* mask, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)M, CH = 2 * Hc, NP = 2 * CH, KC = NP + C;
+    launch_counter()++; trimul_bwd_out_kernel<<<ew_grid(M * C / 4, 256), 256, 0, st>>>(
+        reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2),
+        reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C);
+    EpiStore ey; ey.out = S->dy; ey.ldo = Hc; ey.M = Mi; ey.N = Hc;
+    run_gemm(b.gb_o, ey, st);
+    cln_bwd_c(t, b.cn, S->dy, S->dt, st);
+    EpiStore ea; ea.out = S->dab; ea.ldo = n; ea.bso = M; ea.M = n; ea.N = n;
+    run_gemm(gb_da, ea, st);
+    EpiStore eb = ea; eb.out = S->dab + (long)Hc * M;
+    run_gemm(gb_db, eb, st);
+    dim3 grid((unsigned)(M / 64), CH / 64);
+    launch_counter()++; trimul_bwd_gate_kernel<<<grid, 256, 0, st>>>(S->dab, ab, gate, mask, S->big, KC, M, CH);
+    EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
+    run_gemm(b.gb_cat, ex, st);
+    LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.g_in = g; l.g_out = g; l.M = Mi;
+    ln_bwd_c(C, l, st);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- Gated attention weights
+// modules.Attention parameters (modules.py:345-396) packed for the fused q|k|v|gate projection.
+struct AttnW {
+  bf16 *wqkvg = nullptr, *wqkvg_b = nullptr, *wo = nullptr, *wo_b = nullptr;
+  float *bqkvg = nullptr, *bo = nullptr;
+  void load(DeviceArena& A, const Manifest& m, const std::string& p, int C, int H, int D) {
+    const int HD = H * D;
+    const auto& q = m.get(p + "/query_w");
+    const auto& k = m.get(p + "/key_w");
+    const auto& v = m.get(p + "/value_w");
+    const auto& gw = m.get(p + "/gating_w");
+    const auto& ow = m.get(p + "/output_w");
+    BC2_CHECK(q.size() == (long)C * HD && ow.size() == (long)HD * C, p + ": attention weight shapes");
+    const float scale = 1.f / sqrtf((float)D);
+    std::vector<float> wf((size_t)C * 4 * HD);  // [in][4HD] = backward operand
+    for (int c = 0; c < C; ++c)
+      for (int j = 0; j < HD; ++j) {
+        wf[(size_t)c * 4 * HD + j] = q.data[(size_t)c * HD + j] * scale;
+        wf[(size_t)c * 4 * HD + HD + j] = k.data[(size_t)c * HD + j];
+        wf[(size_t)c * 4 * HD + 2 * HD + j] = v.data[(size_t)c * HD + j];
+        wf[(size_t)c * 4 * HD + 3 * HD + j] = gw.data[(size_t)c * HD + j];
+      }
+    wqkvg_b = A.upload_bf16(wf);
+    wqkvg = A.upload_bf16(transpose_io(wf, C, 4 * HD));
+    wo = A.upload_bf16(transpose_io(ow.data, HD, C));
+    wo_b = A.upload_bf16(ow.data);
+    std::vector<float> bias(4 * HD, 0.f);
+    const auto& gb = m.get(p + "/gating_b");
+    for (int j = 0; j < HD; ++j) bias[3 * HD + j] = gb.data[j];
+    bqkvg = A.upload(bias);
+    bo = A.upload(m.get(p + "/output_b").data);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- Triangle attention
+// modules.TriangleAttention (modules.py:675-734); `ending` = per_column orientation.
+struct TriAttn {
+  int n = 0, C = 0, H = 0, D = 0;
+  bool ending = false;
+  long M = 0;
+  struct W {
+    LnW ln;
+    float* wb = nullptr;  // feat_2d_weights [C][H]
+    AttnW a;
+    GemmPlan g_qkvg, g_o, gb_o, gb_qkvg;
+  };
+  std::vector<W> w;
+  bf16 *qkvg = nullptr, *o = nullptr;
+  float *nb = nullptr, *lse = nullptr;
+  AttnPlan plan;
+  Scratch* S = nullptr;
+
+  void init(DeviceArena& A, Scratch* s, int n_, int C_, int H_, int D_, bool ending_, const float* pair_mask) {
+    S = s; n = n_; C = C_; H = H_; D = D_; ending = ending_;
+    M = (long)n * n;
+    const int HD = H * D;
+    BC2_CHECK(HD == C, "triangle attention: heads x width must equal the channel count");
+    qkvg = A.alloc<bf16>(M * 4 * HD);
+    o = A.alloc<bf16>(M * HD);
+    nb = A.alloc<float>((long)H * M);
+    lse = A.alloc<float>((long)n * H * n);
+    AttnArgs& a = plan.args;
+    a.qkvg = qkvg; a.ld = 4 * HD;
+    a.row_b = ending ? 1 : n; a.row_p = ending ? n : 1;
+    a.B = n; a.N = n; a.H = H; a.D = D;
+    a.bias = nb; a.mask = pair_mask; a.mask_b = ending ? 1 : n; a.mask_k = ending ? n : 1;
+    a.o = o; a.og = S->y; a.lse = lse;
+    a.d_o = S->d_o; a.delta = S->delta; a.d_qkv = S->big; a.d_bias = S->dnb; a.dq_acc = S->dq_acc;
+    plan.rows = M; plan.ref_dkv = S->ref_dkv;
+    attn_prepare(plan);
+  }
+  void set_mask(const float* pair_mask) { plan.args.mask = pair_mask; }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.ln.load(A, m, p + "/query_norm");
+    b.wb = A.upload(m.get(p + "/feat_2d_weights").data);
+    b.a.load(A, m, p + "/attention", C, H, D);
+    const int Mi = (int)M, HD = H * D;
+    b.g_qkvg = make_gemm(kmaj(S->x, C), kmaj(b.a.wqkvg, C), Mi, 4 * HD, C, 1, 256);
+    b.g_o = make_gemm(kmaj(S->y, HD), kmaj(b.a.wo, HD), Mi, C, HD);
+    b.gb_o = make_gemm(kmaj(S->dy, C), kmaj(b.a.wo_b, C), Mi, HD, C);
+    b.gb_qkvg = make_gemm(kmaj(S->big, 4 * HD), kmaj(b.a.wqkvg_b, 4 * HD), Mi, C, 4 * HD);
+    w.push_back(b);
+  }
+  void forward(int blk, const float* in, float* out, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)M, HD = H * D;
+    LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = Mi;
+    l.wb = b.wb; l.nb = nb; l.H = H; l.n = n; l.transposed = ending ? 1 : 0;
+    ln_fwd_c(C, l, st);
+    EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
+    run_gemm(b.g_qkvg, e, st);
+    attn_fwd(plan, st);
+    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.a.bo; er.M = Mi; er.N = C;
+    run_gemm(b.g_o, er, st);
+  }
+  void backward(int blk, const float* in, float* g, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)M, HD = H * D;
+    cvt_f32_bf16(g, S->dy, M * C, st);
+    EpiStore e; e.out = S->y; e.ldo = HD; e.M = Mi; e.N = HD;
+    run_gemm(b.gb_o, e, st);
+    AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, M, plan.args.row_b, plan.args.row_p, n, H, D};
+    attn_bwd_prep(p, st);
+    BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st));
+    attn_bwd(plan, st);
+    EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
+    run_gemm(b.gb_qkvg, ex, st);
+    LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.wb = b.wb; l.dnb = S->dnb; l.H = H; l.n = n;
+    l.transposed = ending ? 1 : 0; l.g_in = g; l.g_out = g; l.M = Mi;
+    ln_bwd_c(C, l, st);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- MSA row attention
+// modules.MSARowAttentionWithPairBias (modules.py:500-563).  The gradient lands on the msa AND the pair stream.
+struct MsaRow {
+  int n = 0, S_ = 0, Cm = 0, Cz = 0, H = 0, D = 0;
+  long Mm = 0, Mp = 0;
+  struct W {
+    LnW qn, fn;
+    float* wb = nullptr;  // feat_2d_weights [Cz][H]
+    AttnW a;
+    GemmPlan g_qkvg, g_o, gb_o, gb_qkvg;
+  };
+  std::vector<W> w;
+  bf16 *qkvg = nullptr, *o = nullptr;
+  float *nb = nullptr, *lse = nullptr, *dnb = nullptr;
+  AttnPlan plan;
+  Scratch* S = nullptr;
+
+  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, int Cz_, int H_, const float* msa_mask) {
+    S = s; n = n_; S_ = S__; Cm = Cm_; Cz = Cz_; H = H_; D = Cm / H;
+    Mm = (long)S_ * n; Mp = (long)n * n;
+    const int HD = H * D;
+    qkvg = A.alloc<bf16>(Mm * 4 * HD);
+    o = A.alloc<bf16>(Mm * HD);
+    nb = A.alloc<float>((long)H * Mp);
+    dnb = A.alloc<float>((long)H * Mp);
+    lse = A.alloc<float>((long)S_ * H * n);
+    AttnArgs& a = plan.args;
+    a.qkvg = qkvg; a.ld = 4 * HD; a.row_b = n; a.row_p = 1; a.B = S_; a.N = n; a.H = H; a.D = D;
+    a.bias = nb; a.mask = msa_mask; a.mask_b = n; a.mask_k = 1;
+    a.o = o; a.og = S->y; a.lse = lse;
+    a.d_o = S->d_o; a.delta = S->delta; a.d_qkv = S->big; a.d_bias = dnb; a.dq_acc = S->dq_acc;
+    plan.rows = Mm; plan.ref_dkv = S->ref_dkv;
+    attn_prepare(plan);
+  }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.qn.load(A, m, p + "/query_norm");
+    b.fn.load(A, m, p + "/feat_2d_norm");
+    b.wb = A.upload(m.get(p + "/feat_2d_weights").data);
+    b.a.load(A, m, p + "/attention", Cm, H, D);
+    const int Mi = (int)Mm, HD = H * D;
+    b.g_qkvg = make_gemm(kmaj(S->x, Cm), kmaj(b.a.wqkvg, Cm), Mi, 4 * HD, Cm, 1, 256);
+    b.g_o = make_gemm(kmaj(S->y, HD), kmaj(b.a.wo, HD), Mi, Cm, HD);
+    b.gb_o = make_gemm(kmaj(S->dy, Cm), kmaj(b.a.wo_b, Cm), Mi, HD, Cm);
+    b.gb_qkvg = make_gemm(kmaj(S->big, 4 * HD), kmaj(b.a.wqkvg_b, 4 * HD), Mi, Cm, 4 * HD);
+    w.push_back(b);
+  }
+  void forward(int blk, const float* msa_in, float* msa_out, const float* pair, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)Mm, HD = H * D;
+    LnArgs l; l.x = msa_in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
+    ln_fwd_c(Cm, l, st);
+    LnArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.offset = b.fn.offset; lp.wb = b.wb; lp.nb = nb; lp.H = H; lp.n = n; lp.M = (int)Mp;
+    ln_fwd_c(Cz, lp, st);
+    EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
+    run_gemm(b.g_qkvg, e, st);
+    attn_fwd(plan, st);
+    EpiResidual er; er.res_in = msa_in; er.res_out = msa_out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm;
+    run_gemm(b.g_o, er, st);
+  }
+  void backward(int blk, const float* msa_in, const float* pair, float* g_msa, float* g_pair, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)Mm, HD = H * D;
+    cvt_f32_bf16(g_msa, S->dy, Mm * Cm, st);
+    EpiStore e; e.out = S->y; e.ldo = HD; e.M = Mi; e.N = HD;
+    run_gemm(b.gb_o, e, st);
+    AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, Mm, (long)n, 1L, n, H, D};
+    attn_bwd_prep(p, st);
+    BC2_CUDA(cudaMemsetAsync(dnb, 0, (size_t)H * Mp * 4, st));
+    attn_bwd(plan, st);
+    EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
+    run_gemm(b.gb_qkvg, ex, st);
+    LnBwdArgs l; l.x = msa_in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;
+    ln_bwd_c(Cm, l, st);
+    LnBwdArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.wb = b.wb; lp.dnb = dnb; lp.H = H; lp.n = n; lp.g_in = g_pair; lp.g_out = g_pair; lp.M = (int)Mp;
+    ln_bwd_c(Cz, lp, st);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- MSA column attention
+// modules.MSAColumnAttention (modules.py:566-616): attention over the alignment depth, per residue column.
+struct MsaCol {
+  int n = 0, S_ = 0, Cm = 0, H = 0;
+  long Mm = 0;
+  struct W {
+    LnW qn;
+    AttnW a;
+    GemmPlan g_qkvg, g_o, gb_o, gb_qkvg;
+  };
+  std::vector<W> w;
+  bf16* qkvg = nullptr;
+  const float* msa_mask = nullptr;
+  Scratch* S = nullptr;
+  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, int H_, const float* mask) {
+    S = s; n = n_; S_ = S__; Cm = Cm_; H = H_; Mm = (long)S_ * n; msa_mask = mask;
+    BC2_CHECK(Cm / H == 32, "MSA column attention kernel is written for head width 32");
+    BC2_CHECK(S_ <= 8, "MSA column attention kernel holds at most 8 alignment rows");
+    qkvg = A.alloc<bf16>(Mm * 4 * Cm);
+  }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.qn.load(A, m, p + "/query_norm");
+    b.a.load(A, m, p + "/attention", Cm, H, Cm / H);
+    const int Mi = (int)Mm;
+    b.g_qkvg = make_gemm(kmaj(S->x, Cm), kmaj(b.a.wqkvg, Cm), Mi, 4 * Cm, Cm, 1, 256);
+    b.g_o = make_gemm(kmaj(S->y, Cm), kmaj(b.a.wo, Cm), Mi, Cm, Cm);
+    b.gb_o = make_gemm(kmaj(S->dy, Cm), kmaj(b.a.wo_b, Cm), Mi, Cm, Cm);
+    b.gb_qkvg = make_gemm(kmaj(S->big, 4 * Cm), kmaj(b.a.wqkvg_b, 4 * Cm), Mi, Cm, 4 * Cm);
+    w.push_back(b);
+  }
+  void forward(int blk, const float* in, float* out, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)Mm;
+    LnArgs l; l.x = in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
+    ln_fwd_c(Cm, l, st);
+    EpiStore e; e.out = qkvg; e.ldo = 4 * Cm; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * Cm; e.M = Mi; e.N = 4 * Cm;
+    run_gemm(b.g_qkvg, e, st);
+    launch_counter()++; msacol_fwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S_, n, H);
+    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm;
+    run_gemm(b.g_o, er, st);
+  }
+  void backward(int blk, const float* in, float* g, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)Mm;
+    cvt_f32_bf16(g, S->dy, Mm * Cm, st);
+    EpiStore e; e.out = S->y; e.ldo = Cm; e.M = Mi; e.N = Cm;
+    run_gemm(b.gb_o, e, st);
+    launch_counter()++; msacol_bwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S->big, S_, n, H);
+    EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
+    run_gemm(b.gb_qkvg, ex, st);
+    LnBwdArgs l; l.x = in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g; l.g_out = g; l.M = Mi;
+    ln_bwd_c(Cm, l, st);
+  }
+};
+
+// ------------------------------------------------------------------------------------------- Outer product mean
+// modules.OuterProductMean (modules.py:1128-1213), reassociated: output_w is folded into the right projection first.
+struct Opm {
+  int n = 0, S_ = 0, Cm = 0;
+  long Mm = 0;
+  struct W {
+    LnW ln;
+    bf16 *wlr = nullptr, *wlr_b = nullptr;
+    float *blr = nullptr, *ow = nullptr, *ob = nullptr;
+    GemmPlan g_lr, gb_lr;
+  };
+  std::vector<W> w;
+  bf16 *lr = nullptr, *dlr_b = nullptr;
+  float *tmp = nullptr, *dtmp = nullptr, *dlr = nullptr;
+  const float* msa_mask = nullptr;
+  Scratch* S = nullptr;
+  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, const float* mask) {
+    S = s; n = n_; S_ = S__; Cm = Cm_; Mm = (long)S_ * n; msa_mask = mask;
+    lr = A.alloc<bf16>(Mm * 64);
+    dlr_b = A.alloc<bf16>(Mm * 64);
+    dlr = A.alloc<float>(Mm * 64);
+    tmp = A.alloc<float>(Mm * OPM_C * OPM_F);
+    dtmp = A.alloc<float>(Mm * OPM_C * OPM_F);
+  }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.ln.load(A, m, p + "/layer_norm_input");
+    const auto& L = m.get(p + "/left_projection/weights");
+    const auto& R = m.get(p + "/right_projection/weights");
+    BC2_CHECK(L.shape.size() == 2 && L.shape[0] == Cm && L.shape[1] == OPM_C, p + ": left_projection shape");
+    std::vector<float> wf((size_t)Cm * 64), bias(64);
+    for (int c = 0; c < Cm; ++c)
+      for (int j = 0; j < OPM_C; ++j) {
+        wf[(size_t)c * 64 + j] = L.data[(size_t)c * OPM_C + j];
+        wf[(size_t)c * 64 + 32 + j] = R.data[(size_t)c * OPM_C + j];
+      }
+    const auto& bl = m.get(p + "/left_projection/bias");
+    const auto& br = m.get(p + "/right_projection/bias");
+    for (int j = 0; j < OPM_C; ++j) { bias[j] = bl.data[j]; bias[32 + j] = br.data[j]; }
+    b.wlr_b = A.upload_bf16(wf);
+    b.wlr = A.upload_bf16(transpose_io(wf, Cm, 64));
+    b.blr = A.upload(bias);
+    b.ow = A.upload(m.get(p + "/output_w").data);
+    b.ob = A.upload(m.get(p + "/output_b").data);
+    b.g_lr = make_gemm(kmaj(S->x, Cm), kmaj(b.wlr, Cm), (int)Mm, 64, Cm);
+    b.gb_lr = make_gemm(kmaj(dlr_b, 64), kmaj(b.wlr_b, 64), (int)Mm, Cm, 64);
+    w.push_back(b);
+  }
+  void forward(int blk, const float* msa_in, const float* pair_in, float* pair_out, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)Mm;
+    LnArgs l; l.x = msa_in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
+    ln_fwd_c(Cm, l, st);
+    EpiStore e; e.out = lr; e.ldo = 64; e.bias = b.blr; e.rowscale = msa_mask; e.M = Mi; e.N = 64;
+    run_gemm(b.g_lr, e, st);
+    launch_counter()++; opm_tmp_kernel<<<dim3(Mi, OPM_C), 128, 0, st>>>(lr, b.ow, tmp, Mi);
+    const size_t sm = (size_t)(32 * S_ * OPM_C + 32) * 4;
+    launch_counter()++; opm_out_kernel<<<dim3(n, cdiv(n, 32)), 128, sm, st>>>(lr, tmp, b.ob, msa_mask, pair_in, pair_out, S_, n);
+  }
+  // g_pair: cotangent of the pair stream after the module (read only: the module adds to the pair stream, so the
+  // cotangent of its pair input is g_pair itself); g_msa accumulates.
+  void backward(int blk, const float* msa_in, const float* g_pair, float* g_msa, cudaStream_t st) {
+    W& b = w[blk];
+    const int Mi = (int)Mm;
+    launch_counter()++; opm_dleft_kernel<<<dim3(n, S_), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n);
+    launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n);
+    launch_counter()++; opm_dright_kernel<<<Mi, 256, 0, st>>>(dtmp, b.ow, dlr, Mi);
+    launch_counter()++; opm_dlr_store_kernel<<<cdiv(Mi * 64, 256), 256, 0, st>>>(dlr, msa_mask, dlr_b, (long)Mi * 64);
+    EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
+    run_gemm(b.gb_lr, ex, st);
+    LnBwdArgs l; l.x = msa_in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;
+    ln_bwd_c(Cm, l, st);
+  }
+};
+
+}  // namespace bc2

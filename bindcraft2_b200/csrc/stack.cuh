@@ -1,0 +1,157 @@
+// Evoformer block and the depth-deep stack with its save-set.
+//
+// Block order is the multimer one (bindcraft/af/alphafold/model/modules.py:1266-1391 with
+// outer_product_mean.first = True, config.py:411-418):
+//   pair += OPM(msa); msa += RowAttn(msa, pair); msa += ColAttn(msa); msa += Transition(msa);
+//   pair += TriMulOut; pair += TriMulIn; pair += TriAttnStart; pair += TriAttnEnd; pair += Transition(pair)
+//
+// The stack keeps the reference's purity contract (native/ffi.cu:17-25): the forward writes every block's input into
+// the caller's save-set (pair as bf16, msa as fp32; slot layout native/stack.cuh:795-829) and the backward needs only
+// that save-set, the masks and the cotangents: per block it re-runs the block forward from the saved input (filling
+// the per-module buffers) and then walks the modules in reverse.
+#pragma once
+#include <memory>
+
+#include "modules.cuh"
+
+namespace bc2 {
+
+struct StackConfig {
+  int N = 0, S = 0, depth = 0;
+  int Cm = 256, Cz = 128;
+  bool pair_only = false, opm_first = true;
+  int tri_hidden = 128, tri_heads = 4, msa_heads = 8, trans_factor = 4;
+};
+
+struct EvoStack {
+  StackConfig cfg;
+  DeviceArena A;
+  long Mp = 0, Mm = 0;
+  Scratch Sp, Sm;
+  Opm opm;
+  MsaRow row;
+  MsaCol col;
+  Transition mtrans, ptrans;
+  TriMul tmo, tmi;
+  TriAttn tas, tae;
+  float* P[7] = {nullptr};   // pair stream after each pair-side step (P[0] = block input)
+  float* Mx[4] = {nullptr};  // msa stream: input, after row, after col, after transition
+  float *pair_mask = nullptr, *msa_mask = nullptr;  // stack-owned copies (stable pointers for the kernels' arguments)
+  float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};  // ping-pong block outputs
+  size_t weight_bytes = 0;
+
+  EvoStack(const StackConfig& c, const std::string& weights_dir) : cfg(c) {
+    BC2_CHECK(c.N > 0 && c.N % 32 == 0, "N must be a positive multiple of 32 (the caller pads and masks)");
+    BC2_CHECK(c.S >= 1 && c.S <= 8, "alignment depth S must be in 1..8");
+    BC2_CHECK(c.depth >= 1, "depth must be positive");
+    BC2_CHECK(!c.pair_only, "pair_only stacks are not built yet");
+    BC2_CHECK(c.opm_first, "only the multimer block order (outer product mean first) is built");
+    const int N = c.N, S = c.S;
+    Mp = (long)N * N;
+    Mm = (long)S * N;
+    Manifest man = Manifest::load(weights_dir);
+    pair_mask = A.alloc<float>(Mp);
+    msa_mask = A.alloc<float>(Mm);
+    const int wide_p = std::max(4 * c.tri_hidden + c.Cz, std::max(4 * c.Cz, c.trans_factor * c.Cz));
+    Sp.init(A, Mp, c.Cz, wide_p, true, N, c.tri_heads);
+    Sm.init(A, Mm, c.Cm, 4 * c.Cm, false, N, c.msa_heads);
+    for (int i = 1; i < 7; ++i) P[i] = A.alloc<float>(Mp * c.Cz);
+    P[0] = A.alloc<float>(Mp * c.Cz);
+    for (int i = 0; i < 4; ++i) Mx[i] = A.alloc<float>(Mm * c.Cm);
+    for (int i = 0; i < 2; ++i) {
+      pp[i] = A.alloc<float>(Mp * c.Cz);
+      mp[i] = A.alloc<float>(Mm * c.Cm);
+    }
+    opm.init(A, &Sm, N, S, c.Cm, msa_mask);
+    row.init(A, &Sm, N, S, c.Cm, c.Cz, c.msa_heads, msa_mask);
+    col.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
+    mtrans.init(A, &Sm, Mm, c.Cm, c.trans_factor);
+    tmo.init(A, &Sp, N, c.Cz, c.tri_hidden, true);
+    tmi.init(A, &Sp, N, c.Cz, c.tri_hidden, false);
+    tas.init(A, &Sp, N, c.Cz, c.tri_heads, c.Cz / c.tri_heads, false, pair_mask);
+    tae.init(A, &Sp, N, c.Cz, c.tri_heads, c.Cz / c.tri_heads, true, pair_mask);
+    ptrans.init(A, &Sp, Mp, c.Cz, c.trans_factor);
+    const size_t before = A.bytes;
+    for (int b = 0; b < c.depth; ++b) {
+      const std::string p = "param/block" + std::to_string(b) + "/";
+      opm.add_block(A, man, p + "outer_product_mean");
+      row.add_block(A, man, p + "msa_row_attention_with_pair_bias");
+      col.add_block(A, man, p + "msa_column_attention");
+      mtrans.add_block(A, man, p + "msa_transition");
+      tmo.add_block(A, man, p + "triangle_multiplication_outgoing");
+      tmi.add_block(A, man, p + "triangle_multiplication_incoming");
+      tas.add_block(A, man, p + "triangle_attention_starting_node");
+      tae.add_block(A, man, p + "triangle_attention_ending_node");
+      ptrans.add_block(A, man, p + "pair_transition");
+    }
+    weight_bytes = A.bytes - before;
+    BC2_CUDA(cudaDeviceSynchronize());
+  }
+
+  // One block.  p_in/m_in are read only; the block output goes to p_out/m_out.
+  void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st) {
+    opm.forward(b, m_in, p_in, P[1], st);
+    row.forward(b, m_in, Mx[1], P[1], st);
+    col.forward(b, Mx[1], Mx[2], st);
+    mtrans.forward(b, Mx[2], m_out, st);
+    tmo.forward(b, P[1], P[2], pair_mask, st);
+    tmi.forward(b, P[2], P[3], pair_mask, st);
+    tas.forward(b, P[3], P[4], st);
+    tae.forward(b, P[4], P[5], st);
+    ptrans.forward(b, P[5], p_out, st);
+  }
+  // Needs the module buffers of block b as left by block_forward(b, p_in, m_in, ...).  g_pair/g_msa: cotangents of the
+  // block outputs on entry, of the block inputs on return.
+  void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
+    ptrans.backward(b, P[5], g_pair, st);
+    tae.backward(b, P[4], g_pair, st);
+    tas.backward(b, P[3], g_pair, st);
+    tmi.backward(b, P[2], g_pair, pair_mask, st);
+    tmo.backward(b, P[1], g_pair, pair_mask, st);
+    mtrans.backward(b, Mx[2], g_msa, st);
+    col.backward(b, Mx[1], g_msa, st);
+    row.backward(b, m_in, P[1], g_msa, g_pair, st);
+    opm.backward(b, m_in, g_pair, g_msa, st);
+  }
+
+  void set_masks(const float* pm, const float* mm, cudaStream_t st) {
+    BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, Mp * 4, cudaMemcpyDeviceToDevice, st));
+    BC2_CUDA(cudaMemcpyAsync(msa_mask, mm, Mm * 4, cudaMemcpyDeviceToDevice, st));
+  }
+
+  // psave: [depth][N][N][Cz] bf16, msave: [depth][S][N][Cm] fp32 (null when save == false).
+  void forward(const float* pair, const float* msa, const float* pm, const float* mm, float* pair_out, float* msa_out,
+               bf16* psave, float* msave, cudaStream_t st) {
+    set_masks(pm, mm, st);
+    const long np = Mp * cfg.Cz, nm = Mm * cfg.Cm;
+    const float *pc = pair, *mc = msa;
+    for (int i = 0; i < cfg.depth; ++i) {
+      if (psave) {
+        cvt_f32_bf16(pc, psave + (long)i * np, np, st);
+        BC2_CUDA(cudaMemcpyAsync(msave + (long)i * nm, mc, nm * 4, cudaMemcpyDeviceToDevice, st));
+      }
+      const bool last = i == cfg.depth - 1;
+      float* po = last ? pair_out : pp[i & 1];
+      float* mo = last ? msa_out : mp[i & 1];
+      block_forward(i, pc, mc, po, mo, st);
+      pc = po;
+      mc = mo;
+    }
+  }
+
+  void backward(const float* ct_pair, const float* ct_msa, const float* pm, const float* mm, const bf16* psave,
+                const float* msave, float* dpair, float* dmsa, cudaStream_t st) {
+    set_masks(pm, mm, st);
+    const long np = Mp * cfg.Cz, nm = Mm * cfg.Cm;
+    if (dpair != ct_pair) BC2_CUDA(cudaMemcpyAsync(dpair, ct_pair, np * 4, cudaMemcpyDeviceToDevice, st));
+    if (dmsa != ct_msa) BC2_CUDA(cudaMemcpyAsync(dmsa, ct_msa, nm * 4, cudaMemcpyDeviceToDevice, st));
+    for (int i = cfg.depth - 1; i >= 0; --i) {
+      cvt_bf16_f32(psave + (long)i * np, P[0], np, st);
+      const float* m_in = msave + (long)i * nm;
+      block_forward(i, P[0], m_in, pp[0], mp[0], st);
+      block_backward(i, m_in, dpair, dmsa, st);
+    }
+  }
+};
+
+}  // namespace bc2

@@ -1,0 +1,105 @@
+// Weight manifests and device buffers.
+//
+// The reference passes no weights through its operator boundary: each handler gets a `weights_dir` holding
+// `manifest.txt` (one line per array: `<name> <file> <ndim> <d0> ...`) and raw little-endian fp32 files, names being
+// the haiku scope paths (writer: bindcraft/af/native.py:171-222; reference reader: native/common.cuh:552-590).
+// This loader reads the same directories, then packs what the kernels want (bf16, [out][in] for forward operands,
+// [in][out] for the backward ones) once per stack object.
+#pragma once
+#include <fstream>
+#include <map>
+#include <sstream>
+#include <vector>
+
+#include "common.cuh"
+
+namespace bc2 {
+
+struct HostArray {
+  std::vector<int> shape;
+  std::vector<float> data;
+  long size() const { return (long)data.size(); }
+};
+
+struct Manifest {
+  std::map<std::string, HostArray> arrays;
+  std::string dir;
+
+  static Manifest load(const std::string& dir) {
+    Manifest m;
+    m.dir = dir;
+    std::ifstream fh(dir + "/manifest.txt");
+    BC2_CHECK(fh.good(), "cannot open " + dir + "/manifest.txt");
+    std::string line;
+    while (std::getline(fh, line)) {
+      if (line.empty()) continue;
+      std::istringstream ss(line);
+      std::string name, file;
+      int nd = 0;
+      ss >> name >> file >> nd;
+      BC2_CHECK(!ss.fail() && nd >= 0 && nd <= 8, "bad manifest line: " + line);
+      HostArray a;
+      long n = 1;
+      for (int i = 0; i < nd; ++i) {
+        int d = 0;
+        ss >> d;
+        BC2_CHECK(!ss.fail() && d >= 0, "bad manifest dims: " + line);
+        a.shape.push_back(d);
+        n *= d;
+      }
+      a.data.resize(n);
+      std::ifstream bf(dir + "/" + file, std::ios::binary);
+      BC2_CHECK(bf.good(), "cannot open weight file " + dir + "/" + file);
+      bf.read(reinterpret_cast<char*>(a.data.data()), n * 4);
+      BC2_CHECK(bf.gcount() == n * 4, "short weight file " + file);
+      m.arrays.emplace(name, std::move(a));
+    }
+    return m;
+  }
+  const HostArray& get(const std::string& name) const {
+    auto it = arrays.find(name);
+    BC2_CHECK(it != arrays.end(), "weights_dir " + dir + " has no array '" + name + "'");
+    return it->second;
+  }
+  bool has(const std::string& name) const { return arrays.count(name) != 0; }
+};
+
+// Owns device allocations for one stack object.
+struct DeviceArena {
+  std::vector<void*> ptrs;
+  size_t bytes = 0;
+  ~DeviceArena() {
+    for (void* p : ptrs) cudaFree(p);
+  }
+  template <class T>
+  T* alloc(size_t n) {
+    void* p = nullptr;
+    const size_t b = ((n * sizeof(T) + 255) / 256) * 256;
+    BC2_CUDA(cudaMalloc(&p, b ? b : 256));
+    ptrs.push_back(p);
+    bytes += b;
+    return reinterpret_cast<T*>(p);
+  }
+  float* upload(const std::vector<float>& v) {
+    float* d = alloc<float>(v.size());
+    BC2_CUDA(cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice));
+    return d;
+  }
+  bf16* upload_bf16(const std::vector<float>& v) {
+    std::vector<bf16> h(v.size());
+    for (size_t i = 0; i < v.size(); ++i) h[i] = __float2bfloat16(v[i]);
+    bf16* d = alloc<bf16>(v.size());
+    BC2_CUDA(cudaMemcpy(d, h.data(), h.size() * 2, cudaMemcpyHostToDevice));
+    return d;
+  }
+};
+
+// w is [in][out] row-major (haiku Linear).  Returns [out][in] (forward B operand, K-major over `in`).
+inline std::vector<float> transpose_io(const std::vector<float>& w, int in, int out) {
+  std::vector<float> t((size_t)in * out);
+  for (int i = 0; i < in; ++i)
+    for (int o = 0; o < out; ++o) t[(size_t)o * in + i] = w[(size_t)i * out + o];
+  return t;
+}
+
+}  // namespace bc2

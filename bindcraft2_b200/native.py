@@ -1,0 +1,263 @@
+"""Host side of the Evoformer-stack operators: the torch-tensor counterpart of the reference's JAX shim.
+
+Mirrors, name for name where it applies, ``bindcraft/af/native.py`` of the reference project:
+
+* ``weights_from_params``  -- writes the weight manifest a ``weights_dir`` attribute points at (reference :171-222);
+* ``_save_slots``          -- save-set slot count declared on the Python side (reference :1250-1273);
+* ``evoformer_fwd`` / ``evoformer_bwd`` -- the two FFI targets ``native_evoformer_fwd`` / ``native_evoformer_bwd``
+  (reference ``_make_stack`` :1409-1489 builds them into a ``jax.custom_vjp``; here ``make_stack`` builds a
+  ``torch.autograd.Function`` with the same residuals: masks, psave, msave, seed);
+* ``make_runner``          -- the hook callable that pads to a multiple of 32 and masks the pad (reference :906-975);
+* ``stack_prealloc``       -- trace-time allocation through ``native_stack_prealloc`` (reference :1279-1406).
+
+Where JAX is present, the same C entry points are what an XLA-FFI handler forwards to; the stub is given in
+INTEGRATION.md.  Operands here are CUDA torch tensors; outputs are allocated by this module the way XLA allocates the
+results of a custom call.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import tempfile
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+CZ, CM = 128, 256  # pair / msa channel widths of the main stack (native/block.cuh in the reference)
+
+_MAIN = 'alphafold/alphafold_iteration/evoformer/evoformer_iteration'
+
+
+# ----------------------------------------------------------------------------------------- manifests
+def write_manifest(arrays: Dict[str, np.ndarray], out_dir: str) -> str:
+    """Writes ``manifest.txt`` + one raw little-endian fp32 file per array.
+
+    Line format ``<name> <file> <ndim> <d0> ...`` with ``<file>`` = name with '/' -> '__' + '.f32', exactly what the
+    reference writes (bindcraft/af/native.py:207-219) and its loader reads (native/common.cuh:552-590)."""
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, 'manifest.txt'), 'w') as fh:
+        for name in sorted(arrays):
+            arr = np.ascontiguousarray(np.asarray(arrays[name], dtype='<f4'))
+            fn = name.replace('/', '__') + '.f32'
+            arr.tofile(os.path.join(out_dir, fn))
+            fh.write(f'{name} {fn} {arr.ndim} {" ".join(str(x) for x in arr.shape)}\n')
+    return out_dir
+
+
+def read_manifest(weights_dir: str) -> Dict[str, np.ndarray]:
+    out = {}
+    with open(os.path.join(weights_dir, 'manifest.txt')) as fh:
+        for line in fh:
+            parts = line.split()
+            if not parts:
+                continue
+            name, fn, nd = parts[0], parts[1], int(parts[2])
+            shape = tuple(int(x) for x in parts[3:3 + nd])
+            out[name] = np.fromfile(os.path.join(weights_dir, fn), dtype='<f4').reshape(shape)
+    return out
+
+
+def weights_from_params(params, out_dir: Optional[str] = None, depth: Optional[int] = None, prefix: str = _MAIN) -> str:
+    """Manifest from a haiku-style param tree ``{module_path: {param_name: array[depth, ...]}}``.
+
+    Same contract as the reference function of this name (bindcraft/af/native.py:171-222): the stacked leading axis
+    is sliced into ``param/block{b}/<module path below prefix>/<param>``, and the directory is keyed on the content so
+    two models with different weights never share one."""
+    mods = {k: v for k, v in params.items() if k.startswith(prefix)}
+    if not mods:
+        raise KeyError(f'no {prefix}* in these params')
+    if depth is None:
+        depth = min(int(np.asarray(a).shape[0]) for d in mods.values() for a in d.values())
+    h = hashlib.sha1()
+    for mod in sorted(mods):
+        for pname in sorted(mods[mod]):
+            h.update(mod.encode())
+            h.update(pname.encode())
+            h.update(np.ascontiguousarray(np.asarray(mods[mod][pname], np.float32)).tobytes()[:4096])
+    out = out_dir or os.path.join(tempfile.gettempdir(), f'bc2_native_{h.hexdigest()[:16]}')
+    if os.path.exists(os.path.join(out, 'manifest.txt')):
+        return out
+    flat = {}
+    for mod in sorted(mods):
+        path = mod[len(prefix) + 1:] if len(mod) > len(prefix) else ''
+        for pname in sorted(mods[mod]):
+            w = np.asarray(mods[mod][pname], np.float32)
+            for b in range(depth):
+                flat[f'param/block{b}/{path}/{pname}'] = w[b]
+    return write_manifest(flat, out)
+
+
+def weights_from_flat(params: Dict[str, torch.Tensor], out_dir: Optional[str] = None) -> str:
+    """Manifest from flat ``block{b}/<path>`` entries (the layout of ``synthetic.make_evoformer_params``)."""
+    out = out_dir or tempfile.mkdtemp(prefix='bc2_native_')
+    return write_manifest({'param/' + k: v.detach().cpu().numpy() for k, v in params.items()}, out)
+
+
+# ----------------------------------------------------------------------------------------- operators
+def _save_slots(depth: int, n: int) -> int:
+    """Slots of the save-set for (depth, padded length); must agree with the library (reference :1250-1273)."""
+    return int(_lib.load().native_save_slots_probe(int(depth), int(n)))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _check_f32(name, t, shape):
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous() or tuple(t.shape) != tuple(shape):
+        raise ValueError(f'{name}: expected contiguous CUDA float32 {tuple(shape)}, got {t.dtype} {tuple(t.shape)} '
+                         f'on {t.device}')
+
+
+def evoformer_fwd(pair, msa, pair_mask, msa_mask, seed, *, depth, save, weights_dir, pair_only=0, own_save=0,
+                  opm_first=1, dropout=0):
+    """FFI target ``native_evoformer_fwd`` (reference handler native/ffi.cu:183-331, 942-961).
+
+    Returns (pair_out f32 [N,N,128], msa_out f32 [S,N,256], psave bf16 [slots,N,N,128], msave f32 [slots,S,N,256]);
+    the save tensors are empty when ``save == 0`` (the detached pass)."""
+    lib = _lib.load()
+    n, s = int(pair.shape[0]), int(msa.shape[0])
+    _check_f32('pair', pair, (n, n, CZ))
+    _check_f32('msa', msa, (s, n, CM))
+    _check_f32('pair_mask', pair_mask, (n, n))
+    _check_f32('msa_mask', msa_mask, (s, n))
+    if n % 32:
+        raise ValueError('N must be a multiple of 32: pad and mask (make_runner does)')
+    slots = _save_slots(depth, n) if save else 0
+    pair_out = torch.empty_like(pair)
+    msa_out = torch.empty_like(msa)
+    psave = torch.empty((slots, n, n, CZ), dtype=torch.bfloat16, device=pair.device)
+    msave = torch.empty((slots, s, n, CM), dtype=torch.float32, device=pair.device)
+    stream = torch.cuda.current_stream(pair.device).cuda_stream
+    with torch.cuda.device(pair.device):
+        _lib.check(lib.bc2_evoformer_fwd(stream, _ptr(pair), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask), _ptr(seed), n, s,
+                                         int(depth), int(save), int(pair_only), int(own_save), int(opm_first),
+                                         int(dropout), os.fsencode(weights_dir), _ptr(pair_out), _ptr(msa_out),
+                                         _ptr(psave) if save else 0, _ptr(msave) if save else 0))
+    return pair_out, msa_out, psave, msave
+
+
+def evoformer_bwd(ct_pair, ct_msa, pair_mask, msa_mask, psave, msave, seed, *, depth, weights_dir, pair_only=0,
+                  own_save=0, opm_first=1, dropout=0):
+    """FFI target ``native_evoformer_bwd`` (reference handler native/ffi.cu:333-371, 963-981): (dpair, dmsa)."""
+    lib = _lib.load()
+    n, s = int(ct_pair.shape[0]), int(ct_msa.shape[0])
+    _check_f32('ct_pair', ct_pair, (n, n, CZ))
+    _check_f32('ct_msa', ct_msa, (s, n, CM))
+    if psave.dtype != torch.bfloat16 or tuple(psave.shape) != (_save_slots(depth, n), n, n, CZ):
+        raise ValueError('psave does not have the shape the forward declared')
+    dpair = torch.empty_like(ct_pair)
+    dmsa = torch.empty_like(ct_msa)
+    stream = torch.cuda.current_stream(ct_pair.device).cuda_stream
+    with torch.cuda.device(ct_pair.device):
+        _lib.check(lib.bc2_evoformer_bwd(stream, _ptr(ct_pair), _ptr(ct_msa), _ptr(pair_mask), _ptr(msa_mask),
+                                         _ptr(psave), _ptr(msave), _ptr(seed), n, s, int(depth), int(pair_only),
+                                         int(own_save), int(opm_first), int(dropout), os.fsencode(weights_dir),
+                                         _ptr(dpair), _ptr(dmsa)))
+    return dpair, dmsa
+
+
+def stack_prealloc(n, s, depth, weights_dir, pair_only=0, opm_first=1, dropout=0) -> None:
+    """Builds the stack object ahead of the first call (reference: native_stack_prealloc at trace time)."""
+    _lib.check(_lib.load().native_stack_prealloc(int(n), int(s), int(depth), os.fsencode(weights_dir), int(pair_only),
+                                                 int(opm_first), int(dropout)))
+
+
+def make_stack(n_block: int, weights_dir: str, dropout: bool = False):
+    """(pair, msa, pair_mask, msa_mask, seed) -> (pair, msa), differentiable in pair and msa.
+
+    The autograd pairing of the reference's ``_make_stack`` (bindcraft/af/native.py:1409-1489): the forward runs with
+    ``save=1`` and keeps (masks, psave, msave, seed) as residuals; the backward is one call of the bwd operator."""
+
+    class _Stack(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, pair, msa, pair_mask, msa_mask, seed):
+            need = pair.requires_grad or msa.requires_grad
+            p, m, psave, msave = evoformer_fwd(pair, msa, pair_mask, msa_mask, seed, depth=n_block, save=int(need),
+                                               weights_dir=weights_dir, dropout=int(dropout))
+            ctx.save_for_backward(pair_mask, msa_mask, psave, msave, seed)
+            return p, m
+
+        @staticmethod
+        def backward(ctx, ct_pair, ct_msa):
+            pair_mask, msa_mask, psave, msave, seed = ctx.saved_tensors
+            dp, dm = evoformer_bwd(ct_pair.contiguous(), ct_msa.contiguous(), pair_mask, msa_mask, psave, msave, seed,
+                                   depth=n_block, weights_dir=weights_dir, dropout=int(dropout))
+            return dp, dm, None, None, None
+
+    return _Stack.apply
+
+
+def make_runner(weights_dir: str, depth: int = 48, dropout: bool = False):
+    """Hook callable ``run(acts, masks, n_block, seed=None)`` with the reference's padding rule.
+
+    The kernels take lengths that are multiples of 32; other lengths are zero-padded and the pad is masked out, then
+    cropped from the result (bindcraft/af/native.py:927-972)."""
+    cache = {}
+
+    def run(acts, masks, n_block=depth, seed=None):
+        n = int(acts['pair'].shape[0])
+        pad = (-n) % 32
+        fn = cache.get(n_block)
+        if fn is None:
+            fn = cache[n_block] = make_stack(int(n_block), weights_dir, dropout)
+        dev = acts['pair'].device
+        if seed is None:
+            seed = torch.zeros(2, dtype=torch.int32, device=dev)  # [seed, enabled]
+        pair, msa = acts['pair'].float(), acts['msa'].float()
+        pair_mask, msa_mask = masks['pair'].float(), masks['msa'].float()
+        if pad:
+            pair = torch.nn.functional.pad(pair, (0, 0, 0, pad, 0, pad))
+            msa = torch.nn.functional.pad(msa, (0, 0, 0, pad))
+            pair_mask = torch.nn.functional.pad(pair_mask, (0, pad, 0, pad))
+            msa_mask = torch.nn.functional.pad(msa_mask, (0, pad))
+        p, m = fn(pair.contiguous(), msa.contiguous(), pair_mask.contiguous(), msa_mask.contiguous(), seed)
+        if pad:
+            p, m = p[:n, :n], m[:, :n]
+        return {'pair': p.to(acts['pair'].dtype), 'msa': m.to(acts['msa'].dtype)}
+
+    return run
+
+
+# ----------------------------------------------------------------------------------------- host-buffer entry
+class HostStep:
+    """Forward + backward of the stack from HOST buffers: the end-to-end call a host-side caller makes.
+
+    Pinned host inputs (pair, msa, masks, cotangents) are copied to the device, the forward (save=1) and backward run,
+    and the outputs and input gradients are copied back to pinned host memory.  Device staging buffers are allocated
+    once per shape."""
+
+    def __init__(self, n, s, depth, weights_dir, device='cuda:0'):
+        self.n, self.s, self.depth, self.dir, self.dev = n, s, depth, weights_dir, torch.device(device)
+        f = dict(dtype=torch.float32, device=self.dev)
+        self.d = {k: torch.empty(shape, **f) for k, shape in self._shapes().items()}
+        self.seed = torch.zeros(2, dtype=torch.int32, device=self.dev)
+        self.h_out = {k: torch.empty(self._shapes()[k], dtype=torch.float32).pin_memory()
+                      for k in ('pair', 'msa', 'ct_pair', 'ct_msa')}
+
+    def _shapes(self):
+        n, s = self.n, self.s
+        return {'pair': (n, n, CZ), 'msa': (s, n, CM), 'pair_mask': (n, n), 'msa_mask': (s, n), 'ct_pair': (n, n, CZ),
+                'ct_msa': (s, n, CM)}
+
+    def h2d_bytes(self):
+        return sum(int(np.prod(v)) * 4 for v in self._shapes().values())
+
+    def d2h_bytes(self):
+        return sum(self.h_out[k].numel() * 4 for k in self.h_out)
+
+    def __call__(self, host: Dict[str, torch.Tensor]):
+        for k, t in self.d.items():
+            t.copy_(host[k], non_blocking=True)
+        p, m, psave, msave = evoformer_fwd(self.d['pair'], self.d['msa'], self.d['pair_mask'], self.d['msa_mask'],
+                                           self.seed, depth=self.depth, save=1, weights_dir=self.dir)
+        dp, dm = evoformer_bwd(self.d['ct_pair'], self.d['ct_msa'], self.d['pair_mask'], self.d['msa_mask'], psave,
+                               msave, self.seed, depth=self.depth, weights_dir=self.dir)
+        self.h_out['pair'].copy_(p, non_blocking=True)
+        self.h_out['msa'].copy_(m, non_blocking=True)
+        self.h_out['ct_pair'].copy_(dp, non_blocking=True)
+        self.h_out['ct_msa'].copy_(dm, non_blocking=True)
+        return self.h_out

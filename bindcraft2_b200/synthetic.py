@@ -1,0 +1,158 @@
+"""Seeded synthetic weights and inputs with the shapes, names and initialisers of the reference model.
+
+No public dataset or checkpoint is involved: AlphaFold2 parameters are a multi-GB download and the reference's own
+gates read oracle dumps that are not shipped with it, so the parity tests, the smoke check and the benchmark all use
+random-init weights (dropout off) drawn here from a fixed seed.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict
+
+import torch
+
+Params = Dict[str, torch.Tensor]
+
+# ----------------------------------------------------------------------------- seeded synthetic weights
+_TRUNC_STD = 0.87962566103423978  # common_modules.py:24-26
+
+
+def _trunc_normal(g, shape, std):
+    """hk.initializers.TruncatedNormal: N(0,std) resampled inside +-2 std (inverse-CDF form)."""
+    u = torch.rand(shape, generator=g, dtype=torch.float64)
+    lo, hi = 0.5 * (1 + math.erf(-2 / math.sqrt(2))), 0.5 * (1 + math.erf(2 / math.sqrt(2)))
+    x = torch.erfinv(2 * (lo + u * (hi - lo)) - 1) * math.sqrt(2)
+    return (x * std).float()
+
+
+def _lin(g, fan_in, shape, kind='linear'):
+    """common_modules.get_initializer_scale (common_modules.py:29-49): fan-in scaled truncated normal."""
+    scale = (2.0 if kind == 'relu' else 1.0) / fan_in
+    return _trunc_normal(g, shape, math.sqrt(scale) / _TRUNC_STD)
+
+
+def _glorot(g, shape, fan_in, fan_out):
+    """hk VarianceScaling(1, fan_avg, uniform) (modules.py:307-310)."""
+    lim = math.sqrt(3.0 * 2.0 / (fan_in + fan_out))
+    return (torch.rand(shape, generator=g) * 2 - 1) * lim
+
+
+def _ln(g, c):
+    """LayerNorm scale 1 / offset 0, perturbed so that both parameters are exercised."""
+    return 1 + 0.1 * torch.randn(c, generator=g), 0.1 * torch.randn(c, generator=g)
+
+
+def _attention_params(g, p, pre, c_in, heads, d, c_out, global_kv=False):
+    p[pre + '/query_w'] = _glorot(g, (c_in, heads, d), c_in, heads * d)
+    if global_kv:
+        p[pre + '/key_w'] = _glorot(g, (c_in, d), c_in, d)
+        p[pre + '/value_w'] = _glorot(g, (c_in, d), c_in, d)
+    else:
+        p[pre + '/key_w'] = _glorot(g, (c_in, heads, d), c_in, heads * d)
+        p[pre + '/value_w'] = _glorot(g, (c_in, heads, d), c_in, heads * d)
+    # the reference zero-initialises gating_w and output_w (modules.py:366-390); that makes a random-init
+    # block the identity, so the oracle uses non-zero draws here and a gate bias of 1.
+    p[pre + '/gating_w'] = _glorot(g, (c_in, heads, d), c_in, heads * d)
+    p[pre + '/gating_b'] = torch.ones(heads, d)
+    p[pre + '/output_w'] = _glorot(g, (heads, d, c_out), heads * d, c_out)
+    p[pre + '/output_b'] = 0.02 * torch.randn(c_out, generator=g)
+
+
+def _transition_params(g, p, pre, c, factor):
+    p[pre + '/input_layer_norm/scale'], p[pre + '/input_layer_norm/offset'] = _ln(g, c)
+    p[pre + '/transition1/weights'] = _lin(g, c, (c, c * factor), 'relu')
+    p[pre + '/transition1/bias'] = 0.02 * torch.randn(c * factor, generator=g)
+    p[pre + '/transition2/weights'] = _lin(g, c * factor, (c * factor, c))
+    p[pre + '/transition2/bias'] = 0.02 * torch.randn(c, generator=g)
+
+
+def _trimul_params(g, p, pre, c, hid):
+    p[pre + '/left_norm_input/scale'], p[pre + '/left_norm_input/offset'] = _ln(g, c)
+    p[pre + '/projection/weights'] = _lin(g, c, (c, 2 * hid))
+    p[pre + '/projection/bias'] = 0.02 * torch.randn(2 * hid, generator=g)
+    p[pre + '/gate/weights'] = _lin(g, c, (c, 2 * hid))
+    p[pre + '/gate/bias'] = torch.ones(2 * hid)
+    p[pre + '/center_norm/scale'], p[pre + '/center_norm/offset'] = _ln(g, hid)
+    p[pre + '/output_projection/weights'] = _lin(g, hid, (hid, c))
+    p[pre + '/output_projection/bias'] = 0.02 * torch.randn(c, generator=g)
+    p[pre + '/gating_linear/weights'] = _lin(g, c, (c, c))
+    p[pre + '/gating_linear/bias'] = torch.ones(c)
+
+
+def _triattn_params(g, p, pre, c, heads, d):
+    p[pre + '/query_norm/scale'], p[pre + '/query_norm/offset'] = _ln(g, c)
+    p[pre + '/feat_2d_weights'] = torch.randn(c, heads, generator=g) / math.sqrt(c)
+    _attention_params(g, p, pre + '/attention', c, heads, d, c)
+
+
+def pair_block_params(g, p, pre, cz, tri_hidden, tri_heads, tri_d, trans_factor):
+    _trimul_params(g, p, pre + 'triangle_multiplication_outgoing', cz, tri_hidden)
+    _trimul_params(g, p, pre + 'triangle_multiplication_incoming', cz, tri_hidden)
+    _triattn_params(g, p, pre + 'triangle_attention_starting_node', cz, tri_heads, tri_d)
+    _triattn_params(g, p, pre + 'triangle_attention_ending_node', cz, tri_heads, tri_d)
+    _transition_params(g, p, pre + 'pair_transition', cz, trans_factor)
+
+
+def make_evoformer_params(seed: int, depth: int, cm=256, cz=128, is_extra_msa=False) -> Params:
+    """Seeded random-init weights for ``depth`` Evoformer blocks, keyed ``block{b}/<haiku path>``.
+
+    Shapes follow the manifest the reference writes (bindcraft/af/native.py:171-222).  Initialisers follow
+    common_modules.py:24-49 and modules.py:307-310,546-551, except that layers the reference zero-initialises
+    get the 'linear' initialiser (a zero-init block is the identity and would test nothing)."""
+    g = torch.Generator().manual_seed(seed)
+    p: Params = {}
+    msa_heads = 8
+    msa_d = cm // msa_heads
+    for b in range(depth):
+        pre = f'block{b}/'
+        o = pre + 'outer_product_mean'
+        p[o + '/layer_norm_input/scale'], p[o + '/layer_norm_input/offset'] = _ln(g, cm)
+        for side in ('left', 'right'):
+            p[o + f'/{side}_projection/weights'] = _lin(g, cm, (cm, 32))
+            p[o + f'/{side}_projection/bias'] = 0.02 * torch.randn(32, generator=g)
+        p[o + '/output_w'] = torch.randn(32, 32, cz, generator=g) * math.sqrt(2.0 / (32 * cz))
+        p[o + '/output_b'] = 0.02 * torch.randn(cz, generator=g)
+        r = pre + 'msa_row_attention_with_pair_bias'
+        p[r + '/query_norm/scale'], p[r + '/query_norm/offset'] = _ln(g, cm)
+        p[r + '/feat_2d_norm/scale'], p[r + '/feat_2d_norm/offset'] = _ln(g, cz)
+        p[r + '/feat_2d_weights'] = torch.randn(cz, msa_heads, generator=g) / math.sqrt(cz)
+        _attention_params(g, p, r + '/attention', cm, msa_heads, msa_d, cm)
+        if is_extra_msa:
+            c = pre + 'msa_column_global_attention'
+            p[c + '/query_norm/scale'], p[c + '/query_norm/offset'] = _ln(g, cm)
+            _attention_params(g, p, c + '/attention', cm, msa_heads, msa_d, cm, global_kv=True)
+        else:
+            c = pre + 'msa_column_attention'
+            p[c + '/query_norm/scale'], p[c + '/query_norm/offset'] = _ln(g, cm)
+            _attention_params(g, p, c + '/attention', cm, msa_heads, msa_d, cm)
+        _transition_params(g, p, pre + 'msa_transition', cm, 4)
+        pair_block_params(g, p, pre, cz, 128, 4, 32, 4)
+    return p
+
+
+def make_template_stack_params(seed: int, depth: int = 2, ct=64) -> Params:
+    """Template pair stack weights at c_t=64: tri-mul hidden 64, tri-attn 4x16, transition x2
+    (config.py template.template_pair_stack; manifest layout bindcraft/af/native.py:264-323)."""
+    g = torch.Generator().manual_seed(seed)
+    p: Params = {}
+    for b in range(depth):
+        pair_block_params(g, p, f'block{b}/', ct, 64, 4, 16, 2)
+    return p
+
+
+def make_block_inputs(seed: int, n: int, s: int, cm=256, cz=128, scale=1.0, shift=0.0, masked=0):
+    """Seeded activations, masks and cotangents for one stack call.  ``masked`` trailing residues are
+    masked out (the reference pads to a multiple of 32 and masks the pad, bindcraft/af/native.py:927-972)."""
+    g = torch.Generator().manual_seed(seed)
+    msa = torch.randn(s, n, cm, generator=g) * scale + shift
+    pair = torch.randn(n, n, cz, generator=g) * scale + shift
+    res_mask = torch.ones(n)
+    if masked:
+        res_mask[n - masked:] = 0
+    msa_mask = res_mask[None, :].repeat(s, 1)
+    pair_mask = res_mask[:, None] * res_mask[None, :]
+    ct_msa = torch.randn(s, n, cm, generator=g)
+    ct_pair = torch.randn(n, n, cz, generator=g)
+    return dict(msa=msa, pair=pair, msa_mask=msa_mask, pair_mask=pair_mask, ct_msa=ct_msa, ct_pair=ct_pair)
+
+

@@ -1,0 +1,95 @@
+/* C ABI of the B200 AlphaFold2 design-step trunk.
+ *
+ * Each entry point is the body of one operator of the reference's JAX-FFI surface (native/ffi.cu in the reference
+ * project): same operands in the same order, same dtypes and dense row-major layouts, same attributes, same results.
+ * Buffers are device pointers; `stream` is the cudaStream_t the operator is ordered on (XLA's stream in the
+ * reference, ffi.cu:945).  Weights are not operands: `weights_dir` names a directory holding `manifest.txt` and raw
+ * fp32 files keyed by haiku scope paths, exactly what the reference's Python shim writes
+ * (bindcraft/af/native.py:171-222).
+ *
+ * Return value: 0 on success, non-zero on failure with the message available from bc2_last_error() (the reference
+ * returns ffi::Error::InvalidArgument for bad shapes and exits the process on CUDA errors, ffi.cu:221-225 and
+ * common.cuh:163-181; this library never exits the process).
+ *
+ * Both stack calls are pure: the backward reads nothing that the forward did not hand back through psave/msave
+ * (ffi.cu:17-25), so interleaved forward/backward pairs of different states cannot corrupt each other.
+ */
+#ifndef BC2_B200_H
+#define BC2_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Replaces the handler NativeEvoformerFwd / FwdImpl (native/ffi.cu:183-331, bound at :942-961), FFI target
+ * `native_evoformer_fwd`.
+ *   pair      f32 [N,N,128]      msa      f32 [S,N,256]
+ *   pair_mask f32 [N,N]          msa_mask f32 [S,N]
+ *   seed      u32 [2] = {seed, dropout_enabled} (device; accepted, dropout itself is not applied)
+ *   attrs     depth, save, pair_only, own_save, opm_first, dropout, weights_dir
+ *   results   pair_out f32 [N,N,128], msa_out f32 [S,N,256],
+ *             psave bf16 [slots,N,N,128], msave f32 [slots,S,N,256]   (slots = bc2 native_save_slots_probe(depth, N);
+ *             both may be null when save == 0: the detached pass)
+ * N must be a multiple of 32 (the caller pads and masks, bindcraft/af/native.py:927-972). */
+int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
+                      const uint32_t* seed, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t pair_only,
+                      int64_t own_save, int64_t opm_first, int64_t dropout, const char* weights_dir, float* pair_out,
+                      float* msa_out, uint16_t* psave, float* msave);
+
+/* Replaces NativeEvoformerBwd / BwdImpl (native/ffi.cu:333-371, bound at :963-981), FFI target
+ * `native_evoformer_bwd`: the VJP of the call above with respect to pair and msa.
+ *   ct_pair f32 [N,N,128], ct_msa f32 [S,N,256], masks, psave, msave, seed as produced/used by the forward
+ *   results dpair f32 [N,N,128], dmsa f32 [S,N,256] */
+int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
+                      const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* seed, int64_t N,
+                      int64_t S, int64_t depth, int64_t pair_only, int64_t own_save, int64_t opm_first, int64_t dropout,
+                      const char* weights_dir, float* dpair, float* dmsa);
+
+/* Same contract as the reference's plain-C entry point of this name (native/ffi.cu:835-855): build (and cache) the
+ * stack object for this shape and weight directory ahead of the first call, so that its device allocations happen at
+ * trace time.  Prints one `native:` line to stderr.  Returns 0 on success. */
+int native_stack_prealloc(int N, int S, int depth, const char* weights_dir, int pair_only, int opm_first, int dropout);
+
+/* Same contract as the reference's native_save_slots_probe (declared for native/stack.cuh:795-808's slot policy,
+ * mirrored in bindcraft/af/native.py:1250-1273): number of save-set slots the forward writes for (depth, n).  A B200
+ * holds the full set at every supported length, so this is `depth`. */
+int native_save_slots_probe(int depth, int n);
+
+/* Drops every cached stack object (device memory and weights).  No counterpart in the reference, which keeps its
+ * caches for the life of the process. */
+void bc2_release_all(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* bc2_last_error(void);
+
+/* Reads and clears the device-side status word that bounded waits inside the kernels set when they give up
+ * (0 = no kernel reported a problem).  Synchronises the device. */
+int bc2_device_status(void);
+
+/* Number of kernels this library has launched on behalf of the calling process since load (for the benchmark's
+ * launch count). */
+int64_t bc2_launch_count(void);
+
+/* ---- bring-up / unit-test entry points (not part of the reference surface) ------------------------------------ */
+
+/* D[z][m][n] = sum_k A[z](m,k) B[z](n,k) with bf16 operands and fp32 accumulate, written as bf16 [batch][M][N].
+ * a_mn / b_mn select MN-major storage of that operand (element (r,k) at base[k*ld + r]).  use_ref != 0 runs the
+ * CUDA-core reference kernel instead of the tcgen05 kernel. */
+int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, int a_mn, const uint16_t* b, int64_t ldb,
+                  int64_t b_bs, int b_mn, uint16_t* d, int64_t M, int64_t N, int64_t K, int64_t batch, int bn,
+                  int use_ref);
+
+/* One gated attention forward+backward on caller buffers (layouts in bindcraft2_b200/csrc/attn.cuh).
+ * qkvg bf16 [rows][4*H*D]; bias f32 [H][N][N]; mask f32 [B][N]; d_og bf16 [rows][H*D].
+ * Outputs: og bf16 [rows][H*D]; d_qkvg bf16 [rows][4*H*D] (dq|dk|dv|d gate-pre); d_bias f32 [H][N][N].
+ * transposed != 0 walks the batch along columns (ending-node orientation). */
+int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, const uint16_t* d_og,
+                       int64_t B, int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og, uint16_t* d_qkvg,
+                       float* d_bias, int use_ref);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BC2_B200_H */

@@ -1,0 +1,234 @@
+"""CPU oracle for the AlphaFold2 design-step trunk: a PyTorch restatement of the reference JAX modules.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this file; the CUDA path must never
+route through it.  It exists so that the parity tests, the smoke check and the CPU-baseline leg of the
+benchmark have an independent statement of the arithmetic.
+
+PARITY UNPINNED: the reference ships no golden vectors, oracle dumps or unit tests for this path, and
+its own implementation (JAX + dm-haiku) cannot be imported where this was written.  The functions below
+follow the reference source line by line (citations are paths inside the reference project) and use
+torch autograd for the input gradients; the fixtures under tests/golden/ are outputs of THIS file.
+
+Parameter names are the haiku scope paths the reference writes into its weight manifests
+(bindcraft/af/native.py:171-222), e.g. ``triangle_multiplication_outgoing/projection/weights``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict
+
+import torch
+
+Params = Dict[str, torch.Tensor]
+
+
+# ----------------------------------------------------------------------------- primitives
+def layer_norm(x, scale, offset, eps=1e-5):
+    """hk.LayerNorm over the last axis, eps inside the rsqrt, learned scale/offset vectors.
+
+    bindcraft/af/alphafold/model/common_modules.py:127-184 (two-pass variance; the fused tri-mul norms ask
+    for the one-pass form, modules.py:909-919, which is the same number in exact arithmetic)."""
+    mean = x.mean(-1, keepdim=True)
+    var = ((x - mean) ** 2).mean(-1, keepdim=True)
+    return (x - mean) * torch.rsqrt(var + eps) * scale + offset
+
+
+def linear(x, w, b=None):
+    """common_modules.Linear, one input dim: einsum('...a,ah->...h') + bias (common_modules.py:97-125)."""
+    y = x @ w
+    return y if b is None else y + b
+
+
+def sub(p: Params, prefix: str) -> Params:
+    """View of the entries under ``prefix/``."""
+    n = len(prefix) + 1
+    return {k[n:]: v for k, v in p.items() if k.startswith(prefix + '/')}
+
+
+LOGIT_CLIP = 1e8  # bindcraft/af/accel.py:7
+
+
+def attention(p: Params, q_data, m_data, bias, nonbatched_bias=None):
+    """modules.Attention.__call__ (modules.py:313-400) with accel._attend_stock (accel.py:13-22).
+
+    q_data [B,Q,A], m_data [B,K,A], bias [B,1,1,K], nonbatched_bias [H,Q,K]."""
+    qw, kw, vw = p['query_w'], p['key_w'], p['value_w']
+    key_dim = qw.shape[-1]
+    q = torch.einsum('bqa,ahc->bqhc', q_data, qw) * key_dim ** (-0.5)
+    k = torch.einsum('bka,ahc->bkhc', m_data, kw)
+    v = torch.einsum('bka,ahc->bkhc', m_data, vw)
+    logits = torch.einsum('bqhc,bkhc->bhqk', q, k) + bias
+    if nonbatched_bias is not None:
+        logits = logits + nonbatched_bias[None]
+    logits = torch.clamp(logits, -LOGIT_CLIP, LOGIT_CLIP)
+    weights = torch.softmax(logits, dim=-1)
+    avg = torch.einsum('bhqk,bkhc->bqhc', weights, v)
+    gate = torch.sigmoid(torch.einsum('bqc,chv->bqhv', q_data, p['gating_w']) + p['gating_b'])
+    avg = avg * gate
+    return torch.einsum('bqhc,hco->bqo', avg, p['output_w']) + p['output_b']
+
+
+def global_attention(p: Params, q_data, m_data, q_mask):
+    """modules.GlobalAttention.__call__ (modules.py:403-497); q_mask [B,Q,1]."""
+    qw = p['query_w']
+    key_dim = qw.shape[-1]
+    v = torch.einsum('bka,ac->bkc', m_data, p['value_w'])
+    # utils.mask_mean(q_mask, q_data, axis=1): sum(mask*x)/(sum(mask)+1e-10)
+    q_avg = (q_mask * q_data).sum(1) / (q_mask.expand_as(q_data).sum(1) + 1e-10)
+    q = torch.einsum('ba,ahc->bhc', q_avg, qw) * key_dim ** (-0.5)
+    k = torch.einsum('bka,ac->bkc', m_data, p['key_w'])
+    bias = 1e9 * (q_mask[:, None, :, 0] - 1.0)
+    logits = torch.einsum('bhc,bkc->bhk', q, k) + bias
+    weights = torch.softmax(logits, dim=-1)
+    avg = torch.einsum('bhk,bkc->bhc', weights, v)
+    gate = torch.sigmoid(torch.einsum('bqc,chv->bqhv', q_data, p['gating_w']) + p['gating_b'])
+    avg = avg[:, None] * gate
+    return torch.einsum('bqhc,hco->bqo', avg, p['output_w']) + p['output_b']
+
+
+# ----------------------------------------------------------------------------- Evoformer modules
+def transition(p: Params, act):
+    """modules.Transition.__call__ (modules.py:252-304); the mask is unused there."""
+    x = layer_norm(act, p['input_layer_norm/scale'], p['input_layer_norm/offset'])
+    h = torch.relu(linear(x, p['transition1/weights'], p['transition1/bias']))
+    return linear(h, p['transition2/weights'], p['transition2/bias'])
+
+
+def outer_product_mean(p: Params, msa, msa_mask):
+    """modules.OuterProductMean.__call__ (modules.py:1128-1213).  msa [S,N,Cm] -> [N,N,Cz]."""
+    mask = msa_mask[..., None]
+    act = layer_norm(msa, p['layer_norm_input/scale'], p['layer_norm_input/offset'])
+    left = mask * linear(act, p['left_projection/weights'], p['left_projection/bias'])
+    right = mask * linear(act, p['right_projection/weights'], p['right_projection/bias'])
+    # einsum('acb,ade->dceb') then ('dceb,cef->dbf') then transpose -> [b,d,f] (modules.py:1195-1198)
+    outer = torch.einsum('abc,ade->bdce', left, right)
+    out = torch.einsum('bdce,cef->bdf', outer, p['output_w']) + p['output_b']
+    norm = torch.einsum('abc,adc->bdc', mask, mask)
+    return out / (1e-3 + norm)
+
+
+def msa_row_attention_with_pair_bias(p: Params, msa, msa_mask, pair):
+    """modules.MSARowAttentionWithPairBias.__call__ (modules.py:500-563)."""
+    bias = (1e9 * (msa_mask - 1.0))[:, None, None, :]
+    m = layer_norm(msa, p['query_norm/scale'], p['query_norm/offset'])
+    z = layer_norm(pair, p['feat_2d_norm/scale'], p['feat_2d_norm/offset'])
+    nb = torch.einsum('qkc,ch->hqk', z, p['feat_2d_weights'])
+    return attention(sub(p, 'attention'), m, m, bias, nb)
+
+
+def msa_column_attention(p: Params, msa, msa_mask):
+    """modules.MSAColumnAttention.__call__ (modules.py:566-616)."""
+    m = msa.transpose(0, 1)
+    mk = msa_mask.transpose(0, 1)
+    bias = (1e9 * (mk - 1.0))[:, None, None, :]
+    m = layer_norm(m, p['query_norm/scale'], p['query_norm/offset'])
+    return attention(sub(p, 'attention'), m, m, bias).transpose(0, 1)
+
+
+def msa_column_global_attention(p: Params, msa, msa_mask):
+    """modules.MSAColumnGlobalAttention.__call__ (modules.py:619-672)."""
+    m = msa.transpose(0, 1)
+    mk = msa_mask.transpose(0, 1)
+    m = layer_norm(m, p['query_norm/scale'], p['query_norm/offset'])
+    return global_attention(sub(p, 'attention'), m, m, mk[..., None]).transpose(0, 1)
+
+
+def triangle_multiplication(p: Params, pair, pair_mask, outgoing: bool):
+    """modules.TriangleMultiplication._fused_triangle_multiplication (modules.py:1043-1088)."""
+    mask = pair_mask[..., None]
+    x = layer_norm(pair, p['left_norm_input/scale'], p['left_norm_input/offset'])
+    proj = mask * linear(x, p['projection/weights'], p['projection/bias'])
+    proj = proj * torch.sigmoid(linear(x, p['gate/weights'], p['gate/bias']))
+    c = proj.shape[-1] // 2
+    left, right = proj[..., :c], proj[..., c:]
+    eq = 'ikc,jkc->ijc' if outgoing else 'kjc,kic->ijc'  # config.py:439-454
+    act = torch.einsum(eq, left, right)
+    act = layer_norm(act, p['center_norm/scale'], p['center_norm/offset'])
+    act = linear(act, p['output_projection/weights'], p['output_projection/bias'])
+    gate = torch.sigmoid(linear(x, p['gating_linear/weights'], p['gating_linear/bias']))
+    return act * gate
+
+
+def triangle_attention(p: Params, pair, pair_mask, per_column: bool):
+    """modules.TriangleAttention.__call__ (modules.py:675-734)."""
+    if per_column:
+        pair = pair.transpose(0, 1)
+        pair_mask = pair_mask.transpose(0, 1)
+    bias = (1e9 * (pair_mask - 1.0))[:, None, None, :]
+    x = layer_norm(pair, p['query_norm/scale'], p['query_norm/offset'])
+    nb = torch.einsum('qkc,ch->hqk', x, p['feat_2d_weights'])
+    out = attention(sub(p, 'attention'), x, x, bias, nb)
+    if per_column:
+        out = out.transpose(0, 1)
+    return out
+
+
+def evoformer_iteration(p: Params, msa, pair, msa_mask, pair_mask, is_extra_msa=False, opm_first=True):
+    """modules.EvoformerIteration.__call__ (modules.py:1266-1391), dropout off, so dropout_wrapper
+    (modules.py:46-76) reduces to ``act + module(act)``.  Multimer order: OPM first (config.py:411-418)."""
+    if opm_first:
+        pair = pair + outer_product_mean(sub(p, 'outer_product_mean'), msa, msa_mask)
+    msa = msa + msa_row_attention_with_pair_bias(sub(p, 'msa_row_attention_with_pair_bias'), msa, msa_mask, pair)
+    if is_extra_msa:
+        msa = msa + msa_column_global_attention(sub(p, 'msa_column_global_attention'), msa, msa_mask)
+    else:
+        msa = msa + msa_column_attention(sub(p, 'msa_column_attention'), msa, msa_mask)
+    msa = msa + transition(sub(p, 'msa_transition'), msa)
+    if not opm_first:
+        pair = pair + outer_product_mean(sub(p, 'outer_product_mean'), msa, msa_mask)
+    pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_outgoing'), pair, pair_mask, True)
+    pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_incoming'), pair, pair_mask, False)
+    pair = pair + triangle_attention(sub(p, 'triangle_attention_starting_node'), pair, pair_mask, False)
+    pair = pair + triangle_attention(sub(p, 'triangle_attention_ending_node'), pair, pair_mask, True)
+    pair = pair + transition(sub(p, 'pair_transition'), pair)
+    return msa, pair
+
+
+def evoformer_stack(p: Params, msa, pair, msa_mask, pair_mask, depth, is_extra_msa=False, opm_first=True):
+    """The layer_stack of EvoformerIteration (modules_multimer.py:619-679; extra stack :547-603).
+    ``p`` holds ``block{b}/...`` entries, one independent weight set per block."""
+    for b in range(depth):
+        msa, pair = evoformer_iteration(sub(p, f'block{b}'), msa, pair, msa_mask, pair_mask,
+                                        is_extra_msa=is_extra_msa, opm_first=opm_first)
+    return msa, pair
+
+
+def template_pair_iteration(p: Params, pair, pair_mask):
+    """modules_multimer.TemplateEmbeddingIteration.__call__ (modules_multimer.py:1008-1077): tri-mul out,
+    tri-mul in, tri-attn start, tri-attn end, pair transition, each residual, dropout off."""
+    pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_outgoing'), pair, pair_mask, True)
+    pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_incoming'), pair, pair_mask, False)
+    pair = pair + triangle_attention(sub(p, 'triangle_attention_starting_node'), pair, pair_mask, False)
+    pair = pair + triangle_attention(sub(p, 'triangle_attention_ending_node'), pair, pair_mask, True)
+    pair = pair + transition(sub(p, 'pair_transition'), pair)
+    return pair
+
+
+def template_pair_stack(p: Params, pair, pair_mask, depth):
+    for b in range(depth):
+        pair = template_pair_iteration(sub(p, f'block{b}'), pair, pair_mask)
+    return pair
+
+
+def stack_fwd_bwd(p: Params, inp, depth, is_extra_msa=False, opm_first=True, dtype=torch.float32):
+    """Forward and input gradients (weights frozen) of the stack for cotangents ``ct_msa``/``ct_pair``."""
+    pp = {k: v.to(dtype) for k, v in p.items()}
+    msa = inp['msa'].to(dtype).clone().requires_grad_(True)
+    pair = inp['pair'].to(dtype).clone().requires_grad_(True)
+    m_out, p_out = evoformer_stack(pp, msa, pair, inp['msa_mask'].to(dtype), inp['pair_mask'].to(dtype), depth,
+                                   is_extra_msa=is_extra_msa, opm_first=opm_first)
+    loss = (m_out * inp['ct_msa'].to(dtype)).sum() + (p_out * inp['ct_pair'].to(dtype)).sum()
+    d_msa, d_pair = torch.autograd.grad(loss, [msa, pair])
+    return dict(msa=m_out.detach(), pair=p_out.detach(), d_msa=d_msa, d_pair=d_pair)
+
+
+# ----------------------------------------------------------------------------- error metrics
+def rel_l2(a, b):
+    """||a-b|| / ||b||, the figure the reference's gates print (native/common.cuh:597-621)."""
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def cosine(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a @ b) / (a.norm() * b.norm()).clamp_min(1e-30))

@@ -1,0 +1,62 @@
+"""CPU tests of the drop-in boundary: the library loads without a GPU and exports what the header declares."""
+import os
+import re
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    src = open(os.path.join(ROOT, 'include', 'bc2_b200.h')).read()
+    src = re.sub(r'/\*.*?\*/', '', src, flags=re.S)
+    return sorted(set(re.findall(r'\b(\w+)\s*\([^;{]*\)\s*;', src)))
+
+
+def test_header_declares_the_reference_surface():
+    names = _declared()
+    for need in ('bc2_evoformer_fwd', 'bc2_evoformer_bwd', 'native_stack_prealloc', 'native_save_slots_probe'):
+        assert need in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    from bindcraft2_b200 import _lib
+    for name in _declared():
+        assert hasattr(lib, name), name
+        assert name in _lib.PROTOTYPES, f'{name} has no ctypes prototype'
+
+
+def test_save_slots_policy(lib):
+    from bindcraft2_b200 import native
+    assert native._save_slots(48, 224) == 48
+    assert native._save_slots(4, 768) == 4
+
+
+def test_bad_weights_dir_is_an_error_not_an_exit(lib, tmp_path):
+    """Host-side failure injection: a missing manifest comes back as a status code and a message."""
+    rc = lib.native_stack_prealloc(32, 1, 1, os.fsencode(str(tmp_path)), 0, 1, 0)
+    assert rc != 0
+    assert lib.bc2_last_error()  # either "no CUDA device" here or "cannot open manifest" on a GPU box
+
+
+def test_manifest_roundtrip(tmp_path):
+    from bindcraft2_b200 import native
+    arrays = {'param/block0/a/weights': np.arange(6, dtype=np.float32).reshape(2, 3), 'param/block0/a/bias': np.ones(3, np.float32)}
+    d = native.write_manifest(arrays, str(tmp_path / 'w'))
+    lines = open(os.path.join(d, 'manifest.txt')).read().splitlines()
+    assert 'param/block0/a/weights param__block0__a__weights.f32 2 2 3' in lines
+    back = native.read_manifest(d)
+    for k in arrays:
+        np.testing.assert_array_equal(back[k], arrays[k])
+
+
+def test_weights_from_params_slices_the_stacked_axis(tmp_path):
+    from bindcraft2_b200 import native
+    pre = native._MAIN
+    params = {pre + '/pair_transition/transition1': {'weights': np.random.rand(3, 4, 8).astype(np.float32)},
+              'unrelated/module': {'w': np.zeros((3, 2), np.float32)}}
+    d = native.weights_from_params(params, out_dir=str(tmp_path / 'm'))
+    back = native.read_manifest(d)
+    assert sorted(back) == [f'param/block{b}/pair_transition/transition1/weights' for b in range(3)]
+    np.testing.assert_array_equal(back['param/block1/pair_transition/transition1/weights'],
+                                  params[pre + '/pair_transition/transition1']['weights'][1])

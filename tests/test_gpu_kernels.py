@@ -1,0 +1,106 @@
+"""GPU unit tests of the tcgen05 kernels through the C ABI, against plain PyTorch fp32 math on the same bf16 inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def _gemm(lib, a, b, M, N, K, batch, a_mn, b_mn, bn, use_ref):
+    from bindcraft2_b200 import _lib
+    d = torch.zeros(batch, M, N, dtype=torch.bfloat16, device='cuda')
+    lda = a.shape[-1]
+    ldb = b.shape[-1]
+    _lib.check(lib.bc2_test_gemm(0, a.data_ptr(), lda, a.shape[-2] * lda, int(a_mn), b.data_ptr(), ldb, b.shape[-2] * ldb,
+                                 int(b_mn), d.data_ptr(), M, N, K, batch, bn, int(use_ref)))
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    return d
+
+
+@pytest.mark.parametrize('M,N,K,batch,bn', [
+    (256, 128, 128, 1, 128), (1024, 512, 128, 1, 256), (384, 128, 512, 1, 128), (224, 256, 256, 1, 256),
+    (224, 64, 256, 1, 64), (1024, 128, 640, 1, 128), (224, 224, 224, 4, 128), (96, 96, 96, 3, 128),
+])
+@pytest.mark.parametrize('use_ref', [0, 1])
+def test_gemm_kmajor(lib, M, N, K, batch, bn, use_ref):
+    g = torch.Generator(device='cuda').manual_seed(M + N + K)
+    a = torch.randn(batch, M, K, device='cuda', generator=g).bfloat16()
+    b = torch.randn(batch, N, K, device='cuda', generator=g).bfloat16()
+    d = _gemm(lib, a, b, M, N, K, batch, False, False, bn, use_ref)
+    want = torch.einsum('zmk,znk->zmn', a.float(), b.float())
+    assert _rel(d, want) < 6e-3
+
+
+@pytest.mark.parametrize('a_mn,b_mn', [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize('n', [224, 96, 128])
+def test_gemm_mn_major_batched(lib, a_mn, b_mn, n):
+    """The operand forms of the triangle-multiplication contractions: [c][k][m] planes read in place."""
+    g = torch.Generator(device='cuda').manual_seed(n)
+    batch = 3
+    a = torch.randn(batch, n, n, device='cuda', generator=g).bfloat16()  # stored [k][m] when a_mn else [m][k]
+    b = torch.randn(batch, n, n, device='cuda', generator=g).bfloat16()
+    d = _gemm(lib, a, b, n, n, n, batch, a_mn, b_mn, 128, 0)
+    af = a.float().transpose(1, 2) if a_mn else a.float()
+    bf = b.float().transpose(1, 2) if b_mn else b.float()
+    want = torch.einsum('zmk,znk->zmn', af, bf)
+    assert _rel(d, want) < 6e-3
+
+
+def _attention_torch(qkvg, bias, mask, d_og, B, N, H, D, transposed):
+    """fp32 autograd reference on the same bf16-rounded operands; returns og, d_qkvg (dq|dk|dv|d gate-pre), d_bias."""
+    HD = H * D
+    x = qkvg.float().clone().requires_grad_(True)
+    bias = bias.clone().requires_grad_(True)
+    t = x.view(B, N, 4 * HD) if not transposed else x.view(N, B, 4 * HD).transpose(0, 1)
+    q, k, v, gpre = [t[..., i * HD:(i + 1) * HD].reshape(B, N, H, D) for i in range(4)]
+    logits = torch.einsum('bqhd,bkhd->bhqk', q, k) + (1e9 * (mask - 1.0))[:, None, None, :] + bias[None]
+    logits = torch.clamp(logits, -1e8, 1e8)
+    w = torch.softmax(logits, -1)
+    o = torch.einsum('bhqk,bkhd->bqhd', w, v)
+    og = (o * gpre).reshape(B, N, HD)
+    if transposed:
+        og = og.transpose(0, 1)
+    og = og.reshape(B * N, HD)
+    (og * d_og.float()).sum().backward()
+    return og.detach(), x.grad, bias.grad
+
+
+@pytest.mark.parametrize('B,N,H,D,transposed', [(64, 64, 4, 32, 0), (224, 224, 4, 32, 0), (96, 96, 4, 32, 1),
+                                                 (2, 160, 8, 32, 0), (64, 64, 4, 16, 1)])
+@pytest.mark.parametrize('use_ref', [0, 1])
+def test_attention_fwd_bwd(lib, B, N, H, D, transposed, use_ref):
+    from bindcraft2_b200 import _lib
+    g = torch.Generator(device='cuda').manual_seed(B * 7 + N)
+    HD = H * D
+    rows = B * N
+    qkvg = torch.randn(rows, 4 * HD, device='cuda', generator=g)
+    qkvg[:, :HD] *= D ** -0.5
+    qkvg[:, 3 * HD:] = torch.sigmoid(qkvg[:, 3 * HD:])  # the buffer holds the gate after the sigmoid
+    qkvg = qkvg.bfloat16()
+    bias = torch.randn(H, N, N, device='cuda', generator=g)
+    mask = (torch.rand(B, N, device='cuda', generator=g) > 0.15).float()
+    mask[:, 0] = 1
+    mask_arg = mask.t().contiguous() if transposed else mask  # element (b,k) at [k*N + b] for the transposed walk
+    d_og = torch.randn(rows, HD, device='cuda', generator=g).bfloat16()
+    og = torch.zeros(rows, HD, dtype=torch.bfloat16, device='cuda')
+    d_qkvg = torch.zeros(rows, 4 * HD, dtype=torch.bfloat16, device='cuda')
+    d_bias = torch.zeros(H, N, N, device='cuda')
+    _lib.check(lib.bc2_test_attention(0, qkvg.data_ptr(), bias.data_ptr(), mask_arg.data_ptr(), d_og.data_ptr(), B, N, H, D,
+                                      transposed, og.data_ptr(), d_qkvg.data_ptr(), d_bias.data_ptr(), use_ref))
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    # the autograd reference differentiates through the stored (post-sigmoid) gate; the kernel returns the gradient
+    # with respect to the gate PRE-activation: d_pre = d_gate * g * (1 - g)
+    want_og, want_dx, want_db = _attention_torch(qkvg, bias, mask, d_og, B, N, H, D, transposed)
+    gate = qkvg[:, 3 * HD:].float()
+    want_dx = want_dx.clone()
+    want_dx[:, 3 * HD:] *= gate * (1 - gate)
+    assert _rel(og, want_og) < 1e-2
+    for i, name in enumerate(['dq', 'dk', 'dv', 'dgate']):
+        assert _rel(d_qkvg[:, i * HD:(i + 1) * HD], want_dx[:, i * HD:(i + 1) * HD]) < 2e-2, name
+    assert _rel(d_bias, want_db) < 2e-2
