@@ -50,7 +50,7 @@ extern "C" {
 
 int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
                       const uint32_t* /*seed*/, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t pair_only,
-                      int64_t /*own_save*/, int64_t opm_first, int64_t /*dropout*/, const char* weights_dir,
+                      int64_t own_save, int64_t opm_first, int64_t /*dropout*/, const char* weights_dir,
                       float* pair_out, float* msa_out, uint16_t* psave, float* msave) {
   try {
     BC2_CHECK(pair && msa && pair_mask && msa_mask && pair_out && msa_out && weights_dir, "null operand");
@@ -58,7 +58,7 @@ int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const f
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
     s->forward(pair, msa, pair_mask, msa_mask, pair_out, msa_out, save ? reinterpret_cast<bf16*>(psave) : nullptr,
-               save ? msave : nullptr, (cudaStream_t)stream);
+               save ? msave : nullptr, own_save != 0, (cudaStream_t)stream);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -68,14 +68,14 @@ int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const f
 
 int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
                       const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* /*seed*/,
-                      int64_t N, int64_t S, int64_t depth, int64_t pair_only, int64_t /*own_save*/, int64_t opm_first,
+                      int64_t N, int64_t S, int64_t depth, int64_t pair_only, int64_t own_save, int64_t opm_first,
                       int64_t /*dropout*/, const char* weights_dir, float* dpair, float* dmsa) {
   try {
     BC2_CHECK(ct_pair && ct_msa && pair_mask && msa_mask && psave && msave && dpair && dmsa && weights_dir, "null operand");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
     s->backward(ct_pair, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave), msave, dpair, dmsa,
-                (cudaStream_t)stream);
+                own_save != 0, (cudaStream_t)stream);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -120,6 +120,8 @@ int bc2_device_status(void) {
 }
 
 int64_t bc2_launch_count(void) { return launch_counter().load(); }
+
+void bc2_test_set_module_mask(uint32_t mask) { module_mask() = mask; }
 
 int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, int a_mn, const uint16_t* b, int64_t ldb,
                   int64_t b_bs, int b_mn, uint16_t* d, int64_t M, int64_t N, int64_t K, int64_t batch, int bn,
@@ -166,7 +168,7 @@ int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, co
     bf16* d_o = A.alloc<bf16>(rows * HD);
     a.o = o;
     a.og = reinterpret_cast<bf16*>(og);
-    a.lse = A.alloc<float>(B * H * N);
+    a.lse = A.alloc<float>(2 * B * H * N);
     float* delta = A.alloc<float>(B * H * N);
     a.d_o = d_o;
     a.delta = delta;
@@ -176,14 +178,20 @@ int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, co
     plan.rows = rows;
     plan.ref_dkv = A.alloc<float>(rows * 2 * HD);
     attn_prepare(plan, use_ref != 0);
+    auto stage = [&](const char* what) {  // test entry only: name the kernel that failed
+      cudaError_t e = cudaStreamSynchronize(st);
+      if (e == cudaSuccess) e = cudaGetLastError();
+      BC2_CHECK(e == cudaSuccess, std::string("attention ") + what + ": " + cudaGetErrorString(e));
+    };
     attn_fwd(plan, st);
+    stage("forward");
     AttnBwdPrepArgs p{reinterpret_cast<const bf16*>(d_og), o, a.qkvg, 4L * HD, d_o, a.d_qkv, delta, rows, a.row_b, a.row_p,
                       (int)N, (int)H, (int)D};
     attn_bwd_prep(p, st);
+    stage("backward prep");
     BC2_CUDA(cudaMemsetAsync(d_bias, 0, (size_t)H * N * N * 4, st));
     attn_bwd(plan, st);
-    BC2_CUDA(cudaStreamSynchronize(st));
-    BC2_CUDA(cudaGetLastError());
+    stage("backward");
     return 0;
   } catch (const std::exception& e) {
     return fail(e);

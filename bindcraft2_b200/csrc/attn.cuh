@@ -10,9 +10,9 @@
 // Forward, one CTA per (128-query tile, head, batch row), flash style on tcgen05:
 //   TMA loads Q, all K and all V of the (b,h) into swizzled shared memory;
 //   S = Q K^T for a 128-key block is one tcgen05.mma chain into TMEM; 128 softmax threads (one query row each)
-//   read it back with tcgen05.ld, add bias and mask, keep the running max/sum in registers (online softmax, base 2),
+//   read it back with tcgen05.ld, add bias and mask, keep the running max/sum in registers (online softmax),
 //   write P as a bf16 K-major swizzled operand; O_blk = P V is a second MMA; the running output is rescaled in
-//   registers.  Outputs: o (ungated), og = o*gate, and the base-2 log-sum-exp per row for the backward.
+//   registers.  Outputs: o (ungated), og = o*gate, and the row max and 1/row-sum for the backward.
 //
 // Backward, one CTA per (head, batch row) (<= 256 keys per CTA; larger N splits keys over CTAs and accumulates dQ
 // with fp32 atomics): recomputes S and P from the saved log-sum-exp, forms dP = dO V^T, dS = P (dP - delta) and the
@@ -47,7 +47,8 @@ struct AttnArgs {
   long mask_b = 0, mask_k = 0;
   bf16* o = nullptr;    // [rows][H*D] ungated output
   bf16* og = nullptr;   // [rows][H*D] gated output
-  float* lse = nullptr; // [B][H][N] base-2 log-sum-exp
+  float* lse = nullptr; // [B][H][N][2]: row max (natural-log units) and 1/row-sum.  Kept apart because a fully masked row
+                        // has max = -1e8*log2(e), where a single log-sum-exp float could not hold log2(sum)
   // backward only
   const bf16* d_o = nullptr;   // [rows][H*D] gradient wrt the ungated output
   const float* delta = nullptr; // [B][H][N] rowsum(dO * O)
@@ -188,7 +189,7 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
       ok = mbar_wait(b_s, j & 1, SITE_ATTN);
       if (!ok) break;
       tc_fence_after();
-      // pass 1: block max (base-2 units)
+      // pass 1: block max
       float mblk = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
@@ -199,8 +200,11 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 32; ++i) mblk = fmaxf(mblk, attn_logit(s[i], sMask[k0 + i], brow, k0 + i, a.N));
       }
-      const float mnew = fmaxf(mrun, mblk * kLog2e);
-      const float alpha = exp2f(mrun - mnew);  // 0 on the first block (mrun = -inf)
+      // Natural-log units, and the max is subtracted BEFORE scaling by log2(e): for a fully masked row every logit
+      // and the max are exactly -1e8, so the difference is exactly 0 whatever the compiler fuses; folding the scale
+      // in first would leave a rounding residue of several units at that magnitude.
+      const float mnew = fmaxf(mrun, mblk);
+      const float alpha = exp2f((mrun - mnew) * kLog2e);  // 0 on the first block (mrun = -inf)
       // fold the previous block's output in before P is overwritten (its MMA has finished once b_o flips)
       if (j > 0) {
         ok = mbar_wait(b_o, (j - 1) & 1, SITE_ATTN);
@@ -225,7 +229,7 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           const float t0 = attn_logit(s[i], sMask[k0 + i], brow, k0 + i, a.N);
           const float t1 = attn_logit(s[i + 1], sMask[k0 + i + 1], brow, k0 + i + 1, a.N);
-          const float p0 = exp2f(t0 * kLog2e - mnew), p1 = exp2f(t1 * kLog2e - mnew);
+          const float p0 = exp2f((t0 - mnew) * kLog2e), p1 = exp2f((t1 - mnew) * kLog2e);
           lblk += p0 + p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
@@ -276,7 +280,7 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
           *reinterpret_cast<uint4*>(op + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
           *reinterpret_cast<uint4*>(ogp + i) = make_uint4(ogw[0], ogw[1], ogw[2], ogw[3]);
         }
-        a.lse[((long)b * a.H + h) * a.N + q] = mrun + log2f(lrun);
+        *reinterpret_cast<float2*>(a.lse + 2 * (((long)b * a.H + h) * a.N + q)) = make_float2(mrun, inv);
       }
     }
   }
@@ -317,7 +321,8 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
   uint64_t* b_p = bars + 3;     // P and dS written (256 arrivals)
   uint64_t* b_g = bars + 4;     // gradient MMAs of the step finished (smem tiles reusable)
   uint64_t* b_qfree = bars + 5; // dQ read out by the epilogue threads (128 arrivals)
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 6);
+  uint64_t* b_tile = bars + 6;  // all MMAs of a q tile finished: its Q/dO tiles may be overwritten
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 7);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y, b = blockIdx.z;
@@ -330,6 +335,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
     mbar_init(b_p, 256);
     mbar_init(b_g, 1);
     mbar_init(b_qfree, 128);
+    mbar_init(b_tile, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm);
     tma_prefetch_desc(&tdo);
@@ -357,8 +363,10 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
       }
       bool ok = true;
       for (int i = 0; i < nqb && ok; ++i) {
-        // the previous q tile's Q/dO are still operands of its last gradient MMAs
-        if (i > 0) ok = mbar_wait(b_g, (i * nkb - 1) & 1, SITE_ATTN_BWD);
+        // The previous q tile's Q/dO are operands of its gradient MMAs.  This thread must see every phase of the
+        // barrier it waits on in order (a parity wait on a phase it skipped returns at once), hence a per-tile barrier
+        // rather than the per-step one.
+        if (i > 0) ok = mbar_wait(b_tile, (i - 1) & 1, SITE_ATTN_BWD);
         if (!ok) break;
         mbar_expect_tx(b_q, 2 * TILE);
         tma_load_3d(sQ, &tm, b_q, h * D, i * 128, b);
@@ -405,6 +413,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
             umma_ss(tDQ, desc_p_kmajor(aDS, k), desc_rows_mnmajor<D>(aK, k), idQ, (j > 0 || k > 0) ? 1u : 0u);
           umma_commit(b_g);
         }
+        if (ok) umma_commit(b_tile);
       }
     }
   } else {
@@ -419,7 +428,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
       const int q = i * 128 + r;
       const bool qin = q < a.N;
       const long lidx = ((long)b * a.H + h) * a.N + q;
-      const float lse = qin ? a.lse[lidx] : 0.f;
+      const float2 ml = qin ? *reinterpret_cast<const float2*>(a.lse + 2 * lidx) : make_float2(0.f, 0.f);
       const float dl = qin ? a.delta[lidx] : 0.f;
       const float* brow = (a.bias && qin) ? a.bias + ((long)h * a.N + q) * a.N : nullptr;
       float* dbrow = (a.d_bias && qin) ? a.d_bias + ((long)h * a.N + q) * a.N : nullptr;
@@ -448,7 +457,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
             const bool kin = k0 + e < a.N;
             const bool live = qin && kin && (t >= -kClip) && (t <= kClip);
             t = fminf(fmaxf(t, -kClip), kClip);
-            const float p = (qin && kin) ? exp2f(t * kLog2e - lse) : 0.f;
+            const float p = (qin && kin) ? exp2f((t - ml.x) * kLog2e) * ml.y : 0.f;
             s[e] = p;
             dsv[e] = live ? p * (dp[e] - dl) : 0.f;
           }
@@ -576,7 +585,8 @@ __global__ void attn_fwd_ref_kernel(AttnArgs a) {
     a.o[rowq * HD + h * D + d] = __float2bfloat16(o);
     a.og[rowq * HD + h * D + d] = __float2bfloat16(o * g);
   }
-  a.lse[((long)b * a.H + h) * a.N + q] = (m + __logf(l)) * kLog2e;
+  a.lse[2 * (((long)b * a.H + h) * a.N + q)] = m;
+  a.lse[2 * (((long)b * a.H + h) * a.N + q) + 1] = 1.f / l;
 }
 
 // dq written directly; dk/dv accumulated with fp32 atomics into dkv_acc [rows][2*H*D] (zeroed by the caller).
@@ -594,7 +604,7 @@ __global__ void attn_bwd_ref_kernel(AttnArgs a, float* dkv_acc) {
     dov[d] = __bfloat162float(a.d_o[rowq * HD + h * D + d]);
     dq[d] = 0.f;
   }
-  const float lse = a.lse[lidx], dl = a.delta[lidx];
+  const float m2 = a.lse[2 * lidx], inv_l = a.lse[2 * lidx + 1], dl = a.delta[lidx];
   for (int k = 0; k < a.N; ++k) {
     const long rowk = (long)b * a.row_b + (long)k * a.row_p;
     float s = 0.f, dp = 0.f;
@@ -606,7 +616,7 @@ __global__ void attn_bwd_ref_kernel(AttnArgs a, float* dkv_acc) {
     if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
     const bool live = s >= -kClip && s <= kClip;
     s = fminf(fmaxf(s, -kClip), kClip);
-    const float p = exp2f(s * kLog2e - lse);
+    const float p = __expf(s - m2) * inv_l;
     const float ds = live ? p * (dp - dl) : 0.f;
     if (a.d_bias) atomicAdd(a.d_bias + ((long)h * a.N + q) * a.N + k, ds);
     for (int d = 0; d < D; ++d) {

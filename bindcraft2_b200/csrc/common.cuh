@@ -8,8 +8,11 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <map>
+#include <mutex>
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 namespace bc2 {
 
@@ -47,6 +50,59 @@ inline std::atomic<long>& launch_counter() {
   static std::atomic<long> c{0};
   return c;
 }
+
+// Optional per-kernel-class timing with CUDA events on the launching stream (the reference has the same idea behind
+// BLK_PROF, native/common.cuh:735-880).  Off by default; mode 1 times every class, mode 2 only the selected one, so a
+// benchmark can time its dominant kernel inside the timed region without paying for thousands of event records.
+struct Prof {
+  int mode = 0;
+  std::string only;
+  struct Rec { cudaEvent_t a, b; int cls; };
+  std::vector<Rec> recs;
+  std::vector<cudaEvent_t> pool;
+  std::map<std::string, int> ids;
+  std::vector<std::string> names;
+  std::mutex mu;
+  int id_of(const char* name) {
+    auto it = ids.find(name);
+    if (it != ids.end()) return it->second;
+    names.push_back(name);
+    return ids[name] = (int)names.size() - 1;
+  }
+  cudaEvent_t ev() {
+    if (!pool.empty()) { cudaEvent_t e = pool.back(); pool.pop_back(); return e; }
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    return e;
+  }
+};
+inline Prof& prof() {
+  static Prof p;
+  return p;
+}
+struct ProfScope {
+  bool on = false;
+  cudaStream_t st;
+  Prof::Rec r;
+  ProfScope(const char* name, cudaStream_t s) : st(s) {
+    Prof& p = prof();
+    if (p.mode == 0) return;
+    if (p.mode == 2 && p.only != name) return;
+    std::lock_guard<std::mutex> l(p.mu);
+    r.cls = p.id_of(name);
+    r.a = p.ev();
+    r.b = p.ev();
+    cudaEventRecord(r.a, st);
+    on = true;
+  }
+  ~ProfScope() {
+    if (!on) return;
+    cudaEventRecord(r.b, st);
+    Prof& p = prof();
+    std::lock_guard<std::mutex> l(p.mu);
+    p.recs.push_back(r);
+  }
+};
 
 // ------------------------------------------------------------------------------------------- small helpers
 __host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }

@@ -18,6 +18,36 @@ __global__ void __launch_bounds__(256) cvt_bf16_f32_kernel(const uint2* __restri
     out[i] = make_float4(a.x, a.y, b.x, b.y);
   }
 }
+// Save-set write: the caller's slot gets the bf16 narrowing (the boundary contract), and the stack keeps the fp32
+// values it narrowed beside it.
+__global__ void __launch_bounds__(256)
+save_narrow_kernel(const float4* __restrict__ in, uint2* __restrict__ out, float4* __restrict__ keep, long n4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const float4 v = in[i];
+    out[i] = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+    keep[i] = v;
+  }
+}
+// Save-set read for the replay.  The bf16 slot is authoritative (the backward is a pure function of its operands);
+// where the kept fp32 value narrows to exactly the slot's bf16 value it is the un-rounded original and is used
+// instead, which removes the rounding of the block input from the gradient.  A slot written by a different forward
+// simply fails the comparison element by element and falls back to the widened bf16 value.
+__global__ void __launch_bounds__(256)
+save_widen_kernel(const uint2* __restrict__ slot, const float4* __restrict__ keep, float4* __restrict__ out, long n4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const uint2 s = slot[i];
+    float4 k = keep ? keep[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float2 a = unpack_bf16(s.x), b = unpack_bf16(s.y);
+    const uint2 kn = make_uint2(pack_bf16(k.x, k.y), pack_bf16(k.z, k.w));
+    float4 o;
+    o.x = (keep && (kn.x & 0xffffu) == (s.x & 0xffffu)) ? k.x : a.x;
+    o.y = (keep && (kn.x >> 16) == (s.x >> 16)) ? k.y : a.y;
+    o.z = (keep && (kn.y & 0xffffu) == (s.y & 0xffffu)) ? k.z : b.x;
+    o.w = (keep && (kn.y >> 16) == (s.y >> 16)) ? k.w : b.y;
+    out[i] = o;
+  }
+}
+
 inline int ew_grid(long n, int per_block) { return (int)std::min<long>((n + per_block - 1) / per_block, 148L * 16); }
 inline void cvt_f32_bf16(const float* in, bf16* out, long n, cudaStream_t st) {
   launch_counter()++; cvt_f32_bf16_kernel<<<ew_grid(n / 4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n / 4);

@@ -328,7 +328,7 @@ struct TriAttn {
     qkvg = A.alloc<bf16>(M * 4 * HD);
     o = A.alloc<bf16>(M * HD);
     nb = A.alloc<float>((long)H * M);
-    lse = A.alloc<float>((long)n * H * n);
+    lse = A.alloc<float>(2L * n * H * n);
     AttnArgs& a = plan.args;
     a.qkvg = qkvg; a.ld = 4 * HD;
     a.row_b = ending ? 1 : n; a.row_p = ending ? n : 1;
@@ -407,7 +407,7 @@ struct MsaRow {
     o = A.alloc<bf16>(Mm * HD);
     nb = A.alloc<float>((long)H * Mp);
     dnb = A.alloc<float>((long)H * Mp);
-    lse = A.alloc<float>((long)S_ * H * n);
+    lse = A.alloc<float>(2L * S_ * H * n);
     AttnArgs& a = plan.args;
     a.qkvg = qkvg; a.ld = 4 * HD; a.row_b = n; a.row_p = 1; a.B = S_; a.N = n; a.H = H; a.D = D;
     a.bias = nb; a.mask = msa_mask; a.mask_b = n; a.mask_k = 1;

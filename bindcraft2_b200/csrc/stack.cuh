@@ -9,6 +9,12 @@
 // the caller's save-set (pair as bf16, msa as fp32; slot layout native/stack.cuh:795-829) and the backward needs only
 // that save-set, the masks and the cotangents: per block it re-runs the block forward from the saved input (filling
 // the per-module buffers) and then walks the modules in reverse.
+//
+// own_save (the reference's attribute of that name, native/ffi.cu:261-271 `useOwnSaveSet`): the stack additionally
+// keeps the fp32 block inputs it narrowed, and the replay uses a kept value wherever it still narrows to the caller's
+// bf16 slot value.  That removes the bf16 rounding of the block inputs from the gradient, at the price the reference's
+// own_save has too: the result then depends on state inside the stack object (within rounding), so callers that
+// interleave states use own_save = 0.
 #pragma once
 #include <memory>
 
@@ -22,6 +28,14 @@ struct StackConfig {
   bool pair_only = false, opm_first = true;
   int tri_hidden = 128, tri_heads = 4, msa_heads = 8, trans_factor = 4;
 };
+
+// Bring-up switch: bit i enables residual step i of the block (0 OPM, 1 row attention, 2 column attention,
+// 3 MSA transition, 4 tri-mul out, 5 tri-mul in, 6 tri-attn start, 7 tri-attn end, 8 pair transition).  A disabled step
+// is the identity.  All steps are enabled unless a unit test narrows the set to check one module against the oracle.
+inline unsigned& module_mask() {
+  static unsigned m = 0x1ffu;
+  return m;
+}
 
 struct EvoStack {
   StackConfig cfg;
@@ -38,6 +52,7 @@ struct EvoStack {
   float* Mx[4] = {nullptr};  // msa stream: input, after row, after col, after transition
   float *pair_mask = nullptr, *msa_mask = nullptr;  // stack-owned copies (stable pointers for the kernels' arguments)
   float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};  // ping-pong block outputs
+  std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
   size_t weight_bytes = 0;
 
   EvoStack(const StackConfig& c, const std::string& weights_dir) : cfg(c) {
@@ -90,28 +105,33 @@ struct EvoStack {
 
   // One block.  p_in/m_in are read only; the block output goes to p_out/m_out.
   void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st) {
-    opm.forward(b, m_in, p_in, P[1], st);
-    row.forward(b, m_in, Mx[1], P[1], st);
-    col.forward(b, Mx[1], Mx[2], st);
-    mtrans.forward(b, Mx[2], m_out, st);
-    tmo.forward(b, P[1], P[2], pair_mask, st);
-    tmi.forward(b, P[2], P[3], pair_mask, st);
-    tas.forward(b, P[3], P[4], st);
-    tae.forward(b, P[4], P[5], st);
-    ptrans.forward(b, P[5], p_out, st);
+    const unsigned en = module_mask();
+    const size_t bp = (size_t)Mp * cfg.Cz * 4, bm = (size_t)Mm * cfg.Cm * 4;
+    auto idp = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, st)); };
+    auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, st)); };
+    if (en & 1) opm.forward(b, m_in, p_in, P[1], st); else idp(p_in, P[1]);
+    if (en & 2) row.forward(b, m_in, Mx[1], P[1], st); else idm(m_in, Mx[1]);
+    if (en & 4) col.forward(b, Mx[1], Mx[2], st); else idm(Mx[1], Mx[2]);
+    if (en & 8) mtrans.forward(b, Mx[2], m_out, st); else idm(Mx[2], m_out);
+    if (en & 16) tmo.forward(b, P[1], P[2], pair_mask, st); else idp(P[1], P[2]);
+    if (en & 32) tmi.forward(b, P[2], P[3], pair_mask, st); else idp(P[2], P[3]);
+    if (en & 64) tas.forward(b, P[3], P[4], st); else idp(P[3], P[4]);
+    if (en & 128) tae.forward(b, P[4], P[5], st); else idp(P[4], P[5]);
+    if (en & 256) ptrans.forward(b, P[5], p_out, st); else idp(P[5], p_out);
   }
   // Needs the module buffers of block b as left by block_forward(b, p_in, m_in, ...).  g_pair/g_msa: cotangents of the
   // block outputs on entry, of the block inputs on return.
   void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
-    ptrans.backward(b, P[5], g_pair, st);
-    tae.backward(b, P[4], g_pair, st);
-    tas.backward(b, P[3], g_pair, st);
-    tmi.backward(b, P[2], g_pair, pair_mask, st);
-    tmo.backward(b, P[1], g_pair, pair_mask, st);
-    mtrans.backward(b, Mx[2], g_msa, st);
-    col.backward(b, Mx[1], g_msa, st);
-    row.backward(b, m_in, P[1], g_msa, g_pair, st);
-    opm.backward(b, m_in, g_pair, g_msa, st);
+    const unsigned en = module_mask();
+    if (en & 256) ptrans.backward(b, P[5], g_pair, st);
+    if (en & 128) tae.backward(b, P[4], g_pair, st);
+    if (en & 64) tas.backward(b, P[3], g_pair, st);
+    if (en & 32) tmi.backward(b, P[2], g_pair, pair_mask, st);
+    if (en & 16) tmo.backward(b, P[1], g_pair, pair_mask, st);
+    if (en & 8) mtrans.backward(b, Mx[2], g_msa, st);
+    if (en & 4) col.backward(b, Mx[1], g_msa, st);
+    if (en & 2) row.backward(b, m_in, P[1], g_msa, g_pair, st);
+    if (en & 1) opm.backward(b, m_in, g_pair, g_msa, st);
   }
 
   void set_masks(const float* pm, const float* mm, cudaStream_t st) {
@@ -121,13 +141,22 @@ struct EvoStack {
 
   // psave: [depth][N][N][Cz] bf16, msave: [depth][S][N][Cm] fp32 (null when save == false).
   void forward(const float* pair, const float* msa, const float* pm, const float* mm, float* pair_out, float* msa_out,
-               bf16* psave, float* msave, cudaStream_t st) {
+               bf16* psave, float* msave, bool own_save, cudaStream_t st) {
     set_masks(pm, mm, st);
     const long np = Mp * cfg.Cz, nm = Mm * cfg.Cm;
     const float *pc = pair, *mc = msa;
     for (int i = 0; i < cfg.depth; ++i) {
       if (psave) {
-        cvt_f32_bf16(pc, psave + (long)i * np, np, st);
+        if (own_save) {
+          if (keep32.empty())
+            for (int d = 0; d < cfg.depth; ++d) keep32.push_back(A.alloc<float>(np));
+          launch_counter()++;
+          save_narrow_kernel<<<ew_grid(np / 4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(pc),
+                                                                  reinterpret_cast<uint2*>(psave + (long)i * np),
+                                                                  reinterpret_cast<float4*>(keep32[i]), np / 4);
+        } else {
+          cvt_f32_bf16(pc, psave + (long)i * np, np, st);
+        }
         BC2_CUDA(cudaMemcpyAsync(msave + (long)i * nm, mc, nm * 4, cudaMemcpyDeviceToDevice, st));
       }
       const bool last = i == cfg.depth - 1;
@@ -140,13 +169,17 @@ struct EvoStack {
   }
 
   void backward(const float* ct_pair, const float* ct_msa, const float* pm, const float* mm, const bf16* psave,
-                const float* msave, float* dpair, float* dmsa, cudaStream_t st) {
+                const float* msave, float* dpair, float* dmsa, bool own_save, cudaStream_t st) {
     set_masks(pm, mm, st);
     const long np = Mp * cfg.Cz, nm = Mm * cfg.Cm;
     if (dpair != ct_pair) BC2_CUDA(cudaMemcpyAsync(dpair, ct_pair, np * 4, cudaMemcpyDeviceToDevice, st));
     if (dmsa != ct_msa) BC2_CUDA(cudaMemcpyAsync(dmsa, ct_msa, nm * 4, cudaMemcpyDeviceToDevice, st));
     for (int i = cfg.depth - 1; i >= 0; --i) {
-      cvt_bf16_f32(psave + (long)i * np, P[0], np, st);
+      launch_counter()++;
+      save_widen_kernel<<<ew_grid(np / 4, 256), 256, 0, st>>>(
+          reinterpret_cast<const uint2*>(psave + (long)i * np),
+          (!own_save || keep32.empty()) ? nullptr : reinterpret_cast<const float4*>(keep32[i]),
+          reinterpret_cast<float4*>(P[0]), np / 4);
       const float* m_in = msave + (long)i * nm;
       block_forward(i, P[0], m_in, pp[0], mp[0], st);
       block_backward(i, m_in, dpair, dmsa, st);

@@ -37,6 +37,16 @@ def _glorot(g, shape, fan_in, fan_out):
     return (torch.rand(shape, generator=g) * 2 - 1) * lim
 
 
+def bf16_representable(p: Params) -> Params:
+    """Rounds every array to the nearest bfloat16 value (kept as float32).
+
+    The reference's bf16 mode casts its parameters to bf16 before use (bindcraft/af/alphafold/model/utils.py:29-45), so
+    weights that are bf16 values are that configuration's weights; using them for the fp32 oracle as well means both
+    sides multiply by the SAME numbers and the comparison measures the kernels, not the weight quantisation (which by
+    itself moves this block's input gradient by 3e-2 through ReLU sign flips in the transitions)."""
+    return {k: v.bfloat16().float() for k, v in p.items()}
+
+
 def _ln(g, c):
     """LayerNorm scale 1 / offset 0, perturbed so that both parameters are exercised."""
     return 1 + 0.1 * torch.randn(c, generator=g), 0.1 * torch.randn(c, generator=g)
@@ -127,7 +137,7 @@ def make_evoformer_params(seed: int, depth: int, cm=256, cz=128, is_extra_msa=Fa
             _attention_params(g, p, c + '/attention', cm, msa_heads, msa_d, cm)
         _transition_params(g, p, pre + 'msa_transition', cm, 4)
         pair_block_params(g, p, pre, cz, 128, 4, 32, 4)
-    return p
+    return bf16_representable(p)
 
 
 def make_template_stack_params(seed: int, depth: int = 2, ct=64) -> Params:
@@ -137,7 +147,7 @@ def make_template_stack_params(seed: int, depth: int = 2, ct=64) -> Params:
     p: Params = {}
     for b in range(depth):
         pair_block_params(g, p, f'block{b}/', ct, 64, 4, 16, 2)
-    return p
+    return bf16_representable(p)
 
 
 def make_block_inputs(seed: int, n: int, s: int, cm=256, cz=128, scale=1.0, shift=0.0, masked=0):

@@ -74,6 +74,12 @@ int64_t bc2_launch_count(void);
 
 /* ---- bring-up / unit-test entry points (not part of the reference surface) ------------------------------------ */
 
+/* Enables a subset of the nine residual steps of every block (bit i = step i in block order: outer product mean, MSA
+ * row attention, MSA column attention, MSA transition, triangle multiplication outgoing / incoming, triangle attention
+ * starting / ending node, pair transition); a disabled step is the identity.  Default 0x1ff.  Lets a unit test compare
+ * one module at a time with the oracle, as the reference's per-module gates do (native/trimul.cu, native/triattn.cu ...). */
+void bc2_test_set_module_mask(uint32_t mask);
+
 /* D[z][m][n] = sum_k A[z](m,k) B[z](n,k) with bf16 operands and fp32 accumulate, written as bf16 [batch][M][N].
  * a_mn / b_mn select MN-major storage of that operand (element (r,k) at base[k*ld + r]).  use_ref != 0 runs the
  * CUDA-core reference kernel instead of the tcgen05 kernel. */

@@ -70,8 +70,8 @@ def _attention_torch(qkvg, bias, mask, d_og, B, N, H, D, transposed):
     return og.detach(), x.grad, bias.grad
 
 
-@pytest.mark.parametrize('B,N,H,D,transposed', [(64, 64, 4, 32, 0), (224, 224, 4, 32, 0), (96, 96, 4, 32, 1),
-                                                 (2, 160, 8, 32, 0), (64, 64, 4, 16, 1)])
+@pytest.mark.parametrize('B,N,H,D,transposed', [(64, 64, 4, 32, 0), (8, 128, 4, 32, 0), (2, 160, 8, 32, 0), (4, 224, 4, 32, 0),
+                                                 (96, 96, 4, 32, 1), (64, 64, 4, 16, 1), (224, 224, 4, 32, 0)])
 @pytest.mark.parametrize('use_ref', [0, 1])
 def test_attention_fwd_bwd(lib, B, N, H, D, transposed, use_ref):
     from bindcraft2_b200 import _lib
@@ -85,6 +85,8 @@ def test_attention_fwd_bwd(lib, B, N, H, D, transposed, use_ref):
     bias = torch.randn(H, N, N, device='cuda', generator=g)
     mask = (torch.rand(B, N, device='cuda', generator=g) > 0.15).float()
     mask[:, 0] = 1
+    if B > 1:
+        mask[1, :] = 0  # a fully masked row: the clip at -1e8 makes its softmax uniform over the N keys
     mask_arg = mask.t().contiguous() if transposed else mask  # element (b,k) at [k*N + b] for the transposed walk
     d_og = torch.randn(rows, HD, device='cuda', generator=g).bfloat16()
     og = torch.zeros(rows, HD, dtype=torch.bfloat16, device='cuda')
