@@ -1,0 +1,380 @@
+"""Benchmark of the design-step trunk hot path: the 48-block Evoformer stack, forward (with save-set) + backward to
+its inputs, at N_res = 224 (80-residue binder + 144-residue target), single-sequence MSA, bf16 operands with fp32
+accumulation, dropout off, random-init weights, synthetic seeded inputs.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (one process per GPU under torchrun)
+    python bench.py --impl reference --steps K --warmup W    # CPU arm: the oracle restatement of the JAX trunk
+
+One JSON line is printed by rank 0.  `value` is design steps per second over all GPUs (independent trajectories, one
+per GPU, no collectives: the reference's own multi-GPU model); `ms_per_step` is the per-trajectory latency.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = 'design steps/sec/box, Evoformer trunk fwd+bwd (48 blocks, N_res=224)'
+UNIT = 'steps/s'
+
+
+# ----------------------------------------------------------------------------------------- workload
+def make_inputs(seed: int, n_binder: int, n_target: int, s: int, cm=256, cz=128):
+    """Synthetic stack inputs with the structure of a design step: the MSA row is a linear embedding of sequence
+    features (binder = softmax of seeded N(0,1) logits, target = one-hot of a seeded sequence), the pair tensor is the
+    outer sum of two single embeddings plus a relative-position embedding (max 32, chains kept apart)."""
+    rng = np.random.default_rng(seed)
+    n = n_binder + n_target
+    logits = rng.standard_normal((n_binder, 20))
+    binder = np.exp(logits - logits.max(-1, keepdims=True))
+    binder /= binder.sum(-1, keepdims=True)
+    target = np.eye(20)[rng.integers(0, 20, n_target)]
+    feat = np.zeros((n, 21), np.float32)
+    feat[:n_binder, :20], feat[n_binder:, :20] = binder, target
+    w_msa = rng.standard_normal((21, cm)).astype(np.float32)
+    w_l, w_r = (rng.standard_normal((21, cz)).astype(np.float32) for _ in range(2))
+    rel_tab = rng.standard_normal((2 * 32 + 2, cz)).astype(np.float32)
+    idx = np.concatenate([np.arange(n_binder), np.arange(n_target)])
+    chain = np.concatenate([np.zeros(n_binder, int), np.ones(n_target, int)])
+    rel = np.clip(idx[:, None] - idx[None, :] + 32, 0, 64)
+    rel = np.where(chain[:, None] == chain[None, :], rel, 65)
+    msa = np.repeat((feat @ w_msa)[None], s, 0)
+    pair = (feat @ w_l)[:, None, :] + (feat @ w_r)[None, :, :] + rel_tab[rel]
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32))
+    g = torch.Generator().manual_seed(seed)
+    return {'pair': t(pair), 'msa': t(msa), 'pair_mask': torch.ones(n, n), 'msa_mask': torch.ones(s, n),
+            'ct_pair': torch.randn(n, n, cz, generator=g), 'ct_msa': torch.randn(s, n, cm, generator=g)}
+
+
+def weights_dir_for(depth: int, rank: int, world: int) -> str:
+    """Seeded random-init weights for `depth` blocks, written once as a reference-format manifest."""
+    from bindcraft2_b200 import native, synthetic
+    d = os.path.join(tempfile.gettempdir(), f'bc2_bench_weights_d{depth}')
+    done = os.path.join(d, '.complete')
+    if rank == 0 and not os.path.exists(done):
+        native.weights_from_flat(synthetic.make_evoformer_params(7, depth), d)
+        open(done, 'w').write('ok')
+    if world > 1:
+        torch.distributed.barrier()
+    assert os.path.exists(done)
+    return d
+
+
+# ----------------------------------------------------------------------------------------- algorithmic work
+def algorithmic_work(n: int, s: int, cm=256, cz=128):
+    """Per-launch algorithmic FLOPs (contractions, 2 per MAC, recompute not counted) or bytes (streaming kernels:
+    operands read + written once at their storage width) of every kernel class the profiler names."""
+    m, mm, h, d = n * n, s * n, 4, 32
+    gemm = lambda M, N, K: ('tensor', 2.0 * M * N * K)
+    w = {}
+    for t in ('TriMul',):
+        w[f'{t}.forward.gemm.g_pg'] = gemm(m, 512, cz)
+        w[f'{t}.forward.gemm.g_con'] = gemm(n, n, n)[0:1] + (2.0 * n * n * n * 128,)
+        w[f'{t}.forward.gemm.g_g2'] = gemm(m, cz, cz)
+        w[f'{t}.forward.gemm.g_o'] = gemm(m, cz, 128)
+        w[f'{t}.backward.gemm.gb_o'] = gemm(m, 128, cz)
+        w[f'{t}.backward.gemm.gb_da'] = ('tensor', 2.0 * n * n * n * 128)
+        w[f'{t}.backward.gemm.gb_db'] = ('tensor', 2.0 * n * n * n * 128)
+        w[f'{t}.backward.gemm.gb_cat'] = gemm(m, cz, 640)
+        w[f'{t}.forward.ln_fwd_c'] = ('hbm', m * cz * (4 + 2.0))
+        w[f'{t}.forward.cln_fwd_c'] = ('hbm', m * 128 * (2 + 2.0))
+        w[f'{t}.backward.cln_bwd_c'] = ('hbm', m * 128 * (2 + 2 + 2.0))
+        w[f'{t}.backward.trimul_bwd_out_kernel'] = ('hbm', m * cz * (4 + 2 + 2 + 2 + 2.0))
+        w[f'{t}.backward.trimul_bwd_gate_kernel'] = ('hbm', m * 256 * (2 + 2 + 2 + 4.0))
+        w[f'{t}.backward.ln_bwd_c'] = ('hbm', m * cz * (4 + 2 + 4 + 4.0))
+    w['TriAttn.forward.gemm.g_qkvg'] = gemm(m, 512, cz)
+    w['TriAttn.forward.gemm.g_o'] = gemm(m, cz, 128)
+    w['TriAttn.backward.gemm.gb_o'] = gemm(m, 128, cz)
+    w['TriAttn.backward.gemm.gb_qkvg'] = gemm(m, cz, 512)
+    w['TriAttn.forward.attn_fwd'] = ('tensor', 2.0 * 2 * n * h * n * n * d)       # QK^T and PV
+    w['TriAttn.backward.attn_bwd'] = ('tensor', 2.0 * 4 * n * h * n * n * d)      # dP, dV, dK, dQ (S recompute not counted)
+    w['TriAttn.forward.ln_fwd_c'] = ('hbm', m * cz * (4 + 2.0))
+    w['TriAttn.backward.ln_bwd_c'] = ('hbm', m * cz * (4 + 2 + 4 + 4.0))
+    w['TriAttn.backward.cvt_f32_bf16'] = ('hbm', m * cz * (4 + 2.0))
+    w['TriAttn.backward.attn_bwd_prep'] = ('hbm', m * 128 * (2 * 5.0))
+    w['PairTransition.forward.ln_fwd_c'] = ('hbm', m * cz * (4 + 2.0))
+    w['PairTransition.forward.gemm.g1'] = gemm(m, 4 * cz, cz)
+    w['PairTransition.forward.gemm.g2'] = gemm(m, cz, 4 * cz)
+    w['PairTransition.backward.gemm.gb2'] = gemm(m, 4 * cz, cz)
+    w['PairTransition.backward.gemm.gb1'] = gemm(m, cz, 4 * cz)
+    w['PairTransition.backward.cvt_f32_bf16'] = ('hbm', m * cz * (4 + 2.0))
+    w['PairTransition.backward.ln_bwd_c'] = ('hbm', m * cz * (4 + 2 + 4 + 4.0))
+    w['MsaRow.forward.ln_fwd_c'] = ('hbm', m * cz * 4.0)  # dominated by the pair-bias pass
+    return w
+
+
+def fwd_bwd_flops(n: int, s: int) -> float:
+    """Algorithmic FLOPs of one block forward + backward: 2*lin + 3*bil, formulas of the scope table (S = MSA rows)."""
+    lin = (2 * n * n * 128 * 768 * 2 + 2 * n * n * 128 * 644 * 2 + 4 * n * n * 128 * 512 + 10 * s * n * 256 ** 2 +
+           2 * n * n * 128 * 8 + 10 * s * n * 256 ** 2 + 4 * s * n * 256 * 1024 + 4 * s * n * 256 * 32)
+    bil = (2 * (2 * n ** 3 * 128) + 2 * (2 * 2 * 4 * n ** 3 * 32) + 4 * s * 8 * n * n * 32 +
+           min(2 * s * n * n * 1024 + 2 * n * n * 1024 * 128, 2 * s * n * 32 * 4096 + 2 * n * n * 32 * s * 128))
+    return 2.0 * lin + 3.0 * bil
+
+
+# ----------------------------------------------------------------------------------------- helpers
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+         'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+         'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        fd, self.path = tempfile.mkstemp(suffix='.csv')
+        os.close(fd)
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.Q}', '--format=csv,noheader,nounits',
+                                          '-lms', '200', '-i', str(self.gpu)], stdout=open(self.path, 'w'),
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[5:9]):
+                if v.lower().startswith('active'):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=float(np.median(sm)), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def profile_report(lib):
+    buf = ctypes.create_string_buffer(1 << 16)
+    lib.bc2_profile_report(buf, len(buf))
+    rows = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.split()
+        rows[name] = (int(cnt), float(ms))
+    return rows
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {'hbm': d['hbm_gbs'], 'tensor': d['bf16_tflops_sustained'], 'source': 'measured'}
+    return {'hbm': 6650.0, 'tensor': 1400.0, 'source': 'fallback'}
+
+
+# ----------------------------------------------------------------------------------------- CPU arm
+def cpu_sample(n: int, s: int, depth: int, reps: int, wdir: str | None):
+    """Times the oracle (PyTorch CPU restatement of the reference JAX trunk; the JAX trunk itself cannot be imported on
+    this box) on a bounded sample: one block forward + backward at full N, all host threads.  Returns seconds/block."""
+    sys.path.insert(0, os.path.join(ROOT, 'oracle'))
+    import evoformer_oracle as O
+    from bindcraft2_b200 import native, synthetic
+    torch.set_num_threads(os.cpu_count() or 1)
+    if wdir is not None:
+        flat = native.read_manifest(wdir)
+        params = {k[len('param/'):]: torch.from_numpy(v.copy()) for k, v in flat.items() if k.startswith('param/block0/')}
+    else:
+        params = synthetic.make_evoformer_params(7, 1)
+    inp = make_inputs(11, n * 80 // 224, n - n * 80 // 224, s)
+    O.stack_fwd_bwd(params, inp, 1)  # warm-up (allocator, thread pool)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        O.stack_fwd_bwd(params, inp, 1)
+    return (time.perf_counter() - t0) / reps
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    n, s, depth = args.n_res, args.msa_rows, args.depth
+    cores = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_sample(n, s, depth, 1, None)
+    t0 = time.perf_counter()
+    per_block = [cpu_sample(n, s, depth, 1, None) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    sec_block = float(np.mean(per_block))
+    value = 1.0 / (sec_block * depth)
+    sample = f'each step = 1 of {depth} blocks forward+backward at N_res={n} (fp32 oracle), scaled x{depth}'
+    print(json.dumps({
+        'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': args.gpus, 'steps': args.steps,
+        'warmup': args.warmup, 'ms_per_step': sec_block * depth * 1e3, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': f'Evoformer stack fwd+bwd, depth {depth}, N_res {n}, S {s}', 'timed': sample},
+        'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': cores, 'kind': 'port', 'sample': sample},
+        'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'wall_s': wall}))
+
+
+# ----------------------------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    from bindcraft2_b200 import _lib, native
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        torch.distributed.init_process_group('nccl', device_id=dev)
+    lib = _lib.load()
+    n, s, depth = args.n_res, args.msa_rows, args.depth
+    nb = n * 80 // 224
+    wdir = weights_dir_for(depth, rank, world)
+    host = make_inputs(100 + rank, nb, n - nb, s)  # a distinct seeded sequence per GPU
+    t = {k: v.to(dev) for k, v in host.items()}
+    seed = torch.zeros(2, dtype=torch.int32, device=dev)
+    native.stack_prealloc(n, s, depth, wdir)
+    kw = dict(depth=depth, weights_dir=wdir, own_save=args.own_save)
+
+    def step():
+        p, m, psave, msave = native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, save=1, **kw)
+        return native.evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, seed, **kw)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+    # warm-up; the first warm-up step is profiled per kernel class to find the dominant kernel
+    step()
+    torch.cuda.synchronize()
+    lib.bc2_profile_mode(1, None)
+    step()
+    classes = profile_report(lib)
+    lib.bc2_profile_mode(0, None)
+    for _ in range(max(args.warmup - 1, 2)):
+        step()
+    work = algorithmic_work(n, s)
+    total_ms = sum(ms for _, ms in classes.values())
+    top = max(classes, key=lambda k: classes[k][1])
+    table = sorted(((k, c, ms) for k, (c, ms) in classes.items()), key=lambda r: -r[2])
+
+    # timed region: K steps, device-resident inputs; only the dominant kernel class carries events
+    lib.bc2_profile_mode(2, top.encode())
+    sampler = ClockSampler(local)
+    sync_all()
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.bc2_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync_all()
+    launches = lib.bc2_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = e0.elapsed_time(e1) / args.steps
+    top_cnt, top_ms = profile_report(lib).get(top, (0, 0.0))
+    lib.bc2_profile_mode(0, None)
+    status = lib.bc2_device_status()
+
+    # end to end: pinned host buffers in, results and gradients back out, copies inside the timed region
+    hs = native.HostStep(n, s, depth, wdir, device=str(dev))
+    pinned = {k: v.pin_memory() for k, v in host.items()}
+    for _ in range(2):
+        hs(pinned)
+    sync_all()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        hs(pinned)
+    f1.record()
+    sync_all()
+    ms_e2e = f0.elapsed_time(f1) / args.steps
+
+    if world > 1:
+        v = torch.tensor([ms_step, ms_e2e], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(v, op=torch.distributed.ReduceOp.MAX)
+        ms_step, ms_e2e = float(v[0]), float(v[1])
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    kind, amount = work.get(top, ('tensor', 0.0))
+    per_launch_s = (top_ms / max(top_cnt, 1)) * 1e-3
+    achieved = (amount / per_launch_s / (1e12 if kind == 'tensor' else 1e9)) if per_launch_s > 0 and amount else None
+    peak = peaks[kind]
+    roofline = {'kernel': top, 'bound': kind, 'achieved': achieved, 'peak': peak,
+                'unit': 'TFLOP/s' if kind == 'tensor' else 'GB/s', 'frac': (achieved / peak) if achieved else None,
+                'traffic': None, 'peak_source': peaks['source'] + (' (sustained bf16)' if kind == 'tensor' else ''),
+                'launches_in_timed_region': top_cnt, 'avg_launch_us': per_launch_s * 1e6,
+                'share_of_step': classes[top][1] / total_ms if total_ms else None}
+    step_flops = fwd_bwd_flops(n, s) * depth
+    out = {
+        'metric': METRIC, 'value': world * 1e3 / ms_step, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+        'warmup': max(args.warmup, 3), 'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'bf16', 'data': 'synthetic',
+        'config': {'workload': f'Evoformer stack fwd(save)+bwd, depth {depth}, N_res {n} ({nb}+{n - nb}), S {s}, '
+                               'dropout off, random-init weights', 'parallelism': f'{world} independent trajectories',
+                   'l2': 'working set per step (save-set 0.6 GB + weights 0.35 GB) exceeds the 126 MB L2',
+                   'own_save': args.own_save},
+        'e2e': {'value': world * 1e3 / ms_e2e, 'unit': UNIT, 'ms_per_step': ms_e2e, 'h2d_bytes_per_step': hs.h2d_bytes(),
+                'd2h_bytes_per_step': hs.d2h_bytes()},
+        'gpu_launches': int(launches), 'clocks': clocks, 'roofline': roofline,
+        'step_tflops': step_flops / (ms_step * 1e-3) / 1e12, 'step_frac_of_tensor_peak': step_flops / (ms_step * 1e-3) / 1e12 / peaks['tensor'],
+        'kernel_classes_top': [{'name': k, 'launches': c, 'ms': round(ms, 4), 'share': round(ms / total_ms, 4)} for k, c, ms in table[:12]],
+        'device_status': status,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        sec_block = cpu_sample(n, s, depth, args.cpu_reps, wdir)
+        cores = os.cpu_count() or 1
+        out['cpu_baseline'] = {'value': 1.0 / (sec_block * depth), 'unit': UNIT, 'cores': cores, 'kind': 'port',
+                               'sample': f'{args.cpu_reps} x (1 of {depth} blocks forward+backward at N_res={n}, fp32 oracle), scaled x{depth}'}
+    print(json.dumps(out))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--n-res', type=int, default=224)
+    ap.add_argument('--msa-rows', type=int, default=1)
+    ap.add_argument('--depth', type=int, default=48)
+    ap.add_argument('--own-save', type=int, default=0)
+    ap.add_argument('--cpu-reps', type=int, default=5)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

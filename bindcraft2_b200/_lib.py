@@ -20,6 +20,8 @@ PROTOTYPES = {
     'bc2_last_error': (_cp, []),
     'bc2_device_status': (_i32, []),
     'bc2_launch_count': (_i64, []),
+    'bc2_profile_mode': (None, [_i32, _cp]),
+    'bc2_profile_report': (_i64, [_vp, _i64]),
     'bc2_test_set_module_mask': (None, [ctypes.c_uint32]),
     'bc2_test_gemm': (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _i32, _vp, _i64, _i64, _i64, _i64, _i32, _i32]),
     'bc2_test_attention': (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _vp, _vp, _vp, _i32]),

@@ -1,6 +1,7 @@
 // extern "C" surface of the library (declared in include/bc2_b200.h): the bodies of the reference's FFI handlers for
 // the Evoformer stack (native/ffi.cu:183-371) on top of EvoStack, the trace-time entry points, and small bring-up
 // calls used by the unit tests.
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -122,6 +123,44 @@ int bc2_device_status(void) {
 int64_t bc2_launch_count(void) { return launch_counter().load(); }
 
 void bc2_test_set_module_mask(uint32_t mask) { module_mask() = mask; }
+
+void bc2_profile_mode(int mode, const char* only) {
+  Prof& p = prof();
+  std::lock_guard<std::mutex> l(p.mu);
+  p.mode = mode;
+  p.only = only ? only : "";
+}
+
+int64_t bc2_profile_report(char* buf, int64_t cap) {
+  Prof& p = prof();
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  std::lock_guard<std::mutex> l(p.mu);
+  std::vector<double> ms(p.names.size(), 0.0);
+  std::vector<long> cnt(p.names.size(), 0);
+  for (auto& r : p.recs) {
+    float t = 0.f;
+    if (cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) {
+      ms[r.cls] += t;
+      cnt[r.cls] += 1;
+    }
+    p.pool.push_back(r.a);
+    p.pool.push_back(r.b);
+  }
+  p.recs.clear();
+  std::string out;
+  for (size_t i = 0; i < p.names.size(); ++i) {
+    if (!cnt[i]) continue;
+    char line[256];
+    snprintf(line, sizeof(line), "%s %ld %.6f\n", p.names[i].c_str(), cnt[i], ms[i]);
+    out += line;
+  }
+  if (buf && cap > 0) {
+    const size_t n = std::min<size_t>(out.size(), (size_t)cap - 1);
+    memcpy(buf, out.data(), n);
+    buf[n] = 0;
+  }
+  return (int64_t)out.size();
+}
 
 int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, int a_mn, const uint16_t* b, int64_t ldb,
                   int64_t b_bs, int b_mn, uint16_t* d, int64_t M, int64_t N, int64_t K, int64_t batch, int bn,

@@ -29,10 +29,10 @@ constexpr float kClip = 1e8f;
 
 // Clipped logit (natural-log units) of one (query, key) pair; keys beyond N (tile padding) are -inf so they get
 // zero weight even when every real key of the row is masked (the reference then attends uniformly to the N keys).
-__device__ __forceinline__ float attn_logit(float s, float mk, const float* brow, int k, int N) {
+__device__ __forceinline__ float attn_logit(float s, float mk, const float* bq, int k, int N) {
   if (k >= N) return -INFINITY;
   float t = s + mk;
-  if (brow) t += brow[k];
+  if (bq) t += bq[(long)k * N];
   return fminf(fmaxf(t, -kClip), kClip);
 }
 
@@ -42,7 +42,7 @@ struct AttnArgs {
   long ld = 0;          // row length of qkvg (= 4*H*D)
   long row_b = 0, row_p = 0;
   int B = 0, N = 0, H = 0, D = 0;
-  const float* bias = nullptr;  // [H][N][N] (query, key) or null
+  const float* bias = nullptr;  // [H][N][N] indexed (head, KEY, query), or null
   const float* mask = nullptr;  // key mask, element (b, k) at mask[b*mask_b + k*mask_k]
   long mask_b = 0, mask_k = 0;
   bf16* o = nullptr;    // [rows][H*D] ungated output
@@ -53,7 +53,7 @@ struct AttnArgs {
   const bf16* d_o = nullptr;   // [rows][H*D] gradient wrt the ungated output
   const float* delta = nullptr; // [B][H][N] rowsum(dO * O)
   bf16* d_qkv = nullptr;       // [rows][ld]: dq | dk | dv written into the first 3*H*D columns
-  float* d_bias = nullptr;     // [H][N][N], accumulated atomically (must be zeroed by the caller)
+  float* d_bias = nullptr;     // [H][N][N] (head, KEY, query), accumulated atomically (zeroed by the caller)
   float* dq_acc = nullptr;     // [rows][H*D] fp32, only when keys are split over several CTAs
 };
 
@@ -178,7 +178,8 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
     const int q = q0 + r;
     const bool qin = q < a.N;
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
-    const float* brow = (a.bias && qin) ? a.bias + ((long)h * a.N + q) * a.N : nullptr;
+    // bias is stored [h][key][query]: the 32 query rows of a warp read 32 consecutive floats per key
+    const float* brow = (a.bias && qin) ? a.bias + (long)h * a.N * a.N + q : nullptr;
     float mrun = -INFINITY, lrun = 0.f;
     float acc[D];
 #pragma unroll
@@ -430,8 +431,8 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
       const long lidx = ((long)b * a.H + h) * a.N + q;
       const float2 ml = qin ? *reinterpret_cast<const float2*>(a.lse + 2 * lidx) : make_float2(0.f, 0.f);
       const float dl = qin ? a.delta[lidx] : 0.f;
-      const float* brow = (a.bias && qin) ? a.bias + ((long)h * a.N + q) * a.N : nullptr;
-      float* dbrow = (a.d_bias && qin) ? a.d_bias + ((long)h * a.N + q) * a.N : nullptr;
+      const float* brow = (a.bias && qin) ? a.bias + (long)h * a.N * a.N + q : nullptr;
+      float* dbrow = (a.d_bias && qin) ? a.d_bias + (long)h * a.N * a.N + q : nullptr;
       for (int j = 0; j < nkb && ok; ++j, ++step) {
         ok = mbar_wait(b_s, step & 1, SITE_ATTN_BWD);
         if (!ok) break;
@@ -453,7 +454,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             float t = s[e] + sMask[kl + e];
-            if (brow && k0 + e < a.N) t += brow[k0 + e];
+            if (brow && k0 + e < a.N) t += brow[(long)(k0 + e) * a.N];
             const bool kin = k0 + e < a.N;
             const bool live = qin && kin && (t >= -kClip) && (t <= kClip);
             t = fminf(fmaxf(t, -kClip), kClip);
@@ -476,11 +477,9 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
           }
           if (dbrow) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
+            for (int e = 0; e < 32; ++e) {  // [h][key][query]: one coalesced 128-byte reduction per warp and key
               if (k0 + e < a.N)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dbrow + k0 + e), "f"(dsv[e]),
-                             "f"(dsv[e + 1]), "f"(dsv[e + 2]), "f"(dsv[e + 3])
-                             : "memory");
+                asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dbrow + (long)(k0 + e) * a.N), "f"(dsv[e]) : "memory");
             }
           }
         }
@@ -562,7 +561,7 @@ __global__ void attn_fwd_ref_kernel(AttnArgs a) {
     float s = 0.f;
     for (int d = 0; d < D; ++d) s += qv[d] * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
     if (a.mask) s += 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
-    if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
+    if (a.bias) s += a.bias[((long)h * a.N + k) * a.N + q];
     s = fminf(fmaxf(s, -kClip), kClip);
     m = fmaxf(m, s);
   }
@@ -573,7 +572,7 @@ __global__ void attn_fwd_ref_kernel(AttnArgs a) {
     float s = 0.f;
     for (int d = 0; d < D; ++d) s += qv[d] * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
     if (a.mask) s += 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
-    if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
+    if (a.bias) s += a.bias[((long)h * a.N + k) * a.N + q];
     s = fminf(fmaxf(s, -kClip), kClip);
     const float p = __expf(s - m);
     l += p;
@@ -613,12 +612,12 @@ __global__ void attn_bwd_ref_kernel(AttnArgs a, float* dkv_acc) {
       dp += dov[d] * __bfloat162float(a.qkvg[rowk * a.ld + 2 * HD + h * D + d]);
     }
     if (a.mask) s += 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
-    if (a.bias) s += a.bias[((long)h * a.N + q) * a.N + k];
+    if (a.bias) s += a.bias[((long)h * a.N + k) * a.N + q];
     const bool live = s >= -kClip && s <= kClip;
     s = fminf(fmaxf(s, -kClip), kClip);
     const float p = __expf(s - m2) * inv_l;
     const float ds = live ? p * (dp - dl) : 0.f;
-    if (a.d_bias) atomicAdd(a.d_bias + ((long)h * a.N + q) * a.N + k, ds);
+    if (a.d_bias) atomicAdd(a.d_bias + ((long)h * a.N + k) * a.N + q, ds);
     for (int d = 0; d < D; ++d) {
       dq[d] += ds * __bfloat162float(a.qkvg[rowk * a.ld + HD + h * D + d]);
       atomicAdd(dkv_acc + rowk * 2 * HD + h * D + d, ds * qv[d]);

@@ -111,22 +111,22 @@ struct Transition {
     W& b = w[blk];
     const int M = (int)rows, FC = F * C;
     LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = M;
-    ln_fwd_c(C, l, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.forward.ln_fwd_c" : "MsaTransition.forward.ln_fwd_c", st); ln_fwd_c(C, l, st); }
     EpiStore e1; e1.out = h; e1.ldo = FC; e1.bias = b.b1; e1.act = 1; e1.M = M; e1.N = FC;
-    run_gemm(b.g1, e1, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.forward.gemm.g1" : "MsaTransition.forward.gemm.g1", st); run_gemm(b.g1, e1, st); }
     EpiResidual e2; e2.res_in = in; e2.res_out = out; e2.ld = C; e2.bias = b.b2; e2.M = M; e2.N = C;
-    run_gemm(b.g2, e2, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.forward.gemm.g2" : "MsaTransition.forward.gemm.g2", st); run_gemm(b.g2, e2, st); }
   }
   void backward(int blk, const float* in, float* g, cudaStream_t st) {
     W& b = w[blk];
     const int M = (int)rows, FC = F * C;
-    cvt_f32_bf16(g, S->dy, rows * C, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.backward.cvt_f32_bf16" : "MsaTransition.backward.cvt_f32_bf16", st); cvt_f32_bf16(g, S->dy, rows * C, st); }
     EpiStore e2; e2.out = S->big; e2.ldo = FC; e2.mul = h; e2.ldm = FC; e2.mul_mode = 2; e2.M = M; e2.N = FC;
-    run_gemm(b.gb2, e2, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.backward.gemm.gb2" : "MsaTransition.backward.gemm.gb2", st); run_gemm(b.gb2, e2, st); }
     EpiStore e1; e1.out = S->dx; e1.ldo = C; e1.M = M; e1.N = C;
-    run_gemm(b.gb1, e1, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.backward.gemm.gb1" : "MsaTransition.backward.gemm.gb1", st); run_gemm(b.gb1, e1, st); }
     LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.g_in = g; l.g_out = g; l.M = M;
-    ln_bwd_c(C, l, st);
+    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.backward.ln_bwd_c" : "MsaTransition.backward.ln_bwd_c", st); ln_bwd_c(C, l, st); }
   }
 };
 
@@ -235,36 +235,34 @@ struct TriMul {
     W& b = w[blk];
     const int Mi = (int)M, CH = 2 * Hc;
     LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = Mi;
-    ln_fwd_c(C, l, st);
+    { ProfScope ps_("TriMul.forward.ln_fwd_c", st); ln_fwd_c(C, l, st); }
     EpiProjGate ep; ep.bias_p = b.bp; ep.bias_g = b.bg; ep.mask = mask; ep.gate_out = gate; ep.ab_out = ab; ep.M = Mi; ep.CH = CH;
-    run_gemm(b.g_pg, ep, st);
+    { ProfScope ps_("TriMul.forward.gemm.g_pg", st); run_gemm(b.g_pg, ep, st); }
     EpiStore ec; ec.out = t; ec.ldo = n; ec.bso = M; ec.M = n; ec.N = n;
-    run_gemm(g_con, ec, st);
-    cln_fwd_c(t, b.cn, S->y, st);
+    { ProfScope ps_("TriMul.forward.gemm.g_con", st); run_gemm(g_con, ec, st); }
+    { ProfScope ps_("TriMul.forward.cln_fwd_c", st); cln_fwd_c(t, b.cn, S->y, st); }
     EpiStore eg; eg.out = g2; eg.ldo = C; eg.bias = b.bg2; eg.act = 2; eg.act_from = 0; eg.M = Mi; eg.N = C;
-    run_gemm(b.g_g2, eg, st);
+    { ProfScope ps_("TriMul.forward.gemm.g_g2", st); run_gemm(b.g_g2, eg, st); }
     EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.bo; er.mul = g2; er.ldm = C; er.save = ob; er.lds = C; er.M = Mi; er.N = C;
-    run_gemm(b.g_o, er, st);
+    { ProfScope ps_("TriMul.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* in, float* g, const float* mask, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)M, CH = 2 * Hc, NP = 2 * CH, KC = NP + C;
-    launch_counter()++; trimul_bwd_out_kernel<<<ew_grid(M * C / 4, 256), 256, 0, st>>>(
-        reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2),
-        reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C);
+    { ProfScope ps_("TriMul.backward.trimul_bwd_out_kernel", st); launch_counter()++; trimul_bwd_out_kernel<<<ew_grid(M * C / 4, 256), 256, 0, st>>>( reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2), reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C); }
     EpiStore ey; ey.out = S->dy; ey.ldo = Hc; ey.M = Mi; ey.N = Hc;
-    run_gemm(b.gb_o, ey, st);
-    cln_bwd_c(t, b.cn, S->dy, S->dt, st);
+    { ProfScope ps_("TriMul.backward.gemm.gb_o", st); run_gemm(b.gb_o, ey, st); }
+    { ProfScope ps_("TriMul.backward.cln_bwd_c", st); cln_bwd_c(t, b.cn, S->dy, S->dt, st); }
     EpiStore ea; ea.out = S->dab; ea.ldo = n; ea.bso = M; ea.M = n; ea.N = n;
-    run_gemm(gb_da, ea, st);
+    { ProfScope ps_("TriMul.backward.gemm.gb_da", st); run_gemm(gb_da, ea, st); }
     EpiStore eb = ea; eb.out = S->dab + (long)Hc * M;
-    run_gemm(gb_db, eb, st);
+    { ProfScope ps_("TriMul.backward.gemm.gb_db", st); run_gemm(gb_db, eb, st); }
     dim3 grid((unsigned)(M / 64), CH / 64);
-    launch_counter()++; trimul_bwd_gate_kernel<<<grid, 256, 0, st>>>(S->dab, ab, gate, mask, S->big, KC, M, CH);
+    { ProfScope ps_("TriMul.backward.trimul_bwd_gate_kernel", st); launch_counter()++; trimul_bwd_gate_kernel<<<grid, 256, 0, st>>>(S->dab, ab, gate, mask, S->big, KC, M, CH); }
     EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
-    run_gemm(b.gb_cat, ex, st);
+    { ProfScope ps_("TriMul.backward.gemm.gb_cat", st); run_gemm(b.gb_cat, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.g_in = g; l.g_out = g; l.M = Mi;
-    ln_bwd_c(C, l, st);
+    { ProfScope ps_("TriMul.backward.ln_bwd_c", st); ln_bwd_c(C, l, st); }
   }
 };
 
@@ -357,28 +355,28 @@ struct TriAttn {
     const int Mi = (int)M, HD = H * D;
     LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = Mi;
     l.wb = b.wb; l.nb = nb; l.H = H; l.n = n; l.transposed = ending ? 1 : 0;
-    ln_fwd_c(C, l, st);
+    { ProfScope ps_("TriAttn.forward.ln_fwd_c", st); ln_fwd_c(C, l, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
-    run_gemm(b.g_qkvg, e, st);
-    attn_fwd(plan, st);
+    { ProfScope ps_("TriAttn.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
+    { ProfScope ps_("TriAttn.forward.attn_fwd", st); attn_fwd(plan, st); }
     EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.a.bo; er.M = Mi; er.N = C;
-    run_gemm(b.g_o, er, st);
+    { ProfScope ps_("TriAttn.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* in, float* g, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)M, HD = H * D;
-    cvt_f32_bf16(g, S->dy, M * C, st);
+    { ProfScope ps_("TriAttn.backward.cvt_f32_bf16", st); cvt_f32_bf16(g, S->dy, M * C, st); }
     EpiStore e; e.out = S->y; e.ldo = HD; e.M = Mi; e.N = HD;
-    run_gemm(b.gb_o, e, st);
+    { ProfScope ps_("TriAttn.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
     AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, M, plan.args.row_b, plan.args.row_p, n, H, D};
-    attn_bwd_prep(p, st);
-    BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st));
-    attn_bwd(plan, st);
+    { ProfScope ps_("TriAttn.backward.attn_bwd_prep", st); attn_bwd_prep(p, st); }
+    { ProfScope ps_("TriAttn.backward.memset", st); BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st)); }
+    { ProfScope ps_("TriAttn.backward.attn_bwd", st); attn_bwd(plan, st); }
     EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
-    run_gemm(b.gb_qkvg, ex, st);
+    { ProfScope ps_("TriAttn.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.wb = b.wb; l.dnb = S->dnb; l.H = H; l.n = n;
     l.transposed = ending ? 1 : 0; l.g_in = g; l.g_out = g; l.M = Mi;
-    ln_bwd_c(C, l, st);
+    { ProfScope ps_("TriAttn.backward.ln_bwd_c", st); ln_bwd_c(C, l, st); }
   }
 };
 
@@ -433,31 +431,31 @@ struct MsaRow {
     W& b = w[blk];
     const int Mi = (int)Mm, HD = H * D;
     LnArgs l; l.x = msa_in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
-    ln_fwd_c(Cm, l, st);
+    { ProfScope ps_("MsaRow.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     LnArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.offset = b.fn.offset; lp.wb = b.wb; lp.nb = nb; lp.H = H; lp.n = n; lp.M = (int)Mp;
-    ln_fwd_c(Cz, lp, st);
+    { ProfScope ps_("MsaRow.forward.ln_fwd_c", st); ln_fwd_c(Cz, lp, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
-    run_gemm(b.g_qkvg, e, st);
-    attn_fwd(plan, st);
+    { ProfScope ps_("MsaRow.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
+    { ProfScope ps_("MsaRow.forward.attn_fwd", st); attn_fwd(plan, st); }
     EpiResidual er; er.res_in = msa_in; er.res_out = msa_out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm;
-    run_gemm(b.g_o, er, st);
+    { ProfScope ps_("MsaRow.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* msa_in, const float* pair, float* g_msa, float* g_pair, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm, HD = H * D;
-    cvt_f32_bf16(g_msa, S->dy, Mm * Cm, st);
+    { ProfScope ps_("MsaRow.backward.cvt_f32_bf16", st); cvt_f32_bf16(g_msa, S->dy, Mm * Cm, st); }
     EpiStore e; e.out = S->y; e.ldo = HD; e.M = Mi; e.N = HD;
-    run_gemm(b.gb_o, e, st);
+    { ProfScope ps_("MsaRow.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
     AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, Mm, (long)n, 1L, n, H, D};
-    attn_bwd_prep(p, st);
-    BC2_CUDA(cudaMemsetAsync(dnb, 0, (size_t)H * Mp * 4, st));
-    attn_bwd(plan, st);
+    { ProfScope ps_("MsaRow.backward.attn_bwd_prep", st); attn_bwd_prep(p, st); }
+    { ProfScope ps_("MsaRow.backward.memset", st); BC2_CUDA(cudaMemsetAsync(dnb, 0, (size_t)H * Mp * 4, st)); }
+    { ProfScope ps_("MsaRow.backward.attn_bwd", st); attn_bwd(plan, st); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
-    run_gemm(b.gb_qkvg, ex, st);
+    { ProfScope ps_("MsaRow.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = msa_in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;
-    ln_bwd_c(Cm, l, st);
+    { ProfScope ps_("MsaRow.backward.ln_bwd_c", st); ln_bwd_c(Cm, l, st); }
     LnBwdArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.wb = b.wb; lp.dnb = dnb; lp.H = H; lp.n = n; lp.g_in = g_pair; lp.g_out = g_pair; lp.M = (int)Mp;
-    ln_bwd_c(Cz, lp, st);
+    { ProfScope ps_("MsaRow.backward.ln_bwd_c", st); ln_bwd_c(Cz, lp, st); }
   }
 };
 
@@ -496,24 +494,24 @@ struct MsaCol {
     W& b = w[blk];
     const int Mi = (int)Mm;
     LnArgs l; l.x = in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
-    ln_fwd_c(Cm, l, st);
+    { ProfScope ps_("MsaCol.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * Cm; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * Cm; e.M = Mi; e.N = 4 * Cm;
-    run_gemm(b.g_qkvg, e, st);
-    launch_counter()++; msacol_fwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S_, n, H);
+    { ProfScope ps_("MsaCol.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
+    { ProfScope ps_("MsaCol.forward.msacol_fwd_kernel", st); launch_counter()++; msacol_fwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S_, n, H); }
     EpiResidual er; er.res_in = in; er.res_out = out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm;
-    run_gemm(b.g_o, er, st);
+    { ProfScope ps_("MsaCol.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* in, float* g, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm;
-    cvt_f32_bf16(g, S->dy, Mm * Cm, st);
+    { ProfScope ps_("MsaCol.backward.cvt_f32_bf16", st); cvt_f32_bf16(g, S->dy, Mm * Cm, st); }
     EpiStore e; e.out = S->y; e.ldo = Cm; e.M = Mi; e.N = Cm;
-    run_gemm(b.gb_o, e, st);
-    launch_counter()++; msacol_bwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S->big, S_, n, H);
+    { ProfScope ps_("MsaCol.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
+    { ProfScope ps_("MsaCol.backward.msacol_bwd_kernel", st); launch_counter()++; msacol_bwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S->big, S_, n, H); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
-    run_gemm(b.gb_qkvg, ex, st);
+    { ProfScope ps_("MsaCol.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g; l.g_out = g; l.M = Mi;
-    ln_bwd_c(Cm, l, st);
+    { ProfScope ps_("MsaCol.backward.ln_bwd_c", st); ln_bwd_c(Cm, l, st); }
   }
 };
 
@@ -569,26 +567,26 @@ struct Opm {
     W& b = w[blk];
     const int Mi = (int)Mm;
     LnArgs l; l.x = msa_in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
-    ln_fwd_c(Cm, l, st);
+    { ProfScope ps_("Opm.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     EpiStore e; e.out = lr; e.ldo = 64; e.bias = b.blr; e.rowscale = msa_mask; e.M = Mi; e.N = 64;
-    run_gemm(b.g_lr, e, st);
-    launch_counter()++; opm_tmp_kernel<<<dim3(Mi, OPM_C), 128, 0, st>>>(lr, b.ow, tmp, Mi);
+    { ProfScope ps_("Opm.forward.gemm.g_lr", st); run_gemm(b.g_lr, e, st); }
+    { ProfScope ps_("Opm.forward.opm_tmp_kernel", st); launch_counter()++; opm_tmp_kernel<<<dim3(Mi, OPM_C), 128, 0, st>>>(lr, b.ow, tmp, Mi); }
     const size_t sm = (size_t)(32 * S_ * OPM_C + 32) * 4;
-    launch_counter()++; opm_out_kernel<<<dim3(n, cdiv(n, 32)), 128, sm, st>>>(lr, tmp, b.ob, msa_mask, pair_in, pair_out, S_, n);
+    { ProfScope ps_("Opm.forward.opm_out_kernel", st); launch_counter()++; opm_out_kernel<<<dim3(n, cdiv(n, 32)), 128, sm, st>>>(lr, tmp, b.ob, msa_mask, pair_in, pair_out, S_, n); }
   }
   // g_pair: cotangent of the pair stream after the module (read only: the module adds to the pair stream, so the
   // cotangent of its pair input is g_pair itself); g_msa accumulates.
   void backward(int blk, const float* msa_in, const float* g_pair, float* g_msa, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm;
-    launch_counter()++; opm_dleft_kernel<<<dim3(n, S_), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n);
-    launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n);
-    launch_counter()++; opm_dright_kernel<<<Mi, 256, 0, st>>>(dtmp, b.ow, dlr, Mi);
-    launch_counter()++; opm_dlr_store_kernel<<<cdiv(Mi * 64, 256), 256, 0, st>>>(dlr, msa_mask, dlr_b, (long)Mi * 64);
+    { ProfScope ps_("Opm.backward.opm_dleft_kernel", st); launch_counter()++; opm_dleft_kernel<<<dim3(n, S_), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dtmp_kernel", st); launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dright_kernel", st); launch_counter()++; opm_dright_kernel<<<Mi, 256, 0, st>>>(dtmp, b.ow, dlr, Mi); }
+    { ProfScope ps_("Opm.backward.opm_dlr_store_kernel", st); launch_counter()++; opm_dlr_store_kernel<<<cdiv(Mi * 64, 256), 256, 0, st>>>(dlr, msa_mask, dlr_b, (long)Mi * 64); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
-    run_gemm(b.gb_lr, ex, st);
+    { ProfScope ps_("Opm.backward.gemm.gb_lr", st); run_gemm(b.gb_lr, ex, st); }
     LnBwdArgs l; l.x = msa_in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;
-    ln_bwd_c(Cm, l, st);
+    { ProfScope ps_("Opm.backward.ln_bwd_c", st); ln_bwd_c(Cm, l, st); }
   }
 };
 

@@ -94,10 +94,12 @@ __device__ __forceinline__ void row_stats(const float (&v)[C / 32], float& mean,
   rstd = rsqrtf(warp_sum(q) * (1.f / C) + 1e-5f);
 }
 
-// Position index of the bias entry for row m of an [n,n] pair tensor: identity, or transposed for the
-// ending-node attention whose bias is built from the transposed activations (modules.py:696-720).
+// Index of the attention-bias entry that row m = (i, j) of an [n,n] pair tensor produces.  The attention kernels keep
+// the bias as [head][KEY][query] (a warp's 32 query rows then read consecutive floats).  Row-wise attention uses
+// bias(q = i, k = j), stored at j*n + i; the ending-node attention is built from the transposed activations
+// (modules.py:696-720), bias(q = j, k = i), stored at i*n + j = m.
 __device__ __forceinline__ long bias_pos(int m, int n, int transposed) {
-  if (!transposed) return m;
+  if (transposed) return m;
   const int i = m / n, j = m - i * n;
   return (long)j * n + i;
 }

@@ -72,6 +72,13 @@ int bc2_device_status(void);
  * launch count). */
 int64_t bc2_launch_count(void);
 
+/* Per-kernel-class timing with CUDA events on the launching stream (the reference has BLK_PROF for the same purpose,
+ * native/common.cuh:735-880).  mode 0 = off (default), 1 = every class, 2 = only the class named `only`.
+ * bc2_profile_report synchronises the device, writes one line per class "<name> <launches> <total ms>" into buf
+ * (NUL terminated, at most cap bytes), clears the records and returns the full text length. */
+void bc2_profile_mode(int mode, const char* only);
+int64_t bc2_profile_report(char* buf, int64_t cap);
+
 /* ---- bring-up / unit-test entry points (not part of the reference surface) ------------------------------------ */
 
 /* Enables a subset of the nine residual steps of every block (bit i = step i in block order: outer product mean, MSA
@@ -88,8 +95,8 @@ int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, in
                   int use_ref);
 
 /* One gated attention forward+backward on caller buffers (layouts in bindcraft2_b200/csrc/attn.cuh).
- * qkvg bf16 [rows][4*H*D]; bias f32 [H][N][N]; mask f32 [B][N]; d_og bf16 [rows][H*D].
- * Outputs: og bf16 [rows][H*D]; d_qkvg bf16 [rows][4*H*D] (dq|dk|dv|d gate-pre); d_bias f32 [H][N][N].
+ * qkvg bf16 [rows][4*H*D]; bias f32 [H][N][N] indexed (head, key, query); mask f32 [B][N]; d_og bf16 [rows][H*D].
+ * Outputs: og bf16 [rows][H*D]; d_qkvg bf16 [rows][4*H*D] (dq|dk|dv|d gate-pre); d_bias f32 [H][N][N] (head, key, query).
  * transposed != 0 walks the batch along columns (ending-node orientation). */
 int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, const uint16_t* d_og,
                        int64_t B, int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og, uint16_t* d_qkvg,
