@@ -94,21 +94,29 @@ __device__ __forceinline__ uint64_t desc_p_mnmajor(uint32_t saddr, int k16) {
 }
 
 // ------------------------------------------------------------------------------------------- forward (tcgen05)
+// 320 threads: warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2..9 softmax.  Two softmax threads share a
+// query row: thread (row r, half) owns keys [64*half, 64*half+64) of every 128-key block and output columns
+// [half*D/2, (half+1)*D/2).  The S block is read once into registers (one pass), the two partial row maxima meet in
+// shared memory behind a named barrier, and both threads then use the same running max, so their partial sums and
+// partial outputs simply add at the end.
 template <int D>
-__global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a) {
+__global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int nkb = cdiv(a.N, 128);
   constexpr int TILE = 128 * D * 2;  // bytes of a [128][D] tile
+  constexpr int DH = D / 2;
   uint8_t* sP = smem;                 // 32 KB
   uint8_t* sQ = sP + 32768;
   uint8_t* sK = sQ + TILE;
   uint8_t* sV = sK + nkb * TILE;
   float* sMask = reinterpret_cast<float*>(sV + nkb * TILE);  // [nkb*128] additive key mask (natural-log units)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sMask + nkb * 128);
+  float* sX = sMask + nkb * 128;                              // [2][2][128] partial row maxima, double buffered
+  float* sL = sX + 512;                                       // [2][128] partial row sums
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + 256);
   uint64_t* b_load = bars;       // Q, K, V landed
   uint64_t* b_s = bars + 1;      // S block ready in TMEM
-  uint64_t* b_p = bars + 2;      // P block written to smem (128 arrivals)
+  uint64_t* b_p = bars + 2;      // P block written to smem (256 arrivals)
   uint64_t* b_o = bars + 3;      // O block ready in TMEM
   uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 4);
 
@@ -119,7 +127,7 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(b_load, 1);
     mbar_init(b_s, 1);
-    mbar_init(b_p, 128);
+    mbar_init(b_p, 256);
     mbar_init(b_o, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm);
@@ -172,38 +180,67 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
       }
     }
   } else {
-    // softmax threads: warps 2..5, TMEM lane quarter = warp & 3
-    const int qd = warp & 3;
+    const int qd = warp & 3, half = (warp - 2) >> 2;
     const int r = qd * 32 + lane;
     const int q = q0 + r;
     const bool qin = q < a.N;
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     // bias is stored [h][key][query]: the 32 query rows of a warp read 32 consecutive floats per key
-    const float* brow = (a.bias && qin) ? a.bias + (long)h * a.N * a.N + q : nullptr;
-    float mrun = -INFINITY, lrun = 0.f;
-    float acc[D];
+    const float* bq = (a.bias && qin) ? a.bias + (long)h * a.N * a.N + q : nullptr;
+    float mrun = -INFINITY, lsum = 0.f;
+    float acc[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
-    float alpha_prev = 1.f;
+    for (int i = 0; i < DH; ++i) acc[i] = 0.f;
     bool ok = true;
+    auto fold_output = [&]() {  // acc += this thread's half of the finished O block
+      float ob[DH];
+      if constexpr (DH == 16) tmem_ld16(tO + lane_off + half * DH, ob);
+      else tmem_ld8(tO + lane_off + half * DH, ob);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < DH; ++i) acc[i] += ob[i];
+    };
     for (int j = 0; j < nkb && ok; ++j) {
       ok = mbar_wait(b_s, j & 1, SITE_ATTN);
       if (!ok) break;
       tc_fence_after();
-      // pass 1: block max
-      float mblk = -INFINITY;
+      // pass 1: logits (+ bias, mask, clip) written back to TMEM, partial row max kept
+      float mpart = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float s[32];
-        tmem_ld32(tS + lane_off + c * 32, s);
-        tmem_ld_wait();
-        const int k0 = j * 128 + c * 32;
+      for (int c = 0; c < 2; ++c) {
+        const int k0 = j * 128 + half * 64 + c * 32;  // N is a multiple of 32: a 32-key chunk is all real or all padding
+        float t[32];
+        if (k0 < a.N) {
+          tmem_ld32(tS + lane_off + half * 64 + c * 32, t);
+          tmem_ld_wait();
+          const float4* mk4 = reinterpret_cast<const float4*>(sMask + k0);
+          const float* bp = bq ? bq + (long)k0 * a.N : nullptr;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mblk = fmaxf(mblk, attn_logit(s[i], sMask[k0 + i], brow, k0 + i, a.N));
+          for (int i = 0; i < 32; i += 4) {
+            const float4 mk = mk4[i >> 2];
+            const float m4[4] = {mk.x, mk.y, mk.z, mk.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float v = t[i + e] + m4[e];
+              if (bp) v += bp[(long)(i + e) * a.N];
+              v = fminf(fmaxf(v, -kClip), kClip);
+              t[i + e] = v;
+              mpart = fmaxf(mpart, v);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) t[i] = -INFINITY;
+        }
+        tmem_st32(tS + lane_off + half * 64 + c * 32, t);
       }
+      tmem_st_wait();
+      float* xb = sX + (j & 1) * 256;
+      xb[half * 128 + r] = mpart;
+      named_barrier(1, 256);
+      const float mblk = fmaxf(mpart, xb[(half ^ 1) * 128 + r]);
       // Natural-log units, and the max is subtracted BEFORE scaling by log2(e): for a fully masked row every logit
-      // and the max are exactly -1e8, so the difference is exactly 0 whatever the compiler fuses; folding the scale
-      // in first would leave a rounding residue of several units at that magnitude.
+      // and the max are exactly -1e8, so the difference is exactly 0 whatever the compiler fuses.
       const float mnew = fmaxf(mrun, mblk);
       const float alpha = exp2f((mrun - mnew) * kLog2e);  // 0 on the first block (mrun = -inf)
       // fold the previous block's output in before P is overwritten (its MMA has finished once b_o flips)
@@ -211,43 +248,31 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
         ok = mbar_wait(b_o, (j - 1) & 1, SITE_ATTN);
         if (!ok) break;
         tc_fence_after();
-        float ob[32];
-        tmem_ld32(tO + lane_off, ob);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < D; ++i) acc[i] = acc[i] * alpha_prev + ob[i];
+        fold_output();
       }
-      // pass 2: probabilities, row sum, P tile
       float lblk = 0.f;
+      uint8_t* blk = sP + half * 16384;  // this thread's 64 keys are one 64-column swizzled block of the P tile
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float s[32];
-        tmem_ld32(tS + lane_off + c * 32, s);
+      for (int c = 0; c < 2; ++c) {
+        float t[32];
+        tmem_ld32(tS + lane_off + half * 64 + c * 32, t);
         tmem_ld_wait();
-        const int k0 = j * 128 + c * 32;
-        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float t0 = attn_logit(s[i], sMask[k0 + i], brow, k0 + i, a.N);
-          const float t1 = attn_logit(s[i + 1], sMask[k0 + i + 1], brow, k0 + i + 1, a.N);
-          const float p0 = exp2f((t0 - mnew) * kLog2e), p1 = exp2f((t1 - mnew) * kLog2e);
-          lblk += p0 + p1;
-          pk[i >> 1] = pack_bf16(p0, p1);
-        }
-        // 32 keys = 4 chunks of 16 bytes; key column inside the 128-wide tile = c*32
-        uint8_t* blk = sP + (c >> 1) * 16384;
+        for (int i = 0; i < 32; i += 8) {
+          uint32_t pk[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int chunk = (c & 1) * 4 + i;
-          *reinterpret_cast<uint4*>(blk + sw128_off(r, chunk)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+          for (int e = 0; e < 8; e += 2) {
+            const float p0 = exp2f((t[i + e] - mnew) * kLog2e), p1 = exp2f((t[i + e + 1] - mnew) * kLog2e);
+            lblk += p0 + p1;
+            pk[e >> 1] = pack_bf16(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(blk + sw128_off(r, c * 4 + (i >> 3))) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
       }
-      lrun = lrun * alpha + lblk;
+      lsum = lsum * alpha + lblk;
       mrun = mnew;
-      alpha_prev = 1.f;  // acc is rescaled by `alpha` lazily: remember it for when this block's output arrives
-      // acc currently holds blocks < j at scale of the previous max; bring it to the new max now
 #pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] *= alpha;
+      for (int i = 0; i < DH; ++i) acc[i] *= alpha;
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(b_p);
@@ -255,33 +280,31 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
     if (ok) ok = mbar_wait(b_o, (nkb - 1) & 1, SITE_ATTN);
     if (ok) {
       tc_fence_after();
-      float ob[32];
-      tmem_ld32(tO + lane_off, ob);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] += ob[i];
+      fold_output();
+      sL[half * 128 + r] = lsum;
+      named_barrier(1, 256);
+      const float inv = 1.f / (lsum + sL[(half ^ 1) * 128 + r]);
       if (qin) {
-        const float inv = 1.f / lrun;
         const long row = (long)b * a.row_b + (long)q * a.row_p;
-        const bf16* gp = a.qkvg + row * a.ld + 3 * HD + h * D;
-        bf16* op = a.o + row * HD + h * D;
-        bf16* ogp = a.og + row * HD + h * D;
+        const bf16* gp = a.qkvg + row * a.ld + 3 * HD + h * D + half * DH;
+        bf16* op = a.o + row * HD + h * D + half * DH;
+        bf16* ogp = a.og + row * HD + h * D + half * DH;
 #pragma unroll
-        for (int i = 0; i < D; i += 8) {
-          uint4 g4 = *reinterpret_cast<const uint4*>(gp + i);
+        for (int i = 0; i < DH; i += 8) {
+          const uint4 g4 = *reinterpret_cast<const uint4*>(gp + i);
           const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w};
           uint32_t ow[4], ogw[4];
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const float o0 = acc[i + 2 * t] * inv, o1 = acc[i + 2 * t + 1] * inv;
-            const float2 g = unpack_bf16(gw[t]);
-            ow[t] = pack_bf16(o0, o1);
-            ogw[t] = pack_bf16(o0 * g.x, o1 * g.y);
+          for (int e = 0; e < 4; ++e) {
+            const float o0 = acc[i + 2 * e] * inv, o1 = acc[i + 2 * e + 1] * inv;
+            const float2 g = unpack_bf16(gw[e]);
+            ow[e] = pack_bf16(o0, o1);
+            ogw[e] = pack_bf16(o0 * g.x, o1 * g.y);
           }
           *reinterpret_cast<uint4*>(op + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
           *reinterpret_cast<uint4*>(ogp + i) = make_uint4(ogw[0], ogw[1], ogw[2], ogw[3]);
         }
-        *reinterpret_cast<float2*>(a.lse + 2 * (((long)b * a.H + h) * a.N + q)) = make_float2(mrun, inv);
+        if (half == 0) *reinterpret_cast<float2*>(a.lse + 2 * (((long)b * a.H + h) * a.N + q)) = make_float2(mrun, inv);
       }
     }
   }
@@ -292,7 +315,7 @@ __global__ void __launch_bounds__(192) attn_fwd_tc_kernel(const __grid_constant_
 
 inline int attn_fwd_smem(int N, int D) {
   const int nkb = cdiv(N, 128);
-  return 1024 + 32768 + 128 * D * 2 * (1 + 2 * nkb) + nkb * 128 * 4 + 128;
+  return 1024 + 32768 + 128 * D * 2 * (1 + 2 * nkb) + nkb * 128 * 4 + 768 * 4 + 128;
 }
 
 // ------------------------------------------------------------------------------------------- backward (tcgen05)
@@ -679,7 +702,7 @@ inline void attn_fwd_launch(const AttnPlan& p, cudaStream_t st) {
     set_for = smem;
   }
   dim3 grid(cdiv(a.N, 128), a.H, a.B);
-  launch_counter()++; attn_fwd_tc_kernel<D><<<grid, 192, smem, st>>>(p.tm, a);
+  launch_counter()++; attn_fwd_tc_kernel<D><<<grid, 320, smem, st>>>(p.tm, a);
 }
 
 template <int D>

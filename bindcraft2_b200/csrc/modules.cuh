@@ -308,7 +308,7 @@ struct TriAttn {
   long M = 0;
   struct W {
     LnW ln;
-    float* wb = nullptr;  // feat_2d_weights [C][H]
+    float* wb = nullptr;  // feat_2d_weights, head-major [H][C]
     AttnW a;
     GemmPlan g_qkvg, g_o, gb_o, gb_qkvg;
   };
@@ -341,7 +341,7 @@ struct TriAttn {
   void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
     W b;
     b.ln.load(A, m, p + "/query_norm");
-    b.wb = A.upload(m.get(p + "/feat_2d_weights").data);
+    b.wb = A.upload(transpose_io(m.get(p + "/feat_2d_weights").data, C, H));  // [H][C]
     b.a.load(A, m, p + "/attention", C, H, D);
     const int Mi = (int)M, HD = H * D;
     b.g_qkvg = make_gemm(kmaj(S->x, C), kmaj(b.a.wqkvg, C), Mi, 4 * HD, C, 1, 256);
@@ -387,7 +387,7 @@ struct MsaRow {
   long Mm = 0, Mp = 0;
   struct W {
     LnW qn, fn;
-    float* wb = nullptr;  // feat_2d_weights [Cz][H]
+    float* wb = nullptr;  // feat_2d_weights, head-major [H][Cz]
     AttnW a;
     GemmPlan g_qkvg, g_o, gb_o, gb_qkvg;
   };
@@ -418,7 +418,7 @@ struct MsaRow {
     W b;
     b.qn.load(A, m, p + "/query_norm");
     b.fn.load(A, m, p + "/feat_2d_norm");
-    b.wb = A.upload(m.get(p + "/feat_2d_weights").data);
+    b.wb = A.upload(transpose_io(m.get(p + "/feat_2d_weights").data, Cz, H));  // [H][Cz]
     b.a.load(A, m, p + "/attention", Cm, H, D);
     const int Mi = (int)Mm, HD = H * D;
     b.g_qkvg = make_gemm(kmaj(S->x, Cm), kmaj(b.a.wqkvg, Cm), Mi, 4 * HD, Cm, 1, 256);

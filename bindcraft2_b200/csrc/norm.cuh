@@ -110,37 +110,50 @@ struct LnArgs {
   const float* offset = nullptr;
   bf16* y = nullptr;            // [M, ldy] or null
   long ldy = 0;
-  const float* wb = nullptr;    // [C, H] bias projection or null
+  const float* wb = nullptr;    // [H, C] bias projection (head-major) or null
   float* nb = nullptr;          // [H][M]
   int H = 0, n = 0, transposed = 0;
   int M = 0;
 };
 
+constexpr int LN_MAXH = 8;
+
+// Persistent: each warp keeps scale, offset and its slice of the bias projection in registers and strides over rows.
 template <int C>
 __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
   using R = RowVec<C>;
   const int lane = threadIdx.x & 31;
-  const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (m >= a.M) return;
-  float v[R::VPL], sc[R::VPL], of[R::VPL];
-  load_row_f32<C>(a.x + (long)m * C, lane, v);
+  const int nwarp = gridDim.x * 8;
+  float sc[R::VPL], of[R::VPL];
   load_row_f32<C>(a.scale, lane, sc);
   load_row_f32<C>(a.offset, lane, of);
-  float mean, rstd;
-  row_stats<C>(v, mean, rstd);
-#pragma unroll
-  for (int i = 0; i < R::VPL; ++i) v[i] = (v[i] - mean) * rstd * sc[i] + of[i];
-  if (a.y) store_row_bf16<C>(a.y + (long)m * a.ldy, lane, v);
+  float wbr[LN_MAXH][R::VPL];
   if (a.wb) {
-    const long pos = bias_pos(m, a.n, a.transposed);
-    for (int h = 0; h < a.H; ++h) {
-      float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < R::NV; ++i)
+    for (int h = 0; h < LN_MAXH; ++h)
+      if (h < a.H) load_row_f32<C>(a.wb + (long)h * C, lane, wbr[h]);
+  }
+  for (int m = blockIdx.x * 8 + (threadIdx.x >> 5); m < a.M; m += nwarp) {
+    float v[R::VPL];
+    load_row_f32<C>(a.x + (long)m * C, lane, v);
+    float mean, rstd;
+    row_stats<C>(v, mean, rstd);
 #pragma unroll
-        for (int j = 0; j < R::VEC; ++j) s += v[i * R::VEC + j] * a.wb[R::idx(lane, i, j) * a.H + h];
-      s = warp_sum(s);
-      if (lane == 0) a.nb[(long)h * a.M + pos] = s;
+    for (int i = 0; i < R::VPL; ++i) v[i] = (v[i] - mean) * rstd * sc[i] + of[i];
+    if (a.y) store_row_bf16<C>(a.y + (long)m * a.ldy, lane, v);
+    if (a.wb) {
+      const long pos = bias_pos(m, a.n, a.transposed);
+      float mine = 0.f;  // lane h ends up holding head h's dot product
+#pragma unroll
+      for (int h = 0; h < LN_MAXH; ++h)
+        if (h < a.H) {
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < R::VPL; ++i) s += v[i] * wbr[h][i];
+          s = warp_sum(s);
+          if (lane == h) mine = s;
+        }
+      if (lane < a.H) a.nb[(long)lane * a.M + pos] = mine;
     }
   }
 }
@@ -150,7 +163,7 @@ struct LnBwdArgs {
   const float* scale = nullptr;
   const bf16* dy = nullptr;      // [M, ldy] gradient wrt the norm output, or null
   long ldy = 0;
-  const float* wb = nullptr;     // [C, H]
+  const float* wb = nullptr;     // [H, C]
   const float* dnb = nullptr;    // [H][M] gradient wrt the bias
   int H = 0, n = 0, transposed = 0;
   const float* g_in = nullptr;   // [M, C] running cotangent or null
@@ -162,56 +175,65 @@ template <int C>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(LnBwdArgs a) {
   using R = RowVec<C>;
   const int lane = threadIdx.x & 31;
-  const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (m >= a.M) return;
-  float v[R::VPL], sc[R::VPL], d[R::VPL];
-  load_row_f32<C>(a.x + (long)m * C, lane, v);
+  const int nwarp = gridDim.x * 8;
+  float sc[R::VPL];
   load_row_f32<C>(a.scale, lane, sc);
-  if (a.dy) load_row_bf16<C>(a.dy + (long)m * a.ldy, lane, d);
-  else {
-#pragma unroll
-    for (int i = 0; i < R::VPL; ++i) d[i] = 0.f;
-  }
+  float wbr[LN_MAXH][R::VPL];
   if (a.wb) {
-    const long pos = bias_pos(m, a.n, a.transposed);
-    for (int h = 0; h < a.H; ++h) {
-      const float gb = a.dnb[(long)h * a.M + pos];
 #pragma unroll
-      for (int i = 0; i < R::NV; ++i)
+    for (int h = 0; h < LN_MAXH; ++h)
+      if (h < a.H) load_row_f32<C>(a.wb + (long)h * C, lane, wbr[h]);
+  }
+  for (int m = blockIdx.x * 8 + (threadIdx.x >> 5); m < a.M; m += nwarp) {
+    float v[R::VPL], d[R::VPL];
+    load_row_f32<C>(a.x + (long)m * C, lane, v);
+    if (a.dy) load_row_bf16<C>(a.dy + (long)m * a.ldy, lane, d);
+    else {
 #pragma unroll
-        for (int j = 0; j < R::VEC; ++j) d[i * R::VEC + j] += gb * a.wb[R::idx(lane, i, j) * a.H + h];
+      for (int i = 0; i < R::VPL; ++i) d[i] = 0.f;
     }
-  }
-  float mean, rstd;
-  row_stats<C>(v, mean, rstd);
-  float s1 = 0.f, s2 = 0.f;
+    if (a.wb) {
+      const long pos = bias_pos(m, a.n, a.transposed);
+      const float mine = lane < a.H ? a.dnb[(long)lane * a.M + pos] : 0.f;
 #pragma unroll
-  for (int i = 0; i < R::VPL; ++i) {
-    v[i] = (v[i] - mean) * rstd;  // xhat
-    d[i] *= sc[i];                // dxhat
-    s1 += d[i];
-    s2 += d[i] * v[i];
-  }
-  s1 = warp_sum(s1) * (1.f / C);
-  s2 = warp_sum(s2) * (1.f / C);
-  float g[R::VPL];
-  if (a.g_in) load_row_f32<C>(a.g_in + (long)m * C, lane, g);
-  else {
+      for (int h = 0; h < LN_MAXH; ++h)
+        if (h < a.H) {
+          const float gb = __shfl_sync(0xffffffffu, mine, h);
 #pragma unroll
-    for (int i = 0; i < R::VPL; ++i) g[i] = 0.f;
-  }
+          for (int i = 0; i < R::VPL; ++i) d[i] += gb * wbr[h][i];
+        }
+    }
+    float mean, rstd;
+    row_stats<C>(v, mean, rstd);
+    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-  for (int i = 0; i < R::VPL; ++i) g[i] += rstd * (d[i] - s1 - v[i] * s2);
-  store_row_f32<C>(a.g_out + (long)m * C, lane, g);
+    for (int i = 0; i < R::VPL; ++i) {
+      v[i] = (v[i] - mean) * rstd;  // xhat
+      d[i] *= sc[i];                // dxhat
+      s1 += d[i];
+      s2 += d[i] * v[i];
+    }
+    s1 = warp_sum(s1) * (1.f / C);
+    s2 = warp_sum(s2) * (1.f / C);
+    float g[R::VPL];
+    if (a.g_in) load_row_f32<C>(a.g_in + (long)m * C, lane, g);
+    else {
+#pragma unroll
+      for (int i = 0; i < R::VPL; ++i) g[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < R::VPL; ++i) g[i] += rstd * (d[i] - s1 - v[i] * s2);
+    store_row_f32<C>(a.g_out + (long)m * C, lane, g);
+  }
 }
 
 template <int C>
 inline void ln_fwd(const LnArgs& a, cudaStream_t st) {
-  launch_counter()++; ln_fwd_kernel<C><<<cdiv(a.M, 8), 256, 0, st>>>(a);
+  launch_counter()++; ln_fwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
 }
 template <int C>
 inline void ln_bwd(const LnBwdArgs& a, cudaStream_t st) {
-  launch_counter()++; ln_bwd_kernel<C><<<cdiv(a.M, 8), 256, 0, st>>>(a);
+  launch_counter()++; ln_bwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
 }
 
 // ------------------------------------------------------------------------------------------- centre norm (transposing)
