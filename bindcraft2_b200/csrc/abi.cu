@@ -237,4 +237,72 @@ int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, co
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Attention forward for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the moment they need an attention forward: a custom call that
+// runs inside somebody else's stream capture, a runtime that has already handed all device memory to its own pool
+// (XLA does this by default), or a real-time loop that forbids allocator locks.  The regular path keeps the two
+// by-products of the forward that only a later backward needs (the ungated output and the per-row softmax statistics)
+// in buffers it allocates; this entry point writes them into a fixed array that lives in the library image instead.
+// The array costs kNoAllocBytes of device memory on every GPU that loads the library, for the life of the process.
+constexpr long kNoAllocMaxRowElems = 1L << 20;  // B*N*H*D  (ungated output, bf16)
+constexpr long kNoAllocMaxStats = 1L << 16;     // B*H*N    (two floats each)
+constexpr long kNoAllocBytes = kNoAllocMaxRowElems * 2 + kNoAllocMaxStats * 8;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// `g_noalloc_scratch` is a host-side handle here, not a device address: the address the kernels need comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+static unsigned char* noalloc_scratch_ptr() {
+  static std::mutex mu;
+  static unsigned char* ptrs[64] = {nullptr};
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  BC2_CHECK(dev >= 0 && dev < 64, "device ordinal out of range");
+  std::lock_guard<std::mutex> l(mu);
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    BC2_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    BC2_CHECK(p != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    ptrs[dev] = static_cast<unsigned char*>(p);
+  }
+  return ptrs[dev];
+}
+
+int bc2_attention_fwd_noalloc(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, int64_t B,
+                              int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og) {
+  try {
+    BC2_CHECK(qkvg && og, "null operand");
+    BC2_CHECK(B > 0 && N > 0 && H > 0 && (D == 16 || D == 32), "bad shape (head width must be 16 or 32)");
+    BC2_CHECK(!transposed || B == N, "transposed orientation needs a square [N,N] batch");
+    const long HD = H * D, rows = B * N;
+    BC2_CHECK(rows * HD <= kNoAllocMaxRowElems && B * H * N <= kNoAllocMaxStats,
+              "bc2_attention_fwd_noalloc: B*N*H*D = " + std::to_string(rows * HD) + " (limit " +
+                  std::to_string(kNoAllocMaxRowElems) + ") or B*H*N = " + std::to_string(B * H * N) + " (limit " +
+                  std::to_string(kNoAllocMaxStats) + ") exceeds the built-in scratch; use the allocating path");
+    unsigned char* scratch = noalloc_scratch_ptr();
+    AttnPlan plan;
+    AttnArgs& a = plan.args;
+    a.qkvg = reinterpret_cast<const bf16*>(qkvg);
+    a.ld = 4 * HD;
+    a.row_b = transposed ? 1 : N;
+    a.row_p = transposed ? N : 1;
+    a.B = (int)B; a.N = (int)N; a.H = (int)H; a.D = (int)D;
+    a.bias = bias;
+    a.mask = mask;
+    a.mask_b = transposed ? 1 : N;
+    a.mask_k = transposed ? N : 1;
+    a.o = reinterpret_cast<bf16*>(scratch);                                  // every valid row is overwritten
+    a.lse = reinterpret_cast<float*>(scratch + kNoAllocMaxRowElems * 2);      // likewise: nothing needs clearing
+    a.og = reinterpret_cast<bf16*>(og);
+    plan.rows = rows;
+    attn_prepare(plan, false);
+    attn_fwd(plan, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 }  // extern "C"

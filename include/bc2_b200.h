@@ -102,6 +102,19 @@ int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, co
                        int64_t B, int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og, uint16_t* d_qkvg,
                        float* d_bias, int use_ref);
 
+/* Gated attention forward that allocates nothing.  No counterpart in the reference.
+ * For hosts that cannot allocate device memory when the call is made (inside a stream capture they do not own, after
+ * a framework has claimed the whole device for its pool, in a loop that must not take allocator locks).  Same
+ * operands and result as the forward half of bc2_test_attention: qkvg bf16 [B*N][4*H*D] (q | k | v | sigmoid gate),
+ * bias f32 [H][N][N] indexed (head, key, query) or null, mask f32 [B][N] or null -> og bf16 [B*N][H*D].
+ * The by-products a backward would need (ungated output, row statistics) go to a 2.5 MiB array inside the library
+ * image, present on every GPU that loads the library.  Limits: B*N*H*D <= 2^20 and B*H*N <= 2^16; larger calls fail
+ * with a message and do nothing.  The first call on a device looks the array's address up (make it before any stream
+ * capture).  All calls share the array: two calls that overlap on the GPU race on it; it needs no clearing between
+ * calls because each call overwrites every entry it later reads. */
+int bc2_attention_fwd_noalloc(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, int64_t B,
+                              int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,59 @@
+"""GPU test of the entry point that allocates nothing (collected last on purpose: if it fails under ``-x`` every other
+test has already run).
+
+Some hosts cannot allocate device memory at call time -- a custom call replayed inside a captured stream, a framework
+that has already taken the whole device for its own pool -- so ``bc2_attention_fwd_noalloc`` keeps the forward's
+by-products in an array built into the library.  The test checks its output against the regular (allocating) entry
+point on two calls in a row, the second with different data, since the built-in array is shared between calls."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(seed, B, N, H, D):
+    g = torch.Generator(device='cuda').manual_seed(seed)
+    HD = H * D
+    qkvg = torch.randn(B * N, 4 * HD, device='cuda', generator=g)
+    qkvg[:, :HD] *= D ** -0.5
+    qkvg[:, 3 * HD:] = torch.sigmoid(qkvg[:, 3 * HD:])
+    bias = torch.randn(H, N, N, device='cuda', generator=g)
+    mask = (torch.rand(B, N, device='cuda', generator=g) > 0.2).float()
+    mask[:, 0] = 1
+    d_og = torch.randn(B * N, HD, device='cuda', generator=g).bfloat16()
+    return qkvg.bfloat16(), bias, mask, d_og
+
+
+def _regular(lib, qkvg, bias, mask, d_og, B, N, H, D):
+    from bindcraft2_b200 import _lib
+    HD = H * D
+    og = torch.zeros(B * N, HD, dtype=torch.bfloat16, device='cuda')
+    d_qkvg = torch.zeros(B * N, 4 * HD, dtype=torch.bfloat16, device='cuda')
+    d_bias = torch.zeros(H, N, N, device='cuda')
+    _lib.check(lib.bc2_test_attention(0, qkvg.data_ptr(), bias.data_ptr(), mask.data_ptr(), d_og.data_ptr(), B, N, H, D, 0,
+                                      og.data_ptr(), d_qkvg.data_ptr(), d_bias.data_ptr(), 0))
+    torch.cuda.synchronize()
+    return og
+
+
+def test_no_alloc_forward_matches_regular_entry_twice(lib):
+    from bindcraft2_b200 import _lib
+    B, N, H, D = 48, 160, 4, 32
+    for seed in (1, 2):  # two calls in a row on the shared built-in scratch
+        qkvg, bias, mask, d_og = _inputs(seed, B, N, H, D)
+        want = _regular(lib, qkvg, bias, mask, d_og, B, N, H, D)
+        og = torch.zeros_like(want)
+        _lib.check(lib.bc2_attention_fwd_noalloc(0, qkvg.data_ptr(), bias.data_ptr(), mask.data_ptr(), B, N, H, D, 0,
+                                                 og.data_ptr()))
+        torch.cuda.synchronize()
+        assert lib.bc2_device_status() == 0
+        err = float((og.float() - want.float()).norm() / want.float().norm())
+        assert err < 1e-2, err
+        assert float(want.float().abs().max()) > 0
+
+
+def test_no_alloc_rejects_sizes_beyond_its_scratch(lib):
+    B, N, H, D = 224, 224, 4, 32  # B*N*H*D = 6.4M > 2^20
+    rc = lib.bc2_attention_fwd_noalloc(0, 1, 0, 0, B, N, H, D, 0, 1)  # rejected before any pointer is touched
+    assert rc != 0
+    assert b'exceeds the built-in scratch' in lib.bc2_last_error()
