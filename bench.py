@@ -171,6 +171,20 @@ class ClockSampler:
         return out
 
 
+def max_over_ranks(values, device):
+    """Slowest rank's figure for each entry (every multi-GPU number is the max over ranks); identity on one rank."""
+    if not (torch.distributed.is_available() and torch.distributed.is_initialized()) or torch.distributed.get_world_size() == 1:
+        return [float(v) for v in values]
+    t = torch.tensor(list(values), device=device, dtype=torch.float64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def trajectory_seed(rank: int) -> int:
+    """Replica sharding: rank r designs its own seeded sequence; there is no data exchange between ranks."""
+    return 100 + rank
+
+
 def profile_report(lib):
     buf = ctypes.create_string_buffer(1 << 16)
     lib.bc2_profile_report(buf, len(buf))
@@ -248,7 +262,7 @@ def run_ours(args):
     n, s, depth = args.n_res, args.msa_rows, args.depth
     nb = n * 80 // 224
     wdir = weights_dir_for(depth, rank, world)
-    host = make_inputs(100 + rank, nb, n - nb, s)  # a distinct seeded sequence per GPU
+    host = make_inputs(trajectory_seed(rank), nb, n - nb, s)  # a distinct seeded sequence per GPU
     t = {k: v.to(dev) for k, v in host.items()}
     seed = torch.zeros(2, dtype=torch.int32, device=dev)
     native.stack_prealloc(n, s, depth, wdir)
@@ -312,10 +326,7 @@ def run_ours(args):
     sync_all()
     ms_e2e = f0.elapsed_time(f1) / args.steps
 
-    if world > 1:
-        v = torch.tensor([ms_step, ms_e2e], device=dev, dtype=torch.float64)
-        torch.distributed.all_reduce(v, op=torch.distributed.ReduceOp.MAX)
-        ms_step, ms_e2e = float(v[0]), float(v[1])
+    ms_step, ms_e2e = max_over_ranks([ms_step, ms_e2e], dev)
     if rank != 0:
         if world > 1:
             torch.distributed.destroy_process_group()

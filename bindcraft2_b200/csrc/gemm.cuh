@@ -97,46 +97,59 @@ struct EpiStore {
   const float* rowscale = nullptr;  // optional per-row factor applied last (row masks)
   int M = 0, N = 0;
   static constexpr bool kPaired = false;
+  // Every option is tested once per 32-column chunk, outside the element loops: a run-time branch per element costs
+  // more than the arithmetic it guards.
   __device__ __forceinline__ void operator()(int z, int m, int n0, const float (&v)[32]) const {
     if (m >= M || n0 >= N) return;
-    const float rs = rowscale ? rowscale[m] : 1.f;
-    uint32_t pk[16];
-    uint4 mv[4];
-    if (mul_mode) {
-      const uint4* mp = reinterpret_cast<const uint4*>(mul + (long)m * ldm + n0);
+    float x[32];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) mv[i] = mp[i];
+    for (int j = 0; j < 32; ++j) x[j] = v[j];
+    if (bias) {
+      const float4* bp = reinterpret_cast<const float4*>(bias + n0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 b4 = bp[j];
+        x[4 * j] += b4.x; x[4 * j + 1] += b4.y; x[4 * j + 2] += b4.z; x[4 * j + 3] += b4.w;
+      }
     }
-    const uint32_t* mw = reinterpret_cast<const uint32_t*>(mv);
+    if (act == 1) {
 #pragma unroll
-    for (int j = 0; j < 32; j += 2) {
-      float a = v[j], b = v[j + 1];
-      if (bias) {
-        a += bias[n0 + j];
-        b += bias[n0 + j + 1];
-      }
-      if (act == 1) {
-        a = fmaxf(a, 0.f);
-        b = fmaxf(b, 0.f);
-      } else if (act == 2 && n0 + j >= act_from) {
-        a = sigmoidf_(a);
-        b = sigmoidf_(b);
-      }
-      if (mul_mode) {
-        float2 mm = unpack_bf16(mw[j >> 1]);
-        if (mul_mode == 1) {
-          a *= mm.x;
-          b *= mm.y;
-        } else {
-          a = mm.x > 0.f ? a : 0.f;
-          b = mm.y > 0.f ? b : 0.f;
+      for (int j = 0; j < 32; ++j) x[j] = fmaxf(x[j], 0.f);
+    } else if (act == 2 && n0 >= act_from) {  // act_from is a multiple of 32: a chunk is all-or-nothing
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x[j] = sigmoidf_(x[j]);
+    }
+    if (mul_mode) {
+      uint32_t mw[16];
+      ld_global_v8(mul + (long)m * ldm + n0, *reinterpret_cast<uint32_t(*)[8]>(&mw[0]));
+      ld_global_v8(mul + (long)m * ldm + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&mw[8]));
+      if (mul_mode == 1) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 mm = unpack_bf16(mw[j]);
+          x[2 * j] *= mm.x;
+          x[2 * j + 1] *= mm.y;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 mm = unpack_bf16(mw[j]);
+          x[2 * j] = mm.x > 0.f ? x[2 * j] : 0.f;
+          x[2 * j + 1] = mm.y > 0.f ? x[2 * j + 1] : 0.f;
         }
       }
-      pk[j >> 1] = pack_bf16(a * rs, b * rs);
     }
-    uint4* op = reinterpret_cast<uint4*>(out + (long)z * bso + (long)m * ldo + n0);
+    if (rowscale) {
+      const float rs = rowscale[m];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) op[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+      for (int j = 0; j < 32; ++j) x[j] *= rs;
+    }
+    uint32_t pk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) pk[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
+    bf16* op = out + (long)z * bso + (long)m * ldo + n0;
+    st_global_v8(op, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
+    st_global_v8(op + 16, *reinterpret_cast<uint32_t(*)[8]>(&pk[8]));
   }
 };
 
@@ -154,25 +167,44 @@ struct EpiResidual {
   static constexpr bool kPaired = false;
   __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
     if (m >= M || n0 >= N) return;
-    const float4* rp = reinterpret_cast<const float4*>(res_in + (long)m * ld + n0);
-    float4* wp = reinterpret_cast<float4*>(res_out + (long)m * ld + n0);
-    const uint4* mp = mul ? reinterpret_cast<const uint4*>(mul + (long)m * ldm + n0) : nullptr;
-    uint4* sp = save ? reinterpret_cast<uint4*>(save + (long)m * lds + n0) : nullptr;
+    float x[32];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float x[8];
+    for (int j = 0; j < 32; ++j) x[j] = v[j];
+    uint32_t r[32];  // the residual row segment: issued first so its latency overlaps the arithmetic below
+    const float* rp = res_in + (long)m * ld + n0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) x[j] = v[i * 8 + j] + (bias ? bias[n0 + i * 8 + j] : 0.f);
-      if (sp) sp[i] = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
-      if (mp) {
-        uint4 mm = mp[i];
-        float2 a = unpack_bf16(mm.x), b = unpack_bf16(mm.y), c = unpack_bf16(mm.z), d = unpack_bf16(mm.w);
-        x[0] *= a.x; x[1] *= a.y; x[2] *= b.x; x[3] *= b.y; x[4] *= c.x; x[5] *= c.y; x[6] *= d.x; x[7] *= d.y;
+    for (int q = 0; q < 4; ++q) ld_global_v8(rp + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
+    if (bias) {
+      const float4* bp = reinterpret_cast<const float4*>(bias + n0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 b4 = bp[j];
+        x[4 * j] += b4.x; x[4 * j + 1] += b4.y; x[4 * j + 2] += b4.z; x[4 * j + 3] += b4.w;
       }
-      float4 r0 = rp[2 * i], r1 = rp[2 * i + 1];
-      wp[2 * i] = make_float4(r0.x + x[0], r0.y + x[1], r0.z + x[2], r0.w + x[3]);
-      wp[2 * i + 1] = make_float4(r1.x + x[4], r1.y + x[5], r1.z + x[6], r1.w + x[7]);
     }
+    if (save) {
+      uint32_t pk[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) pk[j] = pack_bf16(x[2 * j], x[2 * j + 1]);
+      st_global_v8(save + (long)m * lds + n0, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
+      st_global_v8(save + (long)m * lds + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&pk[8]));
+    }
+    if (mul) {
+      uint32_t mw[16];
+      ld_global_v8(mul + (long)m * ldm + n0, *reinterpret_cast<uint32_t(*)[8]>(&mw[0]));
+      ld_global_v8(mul + (long)m * ldm + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&mw[8]));
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float2 mm = unpack_bf16(mw[j]);
+        x[2 * j] *= mm.x;
+        x[2 * j + 1] *= mm.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + x[j]);
+    float* wp = res_out + (long)m * ld + n0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) st_global_v8(wp + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
   }
 };
 
@@ -189,59 +221,96 @@ struct EpiProjGate {
   bf16* ab_out = nullptr;         // [CH][M]
   int M = 0, CH = 0;
   static constexpr bool kPaired = true;
-  // n0 = channel index of vp[0] (already includes the tile's channel base)
+  // n0 = channel index of vp[0] (already includes the tile's channel base).  Called by all 32 lanes of a warp (rows
+  // m .. m+31 of one 128-row tile; M is a multiple of 128 for pair tensors, so a warp is never split by the bound).
   __device__ __forceinline__ void operator()(int, int m, int n0, const float (&vp)[32], const float (&vg)[32]) const {
-    if (m >= M || n0 >= CH) return;
-    float mk = mask[m];
-    uint32_t pk[16];
+    const bool valid = m < M && n0 < CH;
+    float g[32], a[32];
+    const float mk = valid ? mask[m] : 0.f;
+    if (valid) {
+      const float4* bg4 = reinterpret_cast<const float4*>(bias_g + n0);
+      const float4* bp4 = reinterpret_cast<const float4*>(bias_p + n0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 bg = bg4[j], bp = bp4[j];
+        g[4 * j] = sigmoidf_(vg[4 * j] + bg.x); g[4 * j + 1] = sigmoidf_(vg[4 * j + 1] + bg.y);
+        g[4 * j + 2] = sigmoidf_(vg[4 * j + 2] + bg.z); g[4 * j + 3] = sigmoidf_(vg[4 * j + 3] + bg.w);
+        a[4 * j] = mk * (vp[4 * j] + bp.x) * g[4 * j]; a[4 * j + 1] = mk * (vp[4 * j + 1] + bp.y) * g[4 * j + 1];
+        a[4 * j + 2] = mk * (vp[4 * j + 2] + bp.z) * g[4 * j + 2]; a[4 * j + 3] = mk * (vp[4 * j + 3] + bp.w) * g[4 * j + 3];
+      }
+      uint32_t pk[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) pk[j] = pack_bf16(g[2 * j], g[2 * j + 1]);
+      st_global_v8(gate_out + (long)m * CH + n0, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
+      st_global_v8(gate_out + (long)m * CH + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&pk[8]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) a[j] = 0.f;
+    }
+    // Channel-major planes: lanes are consecutive positions.  Neighbouring lanes swap one channel of each pair so
+    // that every lane writes a bf16x2 (positions m, m+1 of one channel): half the store instructions.
+    const bool odd = threadIdx.x & 1;
 #pragma unroll
     for (int j = 0; j < 32; j += 2) {
-      float g0 = sigmoidf_(vg[j] + bias_g[n0 + j]), g1 = sigmoidf_(vg[j + 1] + bias_g[n0 + j + 1]);
-      pk[j >> 1] = pack_bf16(g0, g1);
-      float a0 = mk * (vp[j] + bias_p[n0 + j]) * g0, a1 = mk * (vp[j + 1] + bias_p[n0 + j + 1]) * g1;
-      ab_out[(long)(n0 + j) * M + m] = __float2bfloat16(a0);
-      ab_out[(long)(n0 + j + 1) * M + m] = __float2bfloat16(a1);
+      const float send = odd ? a[j] : a[j + 1];
+      const float got = __shfl_xor_sync(0xffffffffu, send, 1);
+      const float lo = odd ? got : a[j], hi = odd ? a[j + 1] : got;  // (position even, position odd)
+      const int ch = n0 + j + (odd ? 1 : 0);
+      if (valid) *reinterpret_cast<uint32_t*>(ab_out + (long)ch * M + (m & ~1)) = pack_bf16(lo, hi);
     }
-    uint4* gp = reinterpret_cast<uint4*>(gate_out + (long)m * CH + n0);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) gp[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
   }
 };
 
 // ------------------------------------------------------------------------------------------- tcgen05 kernel
+// Persistent and warp-specialised: one CTA per SM walks output tiles (tile = blockIdx.x + i * gridDim.x), so the
+// per-tile fixed costs (TMA round trip, MMA, epilogue) of consecutive tiles overlap:
+//   warp 0      TMA producer: keeps a STAGES-deep ring of [128 x 64] A and [BN x 64] B blocks full, across tile borders
+//   warp 1      MMA issuer: tcgen05.mma into one of TWO TMEM accumulators (2 x BN columns), commits free the ring slots
+//   warps 2..9  epilogue: two warps per TMEM lane quarter, each takes every other 32-column chunk of the finished
+//               accumulator while the MMA warp already fills the other one
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_A_BYTES = GEMM_BM * GEMM_BK * 2;
+constexpr int GEMM_THREADS = 320;
 
-template <int BN, int STAGES>
+template <int BN>
+__host__ __device__ constexpr int gemm_stages() {
+  return BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+}
+template <int BN>
 constexpr int gemm_smem_bytes() {
-  return STAGES * (GEMM_A_BYTES + BN * GEMM_BK * 2) + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  return gemm_stages<BN>() * (GEMM_A_BYTES + BN * GEMM_BK * 2) + 1024 /*alignment slack*/ + 512 /*barriers*/;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
-__global__ void __launch_bounds__(192, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb, int K, Epi epi) {
+template <int BN, bool A_MN, bool B_MN, class Epi>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ CUtensorMap tb, int K, int mt, int nt,
+               int total_tiles, Epi epi) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int STAGES = gemm_stages<BN>();
   constexpr int B_BYTES = BN * GEMM_BK * 2;
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * GEMM_A_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* accb = empty + STAGES;
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(accb + 1);
+  uint64_t* acc_full = empty + STAGES;   // [2] accumulator ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;    // [2] accumulator drained (256 arrivals)
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * BN, z = blockIdx.z;
   const int nkb = cdiv(K, GEMM_BK);
-  constexpr uint32_t TCOLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t TCOLS = 2 * BN < 32 ? 32 : 2 * BN;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accb, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 256);
+    }
     fence_barrier_init();
     tma_prefetch_desc(&ta);
     tma_prefetch_desc(&tb);
@@ -254,74 +323,98 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ C
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, SITE_GEMM_EMPTY)) break;
-        mbar_expect_tx(&full[s], GEMM_A_BYTES + B_BYTES);
-        uint8_t* a = sA + s * GEMM_A_BYTES;
-        uint8_t* b = sB + s * B_BYTES;
-        if (!A_MN) {
-          tma_load_3d(a, &ta, &full[s], kb * GEMM_BK, m0, z);
-        } else {
+      int it = 0;  // k-block counter across all of this CTA's tiles
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int n0 = (tile % nt) * BN, m0 = ((tile / nt) % mt) * GEMM_BM, z = tile / (nt * mt);
+        bool ok = true;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          // A wait on the parity of the phase BEFORE the one being waited for returns at once on a fresh barrier:
+          // the first trip round the ring does not block.
+          ok = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, SITE_GEMM_EMPTY);
+          if (!ok) break;
+          mbar_expect_tx(&full[s], GEMM_A_BYTES + B_BYTES);
+          uint8_t* a = sA + s * GEMM_A_BYTES;
+          uint8_t* b = sB + s * B_BYTES;
+          if (!A_MN) {
+            tma_load_3d(a, &ta, &full[s], kb * GEMM_BK, m0, z);
+          } else {
 #pragma unroll
-          for (int h = 0; h < GEMM_BM / 64; ++h) tma_load_3d(a + h * 8192, &ta, &full[s], m0 + h * 64, kb * GEMM_BK, z);
-        }
-        if (!B_MN) {
-          tma_load_3d(b, &tb, &full[s], kb * GEMM_BK, n0, z);
-        } else {
+            for (int h = 0; h < GEMM_BM / 64; ++h) tma_load_3d(a + h * 8192, &ta, &full[s], m0 + h * 64, kb * GEMM_BK, z);
+          }
+          if (!B_MN) {
+            tma_load_3d(b, &tb, &full[s], kb * GEMM_BK, n0, z);
+          } else {
 #pragma unroll
-          for (int h = 0; h < BN / 64; ++h) tma_load_3d(b + h * 8192, &tb, &full[s], n0 + h * 64, kb * GEMM_BK, z);
+            for (int h = 0; h < BN / 64; ++h) tma_load_3d(b + h * 8192, &tb, &full[s], n0 + h * 64, kb * GEMM_BK, z);
+          }
         }
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int it = 0, i = 0;
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % STAGES;
-        ok = mbar_wait(&full[s], (kb / STAGES) & 1, SITE_GEMM_FULL);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++i) {
+        const int buf = i & 1;
+        ok = mbar_wait(&acc_empty[buf], ((i >> 1) & 1) ^ 1, SITE_GEMM_ACC);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a = smem_u32(sA + s * GEMM_A_BYTES), b = smem_u32(sB + s * B_BYTES);
+        const uint32_t tacc = tmem + buf * BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full[s], (it / STAGES) & 1, SITE_GEMM_FULL);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a = smem_u32(sA + s * GEMM_A_BYTES), b = smem_u32(sB + s * B_BYTES);
 #pragma unroll
-        for (int k = 0; k < GEMM_BK / 16; ++k) {
-          // K-major: 8-row groups are 1024 B apart, a 16-element k step is 32 B inside the swizzled row.
-          // MN-major: each 64-wide box is [64 k][128 B]; 8 k-rows per 1024 B atom, boxes 8192 B apart.
-          const uint64_t ad = A_MN ? umma_desc(a + k * 2048, 8192, 1024, 2) : umma_desc(a + k * 32, 16, 1024, 2);
-          const uint64_t bd = B_MN ? umma_desc(b + k * 2048, 8192, 1024, 2) : umma_desc(b + k * 32, 16, 1024, 2);
-          umma_ss(tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            // K-major: 8-row groups are 1024 B apart, a 16-element k step is 32 B inside the swizzled row.
+            // MN-major: each 64-wide box is [64 k][128 B]; 8 k-rows per 1024 B atom, boxes 8192 B apart.
+            const uint64_t ad = A_MN ? umma_desc(a + k * 2048, 8192, 1024, 2) : umma_desc(a + k * 32, 16, 1024, 2);
+            const uint64_t bd = B_MN ? umma_desc(b + k * 2048, 8192, 1024, 2) : umma_desc(b + k * 32, 16, 1024, 2);
+            umma_ss(tacc, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
         }
-        umma_commit(&empty[s]);
+        if (ok) umma_commit(&acc_full[buf]);
       }
-      umma_commit(accb);
     }
   } else {
-    const bool ok = mbar_wait(accb, 0, SITE_GEMM_ACC);
-    tc_fence_after();
-    const int q = warp & 3;
-    const int m = m0 + q * 32 + lane;
-    const uint32_t tbase = tmem + ((uint32_t)(q * 32) << 16);
-    if (ok) {
+    const int e = warp - 2;
+    const int q = warp & 3, half = e >> 2;
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    int i = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++i) {
+      const int tn = tile % nt, n0 = tn * BN, m0 = ((tile / nt) % mt) * GEMM_BM, z = tile / (nt * mt);
+      const int buf = i & 1;
+      if (!mbar_wait(&acc_full[buf], (i >> 1) & 1, SITE_GEMM_ACC)) break;
+      tc_fence_after();
+      const int m = m0 + q * 32 + lane;
+      const uint32_t tbase = tmem + buf * BN + lane_off;
       if constexpr (Epi::kPaired) {
         static_assert(!Epi::kPaired || BN == 256, "paired epilogue needs a 256-wide tile");
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = half; c < 4; c += 2) {
           float vp[32], vg[32];
           tmem_ld32(tbase + c * 32, vp);
           tmem_ld32(tbase + 128 + c * 32, vg);
           tmem_ld_wait();
-          epi(z, m, blockIdx.y * 128 + c * 32, vp, vg);
+          epi(z, m, tn * 128 + c * 32, vp, vg);
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half; c < BN / 32; c += 2) {
           float v[32];
           tmem_ld32(tbase + c * 32, v);
           tmem_ld_wait();
           epi(z, m, n0 + c * 32, v);
         }
       }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
     }
   }
   tc_fence_before();
@@ -413,17 +506,27 @@ inline GemmPlan make_gemm(Operand a, Operand b, int M, int N, int K, int batch =
   return p;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, class Epi>
+inline int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    BC2_CUDA(cudaGetDevice(&dev));
+    BC2_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN, class Epi>
 inline void launch_tc(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
-  constexpr int smem = gemm_smem_bytes<BN, STAGES>();
+  constexpr int smem = gemm_smem_bytes<BN>();
   static bool attr_set = false;
-  auto kern = gemm_tc_kernel<BN, STAGES, A_MN, B_MN, Epi>;
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, Epi>;
   if (!attr_set) {
     BC2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  dim3 grid(cdiv(p.M, GEMM_BM), cdiv(p.N, BN), p.batch);
-  launch_counter()++; kern<<<grid, 192, smem, st>>>(p.ta, p.tb, p.K, epi);
+  const int mt = cdiv(p.M, GEMM_BM), nt = cdiv(p.N, BN), total = mt * nt * p.batch;
+  launch_counter()++; kern<<<std::min(total, sm_count()), GEMM_THREADS, smem, st>>>(p.ta, p.tb, p.K, mt, nt, total, epi);
 }
 
 template <class Epi>
@@ -436,13 +539,6 @@ inline void launch_ref(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
                                              epi);
 }
 
-template <int BN, bool A_MN, bool B_MN, class Epi>
-inline void launch_tc_stages(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
-  const int nkb = cdiv(p.K, GEMM_BK);
-  if (nkb <= 2) launch_tc<BN, 2, A_MN, B_MN, Epi>(p, epi, st);
-  else launch_tc<BN, 4, A_MN, B_MN, Epi>(p, epi, st);
-}
-
 // Dispatch on tile width and operand majorness.  Only the combinations the trunk uses are instantiated.
 template <class Epi>
 inline void run_gemm(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
@@ -453,19 +549,19 @@ inline void run_gemm(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
   const bool am = p.a.mn_major, bm = p.b.mn_major;
   if constexpr (Epi::kPaired) {
     BC2_CHECK(p.bn == 256 && !am && !bm, "paired epilogue: 256-wide K-major tiles only");
-    launch_tc_stages<256, false, false, Epi>(p, epi, st);
+    launch_tc<256, false, false, Epi>(p, epi, st);
   } else {
     if (am || bm) {
       BC2_CHECK(p.bn == 128, "MN-major operands use 128-wide tiles");
-      if (am && bm) launch_tc_stages<128, true, true, Epi>(p, epi, st);
-      else if (am) launch_tc_stages<128, true, false, Epi>(p, epi, st);
-      else launch_tc_stages<128, false, true, Epi>(p, epi, st);
+      if (am && bm) launch_tc<128, true, true, Epi>(p, epi, st);
+      else if (am) launch_tc<128, true, false, Epi>(p, epi, st);
+      else launch_tc<128, false, true, Epi>(p, epi, st);
     } else {
       switch (p.bn) {
-        case 256: launch_tc_stages<256, false, false, Epi>(p, epi, st); break;
-        case 128: launch_tc_stages<128, false, false, Epi>(p, epi, st); break;
-        case 64: launch_tc_stages<64, false, false, Epi>(p, epi, st); break;
-        default: launch_tc_stages<32, false, false, Epi>(p, epi, st); break;
+        case 256: launch_tc<256, false, false, Epi>(p, epi, st); break;
+        case 128: launch_tc<128, false, false, Epi>(p, epi, st); break;
+        case 64: launch_tc<64, false, false, Epi>(p, epi, st); break;
+        default: launch_tc<32, false, false, Epi>(p, epi, st); break;
       }
     }
   }
