@@ -218,15 +218,16 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float4 mk = mk4[i >> 2];
-            const float m4[4] = {mk.x, mk.y, mk.z, mk.w};
+            t[i] += mk.x; t[i + 1] += mk.y; t[i + 2] += mk.z; t[i + 3] += mk.w;
+          }
+          if (bp) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float v = t[i + e] + m4[e];
-              if (bp) v += bp[(long)(i + e) * a.N];
-              v = fminf(fmaxf(v, -kClip), kClip);
-              t[i + e] = v;
-              mpart = fmaxf(mpart, v);
-            }
+            for (int i = 0; i < 32; ++i) t[i] += bp[(long)i * a.N];
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            t[i] = fminf(fmaxf(t[i], -kClip), kClip);
+            mpart = fmaxf(mpart, t[i]);
           }
         } else {
 #pragma unroll
@@ -474,16 +475,35 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
           const int k0 = (kb0 + j) * 128 + c * 32;  // global key index
           uint32_t pk[16], dk[16];
           float dsv[32];
+          // Row and chunk validity are uniform over the 32 keys (N is a multiple of 32) and tested once; the element
+          // loops below are branch-free.
+          const bool chunk_live = qin && k0 < a.N;
+          if (chunk_live) {
+            const float4* mk4 = reinterpret_cast<const float4*>(sMask + kl);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            float t = s[e] + sMask[kl + e];
-            if (brow && k0 + e < a.N) t += brow[(long)(k0 + e) * a.N];
-            const bool kin = k0 + e < a.N;
-            const bool live = qin && kin && (t >= -kClip) && (t <= kClip);
-            t = fminf(fmaxf(t, -kClip), kClip);
-            const float p = (qin && kin) ? exp2f((t - ml.x) * kLog2e) * ml.y : 0.f;
-            s[e] = p;
-            dsv[e] = live ? p * (dp[e] - dl) : 0.f;
+            for (int e = 0; e < 32; e += 4) {
+              const float4 mk = mk4[e >> 2];
+              s[e] += mk.x; s[e + 1] += mk.y; s[e + 2] += mk.z; s[e + 3] += mk.w;
+            }
+            if (brow) {
+              const float* bp = brow + (long)k0 * a.N;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) s[e] += bp[(long)e * a.N];
+            }
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const float t = s[e];
+              const float tc = fminf(fmaxf(t, -kClip), kClip);
+              const float p = exp2f((tc - ml.x) * kLog2e) * ml.y;
+              s[e] = p;
+              dsv[e] = (tc == t) ? p * (dp[e] - dl) : 0.f;  // the clip passes no gradient
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              s[e] = 0.f;
+              dsv[e] = 0.f;
+            }
           }
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
@@ -498,12 +518,11 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
             *reinterpret_cast<uint4*>(pb + sw128_off(r, chunk)) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
             *reinterpret_cast<uint4*>(db + sw128_off(r, chunk)) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
           }
-          if (dbrow) {
+          if (dbrow && chunk_live) {
+            float* dp0 = dbrow + (long)k0 * a.N;
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {  // [h][key][query]: one coalesced 128-byte reduction per warp and key
-              if (k0 + e < a.N)
-                asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dbrow + (long)(k0 + e) * a.N), "f"(dsv[e]) : "memory");
-            }
+            for (int e = 0; e < 32; ++e)  // [h][key][query]: one coalesced 128-byte reduction per warp and key
+              asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dp0 + (long)e * a.N), "f"(dsv[e]) : "memory");
           }
         }
         tc_fence_before();
