@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
           uint32_t pk[4];
 #pragma unroll
           for (int e = 0; e < 8; e += 2) {
-            const float p0 = exp2f((t[i + e] - mnew) * kLog2e), p1 = exp2f((t[i + e + 1] - mnew) * kLog2e);
+            const float p0 = ex2_approx((t[i + e] - mnew) * kLog2e), p1 = ex2_approx((t[i + e + 1] - mnew) * kLog2e);
             lblk += p0 + p1;
             pk[e >> 1] = pack_bf16(p0, p1);
           }
@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
             for (int e = 0; e < 32; ++e) {
               const float t = s[e];
               const float tc = fminf(fmaxf(t, -kClip), kClip);
-              const float p = exp2f((tc - ml.x) * kLog2e) * ml.y;
+              const float p = ex2_approx((tc - ml.x) * kLog2e) * ml.y;
               s[e] = p;
               dsv[e] = (tc == t) ? p * (dp[e] - dl) : 0.f;  // the clip passes no gradient
             }

@@ -126,6 +126,13 @@ __device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&r)[8]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                : "l"(p));
 }
+// 2^x as one MUFU instruction (flush-to-zero; exp2f proper adds range fix-ups the softmax does not need: its
+// arguments are <= 0 and anything below -126 is zero weight either way).
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float sigmoidf_(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -107,7 +107,8 @@ struct Transition {
     b.gb1 = make_gemm(kmaj(S->big, FC), kmaj(b.w1b, FC), M, C, FC);
     w.push_back(b);
   }
-  void forward(int blk, const float* in, float* out, cudaStream_t st) {
+  // tail = false: stop after the ReLU layer (all a backward needs); the second Linear and the residual are skipped.
+  void forward(int blk, const float* in, float* out, cudaStream_t st, bool tail = true) {
     W& b = w[blk];
     const int M = (int)rows, FC = F * C;
     LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = M;
@@ -115,7 +116,7 @@ struct Transition {
     EpiStore e1; e1.out = h; e1.ldo = FC; e1.bias = b.b1; e1.act = 1; e1.M = M; e1.N = FC;
     { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.forward.gemm.g1" : "MsaTransition.forward.gemm.g1", st); run_gemm(b.g1, e1, st); }
     EpiResidual e2; e2.res_in = in; e2.res_out = out; e2.ld = C; e2.bias = b.b2; e2.M = M; e2.N = C;
-    { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.forward.gemm.g2" : "MsaTransition.forward.gemm.g2", st); run_gemm(b.g2, e2, st); }
+    if (tail) { ProfScope ps_(rows > 4096 * 2 ? "PairTransition.forward.gemm.g2" : "MsaTransition.forward.gemm.g2", st); run_gemm(b.g2, e2, st); }
   }
   void backward(int blk, const float* in, float* g, cudaStream_t st) {
     W& b = w[blk];
@@ -579,8 +580,11 @@ struct Opm {
   void backward(int blk, const float* msa_in, const float* g_pair, float* g_msa, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm;
-    { ProfScope ps_("Opm.backward.opm_dleft_kernel", st); launch_counter()++; opm_dleft_kernel<<<dim3(n, S_), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n); }
-    { ProfScope ps_("Opm.backward.opm_dtmp_kernel", st); launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n); }
+    BC2_CUDA(cudaMemsetAsync(dlr, 0, (size_t)Mm * 64 * 4, st));
+    BC2_CUDA(cudaMemsetAsync(dtmp, 0, (size_t)Mm * OPM_C * OPM_F * 4, st));
+    const int zsplit = std::max(1, std::min(7, 1184 / std::max(1, n * S_)));  // enough blocks to fill the SMs
+    { ProfScope ps_("Opm.backward.opm_dleft_kernel", st); launch_counter()++; opm_dleft_kernel<<<dim3(n, S_, zsplit), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dtmp_kernel", st); launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_, zsplit), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n); }
     { ProfScope ps_("Opm.backward.opm_dright_kernel", st); launch_counter()++; opm_dright_kernel<<<Mi, 256, 0, st>>>(dtmp, b.ow, dlr, Mi); }
     { ProfScope ps_("Opm.backward.opm_dlr_store_kernel", st); launch_counter()++; opm_dlr_store_kernel<<<cdiv(Mi * 64, 256), 256, 0, st>>>(dlr, msa_mask, dlr_b, (long)Mi * 64); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;

@@ -69,14 +69,14 @@ opm_out_kernel(const bf16* __restrict__ lr, const float* __restrict__ tmp, const
 // d_left[s,i,c] = sum_{j,f} d_out[i,j,f] tmp[s,j,c,f]      block = (i, s), 8 warps stride over j, lanes over f
 __global__ void __launch_bounds__(256)
 opm_dleft_kernel(const float* __restrict__ g, const float* __restrict__ tmp, const float* __restrict__ msa_mask,
-                 float* __restrict__ dlr /*[S*N][64] fp32, zeroed*/, int S, int N) {
+                 float* __restrict__ dlr /*[S*N][64] fp32, zeroed by the caller*/, int S, int N) {
   __shared__ float red[8][OPM_C];
   const int i = blockIdx.x, s = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float acc[OPM_C];
 #pragma unroll
   for (int c = 0; c < OPM_C; ++c) acc[c] = 0.f;
-  for (int j = warp; j < N; j += 8) {
+  for (int j = warp + 8 * blockIdx.z; j < N; j += 8 * gridDim.z) {
     float nrm = 0.f;
     for (int ss = 0; ss < S; ++ss) nrm += msa_mask[(long)ss * N + i] * msa_mask[(long)ss * N + j];
     const float inv = 1.f / (1e-3f + nrm);
@@ -97,7 +97,7 @@ opm_dleft_kernel(const float* __restrict__ g, const float* __restrict__ tmp, con
   if (threadIdx.x < OPM_C) {
     float v = 0.f;
     for (int w = 0; w < 8; ++w) v += red[w][threadIdx.x];
-    dlr[((long)s * N + i) * 64 + threadIdx.x] = v;
+    atomicAdd(&dlr[((long)s * N + i) * 64 + threadIdx.x], v);  // gridDim.z blocks share a row; dlr starts at zero
   }
 }
 
@@ -111,7 +111,7 @@ opm_dtmp_kernel(const float* __restrict__ g, const bf16* __restrict__ lr, const 
   float acc[OPM_C];
 #pragma unroll
   for (int c = 0; c < OPM_C; ++c) acc[c] = 0.f;
-  for (int i0 = 0; i0 < N; i0 += 32) {
+  for (int i0 = 32 * blockIdx.z; i0 < N; i0 += 32 * gridDim.z) {
     __syncthreads();
     for (int t = threadIdx.x; t < 32 * OPM_C; t += 128) {
       const int ii = t / OPM_C, c = t % OPM_C;
@@ -131,7 +131,8 @@ opm_dtmp_kernel(const float* __restrict__ g, const bf16* __restrict__ lr, const 
     }
   }
 #pragma unroll
-  for (int c = 0; c < OPM_C; ++c) dtmp[(((long)s * N + j) * OPM_C + c) * OPM_F + f] = acc[c];
+  for (int c = 0; c < OPM_C; ++c)  // gridDim.z blocks each hold a slice of the sum over i; dtmp starts at zero
+    atomicAdd(&dtmp[(((long)s * N + j) * OPM_C + c) * OPM_F + f], acc[c]);
 }
 
 // d_right[s,j,e] = sum_{c,f} d_tmp[s,j,c,f] W[c,e,f]       block = (s,j), warp per e-group, lanes over f

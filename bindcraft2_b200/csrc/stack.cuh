@@ -52,6 +52,8 @@ struct EvoStack {
   float* Mx[4] = {nullptr};  // msa stream: input, after row, after col, after transition
   float *pair_mask = nullptr, *msa_mask = nullptr;  // stack-owned copies (stable pointers for the kernels' arguments)
   float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};  // ping-pong block outputs
+  cudaStream_t side = nullptr;  // MSA-track stream (null: everything on the caller's stream)
+  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
   std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
   size_t weight_bytes = 0;
 
@@ -100,36 +102,66 @@ struct EvoStack {
       ptrans.add_block(A, man, p + "pair_transition");
     }
     weight_bytes = A.bytes - before;
+    const char* ns = getenv("BC2_NO_SIDE_STREAM");
+    if (!(ns && ns[0] == '1')) {
+      BC2_CUDA(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+      for (auto& e : ev) BC2_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
     BC2_CUDA(cudaDeviceSynchronize());
   }
+  ~EvoStack() {
+    for (auto& e : ev)
+      if (e) cudaEventDestroy(e);
+    if (side) cudaStreamDestroy(side);
+  }
 
-  // One block.  p_in/m_in are read only; the block output goes to p_out/m_out.
-  void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st) {
+  // Fork/join helpers.  The MSA track (a few dozen kernels over S*N rows, each a handful of CTAs) runs on a side stream
+  // beside the pair track, which owns the machine-filling kernels; the two tracks have disjoint scratch sets.
+  void fork(cudaStream_t from, cudaStream_t to, cudaEvent_t ev) {
+    BC2_CUDA(cudaEventRecord(ev, from));
+    BC2_CUDA(cudaStreamWaitEvent(to, ev, 0));
+  }
+
+  // One block.  p_in/m_in are read only; the block output goes to p_out/m_out.  `tail` = false skips the two
+  // final GEMMs whose results only the next block would read (the replay before a backward does not need them).
+  void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st,
+                     bool tail = true) {
     const unsigned en = module_mask();
     const size_t bp = (size_t)Mp * cfg.Cz * 4, bm = (size_t)Mm * cfg.Cm * 4;
-    auto idp = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, st)); };
-    auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, st)); };
-    if (en & 1) opm.forward(b, m_in, p_in, P[1], st); else idp(p_in, P[1]);
-    if (en & 2) row.forward(b, m_in, Mx[1], P[1], st); else idm(m_in, Mx[1]);
-    if (en & 4) col.forward(b, Mx[1], Mx[2], st); else idm(Mx[1], Mx[2]);
-    if (en & 8) mtrans.forward(b, Mx[2], m_out, st); else idm(Mx[2], m_out);
-    if (en & 16) tmo.forward(b, P[1], P[2], pair_mask, st); else idp(P[1], P[2]);
-    if (en & 32) tmi.forward(b, P[2], P[3], pair_mask, st); else idp(P[2], P[3]);
-    if (en & 64) tas.forward(b, P[3], P[4], st); else idp(P[3], P[4]);
-    if (en & 128) tae.forward(b, P[4], P[5], st); else idp(P[4], P[5]);
-    if (en & 256) ptrans.forward(b, P[5], p_out, st); else idp(P[5], p_out);
+    cudaStream_t ms = side ? side : st;
+    auto idp = [&](const float* a, float* o, cudaStream_t s_) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, s_)); };
+    auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, ms)); };
+    if (side) fork(st, side, ev[0]);
+    if (en & 1) opm.forward(b, m_in, p_in, P[1], ms); else idp(p_in, P[1], ms);
+    if (side) fork(side, st, ev[1]);  // the pair track may start once the outer product mean has produced P[1]
+    if (en & 2) row.forward(b, m_in, Mx[1], P[1], ms); else idm(m_in, Mx[1]);
+    if (en & 4) col.forward(b, Mx[1], Mx[2], ms); else idm(Mx[1], Mx[2]);
+    if (tail || !(en & 8)) {
+      if (en & 8) mtrans.forward(b, Mx[2], m_out, ms); else idm(Mx[2], m_out);
+    } else {
+      mtrans.forward(b, Mx[2], m_out, ms, /*tail=*/false);
+    }
+    if (en & 16) tmo.forward(b, P[1], P[2], pair_mask, st); else idp(P[1], P[2], st);
+    if (en & 32) tmi.forward(b, P[2], P[3], pair_mask, st); else idp(P[2], P[3], st);
+    if (en & 64) tas.forward(b, P[3], P[4], st); else idp(P[3], P[4], st);
+    if (en & 128) tae.forward(b, P[4], P[5], st); else idp(P[4], P[5], st);
+    if (en & 256) ptrans.forward(b, P[5], p_out, st, tail); else if (tail) idp(P[5], p_out, st);
+    if (side) fork(side, st, ev[2]);  // join
   }
   // Needs the module buffers of block b as left by block_forward(b, p_in, m_in, ...).  g_pair/g_msa: cotangents of the
   // block outputs on entry, of the block inputs on return.
   void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
     const unsigned en = module_mask();
+    cudaStream_t ms = side ? side : st;
+    if (side) fork(st, side, ev[0]);
+    if (en & 8) mtrans.backward(b, Mx[2], g_msa, ms);
+    if (en & 4) col.backward(b, Mx[1], g_msa, ms);
     if (en & 256) ptrans.backward(b, P[5], g_pair, st);
     if (en & 128) tae.backward(b, P[4], g_pair, st);
     if (en & 64) tas.backward(b, P[3], g_pair, st);
     if (en & 32) tmi.backward(b, P[2], g_pair, pair_mask, st);
     if (en & 16) tmo.backward(b, P[1], g_pair, pair_mask, st);
-    if (en & 8) mtrans.backward(b, Mx[2], g_msa, st);
-    if (en & 4) col.backward(b, Mx[1], g_msa, st);
+    if (side) fork(side, st, ev[1]);  // the row attention needs both cotangents; from here on one stream
     if (en & 2) row.backward(b, m_in, P[1], g_msa, g_pair, st);
     if (en & 1) opm.backward(b, m_in, g_pair, g_msa, st);
   }
@@ -181,7 +213,7 @@ struct EvoStack {
           (!own_save || keep32.empty()) ? nullptr : reinterpret_cast<const float4*>(keep32[i]),
           reinterpret_cast<float4*>(P[0]), np / 4);
       const float* m_in = msave + (long)i * nm;
-      block_forward(i, P[0], m_in, pp[0], mp[0], st);
+      block_forward(i, P[0], m_in, pp[0], mp[0], st, /*tail=*/false);
       block_backward(i, m_in, dpair, dmsa, st);
     }
   }
