@@ -14,6 +14,9 @@ _vp, _i64, _i32, _cp = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_c
 PROTOTYPES = {
     'bc2_evoformer_fwd': (_i32, [_vp] * 6 + [_i64] * 8 + [_cp] + [_vp] * 4),
     'bc2_evoformer_bwd': (_i32, [_vp] * 8 + [_i64] * 7 + [_cp] + [_vp] * 2),
+    'bc2_template_pair_stack_fwd': (_i32, [_vp] * 4 + [_i64] * 3 + [_cp] + [_vp] * 2),
+    'bc2_template_pair_stack_bwd': (_i32, [_vp] * 5 + [_i64] * 3 + [_cp] + [_vp]),
+    'native_tplstack_prealloc': (_i32, [_i32, _i32, _cp]),
     'native_stack_prealloc': (_i32, [_i32, _i32, _i32, _cp, _i32, _i32, _i32]),
     'native_save_slots_probe': (_i32, [_i32, _i32]),
     'bc2_release_all': (None, []),

@@ -45,6 +45,21 @@ EvoStack* get_stack(int N, int S, int depth, const std::string& dir, bool pair_o
   return p;
 }
 
+using TplKey = std::tuple<int, int, int, std::string>;
+std::map<TplKey, std::unique_ptr<TplStack>> g_tpl;
+
+TplStack* get_tpl(int N, int depth, const std::string& dir) {
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  TplKey k{dev, N, depth, dir};
+  auto it = g_tpl.find(k);
+  if (it != g_tpl.end()) return it->second.get();
+  auto s = std::make_unique<TplStack>(N, depth, dir);
+  TplStack* p = s.get();
+  g_tpl.emplace(k, std::move(s));
+  return p;
+}
+
 }  // namespace
 
 extern "C" {
@@ -99,11 +114,57 @@ int native_stack_prealloc(int N, int S, int depth, const char* weights_dir, int 
   }
 }
 
+int bc2_template_pair_stack_fwd(void* stream, const float* pair, const float* pair_mask, const uint32_t* /*seed*/,
+                                int64_t N, int64_t depth, int64_t /*dropout*/, const char* weights_dir, float* out,
+                                uint16_t* save) {
+  try {
+    BC2_CHECK(pair && pair_mask && out && weights_dir, "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    TplStack* t = get_tpl((int)N, (int)depth, weights_dir);
+    t->forward(pair, pair_mask, out, reinterpret_cast<bf16*>(save), (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_template_pair_stack_bwd(void* stream, const float* ct, const float* pair_mask, const uint16_t* save,
+                                const uint32_t* /*seed*/, int64_t N, int64_t depth, int64_t /*dropout*/,
+                                const char* weights_dir, float* dpair) {
+  try {
+    BC2_CHECK(ct && pair_mask && save && dpair && weights_dir, "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    TplStack* t = get_tpl((int)N, (int)depth, weights_dir);
+    t->backward(ct, pair_mask, reinterpret_cast<const bf16*>(save), dpair, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int native_tplstack_prealloc(int N, int depth, const char* weights_dir) {
+  try {
+    size_t f0 = 0, f1 = 0, tot = 0;
+    BC2_CUDA(cudaMemGetInfo(&f0, &tot));
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    get_tpl(N, depth, weights_dir);
+    BC2_CUDA(cudaMemGetInfo(&f1, &tot));
+    fprintf(stderr, "native: prealloc tplstack N=%d depth=%d took %.2f GB (%.2f of %.2f GB free after)\n", N, depth,
+            (f0 - f1) / 1e9, f1 / 1e9, tot / 1e9);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 int native_save_slots_probe(int depth, int /*n*/) { return depth; }
 
 void bc2_release_all(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
   g_stacks.clear();
+  g_tpl.clear();
 }
 
 const char* bc2_last_error(void) { return t_error.c_str(); }

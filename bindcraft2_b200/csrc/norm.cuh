@@ -133,9 +133,14 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
     for (int h = 0; h < LN_MAXH; ++h)
       if (h < a.H) load_row_f32<C>(a.wb + (long)h * C, lane, wbr[h]);
   }
-  for (int m = blockIdx.x * 8 + (threadIdx.x >> 5); m < a.M; m += nwarp) {
+  int m = blockIdx.x * 8 + (threadIdx.x >> 5);
+  float vn[R::VPL];  // next row, loaded one iteration ahead so two rows are in flight per warp
+  if (m < a.M) load_row_f32<C>(a.x + (long)m * C, lane, vn);
+  for (; m < a.M; m += nwarp) {
     float v[R::VPL];
-    load_row_f32<C>(a.x + (long)m * C, lane, v);
+#pragma unroll
+    for (int i = 0; i < R::VPL; ++i) v[i] = vn[i];
+    if (m + nwarp < a.M) load_row_f32<C>(a.x + (long)(m + nwarp) * C, lane, vn);
     float mean, rstd;
     row_stats<C>(v, mean, rstd);
 #pragma unroll
@@ -184,14 +189,25 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(LnBwdArgs a) {
     for (int h = 0; h < LN_MAXH; ++h)
       if (h < a.H) load_row_f32<C>(a.wb + (long)h * C, lane, wbr[h]);
   }
-  for (int m = blockIdx.x * 8 + (threadIdx.x >> 5); m < a.M; m += nwarp) {
-    float v[R::VPL], d[R::VPL];
-    load_row_f32<C>(a.x + (long)m * C, lane, v);
-    if (a.dy) load_row_bf16<C>(a.dy + (long)m * a.ldy, lane, d);
-    else {
+  int m = blockIdx.x * 8 + (threadIdx.x >> 5);
+  float vn[R::VPL], dn[R::VPL], gn[R::VPL];  // next row's operands, loaded one iteration ahead
+  auto load_next = [&](int mm) {
+    load_row_f32<C>(a.x + (long)mm * C, lane, vn);
+    if (a.dy) load_row_bf16<C>(a.dy + (long)mm * a.ldy, lane, dn);
+    if (a.g_in) load_row_f32<C>(a.g_in + (long)mm * C, lane, gn);
+  };
 #pragma unroll
-      for (int i = 0; i < R::VPL; ++i) d[i] = 0.f;
+  for (int i = 0; i < R::VPL; ++i) dn[i] = gn[i] = 0.f;
+  if (m < a.M) load_next(m);
+  for (; m < a.M; m += nwarp) {
+    float v[R::VPL], d[R::VPL], g[R::VPL];
+#pragma unroll
+    for (int i = 0; i < R::VPL; ++i) {
+      v[i] = vn[i];
+      d[i] = dn[i];
+      g[i] = gn[i];
     }
+    if (m + nwarp < a.M) load_next(m + nwarp);
     if (a.wb) {
       const long pos = bias_pos(m, a.n, a.transposed);
       const float mine = lane < a.H ? a.dnb[(long)lane * a.M + pos] : 0.f;
@@ -215,12 +231,6 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(LnBwdArgs a) {
     }
     s1 = warp_sum(s1) * (1.f / C);
     s2 = warp_sum(s2) * (1.f / C);
-    float g[R::VPL];
-    if (a.g_in) load_row_f32<C>(a.g_in + (long)m * C, lane, g);
-    else {
-#pragma unroll
-      for (int i = 0; i < R::VPL; ++i) g[i] = 0.f;
-    }
 #pragma unroll
     for (int i = 0; i < R::VPL; ++i) g[i] += rstd * (d[i] - s1 - v[i] * s2);
     store_row_f32<C>(a.g_out + (long)m * C, lane, g);

@@ -219,4 +219,91 @@ struct EvoStack {
   }
 };
 
+// Template pair stack (reference: TemplateEmbeddingIteration, bindcraft/af/alphafold/model/modules_multimer.py:1008-1077;
+// native handlers TemplatePairStackFwd/Bwd, native/ffi.cu:403-465): `depth` blocks of tri-mul out / in, tri-attn start /
+// end and a pair transition on a 64-channel pair tensor (tri-mul hidden 64, attention 4 x 16, transition x2).
+// The save-set is the stack INPUT in bf16; the backward rebuilds each block's input from it and replays that block.
+struct TplStack {
+  int N = 0, depth = 0;
+  static constexpr int C = 64, HID = 64, H = 4, D = 16, F = 2;
+  DeviceArena A;
+  long Mp = 0;
+  Scratch Sp;
+  Transition ptrans;
+  TriMul tmo, tmi;
+  TriAttn tas, tae;
+  float* P[6] = {nullptr};  // block input and the stream after each of the first four steps
+  float *pair_mask = nullptr, *bo[2] = {nullptr, nullptr};
+
+  TplStack(int n, int depth_, const std::string& weights_dir) : N(n), depth(depth_) {
+    BC2_CHECK(n > 0 && n % 32 == 0, "N must be a positive multiple of 32 (the caller pads and masks)");
+    BC2_CHECK(depth >= 1, "depth must be positive");
+    Mp = (long)n * n;
+    Manifest man = Manifest::load(weights_dir);
+    pair_mask = A.alloc<float>(Mp);
+    Sp.init(A, Mp, C, 4 * HID + C, true, n, H);
+    for (auto& p : P) p = A.alloc<float>(Mp * C);
+    for (auto& p : bo) p = A.alloc<float>(Mp * C);
+    tmo.init(A, &Sp, n, C, HID, true);
+    tmi.init(A, &Sp, n, C, HID, false);
+    tas.init(A, &Sp, n, C, H, D, false, pair_mask);
+    tae.init(A, &Sp, n, C, H, D, true, pair_mask);
+    ptrans.init(A, &Sp, Mp, C, F);
+    for (int b = 0; b < depth; ++b) {
+      const std::string p = "param/block" + std::to_string(b) + "/";
+      tmo.add_block(A, man, p + "triangle_multiplication_outgoing");
+      tmi.add_block(A, man, p + "triangle_multiplication_incoming");
+      tas.add_block(A, man, p + "triangle_attention_starting_node");
+      tae.add_block(A, man, p + "triangle_attention_ending_node");
+      ptrans.add_block(A, man, p + "pair_transition");
+    }
+    BC2_CUDA(cudaDeviceSynchronize());
+  }
+  void block_forward(int b, const float* in, float* out, cudaStream_t st, bool tail = true) {
+    tmo.forward(b, in, P[1], pair_mask, st);
+    tmi.forward(b, P[1], P[2], pair_mask, st);
+    tas.forward(b, P[2], P[3], st);
+    tae.forward(b, P[3], P[4], st);
+    ptrans.forward(b, P[4], out, st, tail);
+  }
+  void block_backward(int b, const float* in, float* g, cudaStream_t st) {
+    ptrans.backward(b, P[4], g, st);
+    tae.backward(b, P[3], g, st);
+    tas.backward(b, P[2], g, st);
+    tmi.backward(b, P[1], g, pair_mask, st);
+    tmo.backward(b, in, g, pair_mask, st);
+  }
+  void forward(const float* pair, const float* pm, float* out, bf16* save, cudaStream_t st) {
+    BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, Mp * 4, cudaMemcpyDeviceToDevice, st));
+    const long np = Mp * C;
+    if (save) cvt_f32_bf16(pair, save, np, st);
+    const float* cur = pair;
+    for (int i = 0; i < depth; ++i) {
+      float* o = i == depth - 1 ? out : bo[i & 1];
+      block_forward(i, cur, o, st);
+      cur = o;
+    }
+  }
+  void backward(const float* ct, const float* pm, const bf16* save, float* dpair, cudaStream_t st) {
+    BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, Mp * 4, cudaMemcpyDeviceToDevice, st));
+    const long np = Mp * C;
+    if (dpair != ct) BC2_CUDA(cudaMemcpyAsync(dpair, ct, np * 4, cudaMemcpyDeviceToDevice, st));
+    for (int i = depth - 1; i >= 0; --i) {
+      // rebuild block i's input from the saved stack input (depth is 2 in the model, so the quadratic replay is one
+      // extra block forward), then replay block i itself to fill the per-module buffers
+      cvt_bf16_f32(save, P[0], np, st);
+      const float* cur = P[0];
+      for (int k = 0; k < i; ++k) {
+        block_forward(k, cur, bo[k & 1], st);
+        cur = bo[k & 1];
+      }
+      float* in = P[5];
+      if (cur != P[0]) BC2_CUDA(cudaMemcpyAsync(in, cur, np * 4, cudaMemcpyDeviceToDevice, st));
+      else in = P[0];
+      block_forward(i, in, bo[i & 1], st, /*tail=*/false);
+      block_backward(i, in, dpair, st);
+    }
+  }
+};
+
 }  // namespace bc2

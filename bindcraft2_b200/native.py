@@ -27,6 +27,7 @@ import torch
 from . import _lib
 
 CZ, CM = 128, 256  # pair / msa channel widths of the main stack (native/block.cuh in the reference)
+CT = 64             # template pair channels (native/tplstack.cuh)
 
 _MAIN = 'alphafold/alphafold_iteration/evoformer/evoformer_iteration'
 
@@ -158,6 +159,61 @@ def evoformer_bwd(ct_pair, ct_msa, pair_mask, msa_mask, psave, msave, seed, *, d
                                          int(own_save), int(opm_first), int(dropout), os.fsencode(weights_dir),
                                          _ptr(dpair), _ptr(dmsa)))
     return dpair, dmsa
+
+
+def template_pair_stack_fwd(pair, pair_mask, seed, *, depth, weights_dir, dropout=0, save=1):
+    """FFI target ``template_pair_stack_fwd`` (reference handler native/ffi.cu:403-430; Python pairing
+    bindcraft/af/native.py:977-1046): (out f32 [N,N,64], save bf16 [N*N*64])."""
+    lib = _lib.load()
+    n = int(pair.shape[0])
+    _check_f32('pair', pair, (n, n, CT))
+    _check_f32('pair_mask', pair_mask, (n, n))
+    if n % 32:
+        raise ValueError('N must be a multiple of 32: pad and mask')
+    out = torch.empty_like(pair)
+    sv = torch.empty((n * n * CT if save else 0,), dtype=torch.bfloat16, device=pair.device)
+    stream = torch.cuda.current_stream(pair.device).cuda_stream
+    with torch.cuda.device(pair.device):
+        _lib.check(lib.bc2_template_pair_stack_fwd(stream, _ptr(pair), _ptr(pair_mask), _ptr(seed), n, int(depth),
+                                                   int(dropout), os.fsencode(weights_dir), _ptr(out),
+                                                   _ptr(sv) if save else 0))
+    return out, sv
+
+
+def template_pair_stack_bwd(ct, pair_mask, save, seed, *, depth, weights_dir, dropout=0):
+    """FFI target ``template_pair_stack_bwd`` (reference handler native/ffi.cu:432-465): dpair f32 [N,N,64]."""
+    lib = _lib.load()
+    n = int(ct.shape[0])
+    _check_f32('ct', ct, (n, n, CT))
+    if save.dtype != torch.bfloat16 or save.numel() != n * n * CT:
+        raise ValueError('save does not have the shape the forward declared')
+    dpair = torch.empty_like(ct)
+    stream = torch.cuda.current_stream(ct.device).cuda_stream
+    with torch.cuda.device(ct.device):
+        _lib.check(lib.bc2_template_pair_stack_bwd(stream, _ptr(ct), _ptr(pair_mask), _ptr(save), _ptr(seed), n,
+                                                   int(depth), int(dropout), os.fsencode(weights_dir), _ptr(dpair)))
+    return dpair
+
+
+def make_template_stack(weights_dir: str, depth: int = 2, dropout: bool = False):
+    """(pair, pair_mask, seed) -> pair, differentiable in pair: the autograd pairing of the reference's template-stack
+    ``custom_vjp`` (bindcraft/af/native.py:977-1046; residuals = pair_mask, save, seed)."""
+
+    class _Tpl(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, pair, pair_mask, seed):
+            out, sv = template_pair_stack_fwd(pair, pair_mask, seed, depth=depth, weights_dir=weights_dir,
+                                              dropout=int(dropout))
+            ctx.save_for_backward(pair_mask, sv, seed)
+            return out
+
+        @staticmethod
+        def backward(ctx, ct):
+            pair_mask, sv, seed = ctx.saved_tensors
+            return template_pair_stack_bwd(ct.contiguous(), pair_mask, sv, seed, depth=depth, weights_dir=weights_dir,
+                                           dropout=int(dropout)), None, None
+
+    return _Tpl.apply
 
 
 def stack_prealloc(n, s, depth, weights_dir, pair_only=0, opm_first=1, dropout=0) -> None:

@@ -52,6 +52,23 @@ int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, c
  * trace time.  Prints one `native:` line to stderr.  Returns 0 on success. */
 int native_stack_prealloc(int N, int S, int depth, const char* weights_dir, int pair_only, int opm_first, int dropout);
 
+/* Replaces TemplatePairStackFwd / TplFwdImpl (native/ffi.cu:403-430, bound at :983-994), FFI target
+ * `template_pair_stack_fwd`: `depth` template-embedding iterations (tri-mul out/in, tri-attn start/end, pair transition)
+ * on the 64-channel template pair tensor.
+ *   pair f32 [N,N,64], pair_mask f32 [N,N], seed u32 [2]; attrs depth, dropout, weights_dir
+ *   results out f32 [N,N,64], save bf16 [N*N*64] (the stack input, kept for the replay; may be null) */
+int bc2_template_pair_stack_fwd(void* stream, const float* pair, const float* pair_mask, const uint32_t* seed, int64_t N,
+                                int64_t depth, int64_t dropout, const char* weights_dir, float* out, uint16_t* save);
+
+/* Replaces TemplatePairStackBwd / TplBwdImpl (native/ffi.cu:432-465, bound at :996-1007), FFI target
+ * `template_pair_stack_bwd`: ct f32 [N,N,64], pair_mask, save, seed -> dpair f32 [N,N,64]. */
+int bc2_template_pair_stack_bwd(void* stream, const float* ct, const float* pair_mask, const uint16_t* save,
+                                const uint32_t* seed, int64_t N, int64_t depth, int64_t dropout,
+                                const char* weights_dir, float* dpair);
+
+/* Same contract as the reference's native_tplstack_prealloc (native/ffi.cu:886-899). */
+int native_tplstack_prealloc(int N, int depth, const char* weights_dir);
+
 /* Same contract as the reference's native_save_slots_probe (declared for native/stack.cuh:795-808's slot policy,
  * mirrored in bindcraft/af/native.py:1250-1273): number of save-set slots the forward writes for (depth, n).  A B200
  * holds the full set at every supported length, so this is `depth`. */

@@ -237,6 +237,15 @@ def stack_fwd_bwd(p: Params, inp, depth, is_extra_msa=False, opm_first=True, dty
     return dict(msa=m_out.detach(), pair=p_out.detach(), d_msa=d_msa, d_pair=d_pair)
 
 
+def template_stack_fwd_bwd(p: Params, pair, pair_mask, ct, depth, dtype=torch.float32):
+    """Forward and input gradient of the template pair stack for cotangent ``ct``."""
+    pp = {k: v.to(dtype) for k, v in p.items()}
+    x = pair.to(dtype).clone().requires_grad_(True)
+    out = template_pair_stack(pp, x, pair_mask.to(dtype), depth)
+    (g,) = torch.autograd.grad((out * ct.to(dtype)).sum(), [x])
+    return dict(pair=out.detach(), d_pair=g)
+
+
 # ----------------------------------------------------------------------------- bf16-operand floor
 class _RoundBf16(torch.autograd.Function):
     """Rounds to bfloat16 in the forward and rounds the gradient in the backward."""

@@ -1,0 +1,57 @@
+"""GPU parity of the template pair stack (64-channel pair tensor, tri-mul hidden 64, attention 4 x 16, transition x2)
+through the C ABI against the CPU oracle; same tolerance policy as tests/test_gpu_evoformer.py."""
+import pytest
+import torch
+
+import evoformer_oracle as O
+from bindcraft2_b200 import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(seed, n, masked=0):
+    g = torch.Generator().manual_seed(seed)
+    pair = torch.randn(n, n, 64, generator=g)
+    res = torch.ones(n)
+    if masked:
+        res[n - masked:] = 0
+    return pair, res[:, None] * res[None, :], torch.randn(n, n, 64, generator=g)
+
+
+@pytest.mark.parametrize('n,depth,masked', [(64, 1, 0), (96, 2, 7), (224, 2, 0)])
+def test_template_pair_stack_matches_oracle(lib, tmp_path, n, depth, masked):
+    from bindcraft2_b200 import native
+    params = synthetic.make_template_stack_params(300 + n, depth)
+    pair, mask, ct = _inputs(301 + n, n, masked)
+    wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
+    seed = torch.zeros(2, dtype=torch.int32, device='cuda')
+    out, sv = native.template_pair_stack_fwd(pair.cuda(), mask.cuda(), seed, depth=depth, weights_dir=wdir)
+    dp = native.template_pair_stack_bwd(ct.cuda(), mask.cuda(), sv, seed, depth=depth, weights_dir=wdir)
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    want = O.template_stack_fwd_bwd(params, pair, mask, ct, depth)
+    with O.bf16_operands():
+        floor = O.template_stack_fwd_bwd(params, pair, mask, ct, depth)
+    r = n - masked
+    c = lambda t: t[:r, :r]
+    fwd = O.rel_l2(c(out.cpu()), c(want['pair']))
+    bwd, cos = O.rel_l2(c(dp.cpu()), c(want['d_pair'])), O.cosine(c(dp.cpu()), c(want['d_pair']))
+    f_bwd, f_cos = O.rel_l2(c(floor['d_pair']), c(want['d_pair'])), O.cosine(c(floor['d_pair']), c(want['d_pair']))
+    print(f'template stack N={n} depth={depth}: fwd {fwd:.4f}  bwd {bwd:.4f} cos {cos:.6f}  (bf16 floor {f_bwd:.4f} {f_cos:.6f})')
+    assert fwd <= 2e-2
+    assert bwd <= max(2e-2, 1.3 * f_bwd)
+    assert cos >= min(0.999, 1 - 1.7 * (1 - f_cos))
+
+
+def test_template_stack_autograd(lib, tmp_path):
+    from bindcraft2_b200 import native
+    params = synthetic.make_template_stack_params(310, 2)
+    pair, mask, ct = _inputs(311, 64)
+    wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
+    fn = native.make_template_stack(wdir, depth=2)
+    x = pair.cuda().requires_grad_(True)
+    out = fn(x, mask.cuda(), torch.zeros(2, dtype=torch.int32, device='cuda'))
+    (out * ct.cuda()).sum().backward()
+    want = O.template_stack_fwd_bwd(params, pair, mask, ct, 2)
+    assert O.rel_l2(out.detach().cpu(), want['pair']) <= 2e-2
+    assert O.cosine(x.grad.cpu(), want['d_pair']) >= 0.998
