@@ -163,6 +163,15 @@ inline void attn_bwd_prep(const AttnBwdPrepArgs& a, cudaStream_t st) {
   else throw Error("attn_bwd_prep: unsupported H*D");
 }
 
+// out[m][c] = in[m][c] + v[c]  (fp32 rows of c4*4 channels)
+__global__ void __launch_bounds__(256) add_channel_const_kernel(const float4* __restrict__ in, const float4* __restrict__ v,
+                                                                float4* __restrict__ out, long n4, int c4) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    const float4 x = in[i], y = v[i % c4];
+    out[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+  }
+}
+
 // g_out = g_in + add (fp32), used where a gradient branch lands on an existing cotangent
 __global__ void __launch_bounds__(256) add_f32_kernel(const float4* __restrict__ a, const float4* __restrict__ b,
                                                       float4* __restrict__ o, long n4) {

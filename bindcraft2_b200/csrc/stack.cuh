@@ -52,6 +52,7 @@ struct EvoStack {
   float* Mx[4] = {nullptr};  // msa stream: input, after row, after col, after transition
   float *pair_mask = nullptr, *msa_mask = nullptr;  // stack-owned copies (stable pointers for the kernels' arguments)
   float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};  // ping-pong block outputs
+  std::vector<float*> opm_const;  // pair_only: per-block constant the outer product mean collapses to
   cudaStream_t side = nullptr;  // MSA-track stream (null: everything on the caller's stream)
   cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
   std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
@@ -61,7 +62,6 @@ struct EvoStack {
     BC2_CHECK(c.N > 0 && c.N % 32 == 0, "N must be a positive multiple of 32 (the caller pads and masks)");
     BC2_CHECK(c.S >= 1 && c.S <= 8, "alignment depth S must be in 1..8");
     BC2_CHECK(c.depth >= 1, "depth must be positive");
-    BC2_CHECK(!c.pair_only, "pair_only stacks are not built yet");
     BC2_CHECK(c.opm_first, "only the multimer block order (outer product mean first) is built");
     const int N = c.N, S = c.S;
     Mp = (long)N * N;
@@ -79,10 +79,12 @@ struct EvoStack {
       pp[i] = A.alloc<float>(Mp * c.Cz);
       mp[i] = A.alloc<float>(Mm * c.Cm);
     }
-    opm.init(A, &Sm, N, S, c.Cm, msa_mask);
-    row.init(A, &Sm, N, S, c.Cm, c.Cz, c.msa_heads, msa_mask);
-    col.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
-    mtrans.init(A, &Sm, Mm, c.Cm, c.trans_factor);
+    if (!c.pair_only) {
+      opm.init(A, &Sm, N, S, c.Cm, msa_mask);
+      row.init(A, &Sm, N, S, c.Cm, c.Cz, c.msa_heads, msa_mask);
+      col.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
+      mtrans.init(A, &Sm, Mm, c.Cm, c.trans_factor);
+    }
     tmo.init(A, &Sp, N, c.Cz, c.tri_hidden, true);
     tmi.init(A, &Sp, N, c.Cz, c.tri_hidden, false);
     tas.init(A, &Sp, N, c.Cz, c.tri_heads, c.Cz / c.tri_heads, false, pair_mask);
@@ -91,10 +93,17 @@ struct EvoStack {
     const size_t before = A.bytes;
     for (int b = 0; b < c.depth; ++b) {
       const std::string p = "param/block" + std::to_string(b) + "/";
-      opm.add_block(A, man, p + "outer_product_mean");
-      row.add_block(A, man, p + "msa_row_attention_with_pair_bias");
-      col.add_block(A, man, p + "msa_column_attention");
-      mtrans.add_block(A, man, p + "msa_transition");
+      if (!c.pair_only) {
+        opm.add_block(A, man, p + "outer_product_mean");
+        row.add_block(A, man, p + "msa_row_attention_with_pair_bias");
+        col.add_block(A, man, p + "msa_column_attention");
+        mtrans.add_block(A, man, p + "msa_transition");
+      } else {
+        // a fully masked alignment: left = right = 0 and the norm is 0, so the outer product mean is output_b / 1e-3
+        std::vector<float> ob = man.get(p + "outer_product_mean/output_b").data;
+        for (auto& v : ob) v *= 1000.f;
+        opm_const.push_back(A.upload(ob));
+      }
       tmo.add_block(A, man, p + "triangle_multiplication_outgoing");
       tmi.add_block(A, man, p + "triangle_multiplication_incoming");
       tas.add_block(A, man, p + "triangle_attention_starting_node");
@@ -126,9 +135,24 @@ struct EvoStack {
   // final GEMMs whose results only the next block would read (the replay before a backward does not need them).
   void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st,
                      bool tail = true) {
-    const unsigned en = module_mask();
+    const unsigned en = cfg.pair_only ? (module_mask() & 0x1f0u) : module_mask();
     const size_t bp = (size_t)Mp * cfg.Cz * 4, bm = (size_t)Mm * cfg.Cm * 4;
     cudaStream_t ms = side ? side : st;
+    if (cfg.pair_only) {
+      // The reference's extra-MSA path (native/block.cuh `pair_only`; bindcraft/af/native.py:1131-1193): the MSA side is
+      // not run (its mask is all zeros in a design run) and only the constant of the outer product mean reaches the pair.
+      launch_counter()++;
+      add_channel_const_kernel<<<ew_grid(Mp * cfg.Cz / 4, 256), 256, 0, st>>>(
+          reinterpret_cast<const float4*>(p_in), reinterpret_cast<const float4*>(opm_const[b]),
+          reinterpret_cast<float4*>(P[1]), Mp * cfg.Cz / 4, cfg.Cz / 4);
+      if (tail && m_out != m_in) BC2_CUDA(cudaMemcpyAsync(m_out, m_in, bm, cudaMemcpyDeviceToDevice, st));
+      if (en & 16) tmo.forward(b, P[1], P[2], pair_mask, st); else BC2_CUDA(cudaMemcpyAsync(P[2], P[1], bp, cudaMemcpyDeviceToDevice, st));
+      if (en & 32) tmi.forward(b, P[2], P[3], pair_mask, st); else BC2_CUDA(cudaMemcpyAsync(P[3], P[2], bp, cudaMemcpyDeviceToDevice, st));
+      if (en & 64) tas.forward(b, P[3], P[4], st); else BC2_CUDA(cudaMemcpyAsync(P[4], P[3], bp, cudaMemcpyDeviceToDevice, st));
+      if (en & 128) tae.forward(b, P[4], P[5], st); else BC2_CUDA(cudaMemcpyAsync(P[5], P[4], bp, cudaMemcpyDeviceToDevice, st));
+      if (en & 256) ptrans.forward(b, P[5], p_out, st, tail); else if (tail) BC2_CUDA(cudaMemcpyAsync(p_out, P[5], bp, cudaMemcpyDeviceToDevice, st));
+      return;
+    }
     auto idp = [&](const float* a, float* o, cudaStream_t s_) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, s_)); };
     auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, ms)); };
     if (side) fork(st, side, ev[0]);
@@ -151,9 +175,9 @@ struct EvoStack {
   // Needs the module buffers of block b as left by block_forward(b, p_in, m_in, ...).  g_pair/g_msa: cotangents of the
   // block outputs on entry, of the block inputs on return.
   void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
-    const unsigned en = module_mask();
-    cudaStream_t ms = side ? side : st;
-    if (side) fork(st, side, ev[0]);
+    const unsigned en = cfg.pair_only ? (module_mask() & 0x1f0u) : module_mask();
+    cudaStream_t ms = (side && !cfg.pair_only) ? side : st;
+    if (side && !cfg.pair_only) fork(st, side, ev[0]);
     if (en & 8) mtrans.backward(b, Mx[2], g_msa, ms);
     if (en & 4) col.backward(b, Mx[1], g_msa, ms);
     if (en & 256) ptrans.backward(b, P[5], g_pair, st);
@@ -161,7 +185,7 @@ struct EvoStack {
     if (en & 64) tas.backward(b, P[3], g_pair, st);
     if (en & 32) tmi.backward(b, P[2], g_pair, pair_mask, st);
     if (en & 16) tmo.backward(b, P[1], g_pair, pair_mask, st);
-    if (side) fork(side, st, ev[1]);  // the row attention needs both cotangents; from here on one stream
+    if (side && !cfg.pair_only) fork(side, st, ev[1]);  // the row attention needs both cotangents; from here on one stream
     if (en & 2) row.backward(b, m_in, P[1], g_msa, g_pair, st);
     if (en & 1) opm.backward(b, m_in, g_pair, g_msa, st);
   }

@@ -144,6 +144,38 @@ def test_runner_pads_to_32_and_autograd(lib, tmp_path):
     _check(got, want, floor, 'runner')
 
 
+def test_pair_only_extra_msa_path(lib, tmp_path):
+    """pair_only = 1, the way the reference runs the extra-MSA stack (bindcraft/af/native.py:1131-1193): a fully masked
+    alignment, so only the pair track runs and the outer product mean collapses to output_b / 1e-3."""
+    from bindcraft2_b200 import native
+    depth, n = 2, 64
+    params = synthetic.make_evoformer_params(117, depth)
+    inp = synthetic.make_block_inputs(118, n, 1)
+    inp['msa'] = torch.zeros_like(inp['msa'])
+    inp['msa_mask'] = torch.zeros_like(inp['msa_mask'])
+    wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
+    t = {k: v.cuda() for k, v in inp.items()}
+    seed = torch.zeros(2, dtype=torch.int32, device='cuda')
+    kw = dict(depth=depth, weights_dir=wdir, pair_only=1)
+    p, m, psave, msave = native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, save=1, **kw)
+    dp, dm = native.evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, seed, **kw)
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    steps = {'outer_product_mean'} | set(O.STEPS[4:])
+    want = O.stack_fwd_bwd(params, inp, depth, steps=steps)
+    with O.bf16_operands():
+        floor = O.stack_fwd_bwd(params, inp, depth, steps=steps)
+    got = dict(pair=p.cpu(), msa=m.cpu(), d_pair=dp.cpu(), d_msa=dm.cpu())
+    assert torch.equal(got['msa'], inp['msa']) and torch.equal(got['d_msa'], inp['ct_msa'])  # the msa side passes through
+    for k in ('msa', 'd_msa'):
+        got.pop(k), want.pop(k), floor.pop(k)
+    rep = {k: (O.rel_l2(got[k], want[k]), O.cosine(got[k], want[k])) for k in want}
+    flo = {k: (O.rel_l2(floor[k], want[k]), O.cosine(floor[k], want[k])) for k in want}
+    print('pair_only', rep, flo)
+    assert rep['pair'][0] <= REL_L2
+    assert rep['d_pair'][0] <= max(REL_L2, 1.3 * flo['d_pair'][0]) and rep['d_pair'][1] >= min(COSINE, 1 - 1.7 * (1 - flo['d_pair'][1]))
+
+
 def test_bad_arguments_are_reported(lib, tmp_path):
     from bindcraft2_b200 import native
     params = synthetic.make_evoformer_params(114, 1)
