@@ -60,6 +60,20 @@ TplStack* get_tpl(int N, int depth, const std::string& dir) {
   return p;
 }
 
+std::map<TplKey, std::unique_ptr<TplEmbed>> g_tplembed;
+
+TplEmbed* get_tplembed(int N, int depth, const std::string& dir) {
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  TplKey k{dev, N, depth, dir};
+  auto it = g_tplembed.find(k);
+  if (it != g_tplembed.end()) return it->second.get();
+  auto s = std::make_unique<TplEmbed>(N, depth, dir);
+  TplEmbed* p = s.get();
+  g_tplembed.emplace(k, std::move(s));
+  return p;
+}
+
 }  // namespace
 
 extern "C" {
@@ -144,6 +158,47 @@ int bc2_template_pair_stack_bwd(void* stream, const float* ct, const float* pair
   }
 }
 
+int bc2_template_embedding_fwd(void* stream, const float* query, const float* act_const, const float* pair_mask,
+                               const uint32_t* /*seed*/, int64_t N, int64_t depth, int64_t /*dropout*/,
+                               const char* weights_dir, float* out, uint16_t* save) {
+  try {
+    BC2_CHECK(query && act_const && pair_mask && out && weights_dir, "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    TplEmbed* t = get_tplembed((int)N, (int)depth, weights_dir);
+    t->forward(query, act_const, pair_mask, out, reinterpret_cast<bf16*>(save), (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_template_embedding_bwd(void* stream, const float* ct, const float* query, const float* act_const,
+                               const float* pair_mask, const uint16_t* /*save*/, const uint32_t* /*seed*/, int64_t N,
+                               int64_t depth, int64_t /*dropout*/, const char* weights_dir, float* dquery) {
+  try {
+    BC2_CHECK(ct && query && act_const && pair_mask && dquery && weights_dir, "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    TplEmbed* t = get_tplembed((int)N, (int)depth, weights_dir);
+    t->backward(ct, query, act_const, pair_mask, dquery, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int native_tplembed_prealloc(int N, int depth, const char* weights_dir) {
+  try {
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    get_tplembed(N, depth, weights_dir);
+    fprintf(stderr, "native: prealloc tplembed N=%d depth=%d\n", N, depth);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 int native_tplstack_prealloc(int N, int depth, const char* weights_dir) {
   try {
     size_t f0 = 0, f1 = 0, tot = 0;
@@ -165,6 +220,7 @@ void bc2_release_all(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
   g_stacks.clear();
   g_tpl.clear();
+  g_tplembed.clear();
 }
 
 const char* bc2_last_error(void) { return t_error.c_str(); }

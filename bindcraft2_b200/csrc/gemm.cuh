@@ -171,9 +171,14 @@ struct EpiResidual {
 #pragma unroll
     for (int j = 0; j < 32; ++j) x[j] = v[j];
     uint32_t r[32];  // the residual row segment: issued first so its latency overlaps the arithmetic below
-    const float* rp = res_in + (long)m * ld + n0;
+    if (res_in) {
+      const float* rp = res_in + (long)m * ld + n0;
 #pragma unroll
-    for (int q = 0; q < 4; ++q) ld_global_v8(rp + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
+      for (int q = 0; q < 4; ++q) ld_global_v8(rp + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
+    } else {  // no residual: a plain fp32 store of the value
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;
+    }
     if (bias) {
       const float4* bp = reinterpret_cast<const float4*>(bias + n0);
 #pragma unroll

@@ -113,6 +113,7 @@ struct LnArgs {
   const float* wb = nullptr;    // [H, C] bias projection (head-major) or null
   float* nb = nullptr;          // [H][M]
   int H = 0, n = 0, transposed = 0;
+  int relu = 0;  // y = max(LN(x), 0)
   int M = 0;
 };
 
@@ -145,6 +146,10 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
     row_stats<C>(v, mean, rstd);
 #pragma unroll
     for (int i = 0; i < R::VPL; ++i) v[i] = (v[i] - mean) * rstd * sc[i] + of[i];
+    if (a.relu) {
+#pragma unroll
+      for (int i = 0; i < R::VPL; ++i) v[i] = fmaxf(v[i], 0.f);
+    }
     if (a.y) store_row_bf16<C>(a.y + (long)m * a.ldy, lane, v);
     if (a.wb) {
       const long pos = bias_pos(m, a.n, a.transposed);

@@ -308,14 +308,17 @@ struct TplStack {
       cur = o;
     }
   }
-  void backward(const float* ct, const float* pm, const bf16* save, float* dpair, cudaStream_t st) {
+  // in32: the stack input in fp32 when the caller still has it (then `save` is not read)
+  void backward(const float* ct, const float* pm, const bf16* save, float* dpair, cudaStream_t st,
+                const float* in32 = nullptr) {
     BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, Mp * 4, cudaMemcpyDeviceToDevice, st));
     const long np = Mp * C;
     if (dpair != ct) BC2_CUDA(cudaMemcpyAsync(dpair, ct, np * 4, cudaMemcpyDeviceToDevice, st));
     for (int i = depth - 1; i >= 0; --i) {
       // rebuild block i's input from the saved stack input (depth is 2 in the model, so the quadratic replay is one
       // extra block forward), then replay block i itself to fill the per-module buffers
-      cvt_bf16_f32(save, P[0], np, st);
+      if (in32) BC2_CUDA(cudaMemcpyAsync(P[0], in32, np * 4, cudaMemcpyDeviceToDevice, st));
+      else cvt_bf16_f32(save, P[0], np, st);
       const float* cur = P[0];
       for (int k = 0; k < i; ++k) {
         block_forward(k, cur, bo[k & 1], st);
@@ -327,6 +330,83 @@ struct TplStack {
       block_forward(i, in, bo[i & 1], st, /*tail=*/false);
       block_backward(i, in, dpair, st);
     }
+  }
+};
+
+// Whole template embedding for one template (reference: TemplateEmbedding / SingleTemplateEmbedding,
+// modules_multimer.py:704-1006 with the eight template-only projections hoisted into `act_const`,
+// bindcraft/af/native.py:625-694; native handlers TemplateEmbeddingFwd/Bwd, native/ffi.cu:1071-1098):
+//   act = act_const + Linear_8(LN(query));  act = template_stack(act);  out = Linear_out(relu(LN_out(act)))
+struct TplEmbed {
+  TplStack stack;
+  int N;
+  long M;
+  LnW qn, on;
+  bf16 *w8 = nullptr, *w8_b = nullptr, *wout = nullptr, *wout_b = nullptr;
+  float *b8 = nullptr, *bout = nullptr;
+  bf16 *x128 = nullptr, *y64 = nullptr, *ctb = nullptr, *d64 = nullptr;
+  float *act0 = nullptr, *act1 = nullptr, *g64 = nullptr;
+  GemmPlan g_8, g_out, gb_out, gb_8;
+  static constexpr int CQ = 128, C = TplStack::C;
+
+  TplEmbed(int n, int depth, const std::string& dir) : stack(n, depth, dir), N(n), M((long)n * n) {
+    Manifest man = Manifest::load(dir);
+    DeviceArena& A = stack.A;
+    qn.load(A, man, "param/query_embedding_norm");
+    on.load(A, man, "param/output_layer_norm");
+    const auto& W8 = man.get("param/template_pair_embedding_8/weights");
+    const auto& Wo = man.get("param/output_linear/weights");
+    BC2_CHECK(W8.size() == (long)CQ * C && Wo.size() == (long)C * CQ, "template embedding weight shapes");
+    w8 = A.upload_bf16(transpose_io(W8.data, CQ, C));
+    w8_b = A.upload_bf16(W8.data);
+    wout = A.upload_bf16(transpose_io(Wo.data, C, CQ));
+    wout_b = A.upload_bf16(Wo.data);
+    b8 = A.upload(man.get("param/template_pair_embedding_8/bias").data);
+    bout = A.upload(man.get("param/output_linear/bias").data);
+    x128 = A.alloc<bf16>(M * CQ);
+    ctb = A.alloc<bf16>(M * CQ);
+    y64 = A.alloc<bf16>(M * C);
+    d64 = A.alloc<bf16>(M * C);
+    act0 = A.alloc<float>(M * C);
+    act1 = A.alloc<float>(M * C);
+    g64 = A.alloc<float>(M * C);
+    g_8 = make_gemm(kmaj(x128, CQ), kmaj(w8, CQ), (int)M, C, CQ);
+    g_out = make_gemm(kmaj(y64, C), kmaj(wout, C), (int)M, CQ, C);
+    gb_out = make_gemm(kmaj(ctb, CQ), kmaj(wout_b, CQ), (int)M, C, CQ);
+    gb_8 = make_gemm(kmaj(d64, C), kmaj(w8_b, C), (int)M, CQ, C);
+  }
+  void embed_input(const float* query, const float* act_const, cudaStream_t st) {
+    LnArgs l; l.x = query; l.scale = qn.scale; l.offset = qn.offset; l.y = x128; l.ldy = CQ; l.M = (int)M;
+    ln_fwd<128>(l, st);
+    EpiResidual e; e.res_in = act_const; e.res_out = act0; e.ld = C; e.bias = b8; e.M = (int)M; e.N = C;
+    run_gemm(g_8, e, st);
+  }
+  void forward(const float* query, const float* act_const, const float* pm, float* out, bf16* save, cudaStream_t st) {
+    embed_input(query, act_const, st);
+    stack.forward(act0, pm, act1, save, st);
+    LnArgs l; l.x = act1; l.scale = on.scale; l.offset = on.offset; l.y = y64; l.ldy = C; l.relu = 1; l.M = (int)M;
+    ln_fwd<64>(l, st);
+    EpiResidual e; e.res_in = nullptr; e.res_out = out; e.ld = CQ; e.bias = bout; e.M = (int)M; e.N = CQ;
+    run_gemm(g_out, e, st);
+  }
+  // Pure: everything is rebuilt from the operands (query, act_const); `save` is accepted for the boundary's sake.
+  void backward(const float* ct, const float* query, const float* act_const, const float* pm, float* dquery,
+                cudaStream_t st) {
+    embed_input(query, act_const, st);
+    stack.forward(act0, pm, act1, nullptr, st);
+    LnArgs l; l.x = act1; l.scale = on.scale; l.offset = on.offset; l.y = y64; l.ldy = C; l.relu = 1; l.M = (int)M;
+    ln_fwd<64>(l, st);
+    cvt_f32_bf16(ct, ctb, M * CQ, st);
+    EpiStore e; e.out = d64; e.ldo = C; e.mul = y64; e.ldm = C; e.mul_mode = 2; e.M = (int)M; e.N = C;  // ReLU mask
+    run_gemm(gb_out, e, st);
+    LnBwdArgs lb; lb.x = act1; lb.scale = on.scale; lb.dy = d64; lb.ldy = C; lb.g_in = nullptr; lb.g_out = g64; lb.M = (int)M;
+    ln_bwd<64>(lb, st);
+    stack.backward(g64, pm, nullptr, g64, st, act0);
+    cvt_f32_bf16(g64, d64, M * C, st);
+    EpiStore e2; e2.out = x128; e2.ldo = CQ; e2.M = (int)M; e2.N = CQ;
+    run_gemm(gb_8, e2, st);
+    LnBwdArgs lq; lq.x = query; lq.scale = qn.scale; lq.dy = x128; lq.ldy = CQ; lq.g_in = nullptr; lq.g_out = dquery; lq.M = (int)M;
+    ln_bwd<128>(lq, st);
   }
 };
 

@@ -195,6 +195,36 @@ def template_pair_stack_bwd(ct, pair_mask, save, seed, *, depth, weights_dir, dr
     return dpair
 
 
+def template_embedding_fwd(query, act_const, pair_mask, seed, *, depth, weights_dir, dropout=0):
+    """FFI target ``native_tplembed_fwd`` (reference handler native/ffi.cu:1071-1084): (out f32 [N,N,128], save)."""
+    lib = _lib.load()
+    n = int(query.shape[0])
+    _check_f32('query', query, (n, n, CZ))
+    _check_f32('act_const', act_const, (n, n, CT))
+    _check_f32('pair_mask', pair_mask, (n, n))
+    out = torch.empty_like(query)
+    sv = torch.empty((n * n * CT * 5 * depth,), dtype=torch.bfloat16, device=query.device)  # the reference's shape
+    stream = torch.cuda.current_stream(query.device).cuda_stream
+    with torch.cuda.device(query.device):
+        _lib.check(lib.bc2_template_embedding_fwd(stream, _ptr(query), _ptr(act_const), _ptr(pair_mask), _ptr(seed), n,
+                                                  int(depth), int(dropout), os.fsencode(weights_dir), _ptr(out), _ptr(sv)))
+    return out, sv
+
+
+def template_embedding_bwd(ct, query, act_const, pair_mask, save, seed, *, depth, weights_dir, dropout=0):
+    """FFI target ``native_tplembed_bwd`` (reference handler native/ffi.cu:1085-1098): dquery f32 [N,N,128]."""
+    lib = _lib.load()
+    n = int(ct.shape[0])
+    _check_f32('ct', ct, (n, n, CZ))
+    dq = torch.empty_like(ct)
+    stream = torch.cuda.current_stream(ct.device).cuda_stream
+    with torch.cuda.device(ct.device):
+        _lib.check(lib.bc2_template_embedding_bwd(stream, _ptr(ct), _ptr(query), _ptr(act_const), _ptr(pair_mask),
+                                                  _ptr(save), _ptr(seed), n, int(depth), int(dropout),
+                                                  os.fsencode(weights_dir), _ptr(dq)))
+    return dq
+
+
 def make_template_stack(weights_dir: str, depth: int = 2, dropout: bool = False):
     """(pair, pair_mask, seed) -> pair, differentiable in pair: the autograd pairing of the reference's template-stack
     ``custom_vjp`` (bindcraft/af/native.py:977-1046; residuals = pair_mask, save, seed)."""

@@ -150,6 +150,19 @@ def make_template_stack_params(seed: int, depth: int = 2, ct=64) -> Params:
     return bf16_representable(p)
 
 
+def make_template_embed_params(seed: int, depth: int = 2, cq=128, ct=64) -> Params:
+    """Template embedding weights around the pair stack (manifest names of bindcraft/af/native.py:264-323)."""
+    p = dict(make_template_stack_params(seed, depth, ct))
+    g = torch.Generator().manual_seed(seed + 1000)
+    p['query_embedding_norm/scale'], p['query_embedding_norm/offset'] = _ln(g, cq)
+    p['template_pair_embedding_8/weights'] = _lin(g, cq, (cq, ct), 'relu')
+    p['template_pair_embedding_8/bias'] = 0.02 * torch.randn(ct, generator=g)
+    p['output_layer_norm/scale'], p['output_layer_norm/offset'] = _ln(g, ct)
+    p['output_linear/weights'] = _lin(g, ct, (ct, cq), 'relu')
+    p['output_linear/bias'] = 0.02 * torch.randn(cq, generator=g)
+    return bf16_representable(p)
+
+
 def make_block_inputs(seed: int, n: int, s: int, cm=256, cz=128, scale=1.0, shift=0.0, masked=0):
     """Seeded activations, masks and cotangents for one stack call.  ``masked`` trailing residues are
     masked out (the reference pads to a multiple of 32 and masks the pad, bindcraft/af/native.py:927-972)."""

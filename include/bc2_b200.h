@@ -66,6 +66,26 @@ int bc2_template_pair_stack_bwd(void* stream, const float* ct, const float* pair
                                 const uint32_t* seed, int64_t N, int64_t depth, int64_t dropout,
                                 const char* weights_dir, float* dpair);
 
+/* Replaces TemplateEmbeddingFwd / TeFwdImpl (native/ffi.cu:1071-1084; Python pairing bindcraft/af/native.py:1049-1128),
+ * FFI target `native_tplembed_fwd`: the whole template embedding for one template with the eight template-only input
+ * projections hoisted into act_const:  out = Linear_out(relu(LN_out(stack(act_const + Linear_8(LN(query)))))).
+ *   query f32 [N,N,128], act_const f32 [N,N,64], pair_mask f32 [N,N], seed u32 [2]; attrs depth, dropout, weights_dir
+ *   results out f32 [N,N,128], save bf16 (the reference declares [N*N*64*5*depth]; only the first N*N*64 entries are
+ *   written here, with the stack input; may be null) */
+int bc2_template_embedding_fwd(void* stream, const float* query, const float* act_const, const float* pair_mask,
+                               const uint32_t* seed, int64_t N, int64_t depth, int64_t dropout, const char* weights_dir,
+                               float* out, uint16_t* save);
+
+/* Replaces TemplateEmbeddingBwd / TeBwdImpl (native/ffi.cu:1085-1098), FFI target `native_tplembed_bwd`:
+ * ct f32 [N,N,128], query, act_const, pair_mask, save, seed -> dquery f32 [N,N,128].  As in the reference the backward
+ * replays the forward from its operands; `save` is accepted and not read. */
+int bc2_template_embedding_bwd(void* stream, const float* ct, const float* query, const float* act_const,
+                               const float* pair_mask, const uint16_t* save, const uint32_t* seed, int64_t N,
+                               int64_t depth, int64_t dropout, const char* weights_dir, float* dquery);
+
+/* Same contract as the reference's native_tplembed_prealloc (native/ffi.cu:918-931). */
+int native_tplembed_prealloc(int N, int depth, const char* weights_dir);
+
 /* Same contract as the reference's native_tplstack_prealloc (native/ffi.cu:886-899). */
 int native_tplstack_prealloc(int N, int depth, const char* weights_dir);
 

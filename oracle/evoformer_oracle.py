@@ -237,6 +237,24 @@ def stack_fwd_bwd(p: Params, inp, depth, is_extra_msa=False, opm_first=True, dty
     return dict(msa=m_out.detach(), pair=p_out.detach(), d_msa=d_msa, d_pair=d_pair)
 
 
+def template_embedding(p: Params, query, act_const, pair_mask, depth):
+    """One-template TemplateEmbedding with the eight template-only projections given as ``act_const``
+    (modules_multimer.py:930-956 query_projection, :958-1006 stack + output_layer_norm, :796-809 relu + output_linear)."""
+    q = layer_norm(query, p['query_embedding_norm/scale'], p['query_embedding_norm/offset'])
+    act = act_const + linear(q, p['template_pair_embedding_8/weights'], p['template_pair_embedding_8/bias'])
+    act = template_pair_stack(p, act, pair_mask, depth)
+    act = layer_norm(act, p['output_layer_norm/scale'], p['output_layer_norm/offset'])
+    return linear(torch.relu(act), p['output_linear/weights'], p['output_linear/bias'])
+
+
+def template_embedding_fwd_bwd(p: Params, query, act_const, pair_mask, ct, depth, dtype=torch.float32):
+    pp = {k: v.to(dtype) for k, v in p.items()}
+    x = query.to(dtype).clone().requires_grad_(True)
+    out = template_embedding(pp, x, act_const.to(dtype), pair_mask.to(dtype), depth)
+    (g,) = torch.autograd.grad((out * ct.to(dtype)).sum(), [x])
+    return dict(out=out.detach(), d_query=g)
+
+
 def template_stack_fwd_bwd(p: Params, pair, pair_mask, ct, depth, dtype=torch.float32):
     """Forward and input gradient of the template pair stack for cotangent ``ct``."""
     pp = {k: v.to(dtype) for k, v in p.items()}

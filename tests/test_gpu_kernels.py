@@ -71,7 +71,8 @@ def _attention_torch(qkvg, bias, mask, d_og, B, N, H, D, transposed):
 
 
 @pytest.mark.parametrize('B,N,H,D,transposed', [(64, 64, 4, 32, 0), (8, 128, 4, 32, 0), (2, 160, 8, 32, 0), (4, 224, 4, 32, 0),
-                                                 (96, 96, 4, 32, 1), (64, 64, 4, 16, 1), (224, 224, 4, 32, 0)])
+                                                 (96, 96, 4, 32, 1), (64, 64, 4, 16, 1), (224, 224, 4, 32, 0),
+                                                 (6, 288, 4, 32, 0), (4, 416, 2, 32, 0)])  # > 256 keys: split backward
 @pytest.mark.parametrize('use_ref', [0, 1])
 def test_attention_fwd_bwd(lib, B, N, H, D, transposed, use_ref):
     from bindcraft2_b200 import _lib

@@ -55,3 +55,38 @@ def test_template_stack_autograd(lib, tmp_path):
     want = O.template_stack_fwd_bwd(params, pair, mask, ct, 2)
     assert O.rel_l2(out.detach().cpu(), want['pair']) <= 2e-2
     assert O.cosine(x.grad.cpu(), want['d_pair']) >= 0.998
+
+
+@pytest.mark.parametrize('n,masked', [(64, 0), (96, 11)])
+def test_template_embedding_matches_oracle(lib, tmp_path, n, masked):
+    """Whole template embedding (query norm + projection + act_const, stack, output norm, ReLU, output Linear)."""
+    from bindcraft2_b200 import native
+    depth = 2
+    params = synthetic.make_template_embed_params(320 + n, depth)
+    g = torch.Generator().manual_seed(321 + n)
+    query = torch.randn(n, n, 128, generator=g)
+    act_const = torch.randn(n, n, 64, generator=g)
+    ct = torch.randn(n, n, 128, generator=g)
+    res = torch.ones(n)
+    if masked:
+        res[n - masked:] = 0
+    mask = res[:, None] * res[None, :]
+    wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
+    seed = torch.zeros(2, dtype=torch.int32, device='cuda')
+    out, sv = native.template_embedding_fwd(query.cuda(), act_const.cuda(), mask.cuda(), seed, depth=depth, weights_dir=wdir)
+    dq = native.template_embedding_bwd(ct.cuda(), query.cuda(), act_const.cuda(), mask.cuda(), sv, seed, depth=depth,
+                                       weights_dir=wdir)
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    want = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth)
+    with O.bf16_operands():
+        floor = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth)
+    r = n - masked
+    c = lambda t: t[:r, :r]
+    fwd = O.rel_l2(c(out.cpu()), c(want['out']))
+    bwd, cos = O.rel_l2(c(dq.cpu()), c(want['d_query'])), O.cosine(c(dq.cpu()), c(want['d_query']))
+    f_bwd, f_cos = O.rel_l2(c(floor['d_query']), c(want['d_query'])), O.cosine(c(floor['d_query']), c(want['d_query']))
+    print(f'template embedding N={n}: fwd {fwd:.4f}  bwd {bwd:.4f} cos {cos:.6f}  (bf16 floor {f_bwd:.4f} {f_cos:.6f})')
+    assert fwd <= 2e-2
+    assert bwd <= max(2e-2, 1.3 * f_bwd)
+    assert cos >= min(0.999, 1 - 1.7 * (1 - f_cos))
