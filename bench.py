@@ -257,7 +257,17 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device('cuda', local)
     if world > 1:
-        torch.distributed.init_process_group('nccl', device_id=dev)
+        # the communicator announces its version on stdout: keep stdout for the one JSON line
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            torch.distributed.init_process_group('nccl', device_id=dev)
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
     lib = _lib.load()
     n, s, depth = args.n_res, args.msa_rows, args.depth
     nb = n * 80 // 224
