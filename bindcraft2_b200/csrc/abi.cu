@@ -300,6 +300,22 @@ int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, in
   }
 }
 
+}  // extern "C"
+
+// Test entry helper: the half-precision bias copy the persistent forward reads, plus the rounded fp32 values, from a
+// caller's fp32 [H][key][query] bias.
+__global__ void test_bias_half_kernel(const float* __restrict__ in, float* __restrict__ out32, __half* __restrict__ out16,
+                                      int H, int N) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)H * N * N) return;
+  const int q = (int)(idx % N), k = (int)((idx / N) % N), h = (int)(idx / ((long)N * N));
+  const float v = bc2::bias_round16(in[idx]);
+  out32[idx] = v;
+  out16[(((long)h * (N / 8) + (k >> 3)) * N + q) * 8 + (k & 7)] = __float2half_rn(v);
+}
+
+extern "C" {
+
 int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, const uint16_t* d_og,
                        int64_t B, int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og, uint16_t* d_qkvg,
                        float* d_bias, int use_ref) {
@@ -317,6 +333,14 @@ int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, co
     a.row_p = transposed ? N : 1;
     a.B = (int)B; a.N = (int)N; a.H = (int)H; a.D = (int)D;
     a.bias = bias;
+    if (bias && N % 8 == 0) {  // what the LayerNorm kernels produce in the stack: both arrays hold half-rounded values
+      float* b32 = A.alloc<float>(H * N * N);
+      __half* b16 = A.alloc<__half>(H * N * N);
+      const long tot = H * N * N;
+      test_bias_half_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(bias, b32, b16, (int)H, (int)N);
+      a.bias = b32;
+      a.bias16 = b16;
+    }
     a.mask = mask;
     a.mask_b = transposed ? 1 : N;
     a.mask_k = transposed ? N : 1;

@@ -43,6 +43,8 @@ struct AttnArgs {
   long row_b = 0, row_p = 0;
   int B = 0, N = 0, H = 0, D = 0;
   const float* bias = nullptr;  // [H][N][N] indexed (head, KEY, query), or null
+  const __half* bias16 = nullptr;  // optional copy of the same values as [H][N/8][query][8 keys] halves (the fp32 array then
+                                   // holds the half-rounded values too): enables the persistent forward for N <= 256
   const float* mask = nullptr;  // key mask, element (b, k) at mask[b*mask_b + k*mask_k]
   long mask_b = 0, mask_k = 0;
   bf16* o = nullptr;    // [rows][H*D] ungated output
@@ -317,6 +319,311 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
 inline int attn_fwd_smem(int N, int D) {
   const int nkb = cdiv(N, 128);
   return 1024 + 32768 + 128 * D * 2 * (1 + 2 * nkb) + nkb * 128 * 4 + 768 * 4 + 128;
+}
+
+// ------------------------------------------------------------------------------------------- forward, persistent
+// For N <= 256 keys and a half-precision copy of the bias.  One CTA per SM stays on one (128-query tile, head) and walks
+// batch rows; the bias tile of that (tile, head) is the same for every batch row, so it is read from global memory ONCE
+// into shared memory (as [key/8][query][8 keys] halves: a softmax thread fetches 8 keys of its query row with one
+// conflict-free 128-bit read) instead of once per batch row from L2.  Two independent softmax groups of 256 threads
+// (two threads per query row, as above) each work on their own batch row with their own Q/K/V tiles, TMEM columns,
+// producer warp and MMA warp, so one group's MMA and TMA latencies hide behind the other group's arithmetic; the
+// producer refills Q and K as soon as the last S = Q K^T of an item has finished, V after its last P V.
+//   warps 0,1  TMA producers (group 0,1)     warps 2,3  MMA issuers     warps 4..11 / 12..19  softmax groups
+constexpr int ATTN_P_THREADS = 640;
+constexpr int ATTN_P_BIAS_BYTES = 256 * 128 * 2;
+
+__device__ __forceinline__ bool bar_red_or(int id, int count, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %3, 0;\n\tbarrier.cta.red.or.pred q, %1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(count), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
+
+template <int D>
+__host__ __device__ constexpr int attn_p_group_bytes() { return 32768 + 5 * 128 * D * 2; }  // P, Q, K[2], V[2]
+template <int D>
+constexpr int attn_p_smem() {
+  return 1024 + 2 * attn_p_group_bytes<D>() + ATTN_P_BIAS_BYTES + (512 + 1024 + 512) * 4 + 14 * 8 + 16;
+}
+
+template <int D>
+__global__ void __launch_bounds__(ATTN_P_THREADS, 1)
+attn_fwd_p_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a, int slices) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int TILE = 128 * D * 2;
+  constexpr int DH = D / 2;
+  constexpr int GB = attn_p_group_bytes<D>();
+  const int nkb = cdiv(a.N, 128);  // 1 or 2
+  const int nqt = nkb;
+  uint8_t* sBias = smem + 2 * GB;
+  float* sMask = reinterpret_cast<float*>(sBias + ATTN_P_BIAS_BYTES);  // [2][256] additive key mask of the group's item
+  float* sX = sMask + 512;                                             // [2][2][2][128] partial row maxima
+  float* sL = sX + 1024;                                               // [2][2][128] partial row sums
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sL + 512);              // 7 per group
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 14);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x / slices, slice = blockIdx.x % slices;
+  const int qt = pair % nqt, h = pair / nqt;
+  const int q0 = qt * 128;
+  const int HD = a.H * D;
+  const int bstep = 2 * slices;
+
+  if (threadIdx.x == 0) {
+    for (int g = 0; g < 2; ++g) {
+      uint64_t* bg = bars + 7 * g;
+      mbar_init(bg + 0, 1);    // Q, K landed
+      mbar_init(bg + 1, 1);    // V landed
+      mbar_init(bg + 2, 1);    // last S of the item finished: Q, K reusable
+      mbar_init(bg + 3, 1);    // last P V of the item finished: V reusable
+      mbar_init(bg + 4, 1);    // S block ready in TMEM
+      mbar_init(bg + 5, 256);  // P block written
+      mbar_init(bg + 6, 1);    // O block ready in TMEM
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm);
+  }
+  if (warp == 2) tmem_alloc(tslot, 512);
+  if (a.bias16) {
+    const int nko = a.N / 8;
+    const uint4* src = reinterpret_cast<const uint4*>(a.bias16) + (long)h * nko * a.N;
+    for (int t = threadIdx.x; t < nko * 128; t += ATTN_P_THREADS) {
+      const int ko = t >> 7, r = t & 127;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (q0 + r < a.N) v = src[(long)ko * a.N + q0 + r];
+      reinterpret_cast<uint4*>(sBias)[t] = v;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tslot;
+
+  if (warp < 2) {
+    if (lane == 0) {
+      const int g = warp;
+      uint64_t* bg = bars + 7 * g;
+      uint8_t* sQ = smem + g * GB + 32768;
+      uint8_t* sK = sQ + TILE;
+      uint8_t* sV = sK + 2 * TILE;
+      int it = 0;
+      for (int b = slice * 2 + g; b < a.B; b += bstep, ++it) {
+        if (it > 0 && !mbar_wait(bg + 2, (it - 1) & 1, SITE_ATTN)) break;
+        mbar_expect_tx(bg + 0, TILE * (1 + nkb));
+        tma_load_3d(sQ, &tm, bg + 0, h * D, q0, b);
+        for (int j = 0; j < nkb; ++j) tma_load_3d(sK + j * TILE, &tm, bg + 0, HD + h * D, j * 128, b);
+        if (it > 0 && !mbar_wait(bg + 3, (it - 1) & 1, SITE_ATTN)) break;
+        mbar_expect_tx(bg + 1, TILE * nkb);
+        for (int j = 0; j < nkb; ++j) tma_load_3d(sV + j * TILE, &tm, bg + 1, 2 * HD + h * D, j * 128, b);
+      }
+    }
+  } else if (warp < 4) {
+    if (lane == 0) {
+      const int g = warp - 2;
+      uint64_t* bg = bars + 7 * g;
+      uint8_t* sP = smem + g * GB;
+      uint8_t* sQ = sP + 32768;
+      uint8_t* sK = sQ + TILE;
+      uint8_t* sV = sK + 2 * TILE;
+      const uint32_t tS = tmem + g * 256, tO = tS + 128;
+      constexpr uint32_t idS = umma_idesc(128, 128, 0, 0);
+      constexpr uint32_t idO = umma_idesc(128, D, 0, 1);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      auto issue_s = [&](int j) {
+        const uint32_t aK = smem_u32(sK + j * TILE);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_ss(tS, desc_rows_kmajor<D>(aQ, k), desc_rows_kmajor<D>(aK, k), idS, k > 0 ? 1u : 0u);
+        umma_commit(bg + 4);
+        if (j == nkb - 1) umma_commit(bg + 2);
+      };
+      int it = 0, cnt = 0;
+      bool ok = true;
+      for (int b = slice * 2 + g; b < a.B && ok; b += bstep, ++it) {
+        ok = mbar_wait(bg + 0, it & 1, SITE_ATTN);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(0);
+        for (int j = 0; j < nkb && ok; ++j, ++cnt) {
+          ok = mbar_wait(bg + 5, cnt & 1, SITE_ATTN);
+          if (ok && j == 0) ok = mbar_wait(bg + 1, it & 1, SITE_ATTN);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t aV = smem_u32(sV + j * TILE);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_ss(tO, desc_p_kmajor(aP, k), desc_rows_mnmajor<D>(aV, k), idO, k > 0 ? 1u : 0u);
+          umma_commit(bg + 6);
+          if (j == nkb - 1) umma_commit(bg + 3);
+          if (j + 1 < nkb) issue_s(j + 1);
+        }
+      }
+    }
+  } else {
+    const int g = (warp - 4) >> 3, wl = (warp - 4) & 7;
+    const int qd = warp & 3, half = wl >> 2;
+    const int tid = wl * 32 + lane;
+    const int r = qd * 32 + lane;
+    const int q = q0 + r;
+    const bool qin = q < a.N;
+    uint64_t* bg = bars + 7 * g;
+    uint64_t *b_s = bg + 4, *b_p = bg + 5, *b_o = bg + 6;
+    uint8_t* sP = smem + g * GB;
+    float* gMask = sMask + g * 256;
+    float* gX = sX + g * 512;
+    float* gL = sL + g * 256;
+    const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
+    const uint32_t tS = tmem + g * 256, tO = tS + 128;
+    const bool has_bias = a.bias16 != nullptr;
+    int cnt_s = 0, cnt_o = 0;
+    bool ok = true;
+    for (int b = slice * 2 + g; b < a.B && ok; b += bstep) {
+      float mk0 = 0.f;
+      if (tid < a.N && a.mask) mk0 = 1e9f * (a.mask[(long)b * a.mask_b + (long)tid * a.mask_k] - 1.f);
+      gMask[tid] = mk0;
+      const bool anym = bar_red_or(1 + g, 256, mk0 != 0.f);  // also orders the mask writes before the reads below
+      float mrun = -INFINITY, lsum = 0.f;
+      float acc[DH];
+#pragma unroll
+      for (int i = 0; i < DH; ++i) acc[i] = 0.f;
+      auto fold_output = [&]() {
+        float ob[DH];
+        if constexpr (DH == 16) tmem_ld16(tO + lane_off + half * DH, ob);
+        else tmem_ld8(tO + lane_off + half * DH, ob);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < DH; ++i) acc[i] += ob[i];
+      };
+      for (int j = 0; j < nkb && ok; ++j) {
+        ok = mbar_wait(b_s, cnt_s & 1, SITE_ATTN);
+        ++cnt_s;
+        if (!ok) break;
+        tc_fence_after();
+        float mpart = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          const int k0 = j * 128 + half * 64 + c * 32;  // a 32-key chunk is all real or all padding (N % 32 == 0)
+          float t[32];
+          if (k0 < a.N) {
+            tmem_ld32(tS + lane_off + half * 64 + c * 32, t);
+            tmem_ld_wait();
+            if (anym) {
+              const float4* mk4 = reinterpret_cast<const float4*>(gMask + k0);
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                const float4 mk = mk4[i >> 2];
+                t[i] += mk.x; t[i + 1] += mk.y; t[i + 2] += mk.z; t[i + 3] += mk.w;
+              }
+            }
+            if (has_bias) {
+              const uint4* bp = reinterpret_cast<const uint4*>(sBias) + (k0 >> 3) * 128 + r;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint4 w = bp[i * 128];
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[e]));
+                  t[8 * i + 2 * e] += f.x;
+                  t[8 * i + 2 * e + 1] += f.y;
+                }
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              t[i] = fminf(fmaxf(t[i], -kClip), kClip);
+              mpart = fmaxf(mpart, t[i]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = -INFINITY;
+          }
+          tmem_st32(tS + lane_off + half * 64 + c * 32, t);
+        }
+        tmem_st_wait();
+        float* xb = gX + (j & 1) * 256;
+        xb[half * 128 + r] = mpart;
+        named_barrier(1 + g, 256);
+        const float mblk = fmaxf(mpart, xb[(half ^ 1) * 128 + r]);
+        const float mnew = fmaxf(mrun, mblk);
+        const float alpha = exp2f((mrun - mnew) * kLog2e);
+        if (j > 0) {
+          ok = mbar_wait(b_o, cnt_o & 1, SITE_ATTN);
+          ++cnt_o;
+          if (!ok) break;
+          tc_fence_after();
+          fold_output();
+        }
+        float lblk = 0.f;
+        uint8_t* blk = sP + half * 16384;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          float t[32];
+          tmem_ld32(tS + lane_off + half * 64 + c * 32, t);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const float p0 = ex2_approx((t[i + e] - mnew) * kLog2e), p1 = ex2_approx((t[i + e + 1] - mnew) * kLog2e);
+              lblk += p0 + p1;
+              pk[e >> 1] = pack_bf16(p0, p1);
+            }
+            *reinterpret_cast<uint4*>(blk + sw128_off(r, c * 4 + (i >> 3))) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        }
+        lsum = lsum * alpha + lblk;
+        mrun = mnew;
+#pragma unroll
+        for (int i = 0; i < DH; ++i) acc[i] *= alpha;
+        tc_fence_before();
+        fence_async_smem();
+        mbar_arrive(b_p);
+      }
+      if (!ok) break;
+      // gate values of this thread's half row, fetched while the last P V runs
+      const long row = (long)b * a.row_b + (long)(qin ? q : 0) * a.row_p;
+      const bf16* gp = a.qkvg + row * a.ld + 3 * HD + h * D + half * DH;
+      uint4 g4[DH / 8];
+#pragma unroll
+      for (int i = 0; i < DH / 8; ++i) g4[i] = *reinterpret_cast<const uint4*>(gp + 8 * i);
+      ok = mbar_wait(b_o, cnt_o & 1, SITE_ATTN);
+      ++cnt_o;
+      if (!ok) break;
+      tc_fence_after();
+      fold_output();
+      gL[half * 128 + r] = lsum;
+      named_barrier(1 + g, 256);
+      const float inv = 1.f / (lsum + gL[(half ^ 1) * 128 + r]);
+      if (qin) {
+        bf16* op = a.o + row * HD + h * D + half * DH;
+        bf16* ogp = a.og + row * HD + h * D + half * DH;
+#pragma unroll
+        for (int i = 0; i < DH; i += 8) {
+          const uint32_t gw[4] = {g4[i >> 3].x, g4[i >> 3].y, g4[i >> 3].z, g4[i >> 3].w};
+          uint32_t ow[4], ogw[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float o0 = acc[i + 2 * e] * inv, o1 = acc[i + 2 * e + 1] * inv;
+            const float2 gg = unpack_bf16(gw[e]);
+            ow[e] = pack_bf16(o0, o1);
+            ogw[e] = pack_bf16(o0 * gg.x, o1 * gg.y);
+          }
+          *reinterpret_cast<uint4*>(op + i) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          *reinterpret_cast<uint4*>(ogp + i) = make_uint4(ogw[0], ogw[1], ogw[2], ogw[3]);
+        }
+        if (half == 0) *reinterpret_cast<float2*>(a.lse + 2 * (((long)b * a.H + h) * a.N + q)) = make_float2(mrun, inv);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) tmem_dealloc(tmem, 512);
 }
 
 // ------------------------------------------------------------------------------------------- backward (tcgen05)
@@ -725,6 +1032,20 @@ inline void attn_fwd_launch(const AttnPlan& p, cudaStream_t st) {
 }
 
 template <int D>
+inline void attn_fwd_p_launch(const AttnPlan& p, cudaStream_t st) {
+  const AttnArgs& a = p.args;
+  constexpr int smem = attn_p_smem<D>();
+  static bool set = false;
+  if (!set) {
+    BC2_CUDA(cudaFuncSetAttribute(attn_fwd_p_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    set = true;
+  }
+  const int pairs = cdiv(a.N, 128) * a.H;
+  const int slices = std::max(1, std::min(sm_count() / pairs, cdiv(a.B, 2)));
+  launch_counter()++; attn_fwd_p_kernel<D><<<pairs * slices, ATTN_P_THREADS, smem, st>>>(p.tm, a, slices);
+}
+
+template <int D>
 inline void attn_bwd_launch(const AttnPlan& p, cudaStream_t st) {
   const AttnArgs& a = p.args;
   const int HD = a.H * D;
@@ -752,7 +1073,16 @@ inline void attn_bwd_launch(const AttnPlan& p, cudaStream_t st) {
   }
 }
 
+inline bool attn_fwd_persistent(const AttnPlan& p) {
+  const AttnArgs& a = p.args;
+  return p.tc && a.N <= 256 && (a.bias16 || !a.bias) && getenv("BC2_ATTN_FWD_OLD") == nullptr;
+}
 inline void attn_fwd(const AttnPlan& p, cudaStream_t st) {
+  if (attn_fwd_persistent(p)) {
+    if (p.args.D == 32) attn_fwd_p_launch<32>(p, st);
+    else attn_fwd_p_launch<16>(p, st);
+    return;
+  }
   if (p.args.D == 32) attn_fwd_launch<32>(p, st);
   else attn_fwd_launch<16>(p, st);
 }

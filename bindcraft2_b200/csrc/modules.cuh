@@ -316,6 +316,7 @@ struct TriAttn {
   std::vector<W> w;
   bf16 *qkvg = nullptr, *o = nullptr;
   float *nb = nullptr, *lse = nullptr;
+  __half* nb16 = nullptr;
   AttnPlan plan;
   Scratch* S = nullptr;
 
@@ -327,12 +328,13 @@ struct TriAttn {
     qkvg = A.alloc<bf16>(M * 4 * HD);
     o = A.alloc<bf16>(M * HD);
     nb = A.alloc<float>((long)H * M);
+    nb16 = A.alloc<__half>((long)H * M);
     lse = A.alloc<float>(2L * n * H * n);
     AttnArgs& a = plan.args;
     a.qkvg = qkvg; a.ld = 4 * HD;
     a.row_b = ending ? 1 : n; a.row_p = ending ? n : 1;
     a.B = n; a.N = n; a.H = H; a.D = D;
-    a.bias = nb; a.mask = pair_mask; a.mask_b = ending ? 1 : n; a.mask_k = ending ? n : 1;
+    a.bias = nb; a.bias16 = nb16; a.mask = pair_mask; a.mask_b = ending ? 1 : n; a.mask_k = ending ? n : 1;
     a.o = o; a.og = S->y; a.lse = lse;
     a.d_o = S->d_o; a.delta = S->delta; a.d_qkv = S->big; a.d_bias = S->dnb; a.dq_acc = S->dq_acc;
     plan.rows = M; plan.ref_dkv = S->ref_dkv;
@@ -355,7 +357,7 @@ struct TriAttn {
     W& b = w[blk];
     const int Mi = (int)M, HD = H * D;
     LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = Mi;
-    l.wb = b.wb; l.nb = nb; l.H = H; l.n = n; l.transposed = ending ? 1 : 0;
+    l.wb = b.wb; l.nb = nb; l.nb16 = nb16; l.H = H; l.n = n; l.transposed = ending ? 1 : 0;
     { ProfScope ps_("TriAttn.forward.ln_fwd_c", st); ln_fwd_c(C, l, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
     { ProfScope ps_("TriAttn.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
@@ -395,6 +397,7 @@ struct MsaRow {
   std::vector<W> w;
   bf16 *qkvg = nullptr, *o = nullptr;
   float *nb = nullptr, *lse = nullptr, *dnb = nullptr;
+  __half* nb16 = nullptr;
   AttnPlan plan;
   Scratch* S = nullptr;
 
@@ -405,11 +408,12 @@ struct MsaRow {
     qkvg = A.alloc<bf16>(Mm * 4 * HD);
     o = A.alloc<bf16>(Mm * HD);
     nb = A.alloc<float>((long)H * Mp);
+    nb16 = A.alloc<__half>((long)H * Mp);
     dnb = A.alloc<float>((long)H * Mp);
     lse = A.alloc<float>(2L * S_ * H * n);
     AttnArgs& a = plan.args;
     a.qkvg = qkvg; a.ld = 4 * HD; a.row_b = n; a.row_p = 1; a.B = S_; a.N = n; a.H = H; a.D = D;
-    a.bias = nb; a.mask = msa_mask; a.mask_b = n; a.mask_k = 1;
+    a.bias = nb; a.bias16 = nb16; a.mask = msa_mask; a.mask_b = n; a.mask_k = 1;
     a.o = o; a.og = S->y; a.lse = lse;
     a.d_o = S->d_o; a.delta = S->delta; a.d_qkv = S->big; a.d_bias = dnb; a.dq_acc = S->dq_acc;
     plan.rows = Mm; plan.ref_dkv = S->ref_dkv;
@@ -433,7 +437,7 @@ struct MsaRow {
     const int Mi = (int)Mm, HD = H * D;
     LnArgs l; l.x = msa_in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
     { ProfScope ps_("MsaRow.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
-    LnArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.offset = b.fn.offset; lp.wb = b.wb; lp.nb = nb; lp.H = H; lp.n = n; lp.M = (int)Mp;
+    LnArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.offset = b.fn.offset; lp.wb = b.wb; lp.nb = nb; lp.nb16 = nb16; lp.H = H; lp.n = n; lp.M = (int)Mp;
     { ProfScope ps_("MsaRow.forward.ln_fwd_c", st); ln_fwd_c(Cz, lp, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
     { ProfScope ps_("MsaRow.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
@@ -583,7 +587,9 @@ struct Opm {
     BC2_CUDA(cudaMemsetAsync(dlr, 0, (size_t)Mm * 64 * 4, st));
     BC2_CUDA(cudaMemsetAsync(dtmp, 0, (size_t)Mm * OPM_C * OPM_F * 4, st));
     const int zsplit = std::max(1, std::min(7, 1184 / std::max(1, n * S_)));  // enough blocks to fill the SMs
-    { ProfScope ps_("Opm.backward.opm_dleft_kernel", st); launch_counter()++; opm_dleft_kernel<<<dim3(n, S_, zsplit), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n); }
+    const int ntile = cdiv(n, OPM_IT);
+    const int zleft = std::max(1, std::min(cdiv(n, 8), 1184 / std::max(1, ntile * S_)));
+    { ProfScope ps_("Opm.backward.opm_dleft_kernel", st); launch_counter()++; opm_dleft_kernel<<<dim3(ntile, S_, zleft), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n); }
     { ProfScope ps_("Opm.backward.opm_dtmp_kernel", st); launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_, zsplit), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n); }
     { ProfScope ps_("Opm.backward.opm_dright_kernel", st); launch_counter()++; opm_dright_kernel<<<Mi, 256, 0, st>>>(dtmp, b.ow, dlr, Mi); }
     { ProfScope ps_("Opm.backward.opm_dlr_store_kernel", st); launch_counter()++; opm_dlr_store_kernel<<<cdiv(Mi * 64, 256), 256, 0, st>>>(dlr, msa_mask, dlr_b, (long)Mi * 64); }

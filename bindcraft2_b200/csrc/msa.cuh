@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128)
 opm_out_kernel(const bf16* __restrict__ lr, const float* __restrict__ tmp, const float* __restrict__ bias,
                const float* __restrict__ msa_mask, const float* __restrict__ pair_in, float* __restrict__ pair_out, int S,
                int N) {
-  extern __shared__ float sl[];  // [32][S*32] left tile, then [32] norms
+  extern __shared__ __align__(16) float sl[];  // [32][S*32] left tile, then [32] norms
   const int j = blockIdx.x, i0 = blockIdx.y * 32, f = threadIdx.x;
   const int K = S * OPM_C;
   float* snorm = sl + 32 * K;
@@ -48,11 +48,17 @@ opm_out_kernel(const bf16* __restrict__ lr, const float* __restrict__ tmp, const
   float acc[32];
 #pragma unroll
   for (int ii = 0; ii < 32; ++ii) acc[ii] = 0.f;
-  for (int k = 0; k < K; ++k) {
+  // four k per step: one 128-bit shared-memory broadcast feeds four FMAs (K = 32 S is a multiple of 4)
+  const float4* sl4 = reinterpret_cast<const float4*>(sl);
+  for (int k = 0; k < K; k += 4) {
     const int s = k / OPM_C, c = k % OPM_C;
-    const float t = tmp[(((long)s * N + j) * OPM_C + c) * OPM_F + f];
+    const float* tp = tmp + (((long)s * N + j) * OPM_C + c) * OPM_F + f;
+    const float t0 = tp[0], t1 = tp[OPM_F], t2 = tp[2 * OPM_F], t3 = tp[3 * OPM_F];
 #pragma unroll
-    for (int ii = 0; ii < 32; ++ii) acc[ii] += sl[ii * K + k] * t;
+    for (int ii = 0; ii < 32; ++ii) {
+      const float4 l = sl4[(ii * K + k) >> 2];
+      acc[ii] += l.x * t0 + l.y * t1 + l.z * t2 + l.w * t3;
+    }
   }
   const float b = bias[f];
 #pragma unroll
@@ -66,38 +72,54 @@ opm_out_kernel(const bf16* __restrict__ lr, const float* __restrict__ tmp, const
 }
 
 // Backward.  d_out[i,j,f] = g[i,j,f] / (1e-3 + norm[i,j]).
-// d_left[s,i,c] = sum_{j,f} d_out[i,j,f] tmp[s,j,c,f]      block = (i, s), 8 warps stride over j, lanes over f
+// d_left[s,i,c] = sum_{j,f} d_out[i,j,f] tmp[s,j,c,f]      block = (tile of OPM_IT rows i, s, slice of j); 8 warps stride
+// over j, lanes over f.  Each tmp value read feeds OPM_IT rows, which divides the L2 traffic on tmp by OPM_IT.
+constexpr int OPM_IT = 4;
 __global__ void __launch_bounds__(256)
 opm_dleft_kernel(const float* __restrict__ g, const float* __restrict__ tmp, const float* __restrict__ msa_mask,
                  float* __restrict__ dlr /*[S*N][64] fp32, zeroed by the caller*/, int S, int N) {
-  __shared__ float red[8][OPM_C];
-  const int i = blockIdx.x, s = blockIdx.y;
+  __shared__ float red[8][OPM_IT][OPM_C];
+  const int i0 = blockIdx.x * OPM_IT, s = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float acc[OPM_C];
+  float acc[OPM_IT][OPM_C];
 #pragma unroll
-  for (int c = 0; c < OPM_C; ++c) acc[c] = 0.f;
+  for (int r = 0; r < OPM_IT; ++r)
+#pragma unroll
+    for (int c = 0; c < OPM_C; ++c) acc[r][c] = 0.f;
   for (int j = warp + 8 * blockIdx.z; j < N; j += 8 * gridDim.z) {
-    float nrm = 0.f;
-    for (int ss = 0; ss < S; ++ss) nrm += msa_mask[(long)ss * N + i] * msa_mask[(long)ss * N + j];
-    const float inv = 1.f / (1e-3f + nrm);
-    const float4 d = *reinterpret_cast<const float4*>(g + ((long)i * N + j) * OPM_F + lane * 4);
+    float4 d[OPM_IT];
+#pragma unroll
+    for (int r = 0; r < OPM_IT; ++r) {
+      const int i = min(i0 + r, N - 1);
+      float nrm = 0.f;
+      for (int ss = 0; ss < S; ++ss) nrm += msa_mask[(long)ss * N + i] * msa_mask[(long)ss * N + j];
+      const float inv = (i0 + r < N) ? 1.f / (1e-3f + nrm) : 0.f;
+      d[r] = *reinterpret_cast<const float4*>(g + ((long)i * N + j) * OPM_F + lane * 4);
+      d[r].x *= inv; d[r].y *= inv; d[r].z *= inv; d[r].w *= inv;
+    }
     const float* tp = tmp + ((long)s * N + j) * OPM_C * OPM_F + lane * 4;
 #pragma unroll
     for (int c = 0; c < OPM_C; ++c) {
       const float4 t = *reinterpret_cast<const float4*>(tp + c * OPM_F);
-      acc[c] += inv * (d.x * t.x + d.y * t.y + d.z * t.z + d.w * t.w);
+#pragma unroll
+      for (int r = 0; r < OPM_IT; ++r) acc[r][c] += d[r].x * t.x + d[r].y * t.y + d[r].z * t.z + d[r].w * t.w;
     }
   }
 #pragma unroll
-  for (int c = 0; c < OPM_C; ++c) {
-    const float v = warp_sum(acc[c]);
-    if (lane == 0) red[warp][c] = v;
-  }
+  for (int r = 0; r < OPM_IT; ++r)
+#pragma unroll
+    for (int c = 0; c < OPM_C; ++c) {
+      const float v = warp_sum(acc[r][c]);
+      if (lane == 0) red[warp][r][c] = v;
+    }
   __syncthreads();
-  if (threadIdx.x < OPM_C) {
-    float v = 0.f;
-    for (int w = 0; w < 8; ++w) v += red[w][threadIdx.x];
-    atomicAdd(&dlr[((long)s * N + i) * 64 + threadIdx.x], v);  // gridDim.z blocks share a row; dlr starts at zero
+  if (threadIdx.x < OPM_IT * OPM_C) {
+    const int r = threadIdx.x / OPM_C, c = threadIdx.x % OPM_C;
+    if (i0 + r < N) {
+      float v = 0.f;
+      for (int w = 0; w < 8; ++w) v += red[w][r][c];
+      atomicAdd(&dlr[((long)s * N + i0 + r) * 64 + c], v);  // gridDim.z blocks share a row; dlr starts at zero
+    }
   }
 }
 
@@ -105,7 +127,7 @@ opm_dleft_kernel(const float* __restrict__ g, const float* __restrict__ tmp, con
 __global__ void __launch_bounds__(128)
 opm_dtmp_kernel(const float* __restrict__ g, const bf16* __restrict__ lr, const float* __restrict__ msa_mask,
                 float* __restrict__ dtmp, int S, int N) {
-  __shared__ float sl[32][OPM_C + 1];
+  __shared__ __align__(16) float sl[32][OPM_C + 4];  // rows padded to a multiple of 16 bytes for 128-bit reads
   __shared__ float sinv[32];
   const int j = blockIdx.x, s = blockIdx.y, f = threadIdx.x;
   float acc[OPM_C];
@@ -127,7 +149,10 @@ opm_dtmp_kernel(const float* __restrict__ g, const bf16* __restrict__ lr, const 
     for (int ii = 0; ii < 32 && i0 + ii < N; ++ii) {
       const float d = g[((long)(i0 + ii) * N + j) * OPM_F + f] * sinv[ii];
 #pragma unroll
-      for (int c = 0; c < OPM_C; ++c) acc[c] += sl[ii][c] * d;
+      for (int c = 0; c < OPM_C; c += 4) {
+        const float4 l = *reinterpret_cast<const float4*>(&sl[ii][c]);
+        acc[c] += l.x * d; acc[c + 1] += l.y * d; acc[c + 2] += l.z * d; acc[c + 3] += l.w * d;
+      }
     }
   }
 #pragma unroll

@@ -104,6 +104,18 @@ __device__ __forceinline__ long bias_pos(int m, int n, int transposed) {
   return (long)j * n + i;
 }
 
+// Offset (within one head) of the same entry in the half-precision copy [key/8][query][8 keys].
+__device__ __forceinline__ long bias16_pos(int m, int n, int transposed) {
+  const int i = m / n, j = m - i * n;
+  const int q = transposed ? j : i, k = transposed ? i : j;
+  return ((long)(k >> 3) * n + q) * 8 + (k & 7);
+}
+// Value kept for the attention bias: rounded to half precision (clamped to its finite range) when a half copy is kept,
+// so that every kernel reading either array sees the same number.
+__device__ __forceinline__ float bias_round16(float v) {
+  return __half2float(__float2half_rn(fminf(fmaxf(v, -60000.f), 60000.f)));
+}
+
 struct LnArgs {
   const float* x = nullptr;     // [M, C] fp32
   const float* scale = nullptr; // [C]
@@ -112,6 +124,7 @@ struct LnArgs {
   long ldy = 0;
   const float* wb = nullptr;    // [H, C] bias projection (head-major) or null
   float* nb = nullptr;          // [H][M]
+  __half* nb16 = nullptr;       // optional half copy, [H][n/8][n][8] (see bias16_pos); nb then holds the rounded values
   int H = 0, n = 0, transposed = 0;
   int relu = 0;  // y = max(LN(x), 0)
   int M = 0;
@@ -163,7 +176,13 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
           s = warp_sum(s);
           if (lane == h) mine = s;
         }
-      if (lane < a.H) a.nb[(long)lane * a.M + pos] = mine;
+      if (lane < a.H) {
+        if (a.nb16) {
+          mine = bias_round16(mine);
+          a.nb16[(long)lane * a.M + bias16_pos(m, a.n, a.transposed)] = __float2half_rn(mine);
+        }
+        a.nb[(long)lane * a.M + pos] = mine;
+      }
     }
   }
 }
@@ -242,13 +261,218 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(LnBwdArgs a) {
   }
 }
 
+// ------------------------------------------------------------------------------------------- narrow rows (C <= 128)
+// For C = 64 and 128 a warp per row spends most of its instructions on 5-step reductions over 2..4 values per lane.
+// Here a row belongs to G = C/16 lanes (16 values per lane, 32/G rows per warp): reductions take log2(G) steps and
+// every instruction works on 32/G rows at once.  Lane l of a group owns elements [32*i + 4*l, +4) for i = 0..3, so each
+// 128-bit load of a group covers one full 128-byte line.
+template <int C>
+struct GroupRow {
+  static constexpr int G = C / 16;      // lanes per row
+  static constexpr int RPW = 32 / G;    // rows per warp
+  static constexpr int NV = 4;          // float4 chunks per lane
+  static constexpr int STRIDE = 4 * G;  // elements between a lane's chunks
+};
+
+template <int G>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = G / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int C>
+__device__ __forceinline__ void gload_f32(const float* p, int gl, float (&v)[16]) {
+  using R = GroupRow<C>;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 t = *reinterpret_cast<const float4*>(p + i * R::STRIDE + 4 * gl);
+    v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+  }
+}
+template <int C>
+__device__ __forceinline__ void gstore_f32(float* p, int gl, const float (&v)[16]) {
+  using R = GroupRow<C>;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4*>(p + i * R::STRIDE + 4 * gl) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+template <int C>
+__device__ __forceinline__ void gload_bf16(const bf16* p, int gl, float (&v)[16]) {
+  using R = GroupRow<C>;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p + i * R::STRIDE + 4 * gl);
+    const float2 a = unpack_bf16(t.x), b = unpack_bf16(t.y);
+    v[4 * i] = a.x; v[4 * i + 1] = a.y; v[4 * i + 2] = b.x; v[4 * i + 3] = b.y;
+  }
+}
+template <int C>
+__device__ __forceinline__ void gstore_bf16(bf16* p, int gl, const float (&v)[16]) {
+  using R = GroupRow<C>;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<uint2*>(p + i * R::STRIDE + 4 * gl) =
+        make_uint2(pack_bf16(v[4 * i], v[4 * i + 1]), pack_bf16(v[4 * i + 2], v[4 * i + 3]));
+}
+template <int C>
+__device__ __forceinline__ void group_stats(const float (&v)[16], float& mean, float& rstd) {
+  constexpr int G = GroupRow<C>::G;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += v[i];
+  mean = group_sum<G>(s) * (1.f / C);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float d = v[i] - mean;
+    q += d * d;
+  }
+  rstd = rsqrtf(group_sum<G>(q) * (1.f / C) + 1e-5f);
+}
+
+template <int C>
+__global__ void __launch_bounds__(256) ln_fwd_group_kernel(LnArgs a) {
+  using R = GroupRow<C>;
+  __shared__ float4 s_wb[LN_MAXH * C / 4];  // bias projection, [h][chunk i][group lane]: conflict-free 128-bit reads
+  const int lane = threadIdx.x & 31, gl = lane % R::G, sub = lane / R::G;
+  if (a.wb) {
+    for (int t = threadIdx.x; t < a.H * C / 4; t += blockDim.x) {
+      const int h = t / (C / 4), r = t % (C / 4), i = r / R::G, l = r % R::G;
+      s_wb[t] = *reinterpret_cast<const float4*>(a.wb + (long)h * C + i * R::STRIDE + 4 * l);
+    }
+    __syncthreads();
+  }
+  float sc[16], of[16];
+  gload_f32<C>(a.scale, gl, sc);
+  gload_f32<C>(a.offset, gl, of);
+  const int step = gridDim.x * 8 * R::RPW;
+  // every lane of a warp stays in the loop together (the shuffles below name the full warp); rows past M are clamped
+  for (int mb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * R::RPW; mb < a.M; mb += step) {
+    const int m = mb + sub;
+    const bool live = m < a.M;
+    const int mr = live ? m : a.M - 1;
+    float v[16];
+    gload_f32<C>(a.x + (long)mr * C, gl, v);
+    float mean, rstd;
+    group_stats<C>(v, mean, rstd);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = (v[i] - mean) * rstd * sc[i] + of[i];
+    if (a.relu) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
+    }
+    if (a.y && live) gstore_bf16<C>(a.y + (long)m * a.ldy, gl, v);
+    if (a.wb) {
+      const long pos = bias_pos(mr, a.n, a.transposed);
+      float mine = 0.f;  // group lane h ends up holding head h's dot product (H <= G, checked by the launcher)
+      for (int h = 0; h < a.H; ++h) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 w = s_wb[h * (C / 4) + i * R::G + gl];
+          s += v[4 * i] * w.x + v[4 * i + 1] * w.y + v[4 * i + 2] * w.z + v[4 * i + 3] * w.w;
+        }
+        s = group_sum<R::G>(s);
+        if (gl == h) mine = s;
+      }
+      if (gl < a.H && live) {
+        if (a.nb16) {
+          mine = bias_round16(mine);
+          a.nb16[(long)gl * a.M + bias16_pos(m, a.n, a.transposed)] = __float2half_rn(mine);
+        }
+        a.nb[(long)gl * a.M + pos] = mine;
+      }
+    }
+  }
+}
+
+template <int C>
+__global__ void __launch_bounds__(256) ln_bwd_group_kernel(LnBwdArgs a) {
+  using R = GroupRow<C>;
+  __shared__ float4 s_wb[LN_MAXH * C / 4];
+  const int lane = threadIdx.x & 31, gl = lane % R::G, sub = lane / R::G;
+  if (a.wb) {
+    for (int t = threadIdx.x; t < a.H * C / 4; t += blockDim.x) {
+      const int h = t / (C / 4), r = t % (C / 4), i = r / R::G, l = r % R::G;
+      s_wb[t] = *reinterpret_cast<const float4*>(a.wb + (long)h * C + i * R::STRIDE + 4 * l);
+    }
+    __syncthreads();
+  }
+  float sc[16];
+  gload_f32<C>(a.scale, gl, sc);
+  const int step = gridDim.x * 8 * R::RPW;
+  // rows are handed out so that every lane of a warp stays in the loop together (shuffles below need the full warp)
+  const int m0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * R::RPW;
+  for (int mb = m0; mb < a.M; mb += step) {
+    const int m = mb + sub;
+    const bool live = m < a.M;
+    const int mr = live ? m : a.M - 1;
+    float v[16], d[16];
+    gload_f32<C>(a.x + (long)mr * C, gl, v);
+    if (a.dy) gload_bf16<C>(a.dy + (long)mr * a.ldy, gl, d);
+    else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) d[i] = 0.f;
+    }
+    if (a.wb) {
+      const long pos = bias_pos(mr, a.n, a.transposed);
+      for (int h = 0; h < a.H; ++h) {
+        const float gb = a.dnb[(long)h * a.M + pos];  // same address across the group: one broadcast transaction
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 w = s_wb[h * (C / 4) + i * R::G + gl];
+          d[4 * i] += gb * w.x; d[4 * i + 1] += gb * w.y; d[4 * i + 2] += gb * w.z; d[4 * i + 3] += gb * w.w;
+        }
+      }
+    }
+    float mean, rstd;
+    group_stats<C>(v, mean, rstd);
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      v[i] = (v[i] - mean) * rstd;  // xhat
+      d[i] *= sc[i];                // dxhat
+      s1 += d[i];
+      s2 += d[i] * v[i];
+    }
+    s1 = group_sum<R::G>(s1) * (1.f / C);
+    s2 = group_sum<R::G>(s2) * (1.f / C);
+    if (live) {
+      float g[16];
+      if (a.g_in) gload_f32<C>(a.g_in + (long)m * C, gl, g);
+      else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) g[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) g[i] += rstd * (d[i] - s1 - v[i] * s2);
+      gstore_f32<C>(a.g_out + (long)m * C, gl, g);
+    }
+  }
+}
+
 template <int C>
 inline void ln_fwd(const LnArgs& a, cudaStream_t st) {
-  launch_counter()++; ln_fwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
+  launch_counter()++;
+  if constexpr (C <= 128) {
+    constexpr int rows_per_cta = 8 * GroupRow<C>::RPW;
+    BC2_CHECK(!a.wb || a.H <= GroupRow<C>::G, "LayerNorm bias projection: more heads than lanes per row");
+    ln_fwd_group_kernel<C><<<std::min(cdiv(a.M, rows_per_cta), 148 * 8), 256, 0, st>>>(a);
+  } else {
+    ln_fwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
+  }
 }
 template <int C>
 inline void ln_bwd(const LnBwdArgs& a, cudaStream_t st) {
-  launch_counter()++; ln_bwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
+  launch_counter()++;
+  if constexpr (C <= 128) {
+    constexpr int rows_per_cta = 8 * GroupRow<C>::RPW;
+    BC2_CHECK(!a.wb || a.H <= LN_MAXH, "LayerNorm bias projection: too many heads");
+    ln_bwd_group_kernel<C><<<std::min(cdiv(a.M, rows_per_cta), 148 * 8), 256, 0, st>>>(a);
+  } else {
+    ln_bwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
+  }
 }
 
 // ------------------------------------------------------------------------------------------- centre norm (transposing)
