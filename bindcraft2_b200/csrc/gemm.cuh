@@ -213,6 +213,74 @@ struct EpiResidual {
   }
 };
 
+// fp32 store with a batch stride (partial sums of a split-K product; the caller reduces over z).
+struct EpiPartial {
+  float* out = nullptr;
+  long ld = 0, bs = 0;
+  int M = 0, N = 0;
+  static constexpr bool kPaired = false;
+  __device__ __forceinline__ void operator()(int z, int m, int n0, const float (&v)[32]) const {
+    if (m >= M || n0 >= N) return;
+    float* wp = out + (long)z * bs + (long)m * ld + n0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) st_global_v8(wp + q * 8, *reinterpret_cast<const uint32_t(*)[8]>(&v[q * 8]));
+  }
+};
+
+// Outer product mean, first product: row m = (s, j) of the masked right projection times the permuted output weight
+// gives tmp[s, j, c, f]; the 32 columns of a chunk are (f = n0/32, c = 0..31) and land in the operand layout of the
+// second product, tmpT[(j*128 + f)][s*32 + c] (bf16), as one 64-byte store.
+struct EpiOpmTmp {
+  bf16* out = nullptr;
+  int S = 0, Nres = 0;
+  int M = 0, N = 0;
+  static constexpr bool kPaired = false;
+  __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
+    if (m >= M || n0 >= N) return;
+    const int s = m / Nres, j = m - s * Nres, f = n0 >> 5;
+    uint32_t pk[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) pk[q] = pack_bf16(v[2 * q], v[2 * q + 1]);
+    bf16* wp = out + (((long)j * 128 + f) * S + s) * 32;
+    st_global_v8(wp, *reinterpret_cast<uint32_t(*)[8]>(&pk[0]));
+    st_global_v8(wp + 16, *reinterpret_cast<uint32_t(*)[8]>(&pk[8]));
+  }
+};
+
+// Outer product mean, second product: D[i][(j, f)] = sum_{s,c} left[s,i,c] tmp[s,j,c,f];
+// pair_out[i,j,f] = pair_in[i,j,f] + (D + b[f]) / (1e-3 + sum_s m[s,i] m[s,j])   (modules.py:1198-1211).
+struct EpiOpmOut {
+  const float* res_in = nullptr;
+  float* res_out = nullptr;
+  const float* bias = nullptr;      // [128]
+  const float* msa_mask = nullptr;  // [S][Nres]
+  int S = 0, Nres = 0;
+  int M = 0, N = 0;
+  static constexpr bool kPaired = false;
+  __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
+    if (m >= M || n0 >= N) return;
+    const int j = n0 >> 7, f0 = n0 & 127;
+    const long off = (long)m * N + n0;
+    uint32_t r[32];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) ld_global_v8(res_in + off + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
+    float nrm = 1e-3f;
+    for (int s = 0; s < S; ++s) nrm += msa_mask[(long)s * Nres + m] * msa_mask[(long)s * Nres + j];
+    const float inv = 1.f / nrm;
+    const float4* bp = reinterpret_cast<const float4*>(bias + f0);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float4 b4 = bp[q];
+      r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + (v[4 * q] + b4.x) * inv);
+      r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + (v[4 * q + 1] + b4.y) * inv);
+      r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + (v[4 * q + 2] + b4.z) * inv);
+      r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + (v[4 * q + 3] + b4.w) * inv);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) st_global_v8(res_out + off + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
+  }
+};
+
 // Triangle-multiplication projection+gate.  The packed weight puts, for each 128-channel group t, the 128
 // projection columns followed by the matching 128 gate columns, so one 256-wide accumulator tile holds both:
 //   g  = sigmoid(gate + bg)            -> gate_out [M, CH] row-major (kept for the backward)

@@ -525,24 +525,40 @@ struct MsaCol {
 struct Opm {
   int n = 0, S_ = 0, Cm = 0;
   long Mm = 0;
+  static constexpr int kSplit = 64;  // split-K factor of the d(left) product: K = 128 n is a multiple of 64*64
   struct W {
     LnW ln;
     bf16 *wlr = nullptr, *wlr_b = nullptr;
-    float *blr = nullptr, *ow = nullptr, *ob = nullptr;
-    GemmPlan g_lr, gb_lr;
+    bf16* wp = nullptr;   // output_w as [(f*32 + c)][e]: B operand of the first product
+    float* wq = nullptr;  // output_w as [e][f][c] (fp32): d(right) kernel
+    float *blr = nullptr, *ob = nullptr;
+    GemmPlan g_lr, gb_lr, g_tmp;
   };
   std::vector<W> w;
-  bf16 *lr = nullptr, *dlr_b = nullptr;
-  float *tmp = nullptr, *dtmp = nullptr, *dlr = nullptr;
+  bf16 *lr = nullptr, *dlr_b = nullptr, *leftT = nullptr, *tmpT = nullptr, *dtmpT = nullptr, *dout = nullptr;
+  float* partial = nullptr;
+  GemmPlan g_out, g_dleft, g_dtmp;
   const float* msa_mask = nullptr;
   Scratch* S = nullptr;
   void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, const float* mask) {
     S = s; n = n_; S_ = S__; Cm = Cm_; Mm = (long)S_ * n; msa_mask = mask;
+    const int K = 32 * S_;
+    const long NF = (long)n * OPM_F;
     lr = A.alloc<bf16>(Mm * 64);
     dlr_b = A.alloc<bf16>(Mm * 64);
-    dlr = A.alloc<float>(Mm * 64);
-    tmp = A.alloc<float>(Mm * OPM_C * OPM_F);
-    dtmp = A.alloc<float>(Mm * OPM_C * OPM_F);
+    leftT = A.alloc<bf16>((long)n * K);
+    tmpT = A.alloc<bf16>(NF * K);
+    dtmpT = A.alloc<bf16>(NF * K);
+    dout = A.alloc<bf16>((long)n * NF);
+    partial = A.alloc<float>((long)kSplit * n * K);
+    // second product: D[i][(j,f)] = leftT . tmpT^T
+    g_out = make_gemm(kmaj(leftT, K), kmaj(tmpT, K), n, (int)NF, K, 1, 256);
+    // d(left)[i][k] = sum_{(j,f)} dout[i][(j,f)] tmpT[(j,f)][k], the (j,f) range cut into kSplit batches
+    const long Kc = NF / kSplit;
+    BC2_CHECK(NF % (kSplit * 64) == 0, "outer product mean: n must be a multiple of 32");
+    g_dleft = make_gemm(Operand{dout, NF, Kc, false}, Operand{tmpT, K, Kc * K, true}, n, K, (int)Kc, kSplit, 128);
+    // d(tmpT)[(j,f)][k] = sum_i dout[i][(j,f)] leftT[i][k]: both operands read through their MN-major views
+    g_dtmp = make_gemm(Operand{dout, NF, 0, true}, Operand{leftT, K, 0, true}, (int)NF, K, n, 1, 128);
   }
   void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
     W b;
@@ -562,37 +578,55 @@ struct Opm {
     b.wlr_b = A.upload_bf16(wf);
     b.wlr = A.upload_bf16(transpose_io(wf, Cm, 64));
     b.blr = A.upload(bias);
-    b.ow = A.upload(m.get(p + "/output_w").data);
+    const auto& ow = m.get(p + "/output_w").data;  // [c][e][f]
+    std::vector<float> wp((size_t)OPM_F * OPM_C * OPM_C), wq((size_t)OPM_C * OPM_F * OPM_C);
+    for (int c = 0; c < OPM_C; ++c)
+      for (int e = 0; e < OPM_C; ++e)
+        for (int f = 0; f < OPM_F; ++f) {
+          const float v = ow[((size_t)c * OPM_C + e) * OPM_F + f];
+          wp[((size_t)f * OPM_C + c) * OPM_C + e] = v;
+          wq[((size_t)e * OPM_F + f) * OPM_C + c] = v;
+        }
+    b.wp = A.upload_bf16(wp);
+    b.wq = A.upload(wq);
     b.ob = A.upload(m.get(p + "/output_b").data);
     b.g_lr = make_gemm(kmaj(S->x, Cm), kmaj(b.wlr, Cm), (int)Mm, 64, Cm);
     b.gb_lr = make_gemm(kmaj(dlr_b, 64), kmaj(b.wlr_b, 64), (int)Mm, Cm, 64);
+    // first product: rows (s,j) of the right projection (columns 32..63 of lr) times wp
+    b.g_tmp = make_gemm(kmaj(lr + 32, 64), kmaj(b.wp, OPM_C), (int)Mm, OPM_F * OPM_C, OPM_C, 1, 256);
     w.push_back(b);
   }
-  void forward(int blk, const float* msa_in, const float* pair_in, float* pair_out, cudaStream_t st) {
-    W& b = w[blk];
+  // lr, leftT and tmpT of a block (also what the backward needs from the replayed forward)
+  void products(W& b, const float* msa_in, cudaStream_t st) {
     const int Mi = (int)Mm;
     LnArgs l; l.x = msa_in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
     { ProfScope ps_("Opm.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     EpiStore e; e.out = lr; e.ldo = 64; e.bias = b.blr; e.rowscale = msa_mask; e.M = Mi; e.N = 64;
     { ProfScope ps_("Opm.forward.gemm.g_lr", st); run_gemm(b.g_lr, e, st); }
-    { ProfScope ps_("Opm.forward.opm_tmp_kernel", st); launch_counter()++; opm_tmp_kernel<<<dim3(Mi, OPM_C), 128, 0, st>>>(lr, b.ow, tmp, Mi); }
-    const size_t sm = (size_t)(32 * S_ * OPM_C + 32) * 4;
-    { ProfScope ps_("Opm.forward.opm_out_kernel", st); launch_counter()++; opm_out_kernel<<<dim3(n, cdiv(n, 32)), 128, sm, st>>>(lr, tmp, b.ob, msa_mask, pair_in, pair_out, S_, n); }
+    { ProfScope ps_("Opm.forward.opm_pack_left_kernel", st); launch_counter()++; opm_pack_left_kernel<<<cdiv(n * S_ * 16, 256), 256, 0, st>>>(lr, leftT, S_, n); }
+    EpiOpmTmp et; et.out = tmpT; et.S = S_; et.Nres = n; et.M = Mi; et.N = OPM_F * OPM_C;
+    { ProfScope ps_("Opm.forward.gemm.g_tmp", st); run_gemm(b.g_tmp, et, st); }
+  }
+  void forward(int blk, const float* msa_in, const float* pair_in, float* pair_out, cudaStream_t st) {
+    W& b = w[blk];
+    products(b, msa_in, st);
+    EpiOpmOut eo; eo.res_in = pair_in; eo.res_out = pair_out; eo.bias = b.ob; eo.msa_mask = msa_mask; eo.S = S_; eo.Nres = n;
+    eo.M = n; eo.N = n * OPM_F;
+    { ProfScope ps_("Opm.forward.gemm.g_out", st); run_gemm(g_out, eo, st); }
   }
   // g_pair: cotangent of the pair stream after the module (read only: the module adds to the pair stream, so the
-  // cotangent of its pair input is g_pair itself); g_msa accumulates.
+  // cotangent of its pair input is g_pair itself); g_msa accumulates.  lr / leftT / tmpT must hold this block's
+  // forward values (the replayed forward just before leaves them there).
   void backward(int blk, const float* msa_in, const float* g_pair, float* g_msa, cudaStream_t st) {
     W& b = w[blk];
-    const int Mi = (int)Mm;
-    BC2_CUDA(cudaMemsetAsync(dlr, 0, (size_t)Mm * 64 * 4, st));
-    BC2_CUDA(cudaMemsetAsync(dtmp, 0, (size_t)Mm * OPM_C * OPM_F * 4, st));
-    const int zsplit = std::max(1, std::min(7, 1184 / std::max(1, n * S_)));  // enough blocks to fill the SMs
-    const int ntile = cdiv(n, OPM_IT);
-    const int zleft = std::max(1, std::min(cdiv(n, 8), 1184 / std::max(1, ntile * S_)));
-    { ProfScope ps_("Opm.backward.opm_dleft_kernel", st); launch_counter()++; opm_dleft_kernel<<<dim3(ntile, S_, zleft), 256, 0, st>>>(g_pair, tmp, msa_mask, dlr, S_, n); }
-    { ProfScope ps_("Opm.backward.opm_dtmp_kernel", st); launch_counter()++; opm_dtmp_kernel<<<dim3(n, S_, zsplit), 128, 0, st>>>(g_pair, lr, msa_mask, dtmp, S_, n); }
-    { ProfScope ps_("Opm.backward.opm_dright_kernel", st); launch_counter()++; opm_dright_kernel<<<Mi, 256, 0, st>>>(dtmp, b.ow, dlr, Mi); }
-    { ProfScope ps_("Opm.backward.opm_dlr_store_kernel", st); launch_counter()++; opm_dlr_store_kernel<<<cdiv(Mi * 64, 256), 256, 0, st>>>(dlr, msa_mask, dlr_b, (long)Mi * 64); }
+    const int Mi = (int)Mm, K = 32 * S_;
+    { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_counter()++; opm_dout_kernel<<<cdiv(n * n, 8), 256, 0, st>>>(g_pair, msa_mask, dout, S_, n); }
+    EpiPartial ep; ep.out = partial; ep.ld = K; ep.bs = (long)n * K; ep.M = n; ep.N = K;
+    { ProfScope ps_("Opm.backward.gemm.g_dleft", st); run_gemm(g_dleft, ep, st); }
+    EpiStore ed; ed.out = dtmpT; ed.ldo = K; ed.M = n * OPM_F; ed.N = K;
+    { ProfScope ps_("Opm.backward.gemm.g_dtmp", st); run_gemm(g_dtmp, ed, st); }
+    { ProfScope ps_("Opm.backward.opm_dleft_reduce_kernel", st); launch_counter()++; opm_dleft_reduce_kernel<<<cdiv(n * K, 256), 256, 0, st>>>(partial, kSplit, msa_mask, dlr_b, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dright_tc_kernel", st); launch_counter()++; opm_dright_tc_kernel<<<cdiv(Mi, OPM_DR_ROWS), 256, 0, st>>>(dtmpT, b.wq, msa_mask, dlr_b, S_, n); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
     { ProfScope ps_("Opm.backward.gemm.gb_lr", st); run_gemm(b.gb_lr, ex, st); }
     LnBwdArgs l; l.x = msa_in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;

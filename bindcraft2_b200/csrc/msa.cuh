@@ -72,54 +72,38 @@ opm_out_kernel(const bf16* __restrict__ lr, const float* __restrict__ tmp, const
 }
 
 // Backward.  d_out[i,j,f] = g[i,j,f] / (1e-3 + norm[i,j]).
-// d_left[s,i,c] = sum_{j,f} d_out[i,j,f] tmp[s,j,c,f]      block = (tile of OPM_IT rows i, s, slice of j); 8 warps stride
-// over j, lanes over f.  Each tmp value read feeds OPM_IT rows, which divides the L2 traffic on tmp by OPM_IT.
-constexpr int OPM_IT = 4;
+// d_left[s,i,c] = sum_{j,f} d_out[i,j,f] tmp[s,j,c,f]      block = (i, s), 8 warps stride over j, lanes over f
 __global__ void __launch_bounds__(256)
 opm_dleft_kernel(const float* __restrict__ g, const float* __restrict__ tmp, const float* __restrict__ msa_mask,
                  float* __restrict__ dlr /*[S*N][64] fp32, zeroed by the caller*/, int S, int N) {
-  __shared__ float red[8][OPM_IT][OPM_C];
-  const int i0 = blockIdx.x * OPM_IT, s = blockIdx.y;
+  __shared__ float red[8][OPM_C];
+  const int i = blockIdx.x, s = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float acc[OPM_IT][OPM_C];
+  float acc[OPM_C];
 #pragma unroll
-  for (int r = 0; r < OPM_IT; ++r)
-#pragma unroll
-    for (int c = 0; c < OPM_C; ++c) acc[r][c] = 0.f;
+  for (int c = 0; c < OPM_C; ++c) acc[c] = 0.f;
   for (int j = warp + 8 * blockIdx.z; j < N; j += 8 * gridDim.z) {
-    float4 d[OPM_IT];
-#pragma unroll
-    for (int r = 0; r < OPM_IT; ++r) {
-      const int i = min(i0 + r, N - 1);
-      float nrm = 0.f;
-      for (int ss = 0; ss < S; ++ss) nrm += msa_mask[(long)ss * N + i] * msa_mask[(long)ss * N + j];
-      const float inv = (i0 + r < N) ? 1.f / (1e-3f + nrm) : 0.f;
-      d[r] = *reinterpret_cast<const float4*>(g + ((long)i * N + j) * OPM_F + lane * 4);
-      d[r].x *= inv; d[r].y *= inv; d[r].z *= inv; d[r].w *= inv;
-    }
+    float nrm = 0.f;
+    for (int ss = 0; ss < S; ++ss) nrm += msa_mask[(long)ss * N + i] * msa_mask[(long)ss * N + j];
+    const float inv = 1.f / (1e-3f + nrm);
+    const float4 d = *reinterpret_cast<const float4*>(g + ((long)i * N + j) * OPM_F + lane * 4);
     const float* tp = tmp + ((long)s * N + j) * OPM_C * OPM_F + lane * 4;
 #pragma unroll
     for (int c = 0; c < OPM_C; ++c) {
       const float4 t = *reinterpret_cast<const float4*>(tp + c * OPM_F);
-#pragma unroll
-      for (int r = 0; r < OPM_IT; ++r) acc[r][c] += d[r].x * t.x + d[r].y * t.y + d[r].z * t.z + d[r].w * t.w;
+      acc[c] += inv * (d.x * t.x + d.y * t.y + d.z * t.z + d.w * t.w);
     }
   }
 #pragma unroll
-  for (int r = 0; r < OPM_IT; ++r)
-#pragma unroll
-    for (int c = 0; c < OPM_C; ++c) {
-      const float v = warp_sum(acc[r][c]);
-      if (lane == 0) red[warp][r][c] = v;
-    }
+  for (int c = 0; c < OPM_C; ++c) {
+    const float v = warp_sum(acc[c]);
+    if (lane == 0) red[warp][c] = v;
+  }
   __syncthreads();
-  if (threadIdx.x < OPM_IT * OPM_C) {
-    const int r = threadIdx.x / OPM_C, c = threadIdx.x % OPM_C;
-    if (i0 + r < N) {
-      float v = 0.f;
-      for (int w = 0; w < 8; ++w) v += red[w][r][c];
-      atomicAdd(&dlr[((long)s * N + i0 + r) * 64 + c], v);  // gridDim.z blocks share a row; dlr starts at zero
-    }
+  if (threadIdx.x < OPM_C) {
+    float v = 0.f;
+    for (int w = 0; w < 8; ++w) v += red[w][threadIdx.x];
+    atomicAdd(&dlr[((long)s * N + i) * 64 + threadIdx.x], v);  // gridDim.z blocks share a row; dlr starts at zero
   }
 }
 
@@ -182,6 +166,90 @@ __global__ void opm_dlr_store_kernel(const float* __restrict__ dlr, const float*
                                      bf16* __restrict__ out, long n) {
   const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (t < n) out[t] = __float2bfloat16(dlr[t] * msa_mask[t / 64]);
+}
+
+// ------------------------------------------------------------------------------------------- outer product mean on tensor cores
+// The two products of the reassociated outer product mean and their gradients run as tcgen05 GEMMs (epilogues
+// EpiOpmTmp / EpiOpmOut / EpiPartial); these kernels move operands into the layouts those GEMMs read.
+//   leftT[i][s*32 + c]            masked left projection, K-major operand of the second product
+//   tmpT[(j*128 + f)][s*32 + c]   first product (bf16), K-major B operand of the second product
+//   dout[i][(j*128 + f)]          cotangent of the second product = g / (1e-3 + norm), bf16
+
+// leftT from lr rows (s*N + i): one thread per (i, s, pair of channels)
+__global__ void opm_pack_left_kernel(const bf16* __restrict__ lr, bf16* __restrict__ leftT, int S, int N) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long)N * S * 16) return;
+  const int c2 = (int)(t % 16), s = (int)((t / 16) % S), i = (int)(t / (16L * S));
+  reinterpret_cast<uint32_t*>(leftT)[((long)i * S + s) * 16 + c2] =
+      reinterpret_cast<const uint32_t*>(lr)[((long)s * N + i) * 32 + c2];
+}
+
+// dout = g * 1/(1e-3 + sum_s m[s,i] m[s,j]): one warp per pair position (i,j), 4 channels per lane
+__global__ void __launch_bounds__(256)
+opm_dout_kernel(const float* __restrict__ g, const float* __restrict__ msa_mask, bf16* __restrict__ dout, int S, int N) {
+  const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (m >= (long)N * N) return;
+  const int lane = threadIdx.x & 31;
+  const int i = (int)(m / N), j = (int)(m - (long)i * N);
+  float nrm = 1e-3f;
+  for (int s = 0; s < S; ++s) nrm += msa_mask[(long)s * N + i] * msa_mask[(long)s * N + j];
+  const float inv = 1.f / nrm;
+  const float4 v = *reinterpret_cast<const float4*>(g + m * OPM_F + lane * 4);
+  *reinterpret_cast<uint2*>(dout + m * OPM_F + lane * 4) = make_uint2(pack_bf16(v.x * inv, v.y * inv), pack_bf16(v.z * inv, v.w * inv));
+}
+
+// d(left) from the split-K partial sums: dlr_b[(s*N+i)][c] = mask[s,i] * sum_z partial[z][i][s*32+c]
+__global__ void opm_dleft_reduce_kernel(const float* __restrict__ partial, int nsplit, const float* __restrict__ msa_mask,
+                                        bf16* __restrict__ dlr_b, int S, int N) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int K = 32 * S;
+  if (t >= (long)N * K) return;
+  const int k = (int)(t % K), i = (int)(t / K), s = k / 32, c = k % 32;
+  float acc = 0.f;
+  for (int z = 0; z < nsplit; ++z) acc += partial[((long)z * N + i) * K + k];
+  dlr_b[((long)s * N + i) * 64 + c] = __float2bfloat16(acc * msa_mask[(long)s * N + i]);
+}
+
+// d(right)[s,j,e] = sum_{f,c} dtmpT[(j*128+f)][s*32+c] * Wq[e][f][c]   (Wq = output_w permuted to [e][f][c], fp32)
+// block = two rows (s,j); warp per e (stride 8), lanes over c.  Result masked and stored into dlr_b[(s*N+j)][32+e].
+constexpr int OPM_DR_ROWS = 2;
+__global__ void __launch_bounds__(256)
+opm_dright_tc_kernel(const bf16* __restrict__ dtmpT, const float* __restrict__ Wq, const float* __restrict__ msa_mask,
+                     bf16* __restrict__ dlr_b, int S, int N) {
+  __shared__ float sd[OPM_DR_ROWS][OPM_F][OPM_C];  // 32 KB
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long row0 = (long)blockIdx.x * OPM_DR_ROWS;
+  const long SN = (long)S * N;
+  for (int t = threadIdx.x; t < OPM_DR_ROWS * OPM_F * OPM_C / 2; t += 256) {
+    const int c2 = t % 16, f = (t / 16) % OPM_F, r = t / (16 * OPM_F);
+    const long sj = row0 + r;
+    float2 v = make_float2(0.f, 0.f);
+    if (sj < SN) {
+      const int s = (int)(sj / N), j = (int)(sj - (long)s * N);
+      v = unpack_bf16(reinterpret_cast<const uint32_t*>(dtmpT)[(((long)j * OPM_F + f) * S + s) * 16 + c2]);
+    }
+    sd[r][f][2 * c2] = v.x;
+    sd[r][f][2 * c2 + 1] = v.y;
+  }
+  __syncthreads();
+  for (int e = warp; e < OPM_C; e += 8) {
+    float acc[OPM_DR_ROWS];
+#pragma unroll
+    for (int r = 0; r < OPM_DR_ROWS; ++r) acc[r] = 0.f;
+    const float* wp = Wq + (long)e * OPM_F * OPM_C + lane;
+#pragma unroll 8
+    for (int f = 0; f < OPM_F; ++f) {
+      const float w = wp[f * OPM_C];
+#pragma unroll
+      for (int r = 0; r < OPM_DR_ROWS; ++r) acc[r] += w * sd[r][f][lane];
+    }
+#pragma unroll
+    for (int r = 0; r < OPM_DR_ROWS; ++r) {
+      const float v = warp_sum(acc[r]);
+      const long sj = row0 + r;
+      if (lane == 0 && sj < SN) dlr_b[sj * 64 + 32 + e] = __float2bfloat16(v * msa_mask[sj]);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------- MSA column attention
