@@ -114,6 +114,21 @@ def algorithmic_work(n: int, s: int, cm=256, cz=128):
     return w
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per launch from the ncu --set full captures summarised under
+# profiles/ (N_res = 224, S = 1, the workload this bench runs by default); other sizes report null.
+NCU_TRAFFIC_N224 = {
+    'TriAttn.forward.attn_fwd': (55.5e6, 'profiles/ncu_attn_fwd_p_kernel_triangle_n224.md'),
+    'TriAttn.backward.attn_bwd': (61.1e6, 'profiles/ncu_attn_bwd_tc_kernel_triangle_n224.md'),
+    'TriAttn.forward.ln_fwd_c': (25.7e6, 'profiles/ncu_ln_fwd_group_kernel_pair_n224.md'),
+    'TriMul.forward.ln_fwd_c': (25.7e6, 'profiles/ncu_ln_fwd_group_kernel_pair_n224.md'),
+    'TriAttn.backward.ln_bwd_c': (65.8e6, 'profiles/ncu_ln_bwd_group_kernel_pair_n224.md'),
+    'TriMul.backward.trimul_bwd_gate_kernel': (96.4e6, 'profiles/ncu_trimul_bwd_gate_kernel_n224.md'),
+    'TriMul.forward.cln_fwd_c': (12.9e6, 'profiles/ncu_cln_fwd_kernel_n224.md'),
+    'TriMul.forward.gemm.g_pg': (16.3e6, 'profiles/ncu_gemm_tc_kernel_bn256_epiprojgate_n224.md'),
+    'TriMul.forward.gemm.g_con': (25.7e6, 'profiles/ncu_gemm_tc_kernel_mnmajor_trimul_n224.md'),
+}
+
+
 def fwd_bwd_flops(n: int, s: int) -> float:
     """Algorithmic FLOPs of one block forward + backward: 2*lin + 3*bil, formulas of the scope table (S = MSA rows)."""
     lin = (2 * n * n * 128 * 768 * 2 + 2 * n * n * 128 * 644 * 2 + 4 * n * n * 128 * 512 + 10 * s * n * 256 ** 2 +
@@ -349,7 +364,9 @@ def run_ours(args):
     peak = peaks[kind]
     roofline = {'kernel': top, 'bound': kind, 'achieved': achieved, 'peak': peak,
                 'unit': 'TFLOP/s' if kind == 'tensor' else 'GB/s', 'frac': (achieved / peak) if achieved else None,
-                'traffic': None, 'peak_source': peaks['source'] + (' (sustained bf16)' if kind == 'tensor' else ''),
+                'traffic': NCU_TRAFFIC_N224.get(top, (None, None))[0] if (n == 224 and s == 1) else None,
+                'traffic_source': NCU_TRAFFIC_N224.get(top, (None, None))[1] if (n == 224 and s == 1) else None,
+                'peak_source': peaks['source'] + (' (sustained bf16)' if kind == 'tensor' else ''),
                 'launches_in_timed_region': top_cnt, 'avg_launch_us': per_launch_s * 1e6,
                 'share_of_step': classes[top][1] / total_ms if total_ms else None}
     step_flops = fwd_bwd_flops(n, s) * depth

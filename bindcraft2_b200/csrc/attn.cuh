@@ -57,6 +57,9 @@ struct AttnArgs {
   bf16* d_qkv = nullptr;       // [rows][ld]: dq | dk | dv written into the first 3*H*D columns
   float* d_bias = nullptr;     // [H][N][N] (head, KEY, query), accumulated atomically (zeroed by the caller)
   float* dq_acc = nullptr;     // [rows][H*D] fp32, only when keys are split over several CTAs
+  bf16* ds_store = nullptr;    // optional [B][H][N/8][query][8 keys]: when set, the backward writes dS here (plain stores)
+                               // instead of adding it to d_bias atomically; attn_dbias_reduce then sums over B in a
+                               // fixed order (deterministic, and far less atomic traffic when B is large)
 };
 
 struct AttnMaps {
@@ -825,7 +828,13 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
             *reinterpret_cast<uint4*>(pb + sw128_off(r, chunk)) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
             *reinterpret_cast<uint4*>(db + sw128_off(r, chunk)) = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
           }
-          if (dbrow && chunk_live) {
+          if (a.ds_store) {
+            if (chunk_live) {
+              uint4* dst = reinterpret_cast<uint4*>(a.ds_store) + (((long)b * a.H + h) * (a.N >> 3) + (k0 >> 3)) * a.N + q;
+#pragma unroll
+              for (int t = 0; t < 4; ++t) dst[(long)t * a.N] = make_uint4(dk[4 * t], dk[4 * t + 1], dk[4 * t + 2], dk[4 * t + 3]);
+            }
+          } else if (dbrow && chunk_live) {
             float* dp0 = dbrow + (long)k0 * a.N;
 #pragma unroll
             for (int e = 0; e < 32; ++e)  // [h][key][query]: one coalesced 128-byte reduction per warp and key
@@ -891,6 +900,42 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
 template <int D>
 constexpr int attn_bwd_smem() {
   return 1024 + 65536 + 128 * D * 2 * 6 + 256 * 4 + 128;
+}
+
+// d_bias[h][key][query] = sum_b dS[b][h][key][query] from the bf16 copy the backward stored.  A block owns 32 queries
+// of one (head, key octet); its 8 thread rows each sum a slice of the batch rows in a fixed order, then the slices are
+// added in a fixed order: the result does not depend on scheduling.
+__global__ void __launch_bounds__(256)
+attn_dbias_reduce_kernel(const bf16* __restrict__ ds, float* __restrict__ d_bias, int B, int H, int N) {
+  __shared__ float part[8][32][9];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  const int q = blockIdx.x * 32 + lane, ko = blockIdx.y, h = blockIdx.z;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  if (q < N) {
+    const uint4* src = reinterpret_cast<const uint4*>(ds) + ((long)h * (N >> 3) + ko) * N + q;
+    const long bstride = (long)H * (N >> 3) * N;
+#pragma unroll 4
+    for (int b = slice; b < B; b += 8) {
+      const uint4 v = src[(long)b * bstride];
+      const float2 f0 = unpack_bf16(v.x), f1 = unpack_bf16(v.y), f2 = unpack_bf16(v.z), f3 = unpack_bf16(v.w);
+      acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+      acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) part[slice][lane][e] = acc[e];
+  __syncthreads();
+  // thread (slice = key within the octet, lane = query) adds the 8 slices
+  float v = 0.f;
+#pragma unroll
+  for (int sl = 0; sl < 8; ++sl) v += part[sl][lane][slice];
+  if (q < N) d_bias[((long)h * N + ko * 8 + slice) * N + q] = v;
+}
+inline void attn_dbias_reduce(const AttnArgs& a, cudaStream_t st) {
+  dim3 grid(cdiv(a.N, 32), a.N / 8, a.H);
+  launch_counter()++; attn_dbias_reduce_kernel<<<grid, 256, 0, st>>>(a.ds_store, a.d_bias, a.B, a.H, a.N);
 }
 
 // ------------------------------------------------------------------------------------------- CUDA-core reference

@@ -46,6 +46,7 @@ struct Scratch {
   bf16* big = nullptr;  // [rows][wide]
   bf16 *dt = nullptr, *dab = nullptr;  // channel-major planes (pair stream only)
   float *delta = nullptr, *dnb = nullptr, *dq_acc = nullptr, *ref_dkv = nullptr;
+  bf16* ds_store = nullptr;  // triangle attention backward: dS of every batch row (see AttnArgs::ds_store)
   void init(DeviceArena& A, long rows_, int C_, int wide_, bool pair, int n_res, int max_heads) {
     rows = rows_; C = C_; wide = wide_;
     x = A.alloc<bf16>(rows * C); y = A.alloc<bf16>(rows * C); dx = A.alloc<bf16>(rows * C);
@@ -339,6 +340,15 @@ struct TriAttn {
     a.d_o = S->d_o; a.delta = S->delta; a.d_qkv = S->big; a.d_bias = S->dnb; a.dq_acc = S->dq_acc;
     plan.rows = M; plan.ref_dkv = S->ref_dkv;
     attn_prepare(plan);
+    // BC2_DETERMINISTIC=1: the bias gradient is summed over batch rows in a fixed order from a bf16 copy of dS
+    // (n*H*n*n elements, shared by every triangle attention of the stack; at most 1 GiB, n <= ~500) instead of with
+    // fp32 atomics.  Bit-reproducible from run to run, about 1 % slower at n = 224 (the copy is written and read once).
+    const long ds_elems = (long)n * H * n * n;
+    const char* det = getenv("BC2_DETERMINISTIC");
+    if (det && det[0] == '1' && plan.tc && ds_elems * 2 <= (1L << 30)) {
+      if (!S->ds_store) S->ds_store = A.alloc<bf16>(ds_elems);
+      a.ds_store = S->ds_store;
+    }
   }
   void set_mask(const float* pair_mask) { plan.args.mask = pair_mask; }
   void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
@@ -373,8 +383,9 @@ struct TriAttn {
     { ProfScope ps_("TriAttn.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
     AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, M, plan.args.row_b, plan.args.row_p, n, H, D};
     { ProfScope ps_("TriAttn.backward.attn_bwd_prep", st); attn_bwd_prep(p, st); }
-    { ProfScope ps_("TriAttn.backward.memset", st); BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st)); }
+    if (!plan.args.ds_store) { ProfScope ps_("TriAttn.backward.memset", st); BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st)); }
     { ProfScope ps_("TriAttn.backward.attn_bwd", st); attn_bwd(plan, st); }
+    if (plan.args.ds_store) { ProfScope ps_("TriAttn.backward.attn_dbias_reduce", st); attn_dbias_reduce(plan.args, st); }
     EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
     { ProfScope ps_("TriAttn.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.wb = b.wb; l.dnb = S->dnb; l.H = H; l.n = n;

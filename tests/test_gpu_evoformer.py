@@ -125,6 +125,25 @@ def test_backward_is_pure_under_interleaving(lib, tmp_path):
     assert O.rel_l2(dm2.cpu(), dm1.cpu()) < max(2e-3, 4 * noise)
 
 
+def test_deterministic_mode_is_bit_reproducible(lib, tmp_path, monkeypatch):
+    """BC2_DETERMINISTIC=1 (read when a stack object is built) sums the triangle-attention bias gradient in a fixed
+    order: two backward calls on the same operands agree bit for bit, and the result still matches the oracle."""
+    from bindcraft2_b200 import native
+    monkeypatch.setenv('BC2_DETERMINISTIC', '1')
+    lib.bc2_test_set_module_mask(0x1ff)
+    params = synthetic.make_evoformer_params(131, 2)
+    inp = synthetic.make_block_inputs(132, 64, 1)
+    got, (psave, msave, wdir, t, seed) = _run_cuda(lib, params, inp, 2, tmp_path, own_save=0)
+    kw = dict(depth=2, weights_dir=wdir, own_save=0)
+    dp2, dm2 = native.evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, seed, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(dp2.cpu(), got['d_pair']) and torch.equal(dm2.cpu(), got['d_msa'])
+    want = O.stack_fwd_bwd(params, inp, 2)
+    with O.bf16_operands():
+        floor = O.stack_fwd_bwd(params, inp, 2)
+    _check(got, want, floor, 'deterministic')
+
+
 def test_runner_pads_to_32_and_autograd(lib, tmp_path):
     """The hook callable pads 50 -> 64 and masks the pad; torch autograd reaches the backward operator."""
     from bindcraft2_b200 import native
