@@ -179,3 +179,51 @@ def make_block_inputs(seed: int, n: int, s: int, cm=256, cz=128, scale=1.0, shif
     return dict(msa=msa, pair=pair, msa_mask=msa_mask, pair_mask=pair_mask, ct_msa=ct_msa, ct_pair=ct_pair)
 
 
+
+
+# ----------------------------------------------------------------------------- structure module (fold iteration)
+def make_structure_params(seed: int, cs=384, cz=128, heads=12, sqk=16, sv=16, pqk=4, pv=8) -> Params:
+    """Weights of the structure-module core under the reference's haiku names (post-trunk manifest keys).
+
+    Layers the reference zero-initialises (the output projection, the last transition layer and the rigid update) get
+    the 'linear' initialiser, scaled down for the rigid update so that eight iterations move the frames by a few
+    position units instead of leaving them at the identity or scattering them."""
+    g = torch.Generator().manual_seed(seed)
+    p: Params = {}
+    p['single_layer_norm/scale'], p['single_layer_norm/offset'] = _ln(g, cs)
+    p['pair_layer_norm/scale'], p['pair_layer_norm/offset'] = _ln(g, cz)
+    p['initial_projection/weights'] = _lin(g, cs, (cs, cs))
+    p['initial_projection/bias'] = 0.02 * torch.randn(cs, generator=g)
+    ipa = 'fold_iteration/invariant_point_attention'
+    p[f'{ipa}/trainable_point_weights'] = math.log(math.e - 1.0) + 0.2 * torch.randn(heads, generator=g)
+    for nm, d in (('q_scalar_projection', sqk), ('k_scalar_projection', sqk), ('v_scalar_projection', sv)):
+        p[f'{ipa}/{nm}/weights'] = _lin(g, cs, (cs, heads, d))
+    for nm, d in (('q_point_projection', pqk), ('k_point_projection', pqk), ('v_point_projection', pv)):
+        p[f'{ipa}/{nm}/point_projection/weights'] = _lin(g, cs, (cs, heads, 3 * d))
+        p[f'{ipa}/{nm}/point_projection/bias'] = 0.1 * torch.randn(heads, 3 * d, generator=g)
+    p[f'{ipa}/attention_2d/weights'] = _lin(g, cz, (cz, heads))
+    p[f'{ipa}/attention_2d/bias'] = 0.02 * torch.randn(heads, generator=g)
+    nfinal = heads * sv + heads * pv * 4 + heads * cz
+    p[f'{ipa}/output_projection/weights'] = _lin(g, nfinal, (nfinal, cs))
+    p[f'{ipa}/output_projection/bias'] = 0.02 * torch.randn(cs, generator=g)
+    f = 'fold_iteration'
+    p[f'{f}/attention_layer_norm/scale'], p[f'{f}/attention_layer_norm/offset'] = _ln(g, cs)
+    p[f'{f}/transition_layer_norm/scale'], p[f'{f}/transition_layer_norm/offset'] = _ln(g, cs)
+    for i, nm in enumerate(('transition', 'transition_1', 'transition_2')):
+        p[f'{f}/{nm}/weights'] = _lin(g, cs, (cs, cs), 'relu' if i < 2 else 'linear')
+        p[f'{f}/{nm}/bias'] = 0.02 * torch.randn(cs, generator=g)
+    p[f'{f}/quat_rigid/rigid/weights'] = 0.3 * _lin(g, cs, (cs, 6))
+    p[f'{f}/quat_rigid/rigid/bias'] = 0.02 * torch.randn(6, generator=g)
+    return p
+
+
+def make_structure_inputs(seed: int, n: int, cs=384, cz=128, masked=0):
+    """Seeded N(0,1) single/pair activations, a sequence mask with `masked` trailing pads, and cotangents for the
+    three outputs (final activations, rotations, translations)."""
+    g = torch.Generator().manual_seed(seed)
+    mask = torch.ones(n)
+    if masked:
+        mask[n - masked:] = 0
+    return dict(single=torch.randn(n, cs, generator=g), pair=torch.randn(n, n, cz, generator=g), seq_mask=mask,
+                ct_act=torch.randn(n, cs, generator=g), ct_rot=torch.randn(n, 3, 3, generator=g),
+                ct_trans=0.1 * torch.randn(n, 3, generator=g))
