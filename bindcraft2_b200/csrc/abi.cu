@@ -8,6 +8,7 @@
 
 #include "../../include/bc2_b200.h"
 #include "stack.cuh"
+#include "structure_host.cuh"
 
 namespace {
 
@@ -71,6 +72,22 @@ TplEmbed* get_tplembed(int N, int depth, const std::string& dir) {
   auto s = std::make_unique<TplEmbed>(N, depth, dir);
   TplEmbed* p = s.get();
   g_tplembed.emplace(k, std::move(s));
+  return p;
+}
+
+std::map<TplKey, std::unique_ptr<sm::StructureCore>> g_structure;
+
+sm::StructureCore* get_structure(int N, int depth, const std::string& dir) {
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  TplKey k{dev, N, depth, dir};
+  auto it = g_structure.find(k);
+  if (it != g_structure.end()) return it->second.get();
+  auto s = std::make_unique<sm::StructureCore>();
+  s->build(N, depth, dir);
+  sm::StructureCore* p = s.get();
+  g_structure.emplace(k, std::move(s));
+  fprintf(stderr, "native: structure module N=%d depth=%d (%.1f MB)\n", N, depth, p->A.bytes / 1e6);
   return p;
 }
 
@@ -216,8 +233,44 @@ int native_tplstack_prealloc(int N, int depth, const char* weights_dir) {
 
 int native_save_slots_probe(int depth, int /*n*/) { return depth; }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Structure-module core (fold iterations: invariant point attention, transition, backbone update).
+int bc2_structure_module_fwd(void* stream, const float* single, const float* pair, const float* seq_mask, int64_t N,
+                             int64_t depth, const char* weights_dir, float* act_out, float* rigids_out) {
+  try {
+    BC2_CHECK(single && pair && seq_mask && weights_dir, "null operand");
+    BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    sm::StructureCore* s = get_structure((int)N, (int)depth, weights_dir);
+    s->forward(single, pair, seq_mask, act_out, rigids_out, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_structure_module_bwd(void* stream, const float* single, const float* pair, const float* seq_mask, const float* d_act,
+                             const float* d_rigids, int64_t N, int64_t depth, const char* weights_dir, float* d_single,
+                             float* d_pair) {
+  try {
+    BC2_CHECK(single && pair && seq_mask && d_act && d_rigids && d_single && d_pair && weights_dir, "null operand");
+    BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    sm::StructureCore* s = get_structure((int)N, (int)depth, weights_dir);
+    cudaStream_t st = (cudaStream_t)stream;
+    s->forward(single, pair, seq_mask, nullptr, nullptr, st);  // replay: the call reads only its operands
+    s->backward(single, pair, d_act, d_rigids, d_single, d_pair, st);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 void bc2_release_all(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
+  g_structure.clear();
   g_stacks.clear();
   g_tpl.clear();
   g_tplembed.clear();

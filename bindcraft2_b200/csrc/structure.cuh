@@ -1,0 +1,358 @@
+// Structure-module core: single/pair layer norms, initial projection and eight shared-weight fold iterations
+// (invariant point attention + transition + quaternion backbone update), forward and backward to (single, pair).
+// Reference: bindcraft/af/alphafold/model/folding_multimer.py:65-137 (QuatRigid), :140-185 (PointProjection),
+// :188-371 (InvariantPointAttention), :374-474 (FoldIteration, rotation gradient not stopped), :477-556
+// (generate_monomer_rigids); geometry/rotation_matrix.py:117-140; config.py:574-605.
+//
+// Everything here is fp32 on CUDA cores, as in the reference (its point and rigid Linears ask for HIGHEST precision and
+// the whole module runs in fp32): at N = 400 a full forward is 3 GFLOP, and the only large operand is the normalised pair
+// tensor [N,N,128], which every iteration reads twice (attention bias, attention over the pair rows).  The bias
+// Linear(128 -> 12) does not depend on the iteration (shared weights, static pair input), so it is computed once,
+// fused into the pair LayerNorm; per iteration the pair tensor is then read once, by the attention kernel.
+//
+// Data kept per iteration for the backward (N = 400: 12 MB each): layer input, frames, projections, attention
+// probabilities, concatenated attention output, pre-norm activations, transition hidden layers, rigid update.
+#pragma once
+#include "common.cuh"
+#include "weights.cuh"
+
+namespace bc2 {
+namespace sm {
+
+constexpr int CS = 384, CZ = 128, H = 12, SQK = 16, SV = 16, PQK = 4, PV = 8;
+constexpr int NPROJ = H * (SQK + SQK + SV) + H * 3 * (PQK + PQK + PV);  // 576 + 576 = 1152
+constexpr int OFF_QS = 0, OFF_KS = H * SQK, OFF_VS = 2 * H * SQK, OFF_QP = OFF_VS + H * SV, OFF_KP = OFF_QP + H * 3 * PQK,
+              OFF_VP = OFF_KP + H * 3 * PQK;
+constexpr int NFINAL = H * SV + 4 * H * PV + H * CZ;  // 192 + 384 + 1536 = 2112
+constexpr int F_S = 0, F_X = H * SV, F_Y = F_X + H * PV, F_Z = F_Y + H * PV, F_N = F_Z + H * PV, F_2D = F_N + H * PV;
+constexpr float POSITION_SCALE = 20.f, DIST_EPS2 = 1e-16f;
+constexpr float SQRT13 = 0.5773502691896258f;  // sqrt(1/3): three logit terms
+
+// ------------------------------------------------------------------------------------------- LayerNorm (fp32 out)
+// warp per row; optionally emits the attention bias  b2d[row][h] = y . w2d[:,h] + b2d_bias[h]  (pair norm only)
+template <int C>
+__global__ void __launch_bounds__(256)
+ln_f32_kernel(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ offset,
+              float* __restrict__ y, long M, const float* __restrict__ w2d /*[C][H]*/, const float* __restrict__ b2d_bias,
+              float* __restrict__ b2d /*[M][H]*/) {
+  constexpr int V = C / 32;
+  const int lane = threadIdx.x & 31;
+  const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (m >= M) return;
+  float v[V];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) { v[i] = x[m * C + i * 32 + lane]; s += v[i]; }
+  const float mean = warp_sum(s) * (1.f / C);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) { const float d = v[i] - mean; q += d * d; }
+  const float rstd = rsqrtf(warp_sum(q) * (1.f / C) + 1e-5f);
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    const int c = i * 32 + lane;
+    v[i] = (v[i] - mean) * rstd * scale[c] + offset[c];
+    y[m * C + c] = v[i];
+  }
+  if (w2d) {
+    for (int h = 0; h < H; ++h) {
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < V; ++i) a += v[i] * w2d[(i * 32 + lane) * H + h];
+      a = warp_sum(a);
+      if (lane == 0) b2d[m * H + h] = a + b2d_bias[h];
+    }
+  }
+}
+
+// dx = LN'(x)^T (dy + sum_h db2d[row][h] w2d[:,h]);  written to dx (no accumulation)
+template <int C>
+__global__ void __launch_bounds__(256)
+ln_f32_bwd_kernel(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ dy, float* __restrict__ dx,
+                  long M, const float* __restrict__ w2d, const float* __restrict__ db2d) {
+  constexpr int V = C / 32;
+  const int lane = threadIdx.x & 31;
+  const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (m >= M) return;
+  float v[V], d[V];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) { v[i] = x[m * C + i * 32 + lane]; s += v[i]; d[i] = dy ? dy[m * C + i * 32 + lane] : 0.f; }
+  if (w2d) {
+    for (int h = 0; h < H; ++h) {
+      const float gb = db2d[m * H + h];
+#pragma unroll
+      for (int i = 0; i < V; ++i) d[i] += gb * w2d[(i * 32 + lane) * H + h];
+    }
+  }
+  const float mean = warp_sum(s) * (1.f / C);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) { const float t = v[i] - mean; q += t * t; }
+  const float rstd = rsqrtf(warp_sum(q) * (1.f / C) + 1e-5f);
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    v[i] = (v[i] - mean) * rstd;
+    d[i] *= scale[i * 32 + lane];
+    s1 += d[i];
+    s2 += d[i] * v[i];
+  }
+  s1 = warp_sum(s1) * (1.f / C);
+  s2 = warp_sum(s2) * (1.f / C);
+#pragma unroll
+  for (int i = 0; i < V; ++i) dx[m * C + i * 32 + lane] = rstd * (d[i] - s1 - v[i] * s2);
+}
+
+// ------------------------------------------------------------------------------------------- Linear (fp32)
+// Y[M,N] = act(X[M,K] W[K,N] + bias) (+ R) (* (G > 0)).  64x64 tile, 256 threads, 4x4 outputs per thread.
+struct LinArgs {
+  const float* X = nullptr; const float* W = nullptr; const float* bias = nullptr;
+  const float* R = nullptr;     // residual added after the activation, or null
+  const float* G = nullptr;     // ReLU gate of the backward: output multiplied by (G > 0), or null
+  float* Y = nullptr;
+  int M = 0, N = 0, K = 0, relu = 0, accumulate = 0;  // accumulate: Y += result
+};
+__global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
+  __shared__ float sX[16][64 + 1], sW[16][64];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < a.K; k0 += 16) {
+    for (int t = threadIdx.x; t < 64 * 16; t += 256) {
+      const int r = t >> 4, k = t & 15;
+      sX[k][r] = (m0 + r < a.M && k0 + k < a.K) ? a.X[(long)(m0 + r) * a.K + k0 + k] : 0.f;
+      const int kk = t >> 6, c = t & 63;
+      sW[kk][c] = (k0 + kk < a.K && n0 + c < a.N) ? a.W[(long)(k0 + kk) * a.N + n0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float xv[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xv[i] = sX[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) wv[j] = sW[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += xv[i] * wv[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= a.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= a.N) continue;
+      float v = acc[i][j] + (a.bias ? a.bias[n] : 0.f);
+      if (a.relu) v = fmaxf(v, 0.f);
+      const long idx = (long)m * a.N + n;
+      if (a.R) v += a.R[idx];
+      if (a.G) v = a.G[idx] > 0.f ? v : 0.f;
+      a.Y[idx] = a.accumulate ? a.Y[idx] + v : v;
+    }
+  }
+}
+inline void linear_f32(const LinArgs& a, cudaStream_t st) {
+  dim3 grid(cdiv(a.N, 64), cdiv(a.M, 64));
+  launch_counter()++; linear_f32_kernel<<<grid, 256, 0, st>>>(a);
+}
+
+__global__ void add_f32_inplace_kernel(float* __restrict__ y, const float* __restrict__ x, long n) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < n) y[t] += x[t];
+}
+
+// ------------------------------------------------------------------------------------------- rigid frames
+// Frames are stored per residue as 12 floats: rotation row-major (xx xy xz yx yy yz zx zy zz), then translation.
+__device__ __forceinline__ void quat_rot(float x, float y, float z, float (&r)[9]) {
+  // Rot3Array.from_quaternion(w = 1, x, y, z, normalize=True), rotation_matrix.py:117-140
+  const float inv = rsqrtf(fmaxf(1e-6f, 1.f + x * x + y * y + z * z));
+  const float w = inv;
+  x *= inv; y *= inv; z *= inv;
+  r[0] = 1 - 2 * (y * y + z * z); r[1] = 2 * (x * y - w * z); r[2] = 2 * (x * z + w * y);
+  r[3] = 2 * (x * y + w * z); r[4] = 1 - 2 * (x * x + z * z); r[5] = 2 * (y * z - w * x);
+  r[6] = 2 * (x * z - w * y); r[7] = 2 * (y * z + w * x); r[8] = 1 - 2 * (x * x + y * y);
+}
+// cotangent of (x, y, z) given the cotangent g of the 9 rotation entries
+__device__ __forceinline__ void quat_rot_bwd(float x0, float y0, float z0, const float (&g)[9], float (&d)[3]) {
+  const float n2 = 1.f + x0 * x0 + y0 * y0 + z0 * z0;  // >= 1, the clamp at 1e-6 never binds
+  const float inv = rsqrtf(n2);
+  const float w = inv, x = x0 * inv, y = y0 * inv, z = z0 * inv;
+  // cotangents of the normalised components
+  const float gw = 2 * (-z * g[1] + y * g[2] + z * g[3] - x * g[5] - y * g[6] + x * g[7]);
+  const float gx = 2 * (y * g[1] + z * g[2] + y * g[3] - 2 * x * g[4] - w * g[5] + z * g[6] + w * g[7] - 2 * x * g[8]);
+  const float gy = 2 * (-2 * y * g[0] + x * g[1] + w * g[2] + x * g[3] + z * g[5] - w * g[6] + z * g[7] - 2 * y * g[8]);
+  const float gz = 2 * (-2 * z * g[0] - w * g[1] + x * g[2] + w * g[3] - 2 * z * g[4] + y * g[5] + x * g[6] + y * g[7]);
+  // through the normalisation q = (1, x0, y0, z0) * inv:  d q_a / d u_b = inv (delta_ab - q_a q_b), u = (1, x0, y0, z0)
+  const float dotq = gw * w + gx * x + gy * y + gz * z;
+  d[0] = inv * (gx - x * dotq);
+  d[1] = inv * (gy - y * dotq);
+  d[2] = inv * (gz - z * dotq);
+}
+
+// ------------------------------------------------------------------------------------------- invariant point attention
+// proj [N][NPROJ]: q_s*(1/4) | k_s | v_s (each [H][16]) | q_pt | k_pt ([H][xyz][4]) | v_pt ([H][xyz][8]) in the local frame.
+// gpts [N][H][16][3]: the same points in the global frame, slots 0..3 q, 4..7 k, 8..15 v.
+constexpr int GP = 16;
+__global__ void __launch_bounds__(192)
+ipa_points_kernel(const float* __restrict__ proj, const float* __restrict__ rig, float* __restrict__ gpts) {
+  const int n = blockIdx.x, t = threadIdx.x;  // t = h*16 + slot
+  const int h = t >> 4, slot = t & 15;
+  const float* R = rig + (long)n * 12;
+  const float* pr = proj + (long)n * NPROJ;
+  float l[3];
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+    if (slot < 4) l[a] = pr[OFF_QP + h * 12 + a * 4 + slot];
+    else if (slot < 8) l[a] = pr[OFF_KP + h * 12 + a * 4 + (slot - 4)];
+    else l[a] = pr[OFF_VP + h * 24 + a * 8 + (slot - 8)];
+  }
+  float* g = gpts + ((long)n * H * GP + t) * 3;
+#pragma unroll
+  for (int a = 0; a < 3; ++a) g[a] = R[3 * a] * l[0] + R[3 * a + 1] * l[1] + R[3 * a + 2] * l[2] + R[9 + a];
+}
+
+// Forward attention of one query residue i (block = i).  Dynamic shared memory: N*H logits/probabilities.
+__global__ void __launch_bounds__(256)
+ipa_attn_fwd_kernel(const float* __restrict__ proj, const float* __restrict__ gpts, const float* __restrict__ rig,
+                    const float* __restrict__ pair_ln, const float* __restrict__ b2d, const float* __restrict__ mask,
+                    const float* __restrict__ pw /*[H] point weights*/, float* __restrict__ attn /*[N][N][H]*/,
+                    float* __restrict__ fin /*[N][NFINAL]*/, int N) {
+  extern __shared__ float sl[];  // [N][H]
+  __shared__ float sq[H * SQK], sgq[H * PQK * 3], spg[H * PV * 3], spw[H];
+  const int i = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int t = tid; t < H * SQK; t += 256) sq[t] = proj[(long)i * NPROJ + OFF_QS + t];
+  for (int t = tid; t < H * PQK * 3; t += 256) {
+    const int h = t / 12, r = t % 12;  // r = p*3 + a
+    sgq[t] = gpts[((long)i * H * GP + h * GP) * 3 + r];
+  }
+  if (tid < H) spw[tid] = pw[tid];
+  __syncthreads();
+  const float mi = mask[i];
+  for (int idx = tid; idx < N * H; idx += 256) {
+    const int j = idx / H, h = idx - j * H;
+    const float* ks = proj + (long)j * NPROJ + OFF_KS + h * SQK;
+    float qk = 0.f;
+#pragma unroll
+    for (int c = 0; c < SQK; ++c) qk += sq[h * SQK + c] * ks[c];
+    const float* gk = gpts + (((long)j * H + h) * GP + 4) * 3;
+    float d2 = 0.f;
+#pragma unroll
+    for (int r = 0; r < PQK * 3; ++r) {
+      const float d = sgq[h * 12 + r] - gk[r];
+      d2 += d * d;
+    }
+    float lg = -0.5f * spw[h] * d2 + qk + b2d[((long)i * N + j) * H + h] - 1e5f * (1.f - mi * mask[j]);
+    sl[idx] = lg * SQRT13;
+  }
+  __syncthreads();
+  for (int h = warp; h < H; h += 8) {  // softmax over keys, one warp per head
+    float mx = -INFINITY;
+    for (int j = lane; j < N; j += 32) mx = fmaxf(mx, sl[j * H + h]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int j = lane; j < N; j += 32) {
+      const float e = __expf(sl[j * H + h] - mx);
+      sl[j * H + h] = e;
+      sum += e;
+    }
+    const float inv = 1.f / warp_sum(sum);
+    for (int j = lane; j < N; j += 32) sl[j * H + h] *= inv;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < N * H; idx += 256) attn[(long)i * N * H + idx] = sl[idx];
+  float* fo = fin + (long)i * NFINAL;
+  {  // attention over the pair rows: thread = (channel c, group of 6 heads)
+    const int c = tid & 127, h0 = (tid >> 7) * 6;
+    float acc[6] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float* pr = pair_ln + (long)i * N * CZ + c;
+    for (int j = 0; j < N; ++j) {
+      const float pv = pr[(long)j * CZ];
+#pragma unroll
+      for (int hh = 0; hh < 6; ++hh) acc[hh] += sl[j * H + h0 + hh] * pv;
+    }
+#pragma unroll
+    for (int hh = 0; hh < 6; ++hh) fo[F_2D + (h0 + hh) * CZ + c] = acc[hh];
+  }
+  for (int o = tid; o < H * SV + H * PV * 3; o += 256) {
+    if (o < H * SV) {
+      const int h = o / SV;
+      float acc = 0.f;
+      for (int j = 0; j < N; ++j) acc += sl[j * H + h] * proj[(long)j * NPROJ + OFF_VS + o];
+      fo[F_S + o] = acc;
+    } else {
+      const int r = o - H * SV, h = r / 24, q = r % 24;  // q = p*3 + a
+      float acc = 0.f;
+      for (int j = 0; j < N; ++j) acc += sl[j * H + h] * gpts[(((long)j * H + h) * GP + 8) * 3 + q];
+      spg[r] = acc;
+    }
+  }
+  __syncthreads();
+  if (tid < H * PV) {  // back to the local frame: R^T (x - t), and the norm
+    const float* R = rig + (long)i * 12;
+    const float x0 = spg[tid * 3] - R[9], x1 = spg[tid * 3 + 1] - R[10], x2 = spg[tid * 3 + 2] - R[11];
+    const float l0 = R[0] * x0 + R[3] * x1 + R[6] * x2, l1 = R[1] * x0 + R[4] * x1 + R[7] * x2,
+                l2 = R[2] * x0 + R[5] * x1 + R[8] * x2;
+    fo[F_X + tid] = l0;
+    fo[F_Y + tid] = l1;
+    fo[F_Z + tid] = l2;
+    fo[F_N + tid] = sqrtf(fmaxf(l0 * l0 + l1 * l1 + l2 * l2, DIST_EPS2));
+  }
+}
+
+// rigid_new = rigid o update(upd): R' = R U(q), t' = R u + t      (thread per residue)
+__global__ void rigid_update_kernel(const float* __restrict__ rig, const float* __restrict__ upd, float* __restrict__ out, int N) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float* R = rig + (long)n * 12;
+  const float* u = upd + (long)n * 6;
+  float U[9];
+  quat_rot(u[0], u[1], u[2], U);
+  float* o = out + (long)n * 12;
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+#pragma unroll
+    for (int b = 0; b < 3; ++b) o[3 * a + b] = R[3 * a] * U[b] + R[3 * a + 1] * U[3 + b] + R[3 * a + 2] * U[6 + b];
+    o[9 + a] = R[3 * a] * u[3] + R[3 * a + 1] * u[4] + R[3 * a + 2] * u[5] + R[9 + a];
+  }
+}
+// Given the cotangent g_out of the new frame: cotangent of the old frame (ACCUMULATED into g_in) and of upd (written).
+__global__ void rigid_update_bwd_kernel(const float* __restrict__ rig, const float* __restrict__ upd, const float* __restrict__ g_out,
+                                        float* __restrict__ g_in, float* __restrict__ d_upd, int N) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const float* R = rig + (long)n * 12;
+  const float* u = upd + (long)n * 6;
+  const float* g = g_out + (long)n * 12;
+  float U[9], gU[9];
+  quat_rot(u[0], u[1], u[2], U);
+  float* gi = g_in + (long)n * 12;
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+      // R'_ab = sum_c R_ac U_cb:  dR_ac += g_ab U_cb ;  dU_cb += R_ac g_ab
+      gi[3 * a + b] += g[3 * a] * U[3 * b] + g[3 * a + 1] * U[3 * b + 1] + g[3 * a + 2] * U[3 * b + 2] + g[9 + a] * u[3 + b];
+      gU[3 * a + b] = R[a] * g[b] + R[3 + a] * g[3 + b] + R[6 + a] * g[6 + b];
+    }
+    gi[9 + a] += g[9 + a];
+  }
+  float dq[3];
+  quat_rot_bwd(u[0], u[1], u[2], gU, dq);
+  float* du = d_upd + (long)n * 6;
+  du[0] = dq[0]; du[1] = dq[1]; du[2] = dq[2];
+#pragma unroll
+  for (int b = 0; b < 3; ++b) du[3 + b] = R[b] * g[9] + R[3 + b] * g[10] + R[6 + b] * g[11];  // R^T g_t
+}
+
+}  // namespace sm
+}  // namespace bc2

@@ -1,0 +1,281 @@
+// Backward of the invariant point attention (see structure.cuh for layouts and the reference).
+//
+// Two kernels split the work by which residue a gradient belongs to:
+//   ipa_bwd_query_kernel  block = query residue i: attention-output adjoints, softmax backward (dlogit row i is written
+//                         out), gradients of q scalars / q points, the pair-row gradient, and this residue's frame
+//                         gradient from the output transform and the query points
+//   ipa_bwd_key_kernel    block = key residue j: sums over queries for k scalars, v scalars, k points, v points, and the
+//                         frame gradient they carry
+// Nothing is accumulated atomically: every output element has exactly one writer.
+#pragma once
+#include "structure.cuh"
+
+namespace bc2 {
+namespace sm {
+
+// frame gradient of a point: global g = R l + t.  Given the cotangent dg: dl = R^T dg, dR += dg (x) l, dt += dg.
+__device__ __forceinline__ void point_to_local_bwd(const float* R, const float (&l)[3], const float (&dg)[3], float (&dl)[3],
+                                                   float (&gr)[12]) {
+#pragma unroll
+  for (int b = 0; b < 3; ++b) dl[b] = R[b] * dg[0] + R[3 + b] * dg[1] + R[6 + b] * dg[2];
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+#pragma unroll
+    for (int b = 0; b < 3; ++b) gr[3 * a + b] += dg[a] * l[b];
+    gr[9 + a] += dg[a];
+  }
+}
+
+// Block reduction of 12 per-thread partial sums (frame gradient) into out[12] (+=).  blockDim.x threads, red: [12][32].
+__device__ __forceinline__ void block_reduce12(float (&gr)[12], float* red, float* out, int nthreads) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int k = 0; k < 12; ++k) {
+    const float v = warp_sum(gr[k]);
+    if (lane == 0) red[k * 32 + warp] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 12) {
+    float v = 0.f;
+    for (int w = 0; w < nthreads / 32; ++w) v += red[threadIdx.x * 32 + w];
+    out[threadIdx.x] += v;
+  }
+  __syncthreads();
+}
+
+// Dynamic shared memory: 2*N*H floats (probabilities, then d_a / dlogit).
+__global__ void __launch_bounds__(256)
+ipa_bwd_query_kernel(const float* __restrict__ proj, const float* __restrict__ gpts, const float* __restrict__ rig,
+                     const float* __restrict__ pair_ln, const float* __restrict__ attn, const float* __restrict__ fin,
+                     const float* __restrict__ dfin /*[N][NFINAL]*/, const float* __restrict__ pw,
+                     float* __restrict__ dlogit /*[N][N][H]*/, float* __restrict__ db2d /*[N][N][H], accumulated*/,
+                     float* __restrict__ dpair_ln /*[N][N][CZ], accumulated*/, float* __restrict__ dopg /*[N][H*PV][3]*/,
+                     float* __restrict__ dproj /*[N][NPROJ]: q_s and q_pt parts*/, float* __restrict__ grig /*[N][12], accumulated*/,
+                     int N) {
+  extern __shared__ float sm_[];
+  float* sa = sm_;            // [N][H] probabilities
+  float* sd = sm_ + N * H;    // [N][H] d_a, then dlogit
+  __shared__ float sdf[NFINAL];
+  __shared__ float sdpg[H * PV * 3];
+  __shared__ float sgq[H * PQK * 3], sdgq[H * PQK * 3];
+  __shared__ float spw[H], red[12 * 32], sR[12];
+  const int i = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int t = tid; t < N * H; t += 256) sa[t] = attn[(long)i * N * H + t];
+  for (int t = tid; t < NFINAL; t += 256) sdf[t] = dfin[(long)i * NFINAL + t];
+  for (int t = tid; t < H * PQK * 3; t += 256) {
+    const int h = t / 12, r = t % 12;
+    sgq[t] = gpts[((long)i * H * GP + h * GP) * 3 + r];
+  }
+  if (tid < H) spw[tid] = pw[tid];
+  if (tid < 12) sR[tid] = rig[(long)i * 12 + tid];
+  __syncthreads();
+  float gr[12];
+#pragma unroll
+  for (int k = 0; k < 12; ++k) gr[k] = 0.f;
+  // --- output transform: local = R^T (pg - t); norm.  thread = point (h, p)
+  if (tid < H * PV) {
+    const float* fo = fin + (long)i * NFINAL;
+    const float l[3] = {fo[F_X + tid], fo[F_Y + tid], fo[F_Z + tid]};
+    const float n2 = l[0] * l[0] + l[1] * l[1] + l[2] * l[2];
+    float dl[3] = {sdf[F_X + tid], sdf[F_Y + tid], sdf[F_Z + tid]};
+    if (n2 > DIST_EPS2) {  // below the clamp the norm is constant
+      const float s = sdf[F_N + tid] / fo[F_N + tid];
+      dl[0] += s * l[0]; dl[1] += s * l[1]; dl[2] += s * l[2];
+    }
+    // x = pg - t = R l;  l_a = sum_b R_ba x_b:  dx_b = sum_a R_ba dl_a ;  dR_ba += x_b dl_a ;  dt -= dx
+    float x[3], dx[3];
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+      x[b] = sR[3 * b] * l[0] + sR[3 * b + 1] * l[1] + sR[3 * b + 2] * l[2];
+      dx[b] = sR[3 * b] * dl[0] + sR[3 * b + 1] * dl[1] + sR[3 * b + 2] * dl[2];
+    }
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+#pragma unroll
+      for (int a = 0; a < 3; ++a) gr[3 * b + a] += x[b] * dl[a];
+      gr[9 + b] -= dx[b];
+      sdpg[tid * 3 + b] = dx[b];
+      dopg[((long)i * H * PV + tid) * 3 + b] = dx[b];
+    }
+  }
+  __syncthreads();
+  // --- d_a, pair term (warp per key j, lanes over channels) and the pair-row gradient
+  for (int j = warp; j < N; j += 8) {
+    const float4 pv = *reinterpret_cast<const float4*>(pair_ln + ((long)i * N + j) * CZ + lane * 4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int h = 0; h < H; ++h) {
+      const float4 dv = *reinterpret_cast<const float4*>(&sdf[F_2D + h * CZ + lane * 4]);
+      float part = pv.x * dv.x + pv.y * dv.y + pv.z * dv.z + pv.w * dv.w;
+      part = warp_sum(part);
+      if (lane == 0) sd[j * H + h] = part;
+      const float a = sa[j * H + h];
+      acc.x += a * dv.x; acc.y += a * dv.y; acc.z += a * dv.z; acc.w += a * dv.w;
+    }
+    float4* dst = reinterpret_cast<float4*>(dpair_ln + ((long)i * N + j) * CZ + lane * 4);
+    float4 o = *dst;
+    o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
+    *dst = o;
+  }
+  __syncthreads();
+  // --- d_a, scalar and point value terms: thread = (j, h)
+  for (int idx = tid; idx < N * H; idx += 256) {
+    const int j = idx / H, h = idx - j * H;
+    const float* vs = proj + (long)j * NPROJ + OFF_VS + h * SV;
+    float acc = sd[idx];
+#pragma unroll
+    for (int c = 0; c < SV; ++c) acc += sdf[F_S + h * SV + c] * vs[c];
+    const float* gv = gpts + (((long)j * H + h) * GP + 8) * 3;
+#pragma unroll
+    for (int r = 0; r < PV * 3; ++r) acc += sdpg[h * PV * 3 + r] * gv[r];
+    sd[idx] = acc;
+  }
+  __syncthreads();
+  // --- softmax backward, one warp per head: dlogit = a (d_a - sum_j a d_a) * sqrt(1/3)
+  for (int h = warp; h < H; h += 8) {
+    float dot = 0.f;
+    for (int j = lane; j < N; j += 32) dot += sa[j * H + h] * sd[j * H + h];
+    dot = warp_sum(dot);
+    for (int j = lane; j < N; j += 32) sd[j * H + h] = sa[j * H + h] * (sd[j * H + h] - dot) * SQRT13;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < N * H; idx += 256) {
+    const float v = sd[idx];
+    dlogit[(long)i * N * H + idx] = v;
+    db2d[(long)i * N * H + idx] += v;
+  }
+  // --- query-side gradients: q scalars (192 outputs) and q points in the global frame (144 outputs)
+  for (int o = tid; o < H * SQK + H * PQK * 3; o += 256) {
+    if (o < H * SQK) {
+      const int h = o / SQK;
+      float acc = 0.f;
+      for (int j = 0; j < N; ++j) acc += sd[j * H + h] * proj[(long)j * NPROJ + OFF_KS + o];
+      dproj[(long)i * NPROJ + OFF_QS + o] = acc;
+    } else {
+      const int r = o - H * SQK, h = r / 12, q = r % 12;
+      float acc = 0.f;  // d/dgq of -0.5 w |gq - gk|^2 = -w (gq - gk)
+      for (int j = 0; j < N; ++j) acc += sd[j * H + h] * (sgq[r] - gpts[(((long)j * H + h) * GP + 4) * 3 + q]);
+      sdgq[r] = -spw[h] * acc;
+    }
+  }
+  __syncthreads();
+  if (tid < H * PQK) {  // q points back to the local frame; thread = (h, p)
+    const int h = tid / PQK, p = tid % PQK;
+    const float* pr = proj + (long)i * NPROJ + OFF_QP + h * 12;
+    const float l[3] = {pr[p], pr[4 + p], pr[8 + p]};
+    const float dg[3] = {sdgq[tid * 3], sdgq[tid * 3 + 1], sdgq[tid * 3 + 2]};
+    float dl[3];
+    point_to_local_bwd(sR, l, dg, dl, gr);
+    float* dp = dproj + (long)i * NPROJ + OFF_QP + h * 12;
+    dp[p] = dl[0]; dp[4 + p] = dl[1]; dp[8 + p] = dl[2];
+  }
+  block_reduce12(gr, red, grig + (long)i * 12, 256);
+}
+
+// block = key residue j.  Sums over queries, staged through shared memory eight queries at a time.
+constexpr int KCH = 8;
+__global__ void __launch_bounds__(256)
+ipa_bwd_key_kernel(const float* __restrict__ proj, const float* __restrict__ gpts, const float* __restrict__ rig,
+                   const float* __restrict__ attn, const float* __restrict__ dlogit, const float* __restrict__ dfin,
+                   const float* __restrict__ dopg, const float* __restrict__ pw, float* __restrict__ dproj,
+                   float* __restrict__ grig, int N) {
+  __shared__ float s_dl[KCH][H], s_a[KCH][H], s_qs[KCH][H * SQK], s_dos[KCH][H * SV], s_dpg[KCH][H * PV * 3],
+      s_gq[KCH][H * PQK * 3];
+  __shared__ float s_gk[H * PQK * 3], s_out[H * PQK * 3 + H * PV * 3], spw[H], red[12 * 32], sR[12];
+  const int j = blockIdx.x, tid = threadIdx.x;
+  for (int t = tid; t < H * PQK * 3; t += 256) {
+    const int h = t / 12, r = t % 12;
+    s_gk[t] = gpts[(((long)j * H + h) * GP + 4) * 3 + r];
+  }
+  if (tid < H) spw[tid] = pw[tid];
+  if (tid < 12) sR[tid] = rig[(long)j * 12 + tid];
+  // outputs: [0,192) d_k_s, [192,384) d_v_s, [384,528) d_gk, [528,816) d_gv; thread t owns t, t+256, t+512, t+768
+  constexpr int NOUT = H * SQK + H * SV + H * PQK * 3 + H * PV * 3;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i0 = 0; i0 < N; i0 += KCH) {
+    __syncthreads();
+    for (int t = tid; t < KCH * H; t += 256) {
+      const int ii = t / H, h = t % H, i = i0 + ii;
+      s_dl[ii][h] = i < N ? dlogit[((long)i * N + j) * H + h] : 0.f;
+      s_a[ii][h] = i < N ? attn[((long)i * N + j) * H + h] : 0.f;
+    }
+    for (int t = tid; t < KCH * H * SQK; t += 256) {
+      const int ii = t / (H * SQK), r = t % (H * SQK), i = i0 + ii;
+      s_qs[ii][r] = i < N ? proj[(long)i * NPROJ + OFF_QS + r] : 0.f;
+      s_dos[ii][r] = i < N ? dfin[(long)i * NFINAL + F_S + r] : 0.f;
+    }
+    for (int t = tid; t < KCH * H * PV * 3; t += 256) {
+      const int ii = t / (H * PV * 3), r = t % (H * PV * 3), i = i0 + ii;
+      s_dpg[ii][r] = i < N ? dopg[(long)i * H * PV * 3 + r] : 0.f;
+    }
+    for (int t = tid; t < KCH * H * PQK * 3; t += 256) {
+      const int ii = t / (H * PQK * 3), r = t % (H * PQK * 3), h = r / 12, q = r % 12, i = i0 + ii;
+      s_gq[ii][r] = i < N ? gpts[((long)i * H * GP + h * GP) * 3 + q] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int o = tid + 256 * k;
+      if (o >= NOUT) break;
+      float a = acc[k];
+      if (o < H * SQK) {
+        const int h = o / SQK;
+#pragma unroll
+        for (int ii = 0; ii < KCH; ++ii) a += s_dl[ii][h] * s_qs[ii][o];
+      } else if (o < H * SQK + H * SV) {
+        const int r = o - H * SQK, h = r / SV;
+#pragma unroll
+        for (int ii = 0; ii < KCH; ++ii) a += s_a[ii][h] * s_dos[ii][r];
+      } else if (o < H * SQK + H * SV + H * PQK * 3) {
+        const int r = o - H * SQK - H * SV, h = r / 12;
+#pragma unroll
+        for (int ii = 0; ii < KCH; ++ii) a += s_dl[ii][h] * (s_gq[ii][r] - s_gk[r]);  // padded rows have dl = 0
+      } else {
+        const int r = o - H * SQK - H * SV - H * PQK * 3, h = r / (PV * 3);
+#pragma unroll
+        for (int ii = 0; ii < KCH; ++ii) a += s_a[ii][h] * s_dpg[ii][r];
+      }
+      acc[k] = a;
+    }
+  }
+  __syncthreads();
+  float* dp = dproj + (long)j * NPROJ;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int o = tid + 256 * k;
+    if (o >= NOUT) break;
+    if (o < H * SQK) dp[OFF_KS + o] = acc[k];
+    else if (o < H * SQK + H * SV) dp[OFF_VS + (o - H * SQK)] = acc[k];
+    else if (o < H * SQK + H * SV + H * PQK * 3) {
+      const int r = o - H * SQK - H * SV;
+      s_out[r] = spw[r / 12] * acc[k];  // d/dgk of -0.5 w |gq - gk|^2 = +w (gq - gk)
+    } else s_out[H * PQK * 3 + (o - H * SQK - H * SV - H * PQK * 3)] = acc[k];
+  }
+  __syncthreads();
+  float gr[12];
+#pragma unroll
+  for (int k = 0; k < 12; ++k) gr[k] = 0.f;
+  if (tid < H * PQK) {  // k points
+    const int h = tid / PQK, p = tid % PQK;
+    const float* pr = proj + (long)j * NPROJ + OFF_KP + h * 12;
+    const float l[3] = {pr[p], pr[4 + p], pr[8 + p]};
+    const float dg[3] = {s_out[tid * 3], s_out[tid * 3 + 1], s_out[tid * 3 + 2]};
+    float dl[3];
+    point_to_local_bwd(sR, l, dg, dl, gr);
+    float* d = dp + OFF_KP + h * 12;
+    d[p] = dl[0]; d[4 + p] = dl[1]; d[8 + p] = dl[2];
+  } else if (tid >= 64 && tid < 64 + H * PV) {  // v points
+    const int t = tid - 64, h = t / PV, p = t % PV;
+    const float* pr = proj + (long)j * NPROJ + OFF_VP + h * 24;
+    const float l[3] = {pr[p], pr[8 + p], pr[16 + p]};
+    const float* so = s_out + H * PQK * 3;
+    const float dg[3] = {so[t * 3], so[t * 3 + 1], so[t * 3 + 2]};
+    float dl[3];
+    point_to_local_bwd(sR, l, dg, dl, gr);
+    float* d = dp + OFF_VP + h * 24;
+    d[p] = dl[0]; d[8 + p] = dl[1]; d[16 + p] = dl[2];
+  }
+  block_reduce12(gr, red, grig + (long)j * 12, 256);
+}
+
+}  // namespace sm
+}  // namespace bc2

@@ -1,0 +1,215 @@
+// Host side of the structure-module core: weights from a post-trunk manifest, buffers, forward and backward drivers.
+// Kernels and the reference they follow: structure.cuh, structure_bwd.cuh.
+#pragma once
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "structure_bwd.cuh"
+
+namespace bc2 {
+namespace sm {
+
+inline std::vector<float> transpose2d(const std::vector<float>& w, int rows, int cols) {
+  std::vector<float> t((size_t)rows * cols);
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < cols; ++c) t[(size_t)c * rows + r] = w[(size_t)r * cols + c];
+  return t;
+}
+
+__global__ void scale_translation_kernel(const float* __restrict__ in, float* __restrict__ out, float s, int n) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < n) out[t] = (t % 12 >= 9) ? in[t] * s : in[t];
+}
+
+struct Lin {
+  float *w = nullptr, *wt = nullptr, *b = nullptr;  // [K][N], [N][K], [N]
+  int K = 0, N = 0;
+  void set(DeviceArena& A, const std::vector<float>& W, const std::vector<float>& B, int k, int n) {
+    K = k; N = n;
+    BC2_CHECK((int)W.size() == k * n && (int)B.size() == n, "structure module: Linear shape mismatch");
+    w = A.upload(W);
+    wt = A.upload(transpose2d(W, k, n));
+    b = A.upload(B);
+  }
+};
+
+struct StructureCore {
+  int N = 0, L = 0;
+  DeviceArena A;
+  // weights
+  float *ln_s_scale, *ln_s_off, *ln_p_scale, *ln_p_off, *ln_a_scale, *ln_a_off, *ln_t_scale, *ln_t_off;
+  float *w2d, *b2d_bias, *pw;
+  Lin init, proj, out, t1, t2, t3, quat;
+  // forward state
+  float *single_ln, *pair_ln, *b2d;
+  std::vector<float*> act_in, rig, projv, gpts, attn, fin, act1, ln1, h1, h2, act2, upd;
+  // backward scratch
+  float *g_act, *dA, *dB, *tA, *tB, *d_fin, *d_proj, *dlogit, *db2d, *dpair_ln, *dopg, *g_rig[2], *d_upd;
+  size_t attn_smem = 0;
+
+  static std::vector<float> vec(const Manifest& m, const std::string& k) { return m.get(k).data; }
+
+  void build(int n, int depth, const std::string& dir) {
+    N = n; L = depth;
+    const Manifest m = Manifest::load(dir);
+    const std::string P = "param/", I = P + "fold_iteration/invariant_point_attention/", F = P + "fold_iteration/";
+    auto up = [&](const std::string& k, size_t expect) {
+      const auto& t = m.get(k);
+      BC2_CHECK(t.data.size() == expect, k + ": unexpected size");
+      return A.upload(t.data);
+    };
+    ln_s_scale = up(P + "single_layer_norm/scale", CS); ln_s_off = up(P + "single_layer_norm/offset", CS);
+    ln_p_scale = up(P + "pair_layer_norm/scale", CZ); ln_p_off = up(P + "pair_layer_norm/offset", CZ);
+    ln_a_scale = up(F + "attention_layer_norm/scale", CS); ln_a_off = up(F + "attention_layer_norm/offset", CS);
+    ln_t_scale = up(F + "transition_layer_norm/scale", CS); ln_t_off = up(F + "transition_layer_norm/offset", CS);
+    w2d = up(I + "attention_2d/weights", (size_t)CZ * H);
+    b2d_bias = up(I + "attention_2d/bias", H);
+    {  // point weights: sqrt(1 / (num_point_qk * 9/2)) * softplus(raw)   (folding_multimer.py:258-271)
+      std::vector<float> raw = vec(m, I + "trainable_point_weights"), w(H);
+      BC2_CHECK((int)raw.size() == H, "trainable_point_weights: unexpected size");
+      for (int h = 0; h < H; ++h) w[h] = std::sqrt(1.0 / (PQK * 9.0 / 2.0)) * std::log1p(std::exp((double)raw[h]));
+      pw = A.upload(w);
+    }
+    init.set(A, vec(m, P + "initial_projection/weights"), vec(m, P + "initial_projection/bias"), CS, CS);
+    {  // fused projection [384][1152]: q_s/4 | k_s | v_s | q_pt | k_pt | v_pt
+      std::vector<float> W((size_t)CS * NPROJ), B(NPROJ, 0.f);
+      struct Part { std::string key; int off, width; float scale; bool bias; };
+      const Part parts[6] = {{"q_scalar_projection", OFF_QS, H * SQK, 0.25f, false}, {"k_scalar_projection", OFF_KS, H * SQK, 1.f, false},
+                             {"v_scalar_projection", OFF_VS, H * SV, 1.f, false},
+                             {"q_point_projection/point_projection", OFF_QP, H * 3 * PQK, 1.f, true},
+                             {"k_point_projection/point_projection", OFF_KP, H * 3 * PQK, 1.f, true},
+                             {"v_point_projection/point_projection", OFF_VP, H * 3 * PV, 1.f, true}};
+      for (const Part& p : parts) {
+        const auto& w = m.get(I + p.key + "/weights").data;
+        BC2_CHECK((int)w.size() == CS * p.width, p.key + ": unexpected weight size");
+        for (int c = 0; c < CS; ++c)
+          for (int o = 0; o < p.width; ++o) W[(size_t)c * NPROJ + p.off + o] = p.scale * w[(size_t)c * p.width + o];
+        if (p.bias) {
+          const auto& b = m.get(I + p.key + "/bias").data;
+          BC2_CHECK((int)b.size() == p.width, p.key + ": unexpected bias size");
+          for (int o = 0; o < p.width; ++o) B[p.off + o] = b[o];
+        }
+      }
+      proj.set(A, W, B, CS, NPROJ);
+    }
+    out.set(A, vec(m, I + "output_projection/weights"), vec(m, I + "output_projection/bias"), NFINAL, CS);
+    t1.set(A, vec(m, F + "transition/weights"), vec(m, F + "transition/bias"), CS, CS);
+    t2.set(A, vec(m, F + "transition_1/weights"), vec(m, F + "transition_1/bias"), CS, CS);
+    t3.set(A, vec(m, F + "transition_2/weights"), vec(m, F + "transition_2/bias"), CS, CS);
+    quat.set(A, vec(m, F + "quat_rigid/rigid/weights"), vec(m, F + "quat_rigid/rigid/bias"), CS, 6);
+
+    const size_t n1 = (size_t)N, n2 = n1 * N;
+    single_ln = A.alloc<float>(n1 * CS);
+    pair_ln = A.alloc<float>(n2 * CZ);
+    b2d = A.alloc<float>(n2 * H);
+    for (int l = 0; l <= L; ++l) {
+      act_in.push_back(A.alloc<float>(n1 * CS));
+      rig.push_back(A.alloc<float>(n1 * 12));
+    }
+    for (int l = 0; l < L; ++l) {
+      projv.push_back(A.alloc<float>(n1 * NPROJ));
+      gpts.push_back(A.alloc<float>(n1 * H * GP * 3));
+      attn.push_back(A.alloc<float>(n2 * H));
+      fin.push_back(A.alloc<float>(n1 * NFINAL));
+      act1.push_back(A.alloc<float>(n1 * CS));
+      ln1.push_back(A.alloc<float>(n1 * CS));
+      h1.push_back(A.alloc<float>(n1 * CS));
+      h2.push_back(A.alloc<float>(n1 * CS));
+      act2.push_back(A.alloc<float>(n1 * CS));
+      upd.push_back(A.alloc<float>(n1 * 6));
+    }
+    g_act = A.alloc<float>(n1 * CS); dA = A.alloc<float>(n1 * CS); dB = A.alloc<float>(n1 * CS);
+    tA = A.alloc<float>(n1 * CS); tB = A.alloc<float>(n1 * CS);
+    d_fin = A.alloc<float>(n1 * NFINAL); d_proj = A.alloc<float>(n1 * NPROJ);
+    dlogit = A.alloc<float>(n2 * H); db2d = A.alloc<float>(n2 * H); dpair_ln = A.alloc<float>(n2 * CZ);
+    dopg = A.alloc<float>(n1 * H * PV * 3);
+    g_rig[0] = A.alloc<float>(n1 * 12); g_rig[1] = A.alloc<float>(n1 * 12);
+    d_upd = A.alloc<float>(n1 * 6);
+    attn_smem = 2 * n2 / N * H * sizeof(float);  // 2 * N * H floats
+    BC2_CHECK(attn_smem + 16 * 1024 <= 227 * 1024, "structure module: N too large for the per-query shared-memory rows");
+    BC2_CUDA(cudaFuncSetAttribute(ipa_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem / 2));
+    BC2_CUDA(cudaFuncSetAttribute(ipa_bwd_query_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
+  }
+
+  template <int C>
+  void ln(const float* x, const float* sc, const float* of, float* y, long M, cudaStream_t st, const float* w = nullptr,
+          const float* bb = nullptr, float* bo = nullptr) {
+    launch_counter()++; ln_f32_kernel<C><<<(unsigned)cdiv(M, 8L), 256, 0, st>>>(x, sc, of, y, M, w, bb, bo);
+  }
+  template <int C>
+  void ln_bwd(const float* x, const float* sc, const float* dy, float* dx, long M, cudaStream_t st, const float* w = nullptr,
+              const float* db = nullptr) {
+    launch_counter()++; ln_f32_bwd_kernel<C><<<(unsigned)cdiv(M, 8L), 256, 0, st>>>(x, sc, dy, dx, M, w, db);
+  }
+  void lin(const float* X, const float* W, const float* b, float* Y, int K, int Nn, cudaStream_t st, int relu = 0,
+           const float* R = nullptr, const float* G = nullptr, int accumulate = 0) {
+    LinArgs a; a.X = X; a.W = W; a.bias = b; a.Y = Y; a.M = N; a.N = Nn; a.K = K; a.relu = relu; a.R = R; a.G = G;
+    a.accumulate = accumulate;
+    linear_f32(a, st);
+  }
+
+  void forward(const float* single, const float* pair, const float* mask, float* act_out, float* rig_out, cudaStream_t st) {
+    const long n2 = (long)N * N;
+    ln<CS>(single, ln_s_scale, ln_s_off, single_ln, N, st);
+    lin(single_ln, init.w, init.b, act_in[0], CS, CS, st);
+    ln<CZ>(pair, ln_p_scale, ln_p_off, pair_ln, n2, st, w2d, b2d_bias, b2d);
+    {
+      std::vector<float> id((size_t)N * 12, 0.f);
+      for (int i = 0; i < N; ++i) id[(size_t)i * 12] = id[(size_t)i * 12 + 4] = id[(size_t)i * 12 + 8] = 1.f;
+      BC2_CUDA(cudaMemcpyAsync(rig[0], id.data(), id.size() * 4, cudaMemcpyHostToDevice, st));
+      BC2_CUDA(cudaStreamSynchronize(st));  // the host vector goes out of scope
+    }
+    for (int l = 0; l < L; ++l) {
+      lin(act_in[l], proj.w, proj.b, projv[l], CS, NPROJ, st);
+      launch_counter()++; ipa_points_kernel<<<N, H * GP, 0, st>>>(projv[l], rig[l], gpts[l]);
+      launch_counter()++; ipa_attn_fwd_kernel<<<N, 256, attn_smem / 2, st>>>(projv[l], gpts[l], rig[l], pair_ln, b2d, mask, pw, attn[l], fin[l], N);
+      lin(fin[l], out.w, out.b, act1[l], NFINAL, CS, st, 0, act_in[l]);
+      ln<CS>(act1[l], ln_a_scale, ln_a_off, ln1[l], N, st);
+      lin(ln1[l], t1.w, t1.b, h1[l], CS, CS, st, 1);
+      lin(h1[l], t2.w, t2.b, h2[l], CS, CS, st, 1);
+      lin(h2[l], t3.w, t3.b, act2[l], CS, CS, st, 0, ln1[l]);
+      ln<CS>(act2[l], ln_t_scale, ln_t_off, act_in[l + 1], N, st);
+      lin(act_in[l + 1], quat.w, quat.b, upd[l], CS, 6, st);
+      launch_counter()++; rigid_update_kernel<<<cdiv(N, 128), 128, 0, st>>>(rig[l], upd[l], rig[l + 1], N);
+    }
+    if (act_out) BC2_CUDA(cudaMemcpyAsync(act_out, act_in[L], (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
+    if (rig_out) { launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(rig[L], rig_out, POSITION_SCALE, N * 12); }
+  }
+
+  // Cotangents d_act [N,384] and d_rig [N,12] (rotation entries, then the SCALED translation) -> d_single, d_pair.
+  // The forward state of the same inputs must be in place (the caller replays the forward first).
+  void backward(const float* single, const float* pair, const float* d_act, const float* d_rig, float* d_single,
+                float* d_pair, cudaStream_t st) {
+    const long n2 = (long)N * N;
+    BC2_CUDA(cudaMemcpyAsync(g_act, d_act, (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
+    launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(d_rig, g_rig[0], POSITION_SCALE, N * 12);
+    BC2_CUDA(cudaMemsetAsync(db2d, 0, (size_t)n2 * H * 4, st));
+    BC2_CUDA(cudaMemsetAsync(dpair_ln, 0, (size_t)n2 * CZ * 4, st));
+    int cur = 0;
+    for (int l = L - 1; l >= 0; --l) {
+      float* g_out = g_rig[cur];
+      float* g_in = g_rig[cur ^ 1];
+      BC2_CUDA(cudaMemsetAsync(g_in, 0, (size_t)N * 12 * 4, st));
+      launch_counter()++; rigid_update_bwd_kernel<<<cdiv(N, 128), 128, 0, st>>>(rig[l], upd[l], g_out, g_in, d_upd, N);
+      lin(d_upd, quat.wt, nullptr, g_act, 6, CS, st, 0, nullptr, nullptr, 1);         // g_act += d_upd Wq^T
+      ln_bwd<CS>(act2[l], ln_t_scale, g_act, dA, N, st);                               // dA = d(act2)
+      lin(dA, t3.wt, nullptr, tA, CS, CS, st, 0, nullptr, h2[l]);                      // d(h2 pre-relu)
+      lin(tA, t2.wt, nullptr, tB, CS, CS, st, 0, nullptr, h1[l]);                      // d(h1 pre-relu)
+      lin(tB, t1.wt, nullptr, tA, CS, CS, st, 0, dA);                                  // d(ln1) = dA + . W1^T
+      ln_bwd<CS>(act1[l], ln_a_scale, tA, dB, N, st);                                  // dB = d(act1)
+      lin(dB, out.wt, nullptr, d_fin, CS, NFINAL, st);                                 // d(final)
+      launch_counter()++; ipa_bwd_query_kernel<<<N, 256, attn_smem, st>>>(projv[l], gpts[l], rig[l], pair_ln, attn[l], fin[l], d_fin, pw, dlogit,
+                                                     db2d, dpair_ln, dopg, d_proj, g_in, N);
+      launch_counter()++; ipa_bwd_key_kernel<<<N, 256, 0, st>>>(projv[l], gpts[l], rig[l], attn[l], dlogit, d_fin, dopg, pw, d_proj, g_in, N);
+      lin(d_proj, proj.wt, nullptr, g_act, NPROJ, CS, st, 0, dB);                      // g_act = dB + d_proj Wproj^T
+      cur ^= 1;
+    }
+    lin(g_act, init.wt, nullptr, dA, CS, CS, st);
+    ln_bwd<CS>(single, ln_s_scale, dA, d_single, N, st);
+    ln_bwd<CZ>(pair, ln_p_scale, dpair_ln, d_pair, n2, st, w2d, db2d);
+  }
+};
+
+}  // namespace sm
+}  // namespace bc2

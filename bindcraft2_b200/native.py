@@ -225,6 +225,40 @@ def template_embedding_bwd(ct, query, act_const, pair_mask, save, seed, *, depth
     return dq
 
 
+def structure_module_fwd(single, pair, seq_mask, *, depth=8, weights_dir):
+    """Fold iterations of the reference's ``native_post_trunk_fwd`` (handler native/ffi.cu:1009-1025; model code
+    folding_multimer.py:477-556) without side chains and heads: returns the final single activations [N,384] and the
+    backbone frames [N,12] (rotation row-major, then the translation in Angstrom)."""
+    lib = _lib.load()
+    n = int(single.shape[0])
+    _check_f32('single', single, (n, 384))
+    _check_f32('pair', pair, (n, n, CZ))
+    _check_f32('seq_mask', seq_mask, (n,))
+    act = torch.empty_like(single)
+    rig = torch.empty(n, 12, dtype=torch.float32, device=single.device)
+    stream = torch.cuda.current_stream(single.device).cuda_stream
+    with torch.cuda.device(single.device):
+        _lib.check(lib.bc2_structure_module_fwd(stream, _ptr(single), _ptr(pair), _ptr(seq_mask), n, int(depth),
+                                                os.fsencode(weights_dir), _ptr(act), _ptr(rig)))
+    return act, rig
+
+
+def structure_module_bwd(single, pair, seq_mask, d_act, d_rigids, *, depth=8, weights_dir):
+    """Backward of ``structure_module_fwd`` to (single, pair); replays the forward from its operands like the
+    reference's ``native_post_trunk_bwd`` (native/ffi.cu:1027-1043)."""
+    lib = _lib.load()
+    n = int(single.shape[0])
+    _check_f32('d_act', d_act, (n, 384))
+    _check_f32('d_rigids', d_rigids, (n, 12))
+    d_single, d_pair = torch.empty_like(single), torch.empty_like(pair)
+    stream = torch.cuda.current_stream(single.device).cuda_stream
+    with torch.cuda.device(single.device):
+        _lib.check(lib.bc2_structure_module_bwd(stream, _ptr(single), _ptr(pair), _ptr(seq_mask), _ptr(d_act),
+                                                _ptr(d_rigids), n, int(depth), os.fsencode(weights_dir), _ptr(d_single),
+                                                _ptr(d_pair)))
+    return d_single, d_pair
+
+
 def make_template_stack(weights_dir: str, depth: int = 2, dropout: bool = False):
     """(pair, pair_mask, seed) -> pair, differentiable in pair: the autograd pairing of the reference's template-stack
     ``custom_vjp`` (bindcraft/af/native.py:977-1046; residuals = pair_mask, save, seed)."""

@@ -83,6 +83,27 @@ int bc2_template_embedding_bwd(void* stream, const float* ct, const float* query
                                const float* pair_mask, const uint16_t* save, const uint32_t* seed, int64_t N,
                                int64_t depth, int64_t dropout, const char* weights_dir, float* dquery);
 
+/* Structure-module core: the fold iterations of the reference's StructureHeadsFwd / StructureHeadsBwd handlers
+ * (native/ffi.cu:1009-1043, FFI targets `native_post_trunk_fwd/bwd`; model code
+ * bindcraft/af/alphafold/model/folding_multimer.py:188-556) WITHOUT the side-chain atoms and the output heads, which are
+ * not built yet: instead of atom14 and head logits the forward returns the state those parts consume.
+ *   single f32 [N,384], pair f32 [N,N,128], seq_mask f32 [N] (the reference passes seq_mask (x) seq_mask as [N,N]; only
+ *   the product m_i m_j is used, modules_multimer.py:129,140), depth = number of fold iterations (8), weights_dir = the
+ *   post-trunk manifest (param/single_layer_norm, param/pair_layer_norm, param/initial_projection,
+ *   param/fold_iteration/...), read with the reference's key names.
+ *   -> act_out f32 [N,384] (final single activations), rigids_out f32 [N,12]: per residue the rotation row-major
+ *      (xx xy xz yx yy yz zx zy zz) then the translation in Angstrom (scaled by position_scale = 20, as 'final_rigids').
+ * All arithmetic is fp32, as in the reference.  No padding requirement on N. */
+int bc2_structure_module_fwd(void* stream, const float* single, const float* pair, const float* seq_mask, int64_t N,
+                             int64_t depth, const char* weights_dir, float* act_out, float* rigids_out);
+
+/* Backward of the above to (single, pair), weights frozen.  Like StructureHeadsBwd it replays the forward from its
+ * operands first (native/ffi.cu:1027-1043), so it reads nothing but its arguments.  d_act f32 [N,384] and
+ * d_rigids f32 [N,12] are the cotangents of the two forward results. */
+int bc2_structure_module_bwd(void* stream, const float* single, const float* pair, const float* seq_mask, const float* d_act,
+                             const float* d_rigids, int64_t N, int64_t depth, const char* weights_dir, float* d_single,
+                             float* d_pair);
+
 /* Same contract as the reference's native_tplembed_prealloc (native/ffi.cu:918-931). */
 int native_tplembed_prealloc(int N, int depth, const char* weights_dir);
 
