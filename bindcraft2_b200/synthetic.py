@@ -227,3 +227,63 @@ def make_structure_inputs(seed: int, n: int, cs=384, cz=128, masked=0):
     return dict(single=torch.randn(n, cs, generator=g), pair=torch.randn(n, n, cz, generator=g), seq_mask=mask,
                 ct_act=torch.randn(n, cs, generator=g), ct_rot=torch.randn(n, 3, 3, generator=g),
                 ct_trans=0.1 * torch.randn(n, 3, generator=g))
+
+
+def add_structure_head_params(p: Params, seed: int, cs=384, cz=128, sc=128) -> Params:
+    """Side-chain network and output heads (post-trunk manifest keys), added to ``make_structure_params`` output.
+    Zero-initialised layers of the reference get the 'linear' initialiser, as above."""
+    g = torch.Generator().manual_seed(seed)
+    s = 'fold_iteration/rigid_sidechain'
+    for nm in ('input_projection', 'input_projection_1'):
+        p[f'{s}/{nm}/weights'] = _lin(g, cs, (cs, sc))
+        p[f'{s}/{nm}/bias'] = 0.02 * torch.randn(sc, generator=g)
+    for nm in ('resblock1', 'resblock2', 'resblock1_1', 'resblock2_1'):
+        p[f'{s}/{nm}/weights'] = _lin(g, sc, (sc, sc), 'relu' if 'resblock1' in nm else 'linear')
+        p[f'{s}/{nm}/bias'] = 0.02 * torch.randn(sc, generator=g)
+    p[f'{s}/unnormalized_angles/weights'] = _lin(g, sc, (sc, 14))
+    p[f'{s}/unnormalized_angles/bias'] = 0.1 * torch.randn(14, generator=g)
+    for nm, cin, cout in (('distogram_head/half_logits', cz, 64), ('predicted_aligned_error_head/logits', cz, 64),
+                          ('predicted_lddt_head/act_0', cs, 128), ('predicted_lddt_head/act_1', 128, 128),
+                          ('predicted_lddt_head/logits', 128, 50), ('experimentally_resolved_head/logits', cs, 37)):
+        p[f'{nm}/weights'] = _lin(g, cin, (cin, cout), 'relu' if 'act_' in nm else 'linear')
+        p[f'{nm}/bias'] = 0.02 * torch.randn(cout, generator=g)
+    p['predicted_lddt_head/input_layer_norm/scale'], p['predicted_lddt_head/input_layer_norm/offset'] = _ln(g, cs)
+    return p
+
+
+def make_structure_tables(seed: int):
+    """SYNTHETIC stand-ins for the residue tables the reference exports into the post-trunk manifest
+    (``const/default_frame`` [21,8,4,4], ``const/atom14_to_group`` [21,14], ``const/atom14_lit_pos`` [21,14,3],
+    ``const/atom14_mask`` [21,14]; bindcraft/af/native.py:419-426).  The kernels read whatever the manifest holds, so
+    parity is checked on seeded random rigid frames and positions of the same shapes: proper rotations with
+    translations of a few Angstrom (group 0 = identity, as for the backbone group), every atom assigned to a random
+    group, about three quarters of the atom slots present."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(21, 8, 4, generator=g)
+    q = q / q.norm(dim=-1, keepdim=True)
+    w, x, y, z = q.unbind(-1)
+    rot = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - w * z), 2 * (x * z + w * y),
+                       2 * (x * y + w * z), 1 - 2 * (x * x + z * z), 2 * (y * z - w * x),
+                       2 * (x * z - w * y), 2 * (y * z + w * x), 1 - 2 * (x * x + y * y)], -1).reshape(21, 8, 3, 3)
+    frame = torch.zeros(21, 8, 4, 4)
+    frame[..., :3, :3] = rot
+    frame[..., :3, 3] = 1.5 * torch.randn(21, 8, 3, generator=g)
+    frame[..., 3, 3] = 1.0
+    frame[:, 0] = torch.eye(4)
+    return dict(default_frame=frame, atom14_to_group=torch.randint(0, 8, (21, 14), generator=g).float(),
+                atom14_lit_pos=1.5 * torch.randn(21, 14, 3, generator=g),
+                atom14_mask=(torch.rand(21, 14, generator=g) < 0.75).float())
+
+
+def add_structure_head_inputs(inp, seed: int):
+    """aatype (0..20) and cotangents of the five post-trunk outputs, added to ``make_structure_inputs`` output."""
+    g = torch.Generator().manual_seed(seed)
+    n = inp['single'].shape[0]
+    inp = dict(inp)
+    inp['aatype'] = torch.randint(0, 21, (n,), generator=g)
+    inp['ct_atom14'] = 0.1 * torch.randn(n, 14, 3, generator=g)
+    inp['ct_dgram'] = torch.randn(n, n, 64, generator=g)
+    inp['ct_pae'] = torch.randn(n, n, 64, generator=g)
+    inp['ct_plddt'] = torch.randn(n, 50, generator=g)
+    inp['ct_expres'] = torch.randn(n, 37, generator=g)
+    return inp

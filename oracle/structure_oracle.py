@@ -133,5 +133,90 @@ def structure_core_fwd_bwd(p: Params, inp, depth=NUM_LAYER, dtype=torch.float32)
     return dict(act=act.detach(), rot=rot.detach(), trans=trans.detach(), d_single=d_single, d_pair=d_pair)
 
 
+# ----------------------------------------------------------------------------- side chains and heads
+SC = 'fold_iteration/rigid_sidechain'
+
+
+def _compose(r1, t1, r2, t2):
+    """Rigid3Array.__matmul__ (rigid_matrix_vector.py:37-40): (r1,t1) o (r2,t2)."""
+    return r1 @ r2, torch.einsum('...ab,...b->...a', r1, t2) + t1
+
+
+def sidechain_atoms(p: Params, tables, act, initial_act, rot, trans, aatype):
+    """MultiRigidSidechain (folding_multimer.py:950-1033) + torsion_angles_to_frames and
+    frames_and_literature_positions_to_atom14_pos (all_atom_multimer.py:370-469).
+    rot/trans: backbone frames with the translation in Angstrom.  tables: dict with default_frame [21,8,4,4],
+    atom14_to_group [21,14] (int), atom14_lit_pos [21,14,3], atom14_mask [21,14].  Returns atom14 positions [N,14,3]."""
+    lin = lambda name, x: x @ p[f'{SC}/{name}/weights'] + p[f'{SC}/{name}/bias']
+    x = lin('input_projection', torch.relu(act)) + lin('input_projection_1', torch.relu(initial_act))
+    for suffix in ('', '_1'):
+        old = x
+        x = lin('resblock1' + suffix, torch.relu(x))
+        x = lin('resblock2' + suffix, torch.relu(x))
+        x = x + old
+    n = act.shape[0]
+    ua = lin('unnormalized_angles', torch.relu(x)).reshape(n, 7, 2)
+    ang = ua / torch.sqrt(torch.clamp((ua ** 2).sum(-1, keepdim=True), min=1e-12))
+    m = tables['default_frame'].to(act.dtype)[aatype]                      # [N,8,4,4]
+    r_d, t_d = m[..., :3, :3], m[..., :3, 3]
+    sin = torch.cat([torch.zeros(n, 1, dtype=act.dtype), ang[..., 0]], -1)  # [N,8]
+    cos = torch.cat([torch.ones(n, 1, dtype=act.dtype), ang[..., 1]], -1)
+    zero, one = torch.zeros_like(sin), torch.ones_like(sin)
+    rotx = torch.stack([one, zero, zero, zero, cos, -sin, zero, sin, cos], -1).reshape(n, 8, 3, 3)
+    r_a, t_a = r_d @ rotx, t_d                                             # default o rotation about x
+    frames_r, frames_t = [r_a[:, k] for k in range(5)], [t_a[:, k] for k in range(5)]
+    r, t = r_a[:, 4], t_a[:, 4]
+    for k in (5, 6, 7):
+        r, t = _compose(r, t, r_a[:, k], t_a[:, k])
+        frames_r.append(r)
+        frames_t.append(t)
+    fr, ft = torch.stack(frames_r, 1), torch.stack(frames_t, 1)            # to backbone, [N,8,...]
+    gr, gt = _compose(rot[:, None], trans[:, None], fr, ft)                # to global
+    grp = tables['atom14_to_group'][aatype].long()                          # [N,14]
+    idx = torch.arange(n)[:, None]
+    ar, at = gr[idx, grp], gt[idx, grp]                                     # [N,14,3,3], [N,14,3]
+    lit = tables['atom14_lit_pos'].to(act.dtype)[aatype]
+    pos = torch.einsum('nkab,nkb->nka', ar, lit) + at
+    return pos * tables['atom14_mask'].to(act.dtype)[aatype][..., None]
+
+
+def heads(p: Params, single, pair, act):
+    """Distogram (modules.py:1091-1125), predicted aligned error (:823-861), pLDDT (:777-820) and experimentally
+    resolved (:864-906) logits."""
+    half = pair @ p['distogram_head/half_logits/weights'] + p['distogram_head/half_logits/bias']
+    dgram = half + half.transpose(0, 1)
+    pae = pair @ p['predicted_aligned_error_head/logits/weights'] + p['predicted_aligned_error_head/logits/bias']
+    h = layer_norm(act, p['predicted_lddt_head/input_layer_norm/scale'], p['predicted_lddt_head/input_layer_norm/offset'])
+    h = torch.relu(h @ p['predicted_lddt_head/act_0/weights'] + p['predicted_lddt_head/act_0/bias'])
+    h = torch.relu(h @ p['predicted_lddt_head/act_1/weights'] + p['predicted_lddt_head/act_1/bias'])
+    plddt = h @ p['predicted_lddt_head/logits/weights'] + p['predicted_lddt_head/logits/bias']
+    expres = single @ p['experimentally_resolved_head/logits/weights'] + p['experimentally_resolved_head/logits/bias']
+    return dgram, pae, plddt, expres
+
+
+def structure_heads(p: Params, tables, single, pair, seq_mask, aatype, depth=NUM_LAYER):
+    """What the reference's post-trunk call returns (native/ffi.cu:1009-1025): atom14 [N,14,3], distogram logits
+    [N,N,64], aligned-error logits [N,N,64], pLDDT logits [N,50], experimentally-resolved logits [N,37]."""
+    act, rot, trans = structure_core(p, single, pair, seq_mask, depth)
+    initial_act = layer_norm(single, p['single_layer_norm/scale'], p['single_layer_norm/offset'])
+    atom14 = sidechain_atoms(p, tables, act, initial_act, rot, trans, aatype)
+    return (atom14,) + heads(p, single, pair, act)
+
+
+HEAD_OUTS = ('atom14', 'dgram', 'pae', 'plddt', 'expres')
+
+
+def structure_heads_fwd_bwd(p: Params, tables, inp, depth=NUM_LAYER, dtype=torch.float32):
+    pp = {k: v.to(dtype) for k, v in p.items()}
+    single = inp['single'].to(dtype).clone().requires_grad_(True)
+    pair = inp['pair'].to(dtype).clone().requires_grad_(True)
+    outs = structure_heads(pp, tables, single, pair, inp['seq_mask'].to(dtype), inp['aatype'], depth)
+    loss = sum((o * inp['ct_' + k].to(dtype)).sum() for k, o in zip(HEAD_OUTS, outs))
+    d_single, d_pair = torch.autograd.grad(loss, [single, pair])
+    res = {k: o.detach() for k, o in zip(HEAD_OUTS, outs)}
+    res.update(d_single=d_single, d_pair=d_pair)
+    return res
+
+
 def rel_l2(a, b):
     return float((a.double() - b.double()).norm() / max(float(b.double().norm()), 1e-30))
