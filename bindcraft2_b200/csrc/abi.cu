@@ -8,7 +8,7 @@
 
 #include "../../include/bc2_b200.h"
 #include "stack.cuh"
-#include "structure_host.cuh"
+#include "structure_heads.cuh"
 
 namespace {
 
@@ -88,6 +88,22 @@ sm::StructureCore* get_structure(int N, int depth, const std::string& dir) {
   sm::StructureCore* p = s.get();
   g_structure.emplace(k, std::move(s));
   fprintf(stderr, "native: structure module N=%d depth=%d (%.1f MB)\n", N, depth, p->A.bytes / 1e6);
+  return p;
+}
+
+std::map<TplKey, std::unique_ptr<sm::StructureHeads>> g_heads;
+
+sm::StructureHeads* get_heads(int N, int depth, const std::string& dir) {
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  TplKey k{dev, N, depth, dir};
+  auto it = g_heads.find(k);
+  if (it != g_heads.end()) return it->second.get();
+  auto s = std::make_unique<sm::StructureHeads>();
+  s->build(N, depth, dir);
+  sm::StructureHeads* p = s.get();
+  g_heads.emplace(k, std::move(s));
+  fprintf(stderr, "native: post-trunk N=%d depth=%d (%.1f MB)\n", N, depth, (p->A.bytes + p->core.A.bytes) / 1e6);
   return p;
 }
 
@@ -242,7 +258,7 @@ int bc2_structure_module_fwd(void* stream, const float* single, const float* pai
     BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     sm::StructureCore* s = get_structure((int)N, (int)depth, weights_dir);
-    s->forward(single, pair, seq_mask, act_out, rigids_out, (cudaStream_t)stream);
+    s->forward(single, pair, s->outer_mask(seq_mask, (cudaStream_t)stream), act_out, rigids_out, (cudaStream_t)stream);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -259,7 +275,7 @@ int bc2_structure_module_bwd(void* stream, const float* single, const float* pai
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     sm::StructureCore* s = get_structure((int)N, (int)depth, weights_dir);
     cudaStream_t st = (cudaStream_t)stream;
-    s->forward(single, pair, seq_mask, nullptr, nullptr, st);  // replay: the call reads only its operands
+    s->forward(single, pair, s->outer_mask(seq_mask, st), nullptr, nullptr, st);  // replay: the call reads only its operands
     s->backward(single, pair, d_act, d_rigids, d_single, d_pair, st);
     BC2_CUDA(cudaGetLastError());
     return 0;
@@ -268,8 +284,54 @@ int bc2_structure_module_bwd(void* stream, const float* single, const float* pai
   }
 }
 
+int bc2_structure_heads_fwd(void* stream, const float* single, const float* pair, const float* mask, const float* aatype,
+                            const uint32_t* /*seed*/, int64_t N, int64_t depth, const char* weights_dir, float* atom14,
+                            float* dgram, float* pae, float* plddt, float* expres) {
+  try {
+    BC2_CHECK(single && pair && mask && aatype && weights_dir, "null operand");
+    BC2_CHECK(atom14 && dgram && pae && plddt && expres, "null result");
+    BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    sm::StructureHeads* s = get_heads((int)N, (int)depth, weights_dir);
+    s->forward(single, pair, mask, aatype, atom14, dgram, pae, plddt, expres, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair, const float* mask, const float* aatype,
+                            const uint32_t* /*seed*/, const float* d_atom14, const float* d_dgram, const float* d_pae,
+                            const float* d_plddt, const float* d_expres, int64_t N, int64_t depth, const char* weights_dir,
+                            float* dsingle, float* dpair) {
+  try {
+    BC2_CHECK(single && pair && mask && aatype && weights_dir, "null operand");
+    BC2_CHECK(d_atom14 && d_dgram && d_pae && d_plddt && d_expres && dsingle && dpair, "null cotangent or result");
+    BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    sm::StructureHeads* s = get_heads((int)N, (int)depth, weights_dir);
+    s->backward(single, pair, mask, aatype, d_atom14, d_dgram, d_pae, d_plddt, d_expres, dsingle, dpair, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int native_sm_prealloc(int N, int depth, const char* weights_dir) {
+  try {
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    get_heads(N, depth, weights_dir);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 void bc2_release_all(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
+  g_heads.clear();
   g_structure.clear();
   g_stacks.clear();
   g_tpl.clear();

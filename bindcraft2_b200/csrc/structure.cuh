@@ -112,6 +112,7 @@ struct LinArgs {
   const float* G = nullptr;     // ReLU gate of the backward: output multiplied by (G > 0), or null
   float* Y = nullptr;
   int M = 0, N = 0, K = 0, relu = 0, accumulate = 0;  // accumulate: Y += result
+  int relu_in = 0;                                    // the input is max(X, 0)
 };
 __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
   __shared__ float sX[16][64 + 1], sW[16][64];
@@ -125,7 +126,8 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
   for (int k0 = 0; k0 < a.K; k0 += 16) {
     for (int t = threadIdx.x; t < 64 * 16; t += 256) {
       const int r = t >> 4, k = t & 15;
-      sX[k][r] = (m0 + r < a.M && k0 + k < a.K) ? a.X[(long)(m0 + r) * a.K + k0 + k] : 0.f;
+      float xv = (m0 + r < a.M && k0 + k < a.K) ? a.X[(long)(m0 + r) * a.K + k0 + k] : 0.f;
+      sX[k][r] = a.relu_in ? fmaxf(xv, 0.f) : xv;
       const int kk = t >> 6, c = t & 63;
       sW[kk][c] = (k0 + kk < a.K && n0 + c < a.N) ? a.W[(long)(k0 + kk) * a.N + n0 + c] : 0.f;
     }
@@ -224,7 +226,7 @@ ipa_points_kernel(const float* __restrict__ proj, const float* __restrict__ rig,
 // Forward attention of one query residue i (block = i).  Dynamic shared memory: N*H logits/probabilities.
 __global__ void __launch_bounds__(256)
 ipa_attn_fwd_kernel(const float* __restrict__ proj, const float* __restrict__ gpts, const float* __restrict__ rig,
-                    const float* __restrict__ pair_ln, const float* __restrict__ b2d, const float* __restrict__ mask,
+                    const float* __restrict__ pair_ln, const float* __restrict__ b2d, const float* __restrict__ mask /*[N][N]*/,
                     const float* __restrict__ pw /*[H] point weights*/, float* __restrict__ attn /*[N][N][H]*/,
                     float* __restrict__ fin /*[N][NFINAL]*/, int N) {
   extern __shared__ float sl[];  // [N][H]
@@ -237,7 +239,6 @@ ipa_attn_fwd_kernel(const float* __restrict__ proj, const float* __restrict__ gp
   }
   if (tid < H) spw[tid] = pw[tid];
   __syncthreads();
-  const float mi = mask[i];
   for (int idx = tid; idx < N * H; idx += 256) {
     const int j = idx / H, h = idx - j * H;
     const float* ks = proj + (long)j * NPROJ + OFF_KS + h * SQK;
@@ -251,7 +252,7 @@ ipa_attn_fwd_kernel(const float* __restrict__ proj, const float* __restrict__ gp
       const float d = sgq[h * 12 + r] - gk[r];
       d2 += d * d;
     }
-    float lg = -0.5f * spw[h] * d2 + qk + b2d[((long)i * N + j) * H + h] - 1e5f * (1.f - mi * mask[j]);
+    float lg = -0.5f * spw[h] * d2 + qk + b2d[((long)i * N + j) * H + h] - 1e5f * (1.f - mask[(long)i * N + j]);
     sl[idx] = lg * SQRT13;
   }
   __syncthreads();

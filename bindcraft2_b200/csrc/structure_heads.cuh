@@ -1,0 +1,323 @@
+// Side-chain atoms and output heads on top of the structure-module core: together the body of the reference's post-trunk
+// call (StructureHeadsFwd / StructureHeadsBwd, native/ffi.cu:1009-1043).
+// Reference model code: MultiRigidSidechain folding_multimer.py:950-1033; torsion_angles_to_frames and
+// frames_and_literature_positions_to_atom14_pos all_atom_multimer.py:370-469; heads modules.py:777-906, 1091-1125.
+// The residue tables (default frames, atom -> rigid group, literature positions, atom mask) are read from the manifest
+// (const/...), where the reference's exporter puts them (bindcraft/af/native.py:419-426).
+#pragma once
+#include "structure_host.cuh"
+
+namespace bc2 {
+namespace sm {
+
+constexpr int SCC = 128, NGRP = 8, NATOM = 14, NTYPE = 21;
+
+struct Rigid { float r[9]; float t[3]; };
+__device__ __forceinline__ Rigid rigid_compose(const Rigid& a, const Rigid& b) {  // a o b
+  Rigid o;
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) o.r[3 * i + j] = a.r[3 * i] * b.r[j] + a.r[3 * i + 1] * b.r[3 + j] + a.r[3 * i + 2] * b.r[6 + j];
+    o.t[i] = a.r[3 * i] * b.t[0] + a.r[3 * i + 1] * b.t[1] + a.r[3 * i + 2] * b.t[2] + a.t[i];
+  }
+  return o;
+}
+// o = a o b.  Given the cotangent go of o: ga += ..., gb += ...
+__device__ __forceinline__ void rigid_compose_bwd(const Rigid& a, const Rigid& b, const Rigid& go, Rigid& ga, Rigid& gb) {
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      // o.r_ij = sum_c a.r_ic b.r_cj ; o.t_i = sum_c a.r_ic b.t_c + a.t_i
+      ga.r[3 * i + j] += go.r[3 * i] * b.r[3 * j] + go.r[3 * i + 1] * b.r[3 * j + 1] + go.r[3 * i + 2] * b.r[3 * j + 2] + go.t[i] * b.t[j];
+      gb.r[3 * i + j] += a.r[i] * go.r[j] + a.r[3 + i] * go.r[3 + j] + a.r[6 + i] * go.r[6 + j];
+    }
+    ga.t[i] += go.t[i];
+    gb.t[i] += a.r[i] * go.t[0] + a.r[3 + i] * go.t[1] + a.r[6 + i] * go.t[2];
+  }
+}
+__device__ __forceinline__ Rigid rigid_zero() {
+  Rigid z;
+#pragma unroll
+  for (int i = 0; i < 9; ++i) z.r[i] = 0.f;
+  z.t[0] = z.t[1] = z.t[2] = 0.f;
+  return z;
+}
+
+struct ScTables {
+  const float* default_frame;  // [21][8][4][4]
+  const float* atom_group;     // [21][14]
+  const float* lit_pos;        // [21][14][3]
+  const float* atom_mask;      // [21][14]
+};
+
+// The eight group frames of residue n relative to its backbone frame; A[k] = default_k o rot_x(angle_k) is kept too.
+__device__ __forceinline__ void sidechain_frames(const ScTables& T, int aa, const float* ua /*[14]*/, Rigid (&A)[NGRP], Rigid (&F)[NGRP],
+                                                 float (&sn)[NGRP], float (&cs)[NGRP], float (&inv)[7]) {
+  sn[0] = 0.f; cs[0] = 1.f;
+#pragma unroll
+  for (int k = 0; k < 7; ++k) {
+    const float a = ua[2 * k], b = ua[2 * k + 1];
+    inv[k] = rsqrtf(fmaxf(a * a + b * b, 1e-12f));  // l2_normalize, folding_multimer.py:927-932
+    sn[k + 1] = a * inv[k];
+    cs[k + 1] = b * inv[k];
+  }
+#pragma unroll
+  for (int k = 0; k < NGRP; ++k) {
+    const float* m = T.default_frame + ((long)aa * NGRP + k) * 16;
+    // default rotation times [[1,0,0],[0,c,-s],[0,s,c]]
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const float d0 = m[4 * i], d1 = m[4 * i + 1], d2 = m[4 * i + 2];
+      A[k].r[3 * i] = d0;
+      A[k].r[3 * i + 1] = d1 * cs[k] + d2 * sn[k];
+      A[k].r[3 * i + 2] = -d1 * sn[k] + d2 * cs[k];
+      A[k].t[i] = m[4 * i + 3];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 5; ++k) F[k] = A[k];
+  F[5] = rigid_compose(F[4], A[5]);
+  F[6] = rigid_compose(F[5], A[6]);
+  F[7] = rigid_compose(F[6], A[7]);
+}
+
+__global__ void sidechain_atoms_kernel(ScTables T, const float* __restrict__ aatype, const float* __restrict__ ua,
+                                       const float* __restrict__ rig /*[N][12], Angstrom*/, float* __restrict__ atom14, int N) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const int aa = min(max((int)aatype[n], 0), NTYPE - 1);
+  Rigid A[NGRP], F[NGRP], B;
+  float sn[NGRP], cs[NGRP], inv[7];
+  sidechain_frames(T, aa, ua + (long)n * 14, A, F, sn, cs, inv);
+#pragma unroll
+  for (int i = 0; i < 9; ++i) B.r[i] = rig[(long)n * 12 + i];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) B.t[i] = rig[(long)n * 12 + 9 + i];
+  for (int a = 0; a < NATOM; ++a) {
+    const int g = min(max((int)T.atom_group[aa * NATOM + a], 0), NGRP - 1);
+    const float mk = T.atom_mask[aa * NATOM + a];
+    const float* lp = T.lit_pos + ((long)aa * NATOM + a) * 3;
+    Rigid G = B;
+#pragma unroll
+    for (int k = 0; k < NGRP; ++k)
+      if (k == g) G = rigid_compose(B, F[k]);
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      atom14[((long)n * NATOM + a) * 3 + i] = mk * (G.r[3 * i] * lp[0] + G.r[3 * i + 1] * lp[1] + G.r[3 * i + 2] * lp[2] + G.t[i]);
+  }
+}
+
+// d_atom14 -> d_ua [N][14] and d_rig [N][12] (cotangent of the Angstrom-scaled backbone frame)
+__global__ void sidechain_atoms_bwd_kernel(ScTables T, const float* __restrict__ aatype, const float* __restrict__ ua,
+                                           const float* __restrict__ rig, const float* __restrict__ d_atom14,
+                                           float* __restrict__ d_ua, float* __restrict__ d_rig, int N) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= N) return;
+  const int aa = min(max((int)aatype[n], 0), NTYPE - 1);
+  Rigid A[NGRP], F[NGRP], B;
+  float sn[NGRP], cs[NGRP], inv[7];
+  sidechain_frames(T, aa, ua + (long)n * 14, A, F, sn, cs, inv);
+#pragma unroll
+  for (int i = 0; i < 9; ++i) B.r[i] = rig[(long)n * 12 + i];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) B.t[i] = rig[(long)n * 12 + 9 + i];
+  // cotangent of the global group frames G_k = B o F_k, gathered from the atoms of each group
+  Rigid gG[NGRP];
+#pragma unroll
+  for (int k = 0; k < NGRP; ++k) gG[k] = rigid_zero();
+  for (int a = 0; a < NATOM; ++a) {
+    const int g = min(max((int)T.atom_group[aa * NATOM + a], 0), NGRP - 1);
+    const float mk = T.atom_mask[aa * NATOM + a];
+    const float* lp = T.lit_pos + ((long)aa * NATOM + a) * 3;
+    const float* dp = d_atom14 + ((long)n * NATOM + a) * 3;
+#pragma unroll
+    for (int k = 0; k < NGRP; ++k)
+      if (k == g) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+          const float d = mk * dp[i];
+          gG[k].r[3 * i] += d * lp[0]; gG[k].r[3 * i + 1] += d * lp[1]; gG[k].r[3 * i + 2] += d * lp[2];
+          gG[k].t[i] += d;
+        }
+      }
+  }
+  Rigid gB = rigid_zero(), gF[NGRP], gA[NGRP];
+#pragma unroll
+  for (int k = 0; k < NGRP; ++k) { gF[k] = rigid_zero(); gA[k] = rigid_zero(); }
+#pragma unroll
+  for (int k = 0; k < NGRP; ++k) rigid_compose_bwd(B, F[k], gG[k], gB, gF[k]);
+  // F7 = F6 o A7, F6 = F5 o A6, F5 = F4 o A5, F_k = A_k for k <= 4
+  rigid_compose_bwd(F[6], A[7], gF[7], gF[6], gA[7]);
+  rigid_compose_bwd(F[5], A[6], gF[6], gF[5], gA[6]);
+  rigid_compose_bwd(F[4], A[5], gF[5], gF[4], gA[5]);
+#pragma unroll
+  for (int k = 0; k < 5; ++k) {
+#pragma unroll
+    for (int i = 0; i < 9; ++i) gA[k].r[i] += gF[k].r[i];
+  }
+  // A_k.r = D_k X(s,c):  r_i1 = d1 c + d2 s ; r_i2 = -d1 s + d2 c
+  float* du = d_ua + (long)n * 14;
+#pragma unroll
+  for (int k = 1; k < NGRP; ++k) {
+    const float* m = T.default_frame + ((long)aa * NGRP + k) * 16;
+    float gs = 0.f, gc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const float d1 = m[4 * i + 1], d2 = m[4 * i + 2];
+      gc += gA[k].r[3 * i + 1] * d1 + gA[k].r[3 * i + 2] * d2;
+      gs += gA[k].r[3 * i + 1] * d2 - gA[k].r[3 * i + 2] * d1;
+    }
+    // (s, c) = (a, b) * inv with inv = 1/sqrt(max(a^2 + b^2, 1e-12))
+    const float a = ua[(long)n * 14 + 2 * (k - 1)], b = ua[(long)n * 14 + 2 * (k - 1) + 1];
+    const float iv = inv[k - 1];
+    if (a * a + b * b > 1e-12f) {
+      const float dot = gs * sn[k] + gc * cs[k];
+      du[2 * (k - 1)] = iv * (gs - sn[k] * dot);
+      du[2 * (k - 1) + 1] = iv * (gc - cs[k] * dot);
+    } else {
+      du[2 * (k - 1)] = iv * gs;
+      du[2 * (k - 1) + 1] = iv * gc;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 9; ++i) d_rig[(long)n * 12 + i] = gB.r[i];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) d_rig[(long)n * 12 + 9 + i] = gB.t[i];
+}
+
+// dgram[i,j,:] = half[i,j,:] + half[j,i,:]  (also used on the cotangent in the backward)
+__global__ void symmetrise_kernel(const float* __restrict__ half, float* __restrict__ out, int N, int C) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (long)N * N * C) return;
+  const int c = (int)(t % C);
+  const long ij = t / C;
+  const int j = (int)(ij % N), i = (int)(ij / N);
+  out[t] = half[t] + half[((long)j * N + i) * C + c];
+}
+
+struct StructureHeads {
+  StructureCore core;
+  int N = 0;
+  DeviceArena A;
+  ScTables T;
+  Lin ip, ip1, rb1, rb2, rb1b, rb2b, ang, dg, pae, pl0, pl1, pl2, er;
+  float *pl_scale, *pl_off;
+  float *rig_s, *x0, *r1, *x1, *r2, *x2, *ua, *half, *pl_ln, *ph0, *ph1;
+  float *d_ua, *d_rig, *d_act, *d_ini, *dx, *dt, *d_half, *dpl0, *dpl1, *dpl_ln;
+
+  void build(int n, int depth, const std::string& dir) {
+    N = n;
+    core.build(n, depth, dir);
+    const Manifest m = Manifest::load(dir);
+    auto v = [&](const std::string& k) { return m.get(k).data; };
+    auto table = [&](const std::string& k, size_t expect) {
+      const auto& t = m.get(k);
+      BC2_CHECK(t.data.size() == expect, k + ": unexpected size");
+      return A.upload(t.data);
+    };
+    T.default_frame = table("const/default_frame", (size_t)NTYPE * NGRP * 16);
+    T.atom_group = table("const/atom14_to_group", (size_t)NTYPE * NATOM);
+    T.lit_pos = table("const/atom14_lit_pos", (size_t)NTYPE * NATOM * 3);
+    T.atom_mask = table("const/atom14_mask", (size_t)NTYPE * NATOM);
+    const std::string S = "param/fold_iteration/rigid_sidechain/", P = "param/";
+    ip.set(A, v(S + "input_projection/weights"), v(S + "input_projection/bias"), CS, SCC);
+    ip1.set(A, v(S + "input_projection_1/weights"), v(S + "input_projection_1/bias"), CS, SCC);
+    rb1.set(A, v(S + "resblock1/weights"), v(S + "resblock1/bias"), SCC, SCC);
+    rb2.set(A, v(S + "resblock2/weights"), v(S + "resblock2/bias"), SCC, SCC);
+    rb1b.set(A, v(S + "resblock1_1/weights"), v(S + "resblock1_1/bias"), SCC, SCC);
+    rb2b.set(A, v(S + "resblock2_1/weights"), v(S + "resblock2_1/bias"), SCC, SCC);
+    ang.set(A, v(S + "unnormalized_angles/weights"), v(S + "unnormalized_angles/bias"), SCC, 14);
+    dg.set(A, v(P + "distogram_head/half_logits/weights"), v(P + "distogram_head/half_logits/bias"), CZ, 64);
+    pae.set(A, v(P + "predicted_aligned_error_head/logits/weights"), v(P + "predicted_aligned_error_head/logits/bias"), CZ, 64);
+    pl0.set(A, v(P + "predicted_lddt_head/act_0/weights"), v(P + "predicted_lddt_head/act_0/bias"), CS, 128);
+    pl1.set(A, v(P + "predicted_lddt_head/act_1/weights"), v(P + "predicted_lddt_head/act_1/bias"), 128, 128);
+    pl2.set(A, v(P + "predicted_lddt_head/logits/weights"), v(P + "predicted_lddt_head/logits/bias"), 128, 50);
+    er.set(A, v(P + "experimentally_resolved_head/logits/weights"), v(P + "experimentally_resolved_head/logits/bias"), CS, 37);
+    pl_scale = A.upload(v(P + "predicted_lddt_head/input_layer_norm/scale"));
+    pl_off = A.upload(v(P + "predicted_lddt_head/input_layer_norm/offset"));
+    const size_t n1 = N, n2 = n1 * N;
+    rig_s = A.alloc<float>(n1 * 12);
+    x0 = A.alloc<float>(n1 * SCC); r1 = A.alloc<float>(n1 * SCC); x1 = A.alloc<float>(n1 * SCC);
+    r2 = A.alloc<float>(n1 * SCC); x2 = A.alloc<float>(n1 * SCC); ua = A.alloc<float>(n1 * 14);
+    half = A.alloc<float>(n2 * 64);
+    pl_ln = A.alloc<float>(n1 * CS); ph0 = A.alloc<float>(n1 * 128); ph1 = A.alloc<float>(n1 * 128);
+    d_ua = A.alloc<float>(n1 * 14); d_rig = A.alloc<float>(n1 * 12); d_act = A.alloc<float>(n1 * CS);
+    d_ini = A.alloc<float>(n1 * CS); dx = A.alloc<float>(n1 * SCC); dt = A.alloc<float>(n1 * SCC);
+    d_half = A.alloc<float>(n2 * 64); dpl0 = A.alloc<float>(n1 * 128); dpl1 = A.alloc<float>(n1 * 128);
+    dpl_ln = A.alloc<float>(n1 * CS);
+  }
+
+  // generic Linear on `rows` rows
+  void lin(const float* X, const float* W, const float* b, float* Y, long rows, int K, int Nn, cudaStream_t st, int relu = 0,
+           int relu_in = 0, const float* R = nullptr, const float* G = nullptr, int accumulate = 0) {
+    LinArgs a; a.X = X; a.W = W; a.bias = b; a.Y = Y; a.M = (int)rows; a.N = Nn; a.K = K; a.relu = relu; a.relu_in = relu_in;
+    a.R = R; a.G = G; a.accumulate = accumulate;
+    linear_f32(a, st);
+  }
+
+  // Side-chain network and frames from the core's forward state (final activations, LN(single), final frames).
+  void sidechain_forward(const float* aatype, float* atom14, cudaStream_t st) {
+    const int L = core.L;
+    const float* act = core.act_in[L];
+    launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(core.rig[L], rig_s, POSITION_SCALE, N * 12);
+    lin(act, ip.w, ip.b, x0, N, CS, SCC, st, 0, 1);
+    lin(core.single_ln, ip1.w, ip1.b, x0, N, CS, SCC, st, 0, 1, nullptr, nullptr, 1);
+    lin(x0, rb1.w, rb1.b, r1, N, SCC, SCC, st, 0, 1);
+    lin(r1, rb2.w, rb2.b, x1, N, SCC, SCC, st, 0, 1, x0);
+    lin(x1, rb1b.w, rb1b.b, r2, N, SCC, SCC, st, 0, 1);
+    lin(r2, rb2b.w, rb2b.b, x2, N, SCC, SCC, st, 0, 1, x1);
+    lin(x2, ang.w, ang.b, ua, N, SCC, 14, st, 0, 1);
+    if (atom14) { launch_counter()++; sidechain_atoms_kernel<<<cdiv(N, 64), 64, 0, st>>>(T, aatype, ua, rig_s, atom14, N); }
+  }
+
+  void forward(const float* single, const float* pair, const float* mask2d, const float* aatype, float* atom14, float* dgram,
+               float* pae_out, float* plddt, float* expres, cudaStream_t st) {
+    const long n2 = (long)N * N;
+    core.forward(single, pair, mask2d, nullptr, nullptr, st);
+    sidechain_forward(aatype, atom14, st);
+    if (dgram) {
+      lin(pair, dg.w, dg.b, half, n2, CZ, 64, st);
+      launch_counter()++; symmetrise_kernel<<<(unsigned)cdiv(n2 * 64, 256L), 256, 0, st>>>(half, dgram, N, 64);
+    }
+    if (pae_out) lin(pair, pae.w, pae.b, pae_out, n2, CZ, 64, st);
+    core.ln<CS>(core.act_in[core.L], pl_scale, pl_off, pl_ln, N, st);
+    lin(pl_ln, pl0.w, pl0.b, ph0, N, CS, 128, st, 1);
+    lin(ph0, pl1.w, pl1.b, ph1, N, 128, 128, st, 1);
+    if (plddt) lin(ph1, pl2.w, pl2.b, plddt, N, 128, 50, st);
+    if (expres) lin(single, er.w, er.b, expres, N, CS, 37, st);
+  }
+
+  void backward(const float* single, const float* pair, const float* mask2d, const float* aatype, const float* d_atom14,
+                const float* d_dgram, const float* d_pae, const float* d_plddt, const float* d_expres, float* d_single,
+                float* d_pair, cudaStream_t st) {
+    const long n2 = (long)N * N;
+    const int L = core.L;
+    forward(single, pair, mask2d, aatype, nullptr, nullptr, nullptr, nullptr, nullptr, st);  // replay
+    // side chains: atoms -> (angles, backbone frame) -> network -> (final activations, LN(single))
+    launch_counter()++; sidechain_atoms_bwd_kernel<<<cdiv(N, 64), 64, 0, st>>>(T, aatype, ua, rig_s, d_atom14, d_ua, d_rig, N);
+    lin(d_ua, ang.wt, nullptr, dx, N, 14, SCC, st, 0, 0, nullptr, x2);                 // d(x2)
+    lin(dx, rb2b.wt, nullptr, dt, N, SCC, SCC, st, 0, 0, nullptr, r2);                 // d(r2)
+    lin(dt, rb1b.wt, nullptr, dx, N, SCC, SCC, st, 0, 0, nullptr, x1, 1);              // d(x1) = d(x2) + gated
+    lin(dx, rb2.wt, nullptr, dt, N, SCC, SCC, st, 0, 0, nullptr, r1);                  // d(r1)
+    lin(dt, rb1.wt, nullptr, dx, N, SCC, SCC, st, 0, 0, nullptr, x0, 1);               // d(x0)
+    lin(dx, ip.wt, nullptr, d_act, N, SCC, CS, st, 0, 0, nullptr, core.act_in[L]);     // d(final act), side-chain part
+    lin(dx, ip1.wt, nullptr, d_ini, N, SCC, CS, st, 0, 0, nullptr, core.single_ln);    // d(LN(single)), side-chain part
+    // pLDDT head -> d(final act)
+    lin(d_plddt, pl2.wt, nullptr, dpl1, N, 50, 128, st, 0, 0, nullptr, ph1);
+    lin(dpl1, pl1.wt, nullptr, dpl0, N, 128, 128, st, 0, 0, nullptr, ph0);
+    lin(dpl0, pl0.wt, nullptr, dpl_ln, N, 128, CS, st);
+    core.ln_bwd<CS>(core.act_in[L], pl_scale, dpl_ln, pl_ln, N, st);                   // pl_ln reused as scratch
+    launch_counter()++; add_f32_inplace_kernel<<<cdiv(N * CS, 256), 256, 0, st>>>(d_act, pl_ln, (long)N * CS);
+    core.backward(single, pair, d_act, d_rig, d_single, d_pair, st, d_ini);
+    // heads that read the trunk outputs directly
+    lin(d_expres, er.wt, nullptr, d_single, N, 37, CS, st, 0, 0, nullptr, nullptr, 1);
+    lin(d_pae, pae.wt, nullptr, d_pair, n2, 64, CZ, st, 0, 0, nullptr, nullptr, 1);
+    launch_counter()++; symmetrise_kernel<<<(unsigned)cdiv(n2 * 64, 256L), 256, 0, st>>>(d_dgram, d_half, N, 64);
+    lin(d_half, dg.wt, nullptr, d_pair, n2, 64, CZ, st, 0, 0, nullptr, nullptr, 1);
+  }
+};
+
+}  // namespace sm
+}  // namespace bc2

@@ -22,6 +22,11 @@ __global__ void scale_translation_kernel(const float* __restrict__ in, float* __
   if (t < n) out[t] = (t % 12 >= 9) ? in[t] * s : in[t];
 }
 
+__global__ void outer_mask_kernel(const float* __restrict__ m, float* __restrict__ m2, int N) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < (long)N * N) m2[t] = m[t / N] * m[t % N];
+}
+
 struct Lin {
   float *w = nullptr, *wt = nullptr, *b = nullptr;  // [K][N], [N][K], [N]
   int K = 0, N = 0;
@@ -42,7 +47,7 @@ struct StructureCore {
   float *w2d, *b2d_bias, *pw;
   Lin init, proj, out, t1, t2, t3, quat;
   // forward state
-  float *single_ln, *pair_ln, *b2d;
+  float *single_ln, *pair_ln, *b2d, *mask2d;
   std::vector<float*> act_in, rig, projv, gpts, attn, fin, act1, ln1, h1, h2, act2, upd;
   // backward scratch
   float *g_act, *dA, *dB, *tA, *tB, *d_fin, *d_proj, *dlogit, *db2d, *dpair_ln, *dopg, *g_rig[2], *d_upd;
@@ -103,6 +108,7 @@ struct StructureCore {
     single_ln = A.alloc<float>(n1 * CS);
     pair_ln = A.alloc<float>(n2 * CZ);
     b2d = A.alloc<float>(n2 * H);
+    mask2d = A.alloc<float>(n2);
     for (int l = 0; l <= L; ++l) {
       act_in.push_back(A.alloc<float>(n1 * CS));
       rig.push_back(A.alloc<float>(n1 * 12));
@@ -149,6 +155,13 @@ struct StructureCore {
     linear_f32(a, st);
   }
 
+  // seq_mask [N] -> m_i m_j [N][N] in this object's buffer (the reference's caller passes that product)
+  const float* outer_mask(const float* seq_mask, cudaStream_t st) {
+    launch_counter()++; outer_mask_kernel<<<(unsigned)cdiv((long)N * N, 256L), 256, 0, st>>>(seq_mask, mask2d, N);
+    return mask2d;
+  }
+
+  // mask: [N][N] pair mask (m_i m_j)
   void forward(const float* single, const float* pair, const float* mask, float* act_out, float* rig_out, cudaStream_t st) {
     const long n2 = (long)N * N;
     ln<CS>(single, ln_s_scale, ln_s_off, single_ln, N, st);
@@ -179,8 +192,9 @@ struct StructureCore {
 
   // Cotangents d_act [N,384] and d_rig [N,12] (rotation entries, then the SCALED translation) -> d_single, d_pair.
   // The forward state of the same inputs must be in place (the caller replays the forward first).
+  // d_single_ln_extra: optional cotangent of LN(single) from consumers outside the fold iterations (side chains).
   void backward(const float* single, const float* pair, const float* d_act, const float* d_rig, float* d_single,
-                float* d_pair, cudaStream_t st) {
+                float* d_pair, cudaStream_t st, const float* d_single_ln_extra = nullptr) {
     const long n2 = (long)N * N;
     BC2_CUDA(cudaMemcpyAsync(g_act, d_act, (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
     launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(d_rig, g_rig[0], POSITION_SCALE, N * 12);
@@ -205,7 +219,7 @@ struct StructureCore {
       lin(d_proj, proj.wt, nullptr, g_act, NPROJ, CS, st, 0, dB);                      // g_act = dB + d_proj Wproj^T
       cur ^= 1;
     }
-    lin(g_act, init.wt, nullptr, dA, CS, CS, st);
+    lin(g_act, init.wt, nullptr, dA, CS, CS, st, 0, d_single_ln_extra);
     ln_bwd<CS>(single, ln_s_scale, dA, d_single, N, st);
     ln_bwd<CZ>(pair, ln_p_scale, dpair_ln, d_pair, n2, st, w2d, db2d);
   }

@@ -259,6 +259,70 @@ def structure_module_bwd(single, pair, seq_mask, d_act, d_rigids, *, depth=8, we
     return d_single, d_pair
 
 
+def post_trunk_weights(params: Dict[str, torch.Tensor], tables: Dict[str, torch.Tensor], out_dir: Optional[str] = None) -> str:
+    """Post-trunk manifest: ``param/...`` weights plus the ``const/...`` residue tables, the layout of the reference's
+    ``post_weights_from_params`` (bindcraft/af/native.py:339-444)."""
+    out = out_dir or tempfile.mkdtemp(prefix='bc2_native_')
+    arrays = {'param/' + k: v.detach().cpu().numpy() for k, v in params.items()}
+    arrays.update({'const/' + k: v.detach().cpu().float().numpy() for k, v in tables.items()})
+    return write_manifest(arrays, out)
+
+
+def post_trunk_fwd(single, pair, mask, aatype, seed, *, depth=8, weights_dir):
+    """FFI target ``native_post_trunk_fwd`` (reference handler native/ffi.cu:1009-1025):
+    (atom14 [N,14,3], dgram [N,N,64], pae [N,N,64], plddt [N,50], expres [N,37])."""
+    lib = _lib.load()
+    n = int(single.shape[0])
+    _check_f32('single', single, (n, 384))
+    _check_f32('pair', pair, (n, n, CZ))
+    _check_f32('mask', mask, (n, n))
+    _check_f32('aatype', aatype, (n,))
+    mk = lambda *s: torch.empty(*s, dtype=torch.float32, device=single.device)
+    atom14, dgram, pae, plddt, expres = mk(n, 14, 3), mk(n, n, 64), mk(n, n, 64), mk(n, 50), mk(n, 37)
+    stream = torch.cuda.current_stream(single.device).cuda_stream
+    with torch.cuda.device(single.device):
+        _lib.check(lib.bc2_structure_heads_fwd(stream, _ptr(single), _ptr(pair), _ptr(mask), _ptr(aatype), _ptr(seed), n,
+                                               int(depth), os.fsencode(weights_dir), _ptr(atom14), _ptr(dgram), _ptr(pae),
+                                               _ptr(plddt), _ptr(expres)))
+    return atom14, dgram, pae, plddt, expres
+
+
+def post_trunk_bwd(single, pair, mask, aatype, seed, d_atom14, d_dgram, d_pae, d_plddt, d_expres, *, depth=8, weights_dir):
+    """FFI target ``native_post_trunk_bwd`` (reference handler native/ffi.cu:1027-1043): (dsingle, dpair)."""
+    lib = _lib.load()
+    n = int(single.shape[0])
+    for name, t, shape in (('d_atom14', d_atom14, (n, 14, 3)), ('d_dgram', d_dgram, (n, n, 64)), ('d_pae', d_pae, (n, n, 64)),
+                           ('d_plddt', d_plddt, (n, 50)), ('d_expres', d_expres, (n, 37))):
+        _check_f32(name, t, shape)
+    d_single, d_pair = torch.empty_like(single), torch.empty_like(pair)
+    stream = torch.cuda.current_stream(single.device).cuda_stream
+    with torch.cuda.device(single.device):
+        _lib.check(lib.bc2_structure_heads_bwd(stream, _ptr(single), _ptr(pair), _ptr(mask), _ptr(aatype), _ptr(seed),
+                                               _ptr(d_atom14), _ptr(d_dgram), _ptr(d_pae), _ptr(d_plddt), _ptr(d_expres), n,
+                                               int(depth), os.fsencode(weights_dir), _ptr(d_single), _ptr(d_pair)))
+    return d_single, d_pair
+
+
+def make_post_trunk(weights_dir: str, depth: int = 8):
+    """(single, pair, mask, aatype, seed) -> the five post-trunk outputs, differentiable in single and pair: the autograd
+    pairing of the reference's post-trunk ``custom_vjp`` (bindcraft/af/native.py:447-513; the backward replays)."""
+
+    class _Post(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, single, pair, mask, aatype, seed):
+            ctx.save_for_backward(single, pair, mask, aatype, seed)
+            return post_trunk_fwd(single, pair, mask, aatype, seed, depth=depth, weights_dir=weights_dir)
+
+        @staticmethod
+        def backward(ctx, *cts):
+            single, pair, mask, aatype, seed = ctx.saved_tensors
+            ds, dp = post_trunk_bwd(single, pair, mask, aatype, seed, *[c.contiguous() for c in cts], depth=depth,
+                                    weights_dir=weights_dir)
+            return ds, dp, None, None, None
+
+    return _Post.apply
+
+
 def make_template_stack(weights_dir: str, depth: int = 2, dropout: bool = False):
     """(pair, pair_mask, seed) -> pair, differentiable in pair: the autograd pairing of the reference's template-stack
     ``custom_vjp`` (bindcraft/af/native.py:977-1046; residuals = pair_mask, save, seed)."""

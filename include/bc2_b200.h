@@ -104,6 +104,28 @@ int bc2_structure_module_bwd(void* stream, const float* single, const float* pai
                              const float* d_rigids, int64_t N, int64_t depth, const char* weights_dir, float* d_single,
                              float* d_pair);
 
+/* Replaces StructureHeadsFwd (native/ffi.cu:1009-1025, FFI target `native_post_trunk_fwd`): the structure module with
+ * its side-chain atoms, and the four output heads.
+ *   single f32 [N,384], pair f32 [N,N,128], mask f32 [N,N] (seq_mask (x) seq_mask, the IPA reads mask[q*N+k]),
+ *   aatype f32 [N] (residue type 0..20 as float, as the reference passes it), seed u32 [2] (accepted, unused: no dropout
+ *   in this call), depth = 8 fold iterations, weights_dir = the post-trunk manifest including const/default_frame,
+ *   const/atom14_to_group, const/atom14_lit_pos, const/atom14_mask (bindcraft/af/native.py:339-444).
+ *   -> atom14 f32 [N,14,3] (Angstrom), dgram f32 [N,N,64] (symmetrised distogram logits), pae f32 [N,N,64],
+ *      plddt f32 [N,50], expres f32 [N,37].  No padding requirement on N. */
+int bc2_structure_heads_fwd(void* stream, const float* single, const float* pair, const float* mask, const float* aatype,
+                            const uint32_t* seed, int64_t N, int64_t depth, const char* weights_dir, float* atom14,
+                            float* dgram, float* pae, float* plddt, float* expres);
+
+/* Replaces StructureHeadsBwd (native/ffi.cu:1027-1043, FFI target `native_post_trunk_bwd`): the five cotangents ->
+ * dsingle f32 [N,384], dpair f32 [N,N,128].  Replays the forward from its operands, as the reference does. */
+int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair, const float* mask, const float* aatype,
+                            const uint32_t* seed, const float* d_atom14, const float* d_dgram, const float* d_pae,
+                            const float* d_plddt, const float* d_expres, int64_t N, int64_t depth, const char* weights_dir,
+                            float* dsingle, float* dpair);
+
+/* Same contract as the reference's native_sm_prealloc (native/ffi.cu:910-921). */
+int native_sm_prealloc(int N, int depth, const char* weights_dir);
+
 /* Same contract as the reference's native_tplembed_prealloc (native/ffi.cu:918-931). */
 int native_tplembed_prealloc(int N, int depth, const char* weights_dir);
 

@@ -92,3 +92,72 @@ def test_bad_arguments_return_errors(lib, tmp_path):
         native.structure_module_fwd(t['single'][:, :100].contiguous(), t['pair'], t['seq_mask'], weights_dir=wdir)
     with pytest.raises(RuntimeError):
         native.structure_module_fwd(t['single'], t['pair'], t['seq_mask'], weights_dir=str(tmp_path / 'missing'))
+
+
+# ----------------------------------------------------------------------------- post-trunk call (side chains + heads)
+def _run_heads(lib, params, tables, inp, depth, tmp_path):
+    from bindcraft2_b200 import native
+    wdir = native.post_trunk_weights(params, tables, str(tmp_path / 'w'))
+    t = {k: v.cuda().contiguous() for k, v in inp.items()}
+    mask2d = (t['seq_mask'][:, None] * t['seq_mask'][None, :]).contiguous()
+    aatype = t['aatype'].float()
+    seed = torch.zeros(2, dtype=torch.int32, device='cuda')
+    outs = native.post_trunk_fwd(t['single'], t['pair'], mask2d, aatype, seed, depth=depth, weights_dir=wdir)
+    cts = [t['ct_' + k] for k in SO.HEAD_OUTS]
+    ds, dp = native.post_trunk_bwd(t['single'], t['pair'], mask2d, aatype, seed, *cts, depth=depth, weights_dir=wdir)
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    res = {k: o.cpu() for k, o in zip(SO.HEAD_OUTS, outs)}
+    res.update(d_single=ds.cpu(), d_pair=dp.cpu())
+    return res, (wdir, t, mask2d, aatype, seed)
+
+
+@pytest.mark.parametrize('n,depth,masked', [(24, 1, 0), (48, 3, 4)])
+def test_post_trunk_matches_oracle(lib, tmp_path, n, depth, masked):
+    params = synthetic.add_structure_head_params(synthetic.make_structure_params(401 + n), 402 + n)
+    tables = synthetic.make_structure_tables(403 + n)
+    inp = synthetic.add_structure_head_inputs(synthetic.make_structure_inputs(404 + n, n, masked=masked), 405 + n)
+    got, _ = _run_heads(lib, params, tables, inp, depth, tmp_path)
+    want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth)
+    _check(got, want, f'post-trunk N={n} depth={depth}')
+
+
+def test_post_trunk_each_cotangent_alone(lib, tmp_path):
+    """One output's cotangent at a time, so that a wrong adjoint cannot hide behind the others."""
+    n, depth = 32, 2
+    params = synthetic.add_structure_head_params(synthetic.make_structure_params(411), 412)
+    tables = synthetic.make_structure_tables(413)
+    base = synthetic.add_structure_head_inputs(synthetic.make_structure_inputs(414, n), 415)
+    for only in SO.HEAD_OUTS:
+        inp = dict(base)
+        for k in SO.HEAD_OUTS:
+            if k != only:
+                inp['ct_' + k] = torch.zeros_like(base['ct_' + k])
+        got, _ = _run_heads(lib, params, tables, inp, depth, tmp_path / only)
+        want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth)
+        for k in ('d_single', 'd_pair'):
+            if float(want[k].abs().max()) == 0:
+                assert float(got[k].abs().max()) == 0, (only, k)
+            else:
+                assert SO.rel_l2(got[k], want[k]) <= TOL, (only, k, SO.rel_l2(got[k], want[k]))
+
+
+def test_post_trunk_autograd_pairing(lib, tmp_path):
+    from bindcraft2_b200 import native
+    n = 16
+    params = synthetic.add_structure_head_params(synthetic.make_structure_params(421), 422)
+    tables = synthetic.make_structure_tables(423)
+    inp = synthetic.add_structure_head_inputs(synthetic.make_structure_inputs(424, n), 425)
+    wdir = native.post_trunk_weights(params, tables, str(tmp_path / 'w'))
+    assert lib.native_sm_prealloc(n, 2, wdir.encode()) == 0
+    t = {k: v.cuda() for k, v in inp.items()}
+    single = t['single'].clone().requires_grad_(True)
+    pair = t['pair'].clone().requires_grad_(True)
+    mask2d = (t['seq_mask'][:, None] * t['seq_mask'][None, :]).contiguous()
+    f = native.make_post_trunk(wdir, depth=2)
+    outs = f(single, pair, mask2d, t['aatype'].float(), torch.zeros(2, dtype=torch.int32, device='cuda'))
+    loss = sum((o * t['ct_' + k]).sum() for k, o in zip(SO.HEAD_OUTS, outs))
+    loss.backward()
+    want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=2)
+    assert SO.rel_l2(single.grad.cpu(), want['d_single']) <= TOL
+    assert SO.rel_l2(pair.grad.cpu(), want['d_pair']) <= TOL
