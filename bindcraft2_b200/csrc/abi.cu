@@ -9,6 +9,7 @@
 #include "../../include/bc2_b200.h"
 #include "stack.cuh"
 #include "structure_heads.cuh"
+#include "embedder.cuh"
 
 namespace {
 
@@ -88,6 +89,21 @@ sm::StructureCore* get_structure(int N, int depth, const std::string& dir) {
   sm::StructureCore* p = s.get();
   g_structure.emplace(k, std::move(s));
   fprintf(stderr, "native: structure module N=%d depth=%d (%.1f MB)\n", N, depth, p->A.bytes / 1e6);
+  return p;
+}
+
+std::map<TplKey, std::unique_ptr<emb::Embedder>> g_embed;
+
+emb::Embedder* get_embedder(int N, int S, const std::string& dir) {
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  TplKey k{dev, N, S, dir};
+  auto it = g_embed.find(k);
+  if (it != g_embed.end()) return it->second.get();
+  auto s = std::make_unique<emb::Embedder>();
+  s->build(N, S, dir);
+  emb::Embedder* p = s.get();
+  g_embed.emplace(k, std::move(s));
   return p;
 }
 
@@ -319,6 +335,38 @@ int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair
   }
 }
 
+int bc2_embedder_fwd(void* stream, const float* target_feat, const float* msa_feat, const float* residue_index,
+                     const float* asym_id, const float* entity_id, const float* sym_id, int64_t N, int64_t S,
+                     const char* weights_dir, float* msa, float* pair) {
+  try {
+    BC2_CHECK(target_feat && msa_feat && residue_index && asym_id && entity_id && sym_id && msa && pair && weights_dir,
+              "null operand");
+    BC2_CHECK(N > 0 && S > 0, "bad shape");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    emb::Embedder* e = get_embedder((int)N, (int)S, weights_dir);
+    e->forward(target_feat, msa_feat, residue_index, asym_id, entity_id, sym_id, msa, pair, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_embedder_bwd(void* stream, const float* d_msa, const float* d_pair, const float* /*target_feat*/, int64_t N,
+                     int64_t S, const char* weights_dir, float* d_target_feat, float* d_msa_feat) {
+  try {
+    BC2_CHECK(d_msa && d_pair && d_target_feat && d_msa_feat && weights_dir, "null operand");
+    BC2_CHECK(N > 0 && S > 0, "bad shape");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    emb::Embedder* e = get_embedder((int)N, (int)S, weights_dir);
+    e->backward(d_msa, d_pair, d_target_feat, d_msa_feat, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 int native_sm_prealloc(int N, int depth, const char* weights_dir) {
   try {
     std::lock_guard<std::recursive_mutex> lock(g_mu);
@@ -332,6 +380,7 @@ int native_sm_prealloc(int N, int depth, const char* weights_dir) {
 void bc2_release_all(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
   g_heads.clear();
+  g_embed.clear();
   g_structure.clear();
   g_stacks.clear();
   g_tpl.clear();

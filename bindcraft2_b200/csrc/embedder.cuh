@@ -1,0 +1,111 @@
+// Input embedder of the multimer model: sequence features -> the msa and pair activations the trunk starts from, and
+// the backward that carries the trunk's cotangents onto the sequence features (the body of the reference's
+// EmbedderFwd / EmbedderBwd handlers, native/ffi.cu:1045-1069).
+// Reference model code: bindcraft/af/alphafold/model/modules_multimer.py:447-510 (the four input Linears) and :358-433
+// (relative encoding: a 66-bin residue offset clipped at +-32 with one extra bin for "other chain", a same-entity flag,
+// a 6-bin chain offset clipped at +-2 with one extra bin for "other entity"; the one-hots select rows of the
+// [73,128] position_activations weight, so the Linear is a gather of three rows).
+// fp32 throughout (the reference's native call works in fp32 as well).
+#pragma once
+#include "structure_host.cuh"
+
+namespace bc2 {
+namespace emb {
+
+constexpr int NAA = 21, NMSAF = 49, CM = 256, CZ = 128, MAX_REL = 32, REL_BINS = 2 * MAX_REL + 2, MAX_CHAIN = 2,
+              CHAIN_BINS = 2 * MAX_CHAIN + 2, REL_TOT = REL_BINS + 1 + CHAIN_BINS;  // 73
+
+// pair[i,j,:] = left[i,:] + right[j,:] + W[rel_bin] + same_entity W[66] + W[67 + chain_bin] + b
+__global__ void pair_init_kernel(const float* __restrict__ left, const float* __restrict__ right, const float* __restrict__ wpos,
+                                 const float* __restrict__ bpos, const float* __restrict__ residue_index,
+                                 const float* __restrict__ asym_id, const float* __restrict__ entity_id,
+                                 const float* __restrict__ sym_id, float* __restrict__ pair, int N) {
+  const long ij = (long)blockIdx.x * 2 + (threadIdx.x >> 7);  // two positions per 256-thread block, thread = channel
+  if (ij >= (long)N * N) return;
+  const int c = threadIdx.x & 127;
+  const int j = (int)(ij % N), i = (int)(ij / N);
+  const int off = (int)residue_index[i] - (int)residue_index[j];
+  const int clipped = min(max(off + MAX_REL, 0), 2 * MAX_REL);
+  const int rel_bin = asym_id[i] == asym_id[j] ? clipped : 2 * MAX_REL + 1;
+  const bool same_entity = entity_id[i] == entity_id[j];
+  const int cc = min(max((int)sym_id[i] - (int)sym_id[j] + MAX_CHAIN, 0), 2 * MAX_CHAIN);
+  const int chain_bin = same_entity ? cc : 2 * MAX_CHAIN + 1;
+  float v = left[(long)i * CZ + c] + right[(long)j * CZ + c] + wpos[(long)rel_bin * CZ + c] +
+            wpos[(long)(REL_BINS + 1 + chain_bin) * CZ + c] + bpos[c];
+  if (same_entity) v += wpos[(long)REL_BINS * CZ + c];
+  pair[ij * CZ + c] = v;
+}
+
+// rows[i,c] = sum_j d[i,j,c]   (block = i, thread = channel)
+__global__ void pair_rowsum_kernel(const float* __restrict__ d, float* __restrict__ rows, int N) {
+  const int i = blockIdx.x, c = threadIdx.x;
+  float acc = 0.f;
+  for (int j = 0; j < N; ++j) acc += d[((long)i * N + j) * CZ + c];
+  rows[(long)i * CZ + c] = acc;
+}
+// cols[j,c] = sum_i d[i,j,c]
+__global__ void pair_colsum_kernel(const float* __restrict__ d, float* __restrict__ cols, int N) {
+  const int j = blockIdx.x, c = threadIdx.x;
+  float acc = 0.f;
+  for (int i = 0; i < N; ++i) acc += d[((long)i * N + j) * CZ + c];
+  cols[(long)j * CZ + c] = acc;
+}
+// out[n,c] = sum_s d[s,n,c]
+__global__ void sum_over_rows_kernel(const float* __restrict__ d, float* __restrict__ out, int S, long per) {
+  const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= per) return;
+  float acc = 0.f;
+  for (int s = 0; s < S; ++s) acc += d[(long)s * per + t];
+  out[t] = acc;
+}
+
+struct Embedder {
+  int N = 0, S = 0;
+  DeviceArena A;
+  sm::Lin pre1d, premsa, left, right;
+  float *wpos, *bpos;
+  float *p1, *l, *r, *rows, *cols, *dsum;
+
+  void build(int n, int s, const std::string& dir) {
+    N = n; S = s;
+    const Manifest m = Manifest::load(dir);
+    auto v = [&](const std::string& k) { return m.get("param/" + k).data; };
+    pre1d.set(A, v("preprocess_1d/weights"), v("preprocess_1d/bias"), NAA, CM);
+    premsa.set(A, v("preprocess_msa/weights"), v("preprocess_msa/bias"), NMSAF, CM);
+    left.set(A, v("left_single/weights"), v("left_single/bias"), NAA, CZ);
+    right.set(A, v("right_single/weights"), v("right_single/bias"), NAA, CZ);
+    BC2_CHECK(v("position_activations/weights").size() == (size_t)REL_TOT * CZ, "position_activations: expected [73,128]");
+    wpos = A.upload(v("position_activations/weights"));
+    bpos = A.upload(v("position_activations/bias"));
+    p1 = A.alloc<float>((size_t)N * CM);
+    l = A.alloc<float>((size_t)N * CZ); r = A.alloc<float>((size_t)N * CZ);
+    rows = A.alloc<float>((size_t)N * CZ); cols = A.alloc<float>((size_t)N * CZ);
+    dsum = A.alloc<float>((size_t)N * CM);
+  }
+  void lin(const float* X, const float* W, const float* b, float* Y, long M, int K, int Nn, cudaStream_t st, const float* R = nullptr,
+           int accumulate = 0) {
+    sm::LinArgs a; a.X = X; a.W = W; a.bias = b; a.Y = Y; a.M = (int)M; a.N = Nn; a.K = K; a.R = R; a.accumulate = accumulate;
+    sm::linear_f32(a, st);
+  }
+  void forward(const float* tf, const float* msa_feat, const float* residue_index, const float* asym_id, const float* entity_id,
+               const float* sym_id, float* msa, float* pair, cudaStream_t st) {
+    lin(tf, pre1d.w, pre1d.b, p1, N, NAA, CM, st);
+    for (int s = 0; s < S; ++s)  // msa[s] = preprocess_msa(msa_feat[s]) + preprocess_1d(target_feat)
+      lin(msa_feat + (long)s * N * NMSAF, premsa.w, premsa.b, msa + (long)s * N * CM, N, NMSAF, CM, st, p1);
+    lin(tf, left.w, left.b, l, N, NAA, CZ, st);
+    lin(tf, right.w, right.b, r, N, NAA, CZ, st);
+    launch_counter()++; pair_init_kernel<<<(unsigned)cdiv((long)N * N, 2L), 256, 0, st>>>(l, r, wpos, bpos, residue_index, asym_id, entity_id, sym_id, pair, N);
+  }
+  void backward(const float* d_msa, const float* d_pair, float* d_tf, float* d_msa_feat, cudaStream_t st) {
+    lin(d_msa, premsa.wt, nullptr, d_msa_feat, (long)S * N, CM, NMSAF, st);
+    launch_counter()++; sum_over_rows_kernel<<<(unsigned)cdiv((long)N * CM, 256L), 256, 0, st>>>(d_msa, dsum, S, (long)N * CM);
+    launch_counter()++; pair_rowsum_kernel<<<N, CZ, 0, st>>>(d_pair, rows, N);
+    launch_counter()++; pair_colsum_kernel<<<N, CZ, 0, st>>>(d_pair, cols, N);
+    lin(dsum, pre1d.wt, nullptr, d_tf, N, CM, NAA, st);
+    lin(rows, left.wt, nullptr, d_tf, N, CZ, NAA, st, nullptr, 1);
+    lin(cols, right.wt, nullptr, d_tf, N, CZ, NAA, st, nullptr, 1);
+  }
+};
+
+}  // namespace emb
+}  // namespace bc2

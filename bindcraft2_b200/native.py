@@ -323,6 +323,39 @@ def make_post_trunk(weights_dir: str, depth: int = 8):
     return _Post.apply
 
 
+def embedder_fwd(target_feat, msa_feat, residue_index, asym_id, entity_id, sym_id, *, weights_dir):
+    """FFI target ``native_embed_fwd`` (reference handler native/ffi.cu:1045-1057): (msa [S,N,256], pair [N,N,128])."""
+    lib = _lib.load()
+    n, s = int(target_feat.shape[0]), int(msa_feat.shape[0])
+    _check_f32('target_feat', target_feat, (n, 21))
+    _check_f32('msa_feat', msa_feat, (s, n, 49))
+    for name, t in (('residue_index', residue_index), ('asym_id', asym_id), ('entity_id', entity_id), ('sym_id', sym_id)):
+        _check_f32(name, t, (n,))
+    msa = torch.empty(s, n, CM, dtype=torch.float32, device=target_feat.device)
+    pair = torch.empty(n, n, CZ, dtype=torch.float32, device=target_feat.device)
+    stream = torch.cuda.current_stream(target_feat.device).cuda_stream
+    with torch.cuda.device(target_feat.device):
+        _lib.check(lib.bc2_embedder_fwd(stream, _ptr(target_feat), _ptr(msa_feat), _ptr(residue_index), _ptr(asym_id),
+                                        _ptr(entity_id), _ptr(sym_id), n, s, os.fsencode(weights_dir), _ptr(msa), _ptr(pair)))
+    return msa, pair
+
+
+def embedder_bwd(d_msa, d_pair, target_feat, *, weights_dir):
+    """FFI target ``native_embed_bwd`` (reference handler native/ffi.cu:1059-1069): (d_target_feat [N,21],
+    d_msa_feat [S,N,49])."""
+    lib = _lib.load()
+    s, n = int(d_msa.shape[0]), int(d_msa.shape[1])
+    _check_f32('d_msa', d_msa, (s, n, CM))
+    _check_f32('d_pair', d_pair, (n, n, CZ))
+    d_tf = torch.empty(n, 21, dtype=torch.float32, device=d_msa.device)
+    d_mf = torch.empty(s, n, 49, dtype=torch.float32, device=d_msa.device)
+    stream = torch.cuda.current_stream(d_msa.device).cuda_stream
+    with torch.cuda.device(d_msa.device):
+        _lib.check(lib.bc2_embedder_bwd(stream, _ptr(d_msa), _ptr(d_pair), _ptr(target_feat), n, s, os.fsencode(weights_dir),
+                                        _ptr(d_tf), _ptr(d_mf)))
+    return d_tf, d_mf
+
+
 def make_template_stack(weights_dir: str, depth: int = 2, dropout: bool = False):
     """(pair, pair_mask, seed) -> pair, differentiable in pair: the autograd pairing of the reference's template-stack
     ``custom_vjp`` (bindcraft/af/native.py:977-1046; residuals = pair_mask, save, seed)."""

@@ -123,6 +123,23 @@ int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair
                             const float* d_plddt, const float* d_expres, int64_t N, int64_t depth, const char* weights_dir,
                             float* dsingle, float* dpair);
 
+/* Replaces EmbedderFwd (native/ffi.cu:1045-1057, FFI target `native_embed_fwd`; model code
+ * bindcraft/af/alphafold/model/modules_multimer.py:358-433, 447-510):
+ *   target_feat f32 [N,21] (already padded to 21), msa_feat f32 [S,N,49], residue_index / asym_id / entity_id / sym_id as
+ *   f32 [N] -> msa f32 [S,N,256] = preprocess_1d(target_feat)[None] + preprocess_msa(msa_feat),
+ *   pair f32 [N,N,128] = left_single[:,None] + right_single[None] + position_activations(relative encoding).
+ * weights_dir: the embedder manifest (param/preprocess_1d, preprocess_msa, left_single, right_single,
+ * position_activations; bindcraft/af/native.py:516-570). */
+int bc2_embedder_fwd(void* stream, const float* target_feat, const float* msa_feat, const float* residue_index,
+                     const float* asym_id, const float* entity_id, const float* sym_id, int64_t N, int64_t S,
+                     const char* weights_dir, float* msa, float* pair);
+
+/* Replaces EmbedderBwd (native/ffi.cu:1059-1069, FFI target `native_embed_bwd`): d_msa f32 [S,N,256], d_pair f32
+ * [N,N,128], target_feat (accepted as in the reference; the gradient here does not depend on it) ->
+ * d_target_feat f32 [N,21], d_msa_feat f32 [S,N,49].  This is where a design step's gradient reaches the sequence. */
+int bc2_embedder_bwd(void* stream, const float* d_msa, const float* d_pair, const float* target_feat, int64_t N, int64_t S,
+                     const char* weights_dir, float* d_target_feat, float* d_msa_feat);
+
 /* Same contract as the reference's native_sm_prealloc (native/ffi.cu:910-921). */
 int native_sm_prealloc(int N, int depth, const char* weights_dir);
 

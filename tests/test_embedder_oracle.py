@@ -1,0 +1,35 @@
+"""CPU checks of the embedder oracle: the relative encoding selects exactly three rows of the position weight, and the
+gradient matches finite differences."""
+import torch
+
+import embedder_oracle as EO
+from bindcraft2_b200 import synthetic
+
+
+def test_relative_features_are_three_one_hots():
+    inp = synthetic.make_embedder_inputs(1, 10, 90)
+    rel = EO.relative_features(inp['residue_index'], inp['asym_id'], inp['entity_id'], inp['sym_id'], torch.float64)
+    assert rel.shape == (100, 100, 73)
+    assert torch.all(rel[..., :66].sum(-1) == 1) and torch.all(rel[..., 67:].sum(-1) == 1)
+    assert torch.all(rel[:10, 10:, 65] == 1)       # other chain -> the extra bin
+    assert rel[10, 99, 0] == 1 and rel[99, 10, 64] == 1   # offsets beyond +-32 inside one chain are clipped
+    assert torch.all(rel[:10, :10, 66] == 1) and torch.all(rel[:10, 10:, 66] == 0)
+
+
+def test_gradient_matches_finite_differences():
+    p = synthetic.make_embedder_params(2)
+    inp = synthetic.make_embedder_inputs(3, 6, 14, s=2)
+    out = EO.embedder_fwd_bwd(p, inp, dtype=torch.float64)
+    pp = {k: v.double() for k, v in p.items()}
+    g = torch.Generator().manual_seed(4)
+    dt = torch.randn(inp['target_feat'].shape, generator=g, dtype=torch.float64)
+    dm = torch.randn(inp['msa_feat'].shape, generator=g, dtype=torch.float64)
+
+    def loss(tf, mf):
+        msa, pair = EO.embedder(pp, tf, mf, inp['residue_index'], inp['asym_id'], inp['entity_id'], inp['sym_id'])
+        return float((msa * inp['ct_msa'].double()).sum() + (pair * inp['ct_pair'].double()).sum())
+
+    tf0, mf0, eps = inp['target_feat'].double(), inp['msa_feat'].double(), 1e-6
+    fd = (loss(tf0 + eps * dt, mf0 + eps * dm) - loss(tf0 - eps * dt, mf0 - eps * dm)) / (2 * eps)
+    an = float((out['d_target_feat'] * dt).sum() + (out['d_msa_feat'] * dm).sum())
+    assert abs(fd - an) <= 1e-6 * max(1.0, abs(an))
