@@ -22,6 +22,8 @@ PROTOTYPES = {
     'bc2_structure_module_bwd': (_i32, [_vp] * 6 + [_i64] * 2 + [_cp] + [_vp] * 2),
     'bc2_structure_heads_fwd': (_i32, [_vp] * 6 + [_i64] * 2 + [_cp] + [_vp] * 5),
     'bc2_structure_heads_bwd': (_i32, [_vp] * 11 + [_i64] * 2 + [_cp] + [_vp] * 2),
+    'bc2_extra_msa_stack_fwd': (_i32, [_vp] * 6 + [_i64] * 6 + [_cp] + [_vp] * 4),
+    'bc2_extra_msa_stack_bwd': (_i32, [_vp] * 8 + [_i64] * 5 + [_cp] + [_vp] * 2),
     'bc2_embedder_fwd': (_i32, [_vp] * 7 + [_i64] * 2 + [_cp] + [_vp] * 2),
     'bc2_embedder_bwd': (_i32, [_vp] * 4 + [_i64] * 2 + [_cp] + [_vp] * 2),
     'native_sm_prealloc': (_i32, [_i32, _i32, _cp]),

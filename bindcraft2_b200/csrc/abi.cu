@@ -29,10 +29,10 @@ std::recursive_mutex g_mu;
 using Key = std::tuple<int, int, int, int, int, int, std::string>;
 std::map<Key, std::unique_ptr<EvoStack>> g_stacks;
 
-EvoStack* get_stack(int N, int S, int depth, const std::string& dir, bool pair_only, bool opm_first) {
+EvoStack* get_stack(int N, int S, int depth, const std::string& dir, bool pair_only, bool opm_first, bool extra = false) {
   int dev = 0;
   BC2_CUDA(cudaGetDevice(&dev));
-  Key k{dev, N, S, depth, pair_only ? 1 : 0, opm_first ? 1 : 0, dir};
+  Key k{dev, N, S, depth, (pair_only ? 1 : 0) + (extra ? 2 : 0), opm_first ? 1 : 0, dir};
   auto it = g_stacks.find(k);
   if (it != g_stacks.end()) return it->second.get();
   StackConfig c;
@@ -41,6 +41,8 @@ EvoStack* get_stack(int N, int S, int depth, const std::string& dir, bool pair_o
   c.depth = depth;
   c.pair_only = pair_only;
   c.opm_first = opm_first;
+  c.extra = extra;
+  if (extra) c.Cm = 64;
   auto s = std::make_unique<EvoStack>(c, dir);
   EvoStack* p = s.get();
   g_stacks.emplace(k, std::move(s));
@@ -153,6 +155,41 @@ int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, c
     BC2_CHECK(ct_pair && ct_msa && pair_mask && msa_mask && psave && msave && dpair && dmsa && weights_dir, "null operand");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
+    s->backward(ct_pair, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave), msave, dpair, dmsa,
+                own_save != 0, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_extra_msa_stack_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
+                            const uint32_t* /*seed*/, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t own_save,
+                            int64_t /*dropout*/, const char* weights_dir, float* pair_out, float* msa_out, uint16_t* psave,
+                            float* msave) {
+  try {
+    BC2_CHECK(pair && msa && pair_mask && msa_mask && pair_out && msa_out && weights_dir, "null operand");
+    BC2_CHECK(!save || (psave && msave), "save != 0 needs psave and msave");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, false, true, true);
+    s->forward(pair, msa, pair_mask, msa_mask, pair_out, msa_out, save ? reinterpret_cast<bf16*>(psave) : nullptr,
+               save ? msave : nullptr, own_save != 0, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_extra_msa_stack_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
+                            const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* /*seed*/,
+                            int64_t N, int64_t S, int64_t depth, int64_t own_save, int64_t /*dropout*/,
+                            const char* weights_dir, float* dpair, float* dmsa) {
+  try {
+    BC2_CHECK(ct_pair && ct_msa && pair_mask && msa_mask && psave && msave && dpair && dmsa && weights_dir, "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, false, true, true);
     s->backward(ct_pair, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave), msave, dpair, dmsa,
                 own_save != 0, (cudaStream_t)stream);
     BC2_CUDA(cudaGetLastError());

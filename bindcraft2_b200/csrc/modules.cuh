@@ -11,6 +11,7 @@
 #include "ew.cuh"
 #include "gemm.cuh"
 #include "msa.cuh"
+#include "msa_global.cuh"
 #include "norm.cuh"
 #include "weights.cuh"
 
@@ -273,8 +274,11 @@ struct TriMul {
 struct AttnW {
   bf16 *wqkvg = nullptr, *wqkvg_b = nullptr, *wo = nullptr, *wo_b = nullptr;
   float *bqkvg = nullptr, *bo = nullptr;
-  void load(DeviceArena& A, const Manifest& m, const std::string& p, int C, int H, int D) {
-    const int HD = H * D;
+  // Dp >= D: head width the kernels run with (heads narrower than 16 are zero-padded: padded q/k columns add nothing to
+  // the logits, padded v columns give zero outputs, and their output-projection rows are zero).
+  void load(DeviceArena& A, const Manifest& m, const std::string& p, int C, int H, int D, int Dp = 0) {
+    if (Dp < D) Dp = D;
+    const int HD = H * D, HP = H * Dp;
     const auto& q = m.get(p + "/query_w");
     const auto& k = m.get(p + "/key_w");
     const auto& v = m.get(p + "/value_w");
@@ -282,21 +286,28 @@ struct AttnW {
     const auto& ow = m.get(p + "/output_w");
     BC2_CHECK(q.size() == (long)C * HD && ow.size() == (long)HD * C, p + ": attention weight shapes");
     const float scale = 1.f / sqrtf((float)D);
-    std::vector<float> wf((size_t)C * 4 * HD);  // [in][4HD] = backward operand
+    std::vector<float> wf((size_t)C * 4 * HP, 0.f);  // [in][4HP] = backward operand
     for (int c = 0; c < C; ++c)
-      for (int j = 0; j < HD; ++j) {
-        wf[(size_t)c * 4 * HD + j] = q.data[(size_t)c * HD + j] * scale;
-        wf[(size_t)c * 4 * HD + HD + j] = k.data[(size_t)c * HD + j];
-        wf[(size_t)c * 4 * HD + 2 * HD + j] = v.data[(size_t)c * HD + j];
-        wf[(size_t)c * 4 * HD + 3 * HD + j] = gw.data[(size_t)c * HD + j];
-      }
+      for (int h = 0; h < H; ++h)
+        for (int d = 0; d < D; ++d) {
+          const size_t src = (size_t)c * HD + h * D + d, dst = (size_t)c * 4 * HP + h * Dp + d;
+          wf[dst] = q.data[src] * scale;
+          wf[dst + HP] = k.data[src];
+          wf[dst + 2 * HP] = v.data[src];
+          wf[dst + 3 * HP] = gw.data[src];
+        }
     wqkvg_b = A.upload_bf16(wf);
-    wqkvg = A.upload_bf16(transpose_io(wf, C, 4 * HD));
-    wo = A.upload_bf16(transpose_io(ow.data, HD, C));
-    wo_b = A.upload_bf16(ow.data);
-    std::vector<float> bias(4 * HD, 0.f);
+    wqkvg = A.upload_bf16(transpose_io(wf, C, 4 * HP));
+    std::vector<float> owp((size_t)HP * C, 0.f);  // [HP][C]
+    for (int h = 0; h < H; ++h)
+      for (int d = 0; d < D; ++d)
+        for (int c = 0; c < C; ++c) owp[((size_t)h * Dp + d) * C + c] = ow.data[((size_t)h * D + d) * C + c];
+    wo = A.upload_bf16(transpose_io(owp, HP, C));
+    wo_b = A.upload_bf16(owp);
+    std::vector<float> bias(4 * HP, 0.f);
     const auto& gb = m.get(p + "/gating_b");
-    for (int j = 0; j < HD; ++j) bias[3 * HD + j] = gb.data[j];
+    for (int h = 0; h < H; ++h)
+      for (int d = 0; d < D; ++d) bias[3 * HP + h * Dp + d] = gb.data[h * D + d];
     bqkvg = A.upload(bias);
     bo = A.upload(m.get(p + "/output_b").data);
   }
@@ -397,7 +408,7 @@ struct TriAttn {
 // ------------------------------------------------------------------------------------------- MSA row attention
 // modules.MSARowAttentionWithPairBias (modules.py:500-563).  The gradient lands on the msa AND the pair stream.
 struct MsaRow {
-  int n = 0, S_ = 0, Cm = 0, Cz = 0, H = 0, D = 0;
+  int n = 0, S_ = 0, Cm = 0, Cz = 0, H = 0, D = 0, Dreal = 0;  // D: head width the kernels use (>= 16), Dreal: the model's
   long Mm = 0, Mp = 0;
   struct W {
     LnW qn, fn;
@@ -413,7 +424,7 @@ struct MsaRow {
   Scratch* S = nullptr;
 
   void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, int Cz_, int H_, const float* msa_mask) {
-    S = s; n = n_; S_ = S__; Cm = Cm_; Cz = Cz_; H = H_; D = Cm / H;
+    S = s; n = n_; S_ = S__; Cm = Cm_; Cz = Cz_; H = H_; Dreal = Cm / H; D = std::max(Dreal, 16);
     Mm = (long)S_ * n; Mp = (long)n * n;
     const int HD = H * D;
     qkvg = A.alloc<bf16>(Mm * 4 * HD);
@@ -435,7 +446,7 @@ struct MsaRow {
     b.qn.load(A, m, p + "/query_norm");
     b.fn.load(A, m, p + "/feat_2d_norm");
     b.wb = A.upload(transpose_io(m.get(p + "/feat_2d_weights").data, Cz, H));  // [H][Cz]
-    b.a.load(A, m, p + "/attention", Cm, H, D);
+    b.a.load(A, m, p + "/attention", Cm, H, Dreal, D);
     const int Mi = (int)Mm, HD = H * D;
     b.g_qkvg = make_gemm(kmaj(S->x, Cm), kmaj(b.a.wqkvg, Cm), Mi, 4 * HD, Cm, 1, 256);
     b.g_o = make_gemm(kmaj(S->y, HD), kmaj(b.a.wo, HD), Mi, Cm, HD);
@@ -528,6 +539,57 @@ struct MsaCol {
     { ProfScope ps_("MsaCol.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g; l.g_out = g; l.M = Mi;
     { ProfScope ps_("MsaCol.backward.ln_bwd_c", st); ln_bwd_c(Cm, l, st); }
+  }
+};
+
+// ------------------------------------------------------------------------------------------- Global column attention
+// modules.MSAColumnGlobalAttention (modules.py:619-672) of the extra-MSA stack; kernels in msa_global.cuh.
+struct MsaColGlobal {
+  int n = 0, S_ = 0;
+  long Mm = 0;
+  struct W {
+    LnW qn;
+    GlobalColW g;
+  };
+  std::vector<W> w;
+  const float* msa_mask = nullptr;
+  Scratch* S = nullptr;
+  void init(DeviceArena&, Scratch* s, int n_, int S__, int Cm, int H, const float* mask) {
+    S = s; n = n_; S_ = S__; Mm = (long)S_ * n; msa_mask = mask;
+    BC2_CHECK(Cm == GC && H == GH, "global column attention is written for 64 channels and 8 heads of width 8");
+    BC2_CHECK(S_ <= GS, "global column attention holds at most 8 alignment rows");
+  }
+  void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
+    W b;
+    b.qn.load(A, m, p + "/query_norm");
+    const std::string a = p + "/attention";
+    auto chk = [&](const std::string& k, long n_) {
+      BC2_CHECK(m.get(a + k).size() == n_, a + k + ": unexpected size");
+      return m.get(a + k).data;
+    };
+    const auto wq = chk("/query_w", GC * GC), wk = chk("/key_w", GC * GD), wv = chk("/value_w", GC * GD),
+               wg = chk("/gating_w", GC * GC), bg = chk("/gating_b", GC), wo = chk("/output_w", GC * GC), bo = chk("/output_b", GC);
+    b.g.wq = A.upload(wq); b.g.wk = A.upload(wk); b.g.wv = A.upload(wv); b.g.wg = A.upload(wg); b.g.bg = A.upload(bg);
+    b.g.wo = A.upload(wo); b.g.bo = A.upload(bo);
+    b.g.wq_t = A.upload(transpose_io(wq, GC, GC));
+    b.g.wg_t = A.upload(transpose_io(wg, GC, GC));
+    b.g.wo_t = A.upload(transpose_io(wo, GC, GC));
+    w.push_back(b);
+  }
+  void forward(int blk, const float* in, float* out, cudaStream_t st) {
+    W& b = w[blk];
+    LnArgs l; l.x = in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = GC; l.M = (int)Mm;
+    { ProfScope ps_("MsaColGlobal.forward.ln_fwd_c", st); ln_fwd_c(GC, l, st); }
+    { ProfScope ps_("MsaColGlobal.forward.global_col_fwd_kernel", st); launch_counter()++; global_col_fwd_kernel<<<n, 64, 0, st>>>(b.g, S->x, msa_mask, in, out, S_, n); }
+  }
+  void backward(int blk, const float* in, float* g, cudaStream_t st) {
+    W& b = w[blk];
+    // S->x still holds LN(in) of this block only if nothing else used it since the replayed forward; recompute it
+    LnArgs l; l.x = in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = GC; l.M = (int)Mm;
+    { ProfScope ps_("MsaColGlobal.backward.ln_fwd_c", st); ln_fwd_c(GC, l, st); }
+    { ProfScope ps_("MsaColGlobal.backward.global_col_bwd_kernel", st); launch_counter()++; global_col_bwd_kernel<<<n, 64, 0, st>>>(b.g, S->x, msa_mask, g, S->dx, S_, n); }
+    LnBwdArgs lb; lb.x = in; lb.scale = b.qn.scale; lb.dy = S->dx; lb.ldy = GC; lb.g_in = g; lb.g_out = g; lb.M = (int)Mm;
+    { ProfScope ps_("MsaColGlobal.backward.ln_bwd_c", st); ln_bwd_c(GC, lb, st); }
   }
 };
 

@@ -1,0 +1,205 @@
+// Global column attention of the extra-MSA stack (reference: modules.MSAColumnGlobalAttention + GlobalAttention,
+// bindcraft/af/alphafold/model/modules.py:619-672 and :403-497), forward and backward.
+//
+// Per residue column n the module sees S <= 8 alignment rows of C = 64 channels:
+//   x = LN(msa)[:, n]                      q_avg = sum_s m_s x_s / (sum_s m_s + 1e-10)
+//   q[h,d] = q_avg . Wq[:,h,d] * D^-1/2    k[s,d] = x_s . Wk[:,d]     v[s,d] = x_s . Wv[:,d]     (one shared k/v head)
+//   w[h,s] = softmax_s(q[h].k[s] + 1e9 (m_s - 1))       avg[h,d] = sum_s w[h,s] v[s,d]
+//   gate[s,h,d] = sigmoid(x_s . Wg[:,h,d] + bg[h,d])    out_s = (avg * gate_s) . Wo + bo        msa_out = msa_in + out
+// It is a few hundred kFLOP per column, so one block per column does all of it in fp32 on CUDA cores; weights are read
+// from L2 (48 KB per block).  thread t = channel c on the input side and (h,d) on the head side (both 64 wide).
+#pragma once
+#include "common.cuh"
+
+namespace bc2 {
+
+constexpr int GC = 64, GH = 8, GD = 8, GS = 8;  // channels, heads, head width, max alignment rows
+
+struct GlobalColW {
+  const float *wq, *wk, *wv, *wg, *bg, *wo, *bo;  // [64][64], [64][8], [64][8], [64][64], [64], [64][64] ([hd][out]), [64]
+  const float *wq_t, *wg_t, *wo_t;                 // transposes [hd][c], [hd][c], [out][hd] for the backward
+};
+
+// x: LN output bf16 [S*N][64]; in/out: fp32 msa streams [S*N][64]; mask [S][N].
+__global__ void __launch_bounds__(64)
+global_col_fwd_kernel(GlobalColW W, const bf16* __restrict__ x, const float* __restrict__ mask, const float* __restrict__ in,
+                      float* __restrict__ out, int S, int N) {
+  __shared__ float sx[GS][GC], sq[GC], sk[GS][GD], sv[GS][GD], sw[GH][GS], savg[GC], sy[GS][GC], sm[GS];
+  const int n = blockIdx.x, t = threadIdx.x;
+  float msum = 0.f;
+  for (int s = 0; s < S; ++s) {
+    sx[s][t] = __bfloat162float(x[((long)s * N + n) * GC + t]);
+    if (t == 0) sm[s] = mask[(long)s * N + n];
+  }
+  __syncthreads();
+  float qa = 0.f;
+  for (int s = 0; s < S; ++s) { qa += sm[s] * sx[s][t]; msum += sm[s]; }
+  sq[t] = qa / (msum + 1e-10f);  // q_avg[c] for now
+  __syncthreads();
+  float q = 0.f;
+  for (int c = 0; c < GC; ++c) q += sq[c] * W.wq[c * GC + t];
+  q *= rsqrtf((float)GD);
+  if (t < 2 * GD) {  // k and v: 16 outputs per row
+    const float* w = t < GD ? W.wk : W.wv;
+    const int d = t & (GD - 1);
+    for (int s = 0; s < S; ++s) {
+      float a = 0.f;
+      for (int c = 0; c < GC; ++c) a += sx[s][c] * w[c * GD + d];
+      (t < GD ? sk : sv)[s][d] = a;
+    }
+  }
+  __syncthreads();
+  sq[t] = q;  // q[h*8+d]
+  __syncthreads();
+  {  // logits and softmax: thread = (h, s)
+    const int h = t >> 3, s = t & 7;
+    float lg = -INFINITY;
+    if (s < S) {
+      lg = 1e9f * (sm[s] - 1.f);
+      for (int d = 0; d < GD; ++d) lg += sq[h * GD + d] * sk[s][d];
+    }
+    float mx = lg;
+    for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float e = s < S ? __expf(lg - mx) : 0.f;
+    float sum = e;
+    for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    sw[h][s] = e / sum;
+  }
+  __syncthreads();
+  {
+    const int h = t >> 3, d = t & 7;
+    float a = 0.f;
+    for (int s = 0; s < S; ++s) a += sw[h][s] * sv[s][d];
+    savg[t] = a;
+  }
+  for (int s = 0; s < S; ++s) {  // gate and gated value: thread = (h,d)
+    float g = W.bg[t];
+    for (int c = 0; c < GC; ++c) g += sx[s][c] * W.wg[c * GC + t];
+    sy[s][t] = savg[t] * sigmoidf_(g);
+  }
+  __syncthreads();
+  for (int s = 0; s < S; ++s) {  // output projection + residual: thread = output channel
+    float o = W.bo[t];
+    for (int k = 0; k < GC; ++k) o += sy[s][k] * W.wo[k * GC + t];
+    const long idx = ((long)s * N + n) * GC + t;
+    out[idx] = in[idx] + o;
+  }
+}
+
+// g: cotangent of the module output rows (fp32 msa cotangent stream, read only); dx: cotangent of the LN output (bf16).
+__global__ void __launch_bounds__(64)
+global_col_bwd_kernel(GlobalColW W, const bf16* __restrict__ x, const float* __restrict__ mask, const float* __restrict__ g,
+                      bf16* __restrict__ dx, int S, int N) {
+  __shared__ float sx[GS][GC], sq[GC], sqa[GC], sk[GS][GD], sv[GS][GD], sw[GH][GS], savg[GC], sgate[GS][GC], sm[GS];
+  __shared__ float sg[GS][GC], sdy[GS][GC], sdavg[GC], sdl[GH][GS], sdq[GC], sdk[GS][GD], sdv[GS][GD], sdgp[GS][GC];
+  const int n = blockIdx.x, t = threadIdx.x;
+  float msum = 0.f;
+  for (int s = 0; s < S; ++s) {
+    const long idx = ((long)s * N + n) * GC + t;
+    sx[s][t] = __bfloat162float(x[idx]);
+    sg[s][t] = g[idx];
+    if (t == 0) sm[s] = mask[(long)s * N + n];
+  }
+  __syncthreads();
+  // ---- forward recompute (same arithmetic as above)
+  float qa = 0.f;
+  for (int s = 0; s < S; ++s) { qa += sm[s] * sx[s][t]; msum += sm[s]; }
+  const float inv_m = 1.f / (msum + 1e-10f);
+  sqa[t] = qa * inv_m;
+  __syncthreads();
+  float q = 0.f;
+  for (int c = 0; c < GC; ++c) q += sqa[c] * W.wq[c * GC + t];
+  sq[t] = q * rsqrtf((float)GD);
+  if (t < 2 * GD) {
+    const float* w = t < GD ? W.wk : W.wv;
+    const int d = t & (GD - 1);
+    for (int s = 0; s < S; ++s) {
+      float a = 0.f;
+      for (int c = 0; c < GC; ++c) a += sx[s][c] * w[c * GD + d];
+      (t < GD ? sk : sv)[s][d] = a;
+    }
+  }
+  __syncthreads();
+  {
+    const int h = t >> 3, s = t & 7;
+    float lg = -INFINITY;
+    if (s < S) {
+      lg = 1e9f * (sm[s] - 1.f);
+      for (int d = 0; d < GD; ++d) lg += sq[h * GD + d] * sk[s][d];
+    }
+    float mx = lg;
+    for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float e = s < S ? __expf(lg - mx) : 0.f;
+    float sum = e;
+    for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    sw[h][s] = e / sum;
+  }
+  __syncthreads();
+  {
+    const int h = t >> 3, d = t & 7;
+    float a = 0.f;
+    for (int s = 0; s < S; ++s) a += sw[h][s] * sv[s][d];
+    savg[t] = a;
+  }
+  for (int s = 0; s < S; ++s) {
+    float gp = W.bg[t];
+    for (int c = 0; c < GC; ++c) gp += sx[s][c] * W.wg[c * GC + t];
+    sgate[s][t] = sigmoidf_(gp);
+  }
+  __syncthreads();
+  // ---- backward.  y[s][hd] = avg[hd] gate[s][hd];  out_s = y_s Wo
+  float davg = 0.f;
+  for (int s = 0; s < S; ++s) {  // thread = hd
+    float dy = 0.f;
+    for (int o = 0; o < GC; ++o) dy += sg[s][o] * W.wo_t[o * GC + t];
+    sdy[s][t] = dy;
+    davg += dy * sgate[s][t];
+    const float gt = sgate[s][t];
+    sdgp[s][t] = dy * savg[t] * gt * (1.f - gt);  // cotangent of the gate pre-activation
+  }
+  sdavg[t] = davg;
+  __syncthreads();
+  {  // softmax backward: thread = (h, s)
+    const int h = t >> 3, s = t & 7;
+    float dw = 0.f;
+    if (s < S)
+      for (int d = 0; d < GD; ++d) dw += sdavg[h * GD + d] * sv[s][d];
+    const float wv = s < S ? sw[h][s] : 0.f;
+    float dot = wv * dw;
+    for (int o = 4; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    sdl[h][s] = wv * (dw - dot);
+  }
+  __syncthreads();
+  {  // d_q[h,d] (thread = hd), d_k[s,d] and d_v[s,d] (threads 0..15 over d, loop s)
+    const int h = t >> 3, d = t & 7;
+    float dq = 0.f;
+    for (int s = 0; s < S; ++s) dq += sdl[h][s] * sk[s][d];
+    sdq[t] = dq * rsqrtf((float)GD);
+    if (t < GD) {
+      for (int s = 0; s < S; ++s) {
+        float a = 0.f;
+        for (int hh = 0; hh < GH; ++hh) a += sdl[hh][s] * sq[hh * GD + t];
+        sdk[s][t] = a;
+      }
+    } else if (t < 2 * GD) {
+      const int dd = t - GD;
+      for (int s = 0; s < S; ++s) {
+        float a = 0.f;
+        for (int hh = 0; hh < GH; ++hh) a += sw[hh][s] * sdavg[hh * GD + dd];
+        sdv[s][dd] = a;
+      }
+    }
+  }
+  __syncthreads();
+  // ---- cotangent of x: thread = input channel c
+  float dqa = 0.f;
+  for (int k = 0; k < GC; ++k) dqa += sdq[k] * W.wq_t[k * GC + t];
+  for (int s = 0; s < S; ++s) {
+    float a = sm[s] * inv_m * dqa;
+    for (int k = 0; k < GC; ++k) a += sdgp[s][k] * W.wg_t[k * GC + t];
+    for (int d = 0; d < GD; ++d) a += sdk[s][d] * W.wk[t * GD + d] + sdv[s][d] * W.wv[t * GD + d];
+    dx[((long)s * N + n) * GC + t] = __float2bfloat16(a);
+  }
+}
+
+}  // namespace bc2

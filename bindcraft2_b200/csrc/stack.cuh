@@ -26,6 +26,7 @@ struct StackConfig {
   int N = 0, S = 0, depth = 0;
   int Cm = 256, Cz = 128;
   bool pair_only = false, opm_first = true;
+  bool extra = false;  // extra-MSA stack: Cm = 64, global column attention (modules_multimer.py:547-603)
   int tri_hidden = 128, tri_heads = 4, msa_heads = 8, trans_factor = 4;
 };
 
@@ -45,6 +46,7 @@ struct EvoStack {
   Opm opm;
   MsaRow row;
   MsaCol col;
+  MsaColGlobal colg;
   Transition mtrans, ptrans;
   TriMul tmo, tmi;
   TriAttn tas, tae;
@@ -71,7 +73,9 @@ struct EvoStack {
     msa_mask = A.alloc<float>(Mm);
     const int wide_p = std::max(4 * c.tri_hidden + c.Cz, std::max(4 * c.Cz, c.trans_factor * c.Cz));
     Sp.init(A, Mp, c.Cz, wide_p, true, N, c.tri_heads);
-    Sm.init(A, Mm, c.Cm, 4 * c.Cm, false, N, c.msa_heads);
+    // the MSA row attention runs heads narrower than 16 zero-padded to 16: its buffers are msa_heads*16 wide then
+    const int cms = std::max(c.Cm, c.msa_heads * 16);
+    Sm.init(A, Mm, cms, 4 * cms, false, N, c.msa_heads);
     for (int i = 1; i < 7; ++i) P[i] = A.alloc<float>(Mp * c.Cz);
     P[0] = A.alloc<float>(Mp * c.Cz);
     for (int i = 0; i < 4; ++i) Mx[i] = A.alloc<float>(Mm * c.Cm);
@@ -82,7 +86,8 @@ struct EvoStack {
     if (!c.pair_only) {
       opm.init(A, &Sm, N, S, c.Cm, msa_mask);
       row.init(A, &Sm, N, S, c.Cm, c.Cz, c.msa_heads, msa_mask);
-      col.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
+      if (c.extra) colg.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
+      else col.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
       mtrans.init(A, &Sm, Mm, c.Cm, c.trans_factor);
     }
     tmo.init(A, &Sp, N, c.Cz, c.tri_hidden, true);
@@ -96,7 +101,8 @@ struct EvoStack {
       if (!c.pair_only) {
         opm.add_block(A, man, p + "outer_product_mean");
         row.add_block(A, man, p + "msa_row_attention_with_pair_bias");
-        col.add_block(A, man, p + "msa_column_attention");
+        if (c.extra) colg.add_block(A, man, p + "msa_column_global_attention");
+        else col.add_block(A, man, p + "msa_column_attention");
         mtrans.add_block(A, man, p + "msa_transition");
       } else {
         // a fully masked alignment: left = right = 0 and the norm is 0, so the outer product mean is output_b / 1e-3
@@ -159,7 +165,7 @@ struct EvoStack {
     if (en & 1) opm.forward(b, m_in, p_in, P[1], ms); else idp(p_in, P[1], ms);
     if (side) fork(side, st, ev[1]);  // the pair track may start once the outer product mean has produced P[1]
     if (en & 2) row.forward(b, m_in, Mx[1], P[1], ms); else idm(m_in, Mx[1]);
-    if (en & 4) col.forward(b, Mx[1], Mx[2], ms); else idm(Mx[1], Mx[2]);
+    if (en & 4) { if (cfg.extra) colg.forward(b, Mx[1], Mx[2], ms); else col.forward(b, Mx[1], Mx[2], ms); } else idm(Mx[1], Mx[2]);
     if (tail || !(en & 8)) {
       if (en & 8) mtrans.forward(b, Mx[2], m_out, ms); else idm(Mx[2], m_out);
     } else {
@@ -179,7 +185,7 @@ struct EvoStack {
     cudaStream_t ms = (side && !cfg.pair_only) ? side : st;
     if (side && !cfg.pair_only) fork(st, side, ev[0]);
     if (en & 8) mtrans.backward(b, Mx[2], g_msa, ms);
-    if (en & 4) col.backward(b, Mx[1], g_msa, ms);
+    if (en & 4) { if (cfg.extra) colg.backward(b, Mx[1], g_msa, ms); else col.backward(b, Mx[1], g_msa, ms); }
     if (en & 256) ptrans.backward(b, P[5], g_pair, st);
     if (en & 128) tae.backward(b, P[4], g_pair, st);
     if (en & 64) tas.backward(b, P[3], g_pair, st);

@@ -120,9 +120,11 @@ def evoformer_fwd(pair, msa, pair_mask, msa_mask, seed, *, depth, save, weights_
     Returns (pair_out f32 [N,N,128], msa_out f32 [S,N,256], psave bf16 [slots,N,N,128], msave f32 [slots,S,N,256]);
     the save tensors are empty when ``save == 0`` (the detached pass)."""
     lib = _lib.load()
-    n, s = int(pair.shape[0]), int(msa.shape[0])
+    n, s, cm = int(pair.shape[0]), int(msa.shape[0]), int(msa.shape[-1])
+    if cm not in (CM, 64):
+        raise ValueError('msa must have 256 channels (main stack) or 64 (extra-MSA stack)')
     _check_f32('pair', pair, (n, n, CZ))
-    _check_f32('msa', msa, (s, n, CM))
+    _check_f32('msa', msa, (s, n, cm))
     _check_f32('pair_mask', pair_mask, (n, n))
     _check_f32('msa_mask', msa_mask, (s, n))
     if n % 32:
@@ -131,9 +133,15 @@ def evoformer_fwd(pair, msa, pair_mask, msa_mask, seed, *, depth, save, weights_
     pair_out = torch.empty_like(pair)
     msa_out = torch.empty_like(msa)
     psave = torch.empty((slots, n, n, CZ), dtype=torch.bfloat16, device=pair.device)
-    msave = torch.empty((slots, s, n, CM), dtype=torch.float32, device=pair.device)
+    msave = torch.empty((slots, s, n, cm), dtype=torch.float32, device=pair.device)
     stream = torch.cuda.current_stream(pair.device).cuda_stream
     with torch.cuda.device(pair.device):
+        if cm == 64 and not pair_only:  # the extra-MSA stack with a live alignment: dispatched on the msa width
+            _lib.check(lib.bc2_extra_msa_stack_fwd(stream, _ptr(pair), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask), _ptr(seed),
+                                                   n, s, int(depth), int(save), int(own_save), int(dropout),
+                                                   os.fsencode(weights_dir), _ptr(pair_out), _ptr(msa_out),
+                                                   _ptr(psave) if save else 0, _ptr(msave) if save else 0))
+            return pair_out, msa_out, psave, msave
         _lib.check(lib.bc2_evoformer_fwd(stream, _ptr(pair), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask), _ptr(seed), n, s,
                                          int(depth), int(save), int(pair_only), int(own_save), int(opm_first),
                                          int(dropout), os.fsencode(weights_dir), _ptr(pair_out), _ptr(msa_out),
@@ -145,15 +153,20 @@ def evoformer_bwd(ct_pair, ct_msa, pair_mask, msa_mask, psave, msave, seed, *, d
                   own_save=0, opm_first=1, dropout=0):
     """FFI target ``native_evoformer_bwd`` (reference handler native/ffi.cu:333-371, 963-981): (dpair, dmsa)."""
     lib = _lib.load()
-    n, s = int(ct_pair.shape[0]), int(ct_msa.shape[0])
+    n, s, cm = int(ct_pair.shape[0]), int(ct_msa.shape[0]), int(ct_msa.shape[-1])
     _check_f32('ct_pair', ct_pair, (n, n, CZ))
-    _check_f32('ct_msa', ct_msa, (s, n, CM))
+    _check_f32('ct_msa', ct_msa, (s, n, cm))
     if psave.dtype != torch.bfloat16 or tuple(psave.shape) != (_save_slots(depth, n), n, n, CZ):
         raise ValueError('psave does not have the shape the forward declared')
     dpair = torch.empty_like(ct_pair)
     dmsa = torch.empty_like(ct_msa)
     stream = torch.cuda.current_stream(ct_pair.device).cuda_stream
     with torch.cuda.device(ct_pair.device):
+        if cm == 64 and not pair_only:
+            _lib.check(lib.bc2_extra_msa_stack_bwd(stream, _ptr(ct_pair), _ptr(ct_msa), _ptr(pair_mask), _ptr(msa_mask),
+                                                   _ptr(psave), _ptr(msave), _ptr(seed), n, s, int(depth), int(own_save),
+                                                   int(dropout), os.fsencode(weights_dir), _ptr(dpair), _ptr(dmsa)))
+            return dpair, dmsa
         _lib.check(lib.bc2_evoformer_bwd(stream, _ptr(ct_pair), _ptr(ct_msa), _ptr(pair_mask), _ptr(msa_mask),
                                          _ptr(psave), _ptr(msave), _ptr(seed), n, s, int(depth), int(pair_only),
                                          int(own_save), int(opm_first), int(dropout), os.fsencode(weights_dir),

@@ -85,8 +85,8 @@ int bc2_template_embedding_bwd(void* stream, const float* ct, const float* query
 
 /* Structure-module core: the fold iterations of the reference's StructureHeadsFwd / StructureHeadsBwd handlers
  * (native/ffi.cu:1009-1043, FFI targets `native_post_trunk_fwd/bwd`; model code
- * bindcraft/af/alphafold/model/folding_multimer.py:188-556) WITHOUT the side-chain atoms and the output heads, which are
- * not built yet: instead of atom14 and head logits the forward returns the state those parts consume.
+ * bindcraft/af/alphafold/model/folding_multimer.py:188-556) WITHOUT the side-chain atoms and the output heads (the full
+ * call is bc2_structure_heads_fwd below): instead of atom14 and head logits this returns the state those parts consume.
  *   single f32 [N,384], pair f32 [N,N,128], seq_mask f32 [N] (the reference passes seq_mask (x) seq_mask as [N,N]; only
  *   the product m_i m_j is used, modules_multimer.py:129,140), depth = number of fold iterations (8), weights_dir = the
  *   post-trunk manifest (param/single_layer_norm, param/pair_layer_norm, param/initial_projection,
@@ -103,6 +103,22 @@ int bc2_structure_module_fwd(void* stream, const float* single, const float* pai
 int bc2_structure_module_bwd(void* stream, const float* single, const float* pair, const float* seq_mask, const float* d_act,
                              const float* d_rigids, int64_t N, int64_t depth, const char* weights_dir, float* d_single,
                              float* d_pair);
+
+/* The extra-MSA stack with a LIVE alignment: NativeEvoformerFwd / NativeEvoformerBwd (native/ffi.cu:183-371) called with an
+ * msa operand of 64 channels (model code bindcraft/af/alphafold/model/modules_multimer.py:547-603,
+ * EvoformerIteration(is_extra_msa=True): row attention with 8 heads of width 8, MSAColumnGlobalAttention modules.py:619-672,
+ * transition, outer product mean from 64 channels; the pair track as in the main stack).  An FFI binding dispatches on
+ * the msa buffer's last dimension: 256 -> bc2_evoformer_*, 64 -> these.  Operands as bc2_evoformer_fwd/bwd with
+ * msa f32 [S,N,64], S <= 8, msave f32 [depth,S,N,64].  The reference itself only ever runs this stack with a fully
+ * masked alignment (pair_only = 1 of bc2_evoformer_fwd); this is the general path of the same model code. */
+int bc2_extra_msa_stack_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
+                            const uint32_t* seed, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t own_save,
+                            int64_t dropout, const char* weights_dir, float* pair_out, float* msa_out, uint16_t* psave,
+                            float* msave);
+int bc2_extra_msa_stack_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
+                            const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* seed,
+                            int64_t N, int64_t S, int64_t depth, int64_t own_save, int64_t dropout,
+                            const char* weights_dir, float* dpair, float* dmsa);
 
 /* Replaces StructureHeadsFwd (native/ffi.cu:1009-1025, FFI target `native_post_trunk_fwd`): the structure module with
  * its side-chain atoms, and the four output heads.

@@ -74,6 +74,12 @@ def test_single_block_n128_s1(lib, tmp_path):
     _case(lib, tmp_path, 101, 102, 128, 1, 1, tag='cfg1')
 
 
+def test_single_block_n768_long_complex(lib, tmp_path):
+    """The long-complex length (N_res = 768 = 120 + 648) on one GPU: attention takes the general kernels here (six key
+    blocks forward, keys split over three CTAs with fp32 dQ accumulation backward)."""
+    _case(lib, tmp_path, 141, 142, 768, 1, 1, tag='N=768')
+
+
 @pytest.mark.parametrize('step', O.STEPS)
 def test_each_module_alone_s2_masked(lib, tmp_path, step):
     """One residual step at a time (the reference gates its modules one by one too), two alignment rows and a masked pad."""
@@ -208,3 +214,33 @@ def test_bad_arguments_are_reported(lib, tmp_path):
     t = {k: v.cuda() for k, v in inp.items()}
     with pytest.raises(RuntimeError):  # depth 2 asked from a 1-block manifest
         native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, depth=2, save=1, weights_dir=wdir)
+
+
+def _extra_case(lib, tmp_path, wseed, iseed, n, s, depth, masked=0, steps=None, tag=''):
+    """The extra-MSA stack with a live alignment: 64 msa channels, row attention heads of width 8, global column
+    attention (EvoformerIteration(is_extra_msa=True), modules_multimer.py:547-603)."""
+    params = synthetic.make_evoformer_params(wseed, depth, cm=64, is_extra_msa=True)
+    inp = synthetic.make_block_inputs(iseed, n, s, cm=64, masked=masked)
+    mask = 0x1ff if steps is None else sum(1 << i for i, x in enumerate(O.STEPS) if x in steps)
+    lib.bc2_test_set_module_mask(mask)
+    try:
+        got, _ = _run_cuda(lib, params, inp, depth, tmp_path, own_save=0)
+    finally:
+        lib.bc2_test_set_module_mask(0x1ff)
+    want = O.stack_fwd_bwd(params, inp, depth, is_extra_msa=True, steps=steps)
+    with O.bf16_operands():
+        floor = O.stack_fwd_bwd(params, inp, depth, is_extra_msa=True, steps=steps)
+    real = n - masked
+    return _check(_crop(got, real), _crop(want, real), _crop(floor, real), tag)
+
+
+@pytest.mark.parametrize('step', ['msa_row_attention_with_pair_bias', 'msa_column_attention', 'msa_transition',
+                                  'outer_product_mean'])
+def test_extra_msa_modules_alone(lib, tmp_path, step):
+    """The MSA-side residual steps of the extra stack one at a time, 8 alignment rows, a masked pad."""
+    _extra_case(lib, tmp_path, 151, 152, 64, 8, 1, masked=7, steps={step}, tag='extra ' + step)
+
+
+def test_extra_msa_stack_general_path(lib, tmp_path):
+    """Configuration 3's extra-MSA part: 4 blocks, c_e = 64, 8 rows, global column attention, at N_res = 224."""
+    _extra_case(lib, tmp_path, 153, 154, 224, 8, 4, tag='extra stack N=224 S=8 depth=4')

@@ -142,6 +142,40 @@ def test_post_trunk_each_cotangent_alone(lib, tmp_path):
                 assert SO.rel_l2(got[k], want[k]) <= TOL, (only, k, SO.rel_l2(got[k], want[k]))
 
 
+def test_post_trunk_n400_depth8_parity_and_timing(lib, tmp_path):
+    """The structure-module configuration (N_res = 400, 8 iterations) through the full post-trunk call: outputs against
+    the oracle, and the device time of a forward and of a backward (CUDA events, 5 repetitions after 2 warm-ups)."""
+    from bindcraft2_b200 import native
+    n, depth = 400, 8
+    params = synthetic.add_structure_head_params(synthetic.make_structure_params(431), 432)
+    tables = synthetic.make_structure_tables(433)
+    inp = synthetic.add_structure_head_inputs(synthetic.make_structure_inputs(434, n), 435)
+    got, (wdir, t, mask2d, aatype, seed) = _run_heads(lib, params, tables, inp, depth, tmp_path)
+    want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth, dtype=torch.float64)
+    rep = {k: SO.rel_l2(got[k], want[k]) for k in want}
+    print('post-trunk N=400 depth=8', {k: f'{v:.2e}' for k, v in rep.items()})
+    for k in SO.HEAD_OUTS:
+        assert rep[k] <= 1e-4, (k, rep)
+    for k in ('d_single', 'd_pair'):   # see test_structure_core_n400_depth8 for why this is not 1e-3
+        assert rep[k] <= 2e-2, (k, rep)
+    cts = [t['ct_' + k] for k in SO.HEAD_OUTS]
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    for rep_i in range(2):
+        native.post_trunk_fwd(t['single'], t['pair'], mask2d, aatype, seed, depth=depth, weights_dir=wdir)
+        native.post_trunk_bwd(t['single'], t['pair'], mask2d, aatype, seed, *cts, depth=depth, weights_dir=wdir)
+    torch.cuda.synchronize()
+    ev[0].record()
+    for _ in range(5):
+        native.post_trunk_fwd(t['single'], t['pair'], mask2d, aatype, seed, depth=depth, weights_dir=wdir)
+    ev[1].record()
+    for _ in range(5):
+        native.post_trunk_bwd(t['single'], t['pair'], mask2d, aatype, seed, *cts, depth=depth, weights_dir=wdir)
+    ev[2].record()
+    torch.cuda.synchronize()
+    print('post-trunk N=400 depth=8: forward %.2f ms, backward (with its replay) %.2f ms'
+          % (ev[0].elapsed_time(ev[1]) / 5, ev[1].elapsed_time(ev[2]) / 5))
+
+
 def test_post_trunk_autograd_pairing(lib, tmp_path):
     from bindcraft2_b200 import native
     n = 16

@@ -28,6 +28,16 @@ def test_oracle_matches_golden(name):
         np.testing.assert_allclose(got[k], want[k], rtol=1e-9, atol=1e-9, err_msg=f'{name}:{k}')
 
 
+@pytest.mark.parametrize('name', ['extra_msa_block_n32_s4_masked', 'post_trunk_n12_depth3', 'embedder_n48_s2'])
+def test_other_oracles_match_golden(name):
+    """The extra-MSA block (global column attention), the post-trunk call and the embedder against their fixtures."""
+    mg = _golden_cases()
+    got = mg.run_other(name)
+    want = np.load(os.path.join(GOLD, name + '.npz'))
+    for k in want.files:
+        np.testing.assert_allclose(got[k], want[k], rtol=1e-9, atol=1e-9, err_msg=f'{name}:{k}')
+
+
 def test_fp32_agrees_with_fp64():
     p = synthetic.make_evoformer_params(1, 1)
     inp = synthetic.make_block_inputs(2, 32, 2)
