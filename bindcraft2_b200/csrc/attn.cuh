@@ -765,9 +765,24 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
       const long lidx = ((long)b * a.H + h) * a.N + q;
       const float2 ml = qin ? *reinterpret_cast<const float2*>(a.lse + 2 * lidx) : make_float2(0.f, 0.f);
       const float dl = qin ? a.delta[lidx] : 0.f;
-      const float* brow = (a.bias && qin) ? a.bias + (long)h * a.N * a.N + q : nullptr;
+      // bias: the half-precision octet copy when there is one (same values as the fp32 array), else the fp32 array
+      const uint4* b16row = (a.bias16 && qin) ? reinterpret_cast<const uint4*>(a.bias16) + (long)h * (a.N >> 3) * a.N + q : nullptr;
+      const float* brow = (a.bias && qin && !b16row) ? a.bias + (long)h * a.N * a.N + q : nullptr;
       float* dbrow = (a.d_bias && qin) ? a.d_bias + (long)h * a.N * a.N + q : nullptr;
       for (int j = 0; j < nkb && ok; ++j, ++step) {
+        // The bias of this step's two 32-key chunks does not depend on the MMAs: fetch it (8 keys per 128-bit load from
+        // the half-precision octet copy) before waiting for S and dP, so that its latency hides behind that wait.
+        uint4 bb[2][4];
+        if (b16row) {
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int k0 = (kb0 + j) * 128 + (half * 2 + cc) * 32;
+            if (k0 < a.N) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) bb[cc][t] = b16row[(long)((k0 >> 3) + t) * a.N];
+            }
+          }
+        }
         ok = mbar_wait(b_s, step & 1, SITE_ATTN_BWD);
         if (!ok) break;
         // P/dS tiles are operands of the previous step's gradient MMAs until b_g flips
@@ -795,7 +810,19 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
               const float4 mk = mk4[e >> 2];
               s[e] += mk.x; s[e + 1] += mk.y; s[e + 2] += mk.z; s[e + 3] += mk.w;
             }
-            if (brow) {
+            if (b16row) {
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                const uint4 w = cc == 0 ? bb[0][t] : bb[1][t];
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[e]));
+                  s[8 * t + 2 * e] += f.x;
+                  s[8 * t + 2 * e + 1] += f.y;
+                }
+              }
+            } else if (brow) {
               const float* bp = brow + (long)k0 * a.N;
 #pragma unroll
               for (int e = 0; e < 32; ++e) s[e] += bp[(long)e * a.N];
