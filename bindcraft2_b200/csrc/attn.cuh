@@ -676,14 +676,18 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
     tma_prefetch_desc(&tdo);
   }
   if (warp == 1) tmem_alloc(tslot, 512);
+  bool my_masked = false;
   for (int k = threadIdx.x; k < 256; k += blockDim.x) {
     const int kk = kb0 * 128 + k;
     float mk = 0.f;
     if (kk < a.N && a.mask) mk = 1e9f * (a.mask[(long)b * a.mask_b + (long)kk * a.mask_k] - 1.f);
     sMask[k] = mk;
+    my_masked |= mk != 0.f;
   }
   tc_fence_before();
-  __syncthreads();
+  // any masked key in this CTA's key range?  Without one no logit comes near the clip value, and the element loops
+  // below skip the mask add, the clip and its gradient gate.
+  const bool anym = __syncthreads_or(my_masked);
   tc_fence_after();
   const uint32_t tmem = *tslot;
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
@@ -804,11 +808,13 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
           // loops below are branch-free.
           const bool chunk_live = qin && k0 < a.N;
           if (chunk_live) {
-            const float4* mk4 = reinterpret_cast<const float4*>(sMask + kl);
+            if (anym) {
+              const float4* mk4 = reinterpret_cast<const float4*>(sMask + kl);
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-              const float4 mk = mk4[e >> 2];
-              s[e] += mk.x; s[e + 1] += mk.y; s[e + 2] += mk.z; s[e + 3] += mk.w;
+              for (int e = 0; e < 32; e += 4) {
+                const float4 mk = mk4[e >> 2];
+                s[e] += mk.x; s[e + 1] += mk.y; s[e + 2] += mk.z; s[e + 3] += mk.w;
+              }
             }
             if (b16row) {
 #pragma unroll
@@ -827,13 +833,23 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
 #pragma unroll
               for (int e = 0; e < 32; ++e) s[e] += bp[(long)e * a.N];
             }
+            if (anym) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float t = s[e];
-              const float tc = fminf(fmaxf(t, -kClip), kClip);
-              const float p = ex2_approx((tc - ml.x) * kLog2e) * ml.y;
-              s[e] = p;
-              dsv[e] = (tc == t) ? p * (dp[e] - dl) : 0.f;  // the clip passes no gradient
+              for (int e = 0; e < 32; ++e) {
+                const float t = s[e];
+                const float tc = fminf(fmaxf(t, -kClip), kClip);
+                const float p = ex2_approx((tc - ml.x) * kLog2e) * ml.y;  // subtract first: exact for fully masked rows
+                s[e] = p;
+                dsv[e] = (tc == t) ? p * (dp[e] - dl) : 0.f;  // the clip passes no gradient
+              }
+            } else {
+              const float nml = -ml.x * kLog2e;
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                const float p = ex2_approx(fmaf(s[e], kLog2e, nml)) * ml.y;
+                s[e] = p;
+                dsv[e] = p * (dp[e] - dl);
+              }
             }
           } else {
 #pragma unroll

@@ -85,29 +85,45 @@ trimul_bwd_out_kernel(const float4* __restrict__ dz, const uint2* __restrict__ o
 __global__ void __launch_bounds__(256)
 trimul_bwd_gate_kernel(const bf16* __restrict__ d_ab, const bf16* __restrict__ ab, const bf16* __restrict__ gate,
                        const float* __restrict__ mask, bf16* __restrict__ dcat, long ldd, long M, int CH) {
-  __shared__ float sd[64][65], sa[64][65];
+  // [64 channels][64 positions] of each plane as bf16, rows padded to 66 (33 words: column reads of channel groups 16
+  // apart land two per bank instead of four)
+  __shared__ __align__(16) bf16 sd[64][66], sa[64][66];
   const long p0 = (long)blockIdx.x * 64;
   const int c0 = blockIdx.y * 64;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = warp; c < 64; c += 8) {
-    const long p = p0 + 2 * lane;
-    const float2 d = unpack_bf16(*reinterpret_cast<const uint32_t*>(d_ab + (long)(c0 + c) * M + p));
-    const float2 a = unpack_bf16(*reinterpret_cast<const uint32_t*>(ab + (long)(c0 + c) * M + p));
-    sd[c][2 * lane] = d.x; sd[c][2 * lane + 1] = d.y;
-    sa[c][2 * lane] = a.x; sa[c][2 * lane + 1] = a.y;
+  {  // planes -> shared memory, 8 positions (one 128-bit load) per thread
+    const int pg = threadIdx.x & 7;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const int c = (threadIdx.x >> 3) + 32 * pass;
+      const uint4 d = *reinterpret_cast<const uint4*>(d_ab + (long)(c0 + c) * M + p0 + pg * 8);
+      const uint4 a = *reinterpret_cast<const uint4*>(ab + (long)(c0 + c) * M + p0 + pg * 8);
+      uint32_t* dd = reinterpret_cast<uint32_t*>(&sd[c][pg * 8]);
+      uint32_t* da = reinterpret_cast<uint32_t*>(&sa[c][pg * 8]);
+      dd[0] = d.x; dd[1] = d.y; dd[2] = d.z; dd[3] = d.w;
+      da[0] = a.x; da[1] = a.y; da[2] = a.z; da[3] = a.w;
+    }
   }
   __syncthreads();
-  for (int r = warp; r < 64; r += 8) {
-    const long p = p0 + r;
-    const float mk = mask[p];
-    const int c = 2 * lane;
-    const float2 g = unpack_bf16(*reinterpret_cast<const uint32_t*>(gate + p * CH + c0 + c));
-    const float d0 = sd[c][r], d1 = sd[c + 1][r], a0 = sa[c][r], a1 = sa[c + 1][r];
-    const int ch = c0 + c;
-    const long col = (long)(ch / 128) * 256 + ch % 128;
-    *reinterpret_cast<uint32_t*>(dcat + p * ldd + col) = pack_bf16(d0 * mk * g.x, d1 * mk * g.y);
-    *reinterpret_cast<uint32_t*>(dcat + p * ldd + col + 128) = pack_bf16(d0 * a0 * (1.f - g.x), d1 * a1 * (1.f - g.y));
+  // rows out: thread = (position, group of 16 channels); four threads cover 128 contiguous bytes of a row
+  const int pl = threadIdx.x >> 2, cg = threadIdx.x & 3;
+  const long p = p0 + pl;
+  const float mk = mask[p];
+  const int ch = c0 + cg * 16;
+  const long col = (long)(ch / 128) * 256 + ch % 128;
+  uint32_t gw[8];
+  ld_global_v8(gate + p * CH + ch, gw);
+  uint32_t o1[8], o2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float2 g = unpack_bf16(gw[e]);
+    const int c = cg * 16 + 2 * e;
+    const float d0 = __bfloat162float(sd[c][pl]), d1 = __bfloat162float(sd[c + 1][pl]);
+    const float a0 = __bfloat162float(sa[c][pl]), a1 = __bfloat162float(sa[c + 1][pl]);
+    o1[e] = pack_bf16(d0 * mk * g.x, d1 * mk * g.y);
+    o2[e] = pack_bf16(d0 * a0 * (1.f - g.x), d1 * a1 * (1.f - g.y));
   }
+  st_global_v8(dcat + p * ldd + col, o1);
+  st_global_v8(dcat + p * ldd + col + 128, o2);
 }
 
 // Attention backward, output side.  og = o * gate.  Given d_og:

@@ -476,36 +476,60 @@ inline void ln_bwd(const LnBwdArgs& a, cudaStream_t st) {
 }
 
 // ------------------------------------------------------------------------------------------- centre norm (transposing)
-// t: [C][M] bf16 planes.  A block stages a [C x 64-position] tile through shared memory (reads coalesced along
-// positions), then each warp normalises whole positions and writes row-major (coalesced along channels).
+// t: [C][M] bf16 planes.  A block stages a [C x 64-position] tile in shared memory with 128-bit plane reads, then
+// thread (position, quarter of the channels) normalises: partial sums meet across the four threads of a position by
+// shuffles, and the four threads write one contiguous row (256-bit stores).
+template <int C>
+struct ClnTile {
+  static constexpr int PITCH = 66;     // bf16 per row: 33 words, so channel groups C/4 apart land two per bank
+  static constexpr int CPT = C / 4;    // channels per thread
+};
+
+template <int C>
+__device__ __forceinline__ void cln_load_tile(const bf16* __restrict__ t, bf16 (*tile)[ClnTile<C>::PITCH], long p0, long M) {
+  const int pg = threadIdx.x & 7;
+  for (int c = threadIdx.x >> 3; c < C; c += 32) {
+    const uint4 v = *reinterpret_cast<const uint4*>(t + (long)c * M + p0 + pg * 8);
+    uint32_t* d = reinterpret_cast<uint32_t*>(&tile[c][pg * 8]);
+    d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+  }
+}
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
+
 template <int C>
 __global__ void __launch_bounds__(256) cln_fwd_kernel(const bf16* __restrict__ t, const float* __restrict__ scale,
                                                       const float* __restrict__ offset, bf16* __restrict__ y, int M) {
-  __shared__ float tile[C][65];
-  const int p0 = blockIdx.x * 64;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = warp; c < C; c += 8) {
-    const int p = p0 + 2 * lane;
-    float2 f = make_float2(0.f, 0.f);
-    if (p < M) f = unpack_bf16(*reinterpret_cast<const uint32_t*>(t + (long)c * M + p));
-    tile[c][2 * lane] = f.x;
-    tile[c][2 * lane + 1] = f.y;
-  }
+  using T = ClnTile<C>;
+  __shared__ __align__(16) bf16 tile[C][T::PITCH];
+  __shared__ float ssc[C], sof[C];
+  const long p0 = (long)blockIdx.x * 64;
+  for (int c = threadIdx.x; c < C; c += 256) { ssc[c] = scale[c]; sof[c] = offset[c]; }
+  cln_load_tile<C>(t, tile, p0, M);
   __syncthreads();
-  constexpr int VPL = C / 32;
-  for (int r = warp; r < 64; r += 8) {
-    const int p = p0 + r;
-    if (p >= M) break;
-    float v[VPL];
+  const int pl = threadIdx.x >> 2, cg = threadIdx.x & 3;
+  float v[T::CPT];
+  float s = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) v[i] = tile[i * 32 + lane][r];
-    float mean, rstd;
-    row_stats<C>(v, mean, rstd);
+  for (int i = 0; i < T::CPT; ++i) { v[i] = __bfloat162float(tile[cg * T::CPT + i][pl]); s += v[i]; }
+  const float mean = quad_sum(s) * (1.f / C);
+  float q = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-      const int c = i * 32 + lane;
-      y[(long)p * C + c] = __float2bfloat16((v[i] - mean) * rstd * scale[c] + offset[c]);
+  for (int i = 0; i < T::CPT; ++i) { const float d = v[i] - mean; q += d * d; }
+  const float rstd = rsqrtf(quad_sum(q) * (1.f / C) + 1e-5f);
+  bf16* dst = y + (p0 + pl) * C + cg * T::CPT;
+#pragma unroll
+  for (int i = 0; i < T::CPT; i += 16) {
+    uint32_t pk[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = cg * T::CPT + i + 2 * e;
+      pk[e] = pack_bf16((v[i + 2 * e] - mean) * rstd * ssc[c] + sof[c], (v[i + 2 * e + 1] - mean) * rstd * ssc[c + 1] + sof[c + 1]);
     }
+    st_global_v8(dst + i, pk);
   }
 }
 
@@ -513,45 +537,52 @@ __global__ void __launch_bounds__(256) cln_fwd_kernel(const bf16* __restrict__ t
 template <int C>
 __global__ void __launch_bounds__(256) cln_bwd_kernel(const bf16* __restrict__ t, const float* __restrict__ scale,
                                                       const bf16* __restrict__ dy, bf16* __restrict__ dt, int M) {
-  __shared__ float tile[C][65];
-  const int p0 = blockIdx.x * 64;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = warp; c < C; c += 8) {
-    const int p = p0 + 2 * lane;
-    float2 f = make_float2(0.f, 0.f);
-    if (p < M) f = unpack_bf16(*reinterpret_cast<const uint32_t*>(t + (long)c * M + p));
-    tile[c][2 * lane] = f.x;
-    tile[c][2 * lane + 1] = f.y;
-  }
+  using T = ClnTile<C>;
+  __shared__ __align__(16) bf16 tile[C][T::PITCH];
+  __shared__ float ssc[C];
+  const long p0 = (long)blockIdx.x * 64;
+  for (int c = threadIdx.x; c < C; c += 256) ssc[c] = scale[c];
+  cln_load_tile<C>(t, tile, p0, M);
   __syncthreads();
-  constexpr int VPL = C / 32;
-  for (int r = warp; r < 64; r += 8) {
-    const int p = p0 + r;
-    if (p < M) {
-      float v[VPL], d[VPL];
+  const int pl = threadIdx.x >> 2, cg = threadIdx.x & 3;
+  float v[T::CPT], d[T::CPT];
+  float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < VPL; ++i) v[i] = tile[i * 32 + lane][r];
-      float mean, rstd;
-      row_stats<C>(v, mean, rstd);
-      float s1 = 0.f, s2 = 0.f;
+  for (int i = 0; i < T::CPT; ++i) { v[i] = __bfloat162float(tile[cg * T::CPT + i][pl]); s += v[i]; }
+  const float mean = quad_sum(s) * (1.f / C);
+  float q = 0.f;
 #pragma unroll
-      for (int i = 0; i < VPL; ++i) {
-        const int c = i * 32 + lane;
-        v[i] = (v[i] - mean) * rstd;
-        d[i] = __bfloat162float(dy[(long)p * C + c]) * scale[c];
-        s1 += d[i];
-        s2 += d[i] * v[i];
-      }
-      s1 = warp_sum(s1) * (1.f / C);
-      s2 = warp_sum(s2) * (1.f / C);
+  for (int i = 0; i < T::CPT; ++i) { const float x = v[i] - mean; q += x * x; }
+  const float rstd = rsqrtf(quad_sum(q) * (1.f / C) + 1e-5f);
+  const bf16* src = dy + (p0 + pl) * C + cg * T::CPT;
+  float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int i = 0; i < VPL; ++i) tile[i * 32 + lane][r] = rstd * (d[i] - s1 - v[i] * s2);
+  for (int i = 0; i < T::CPT; i += 16) {
+    uint32_t w[8];
+    ld_global_v8(src + i, w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float2 f = unpack_bf16(w[e]);
+      const int c = cg * T::CPT + i + 2 * e;
+      d[i + 2 * e] = f.x * ssc[c];
+      d[i + 2 * e + 1] = f.y * ssc[c + 1];
     }
   }
+#pragma unroll
+  for (int i = 0; i < T::CPT; ++i) {
+    v[i] = (v[i] - mean) * rstd;
+    s1 += d[i];
+    s2 += d[i] * v[i];
+  }
+  s1 = quad_sum(s1) * (1.f / C);
+  s2 = quad_sum(s2) * (1.f / C);
+#pragma unroll
+  for (int i = 0; i < T::CPT; ++i) tile[cg * T::CPT + i][pl] = __float2bfloat16(rstd * (d[i] - s1 - v[i] * s2));
   __syncthreads();
-  for (int c = warp; c < C; c += 8) {
-    const int p = p0 + 2 * lane;
-    if (p < M) *reinterpret_cast<uint32_t*>(dt + (long)c * M + p) = pack_bf16(tile[c][2 * lane], tile[c][2 * lane + 1]);
+  const int pg = threadIdx.x & 7;
+  for (int c = threadIdx.x >> 3; c < C; c += 32) {
+    const uint32_t* sp = reinterpret_cast<const uint32_t*>(&tile[c][pg * 8]);
+    *reinterpret_cast<uint4*>(dt + (long)c * M + p0 + pg * 8) = make_uint4(sp[0], sp[1], sp[2], sp[3]);
   }
 }
 

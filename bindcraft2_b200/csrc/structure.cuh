@@ -163,9 +163,54 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
     }
   }
 }
+// Same contract on 32x32 tiles (one output row, four columns per thread): with a few hundred rows the 64x64 tiling
+// leaves most SMs idle (M = 400, N = 384 is 42 blocks), this one gives four times as many.
+__global__ void __launch_bounds__(256) linear_f32_small_kernel(LinArgs a) {
+  __shared__ float sX[16][32 + 1];
+  __shared__ __align__(16) float sW[16][32];
+  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
+  const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < a.K; k0 += 16) {
+    for (int t = threadIdx.x; t < 32 * 16; t += 256) {
+      const int r = t >> 4, k = t & 15;
+      float xv = (m0 + r < a.M && k0 + k < a.K) ? a.X[(long)(m0 + r) * a.K + k0 + k] : 0.f;
+      sX[k][r] = a.relu_in ? fmaxf(xv, 0.f) : xv;
+      const int kk = t >> 5, c = t & 31;
+      sW[kk][c] = (k0 + kk < a.K && n0 + c < a.N) ? a.W[(long)(k0 + kk) * a.N + n0 + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const float xv = sX[k][ty];
+      const float4 w = *reinterpret_cast<const float4*>(&sW[k][tx * 4]);
+      acc[0] += xv * w.x; acc[1] += xv * w.y; acc[2] += xv * w.z; acc[3] += xv * w.w;
+    }
+    __syncthreads();
+  }
+  const int m = m0 + ty;
+  if (m >= a.M) return;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int n = n0 + tx * 4 + j;
+    if (n >= a.N) continue;
+    float v = acc[j] + (a.bias ? a.bias[n] : 0.f);
+    if (a.relu) v = fmaxf(v, 0.f);
+    const long idx = (long)m * a.N + n;
+    if (a.R) v += a.R[idx];
+    if (a.G) v = a.G[idx] > 0.f ? v : 0.f;
+    a.Y[idx] = a.accumulate ? a.Y[idx] + v : v;
+  }
+}
 inline void linear_f32(const LinArgs& a, cudaStream_t st) {
-  dim3 grid(cdiv(a.N, 64), cdiv(a.M, 64));
-  launch_counter()++; linear_f32_kernel<<<grid, 256, 0, st>>>(a);
+  launch_counter()++;
+  if (a.M <= 2048) {
+    dim3 grid(cdiv(a.N, 32), cdiv(a.M, 32));
+    linear_f32_small_kernel<<<grid, 256, 0, st>>>(a);
+  } else {
+    dim3 grid(cdiv(a.N, 64), cdiv(a.M, 64));
+    linear_f32_kernel<<<grid, 256, 0, st>>>(a);
+  }
 }
 
 __global__ void add_f32_inplace_kernel(float* __restrict__ y, const float* __restrict__ x, long n) {
