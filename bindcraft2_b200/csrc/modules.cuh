@@ -605,33 +605,42 @@ struct Opm {
     bf16* wp = nullptr;   // output_w as [(f*32 + c)][e]: B operand of the first product
     float* wq = nullptr;  // output_w as [e][f][c] (fp32): d(right) kernel
     float *blr = nullptr, *ob = nullptr;
-    GemmPlan g_lr, gb_lr, g_tmp;
+    GemmPlan g_lr2[2], gb_lr, g_tmp2[2];
   };
   std::vector<W> w;
-  bf16 *lr = nullptr, *dlr_b = nullptr, *leftT = nullptr, *tmpT = nullptr, *dtmpT = nullptr, *dout = nullptr;
+  // The forward operands the backward needs (lr, leftT, tmpT) exist twice, used by blocks of even / odd index: the
+  // replayed forward of block b-1 may then run while the backward of block b still reads its own set.  The LayerNorm
+  // output has its own buffer for the same reason (the MSA scratch set is busy with the backward meanwhile).
+  bf16 *lr2[2] = {nullptr, nullptr}, *leftT2[2] = {nullptr, nullptr}, *tmpT2[2] = {nullptr, nullptr};
+  bf16 *xln = nullptr, *dlr_b = nullptr, *dtmpT = nullptr, *dout = nullptr;
   float* partial = nullptr;
-  GemmPlan g_out, g_dleft, g_dtmp;
+  GemmPlan g_out2[2], g_dleft2[2], g_dtmp2[2];
   const float* msa_mask = nullptr;
   Scratch* S = nullptr;
   void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, const float* mask) {
     S = s; n = n_; S_ = S__; Cm = Cm_; Mm = (long)S_ * n; msa_mask = mask;
     const int K = 32 * S_;
     const long NF = (long)n * OPM_F;
-    lr = A.alloc<bf16>(Mm * 64);
+    for (int i = 0; i < 2; ++i) {
+      lr2[i] = A.alloc<bf16>(Mm * 64);
+      leftT2[i] = A.alloc<bf16>((long)n * K);
+      tmpT2[i] = A.alloc<bf16>(NF * K);
+    }
+    xln = A.alloc<bf16>(Mm * Cm);
     dlr_b = A.alloc<bf16>(Mm * 64);
-    leftT = A.alloc<bf16>((long)n * K);
-    tmpT = A.alloc<bf16>(NF * K);
     dtmpT = A.alloc<bf16>(NF * K);
     dout = A.alloc<bf16>((long)n * NF);
     partial = A.alloc<float>((long)kSplit * n * K);
-    // second product: D[i][(j,f)] = leftT . tmpT^T
-    g_out = make_gemm(kmaj(leftT, K), kmaj(tmpT, K), n, (int)NF, K, 1, 256);
-    // d(left)[i][k] = sum_{(j,f)} dout[i][(j,f)] tmpT[(j,f)][k], the (j,f) range cut into kSplit batches
     const long Kc = NF / kSplit;
     BC2_CHECK(NF % (kSplit * 64) == 0, "outer product mean: n must be a multiple of 32");
-    g_dleft = make_gemm(Operand{dout, NF, Kc, false}, Operand{tmpT, K, Kc * K, true}, n, K, (int)Kc, kSplit, 128);
-    // d(tmpT)[(j,f)][k] = sum_i dout[i][(j,f)] leftT[i][k]: both operands read through their MN-major views
-    g_dtmp = make_gemm(Operand{dout, NF, 0, true}, Operand{leftT, K, 0, true}, (int)NF, K, n, 1, 128);
+    for (int i = 0; i < 2; ++i) {
+      // second product: D[i][(j,f)] = leftT . tmpT^T
+      g_out2[i] = make_gemm(kmaj(leftT2[i], K), kmaj(tmpT2[i], K), n, (int)NF, K, 1, 256);
+      // d(left)[i][k] = sum_{(j,f)} dout[i][(j,f)] tmpT[(j,f)][k], the (j,f) range cut into kSplit batches
+      g_dleft2[i] = make_gemm(Operand{dout, NF, Kc, false}, Operand{tmpT2[i], K, Kc * K, true}, n, K, (int)Kc, kSplit, 128);
+      // d(tmpT)[(j,f)][k] = sum_i dout[i][(j,f)] leftT[i][k]: both operands read through their MN-major views
+      g_dtmp2[i] = make_gemm(Operand{dout, NF, 0, true}, Operand{leftT2[i], K, 0, true}, (int)NF, K, n, 1, 128);
+    }
   }
   void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
     W b;
@@ -663,29 +672,32 @@ struct Opm {
     b.wp = A.upload_bf16(wp);
     b.wq = A.upload(wq);
     b.ob = A.upload(m.get(p + "/output_b").data);
-    b.g_lr = make_gemm(kmaj(S->x, Cm), kmaj(b.wlr, Cm), (int)Mm, 64, Cm);
     b.gb_lr = make_gemm(kmaj(dlr_b, 64), kmaj(b.wlr_b, 64), (int)Mm, Cm, 64);
-    // first product: rows (s,j) of the right projection (columns 32..63 of lr) times wp
-    b.g_tmp = make_gemm(kmaj(lr + 32, 64), kmaj(b.wp, OPM_C), (int)Mm, OPM_F * OPM_C, OPM_C, 1, 256);
+    for (int i = 0; i < 2; ++i) {
+      b.g_lr2[i] = make_gemm(kmaj(xln, Cm), kmaj(b.wlr, Cm), (int)Mm, 64, Cm);
+      // first product: rows (s,j) of the right projection (columns 32..63 of lr) times wp
+      b.g_tmp2[i] = make_gemm(kmaj(lr2[i] + 32, 64), kmaj(b.wp, OPM_C), (int)Mm, OPM_F * OPM_C, OPM_C, 1, 256);
+    }
     w.push_back(b);
   }
   // lr, leftT and tmpT of a block (also what the backward needs from the replayed forward)
-  void products(W& b, const float* msa_in, cudaStream_t st) {
+  void products(W& b, int set, const float* msa_in, cudaStream_t st) {
     const int Mi = (int)Mm;
-    LnArgs l; l.x = msa_in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
+    bf16 *lr = lr2[set], *leftT = leftT2[set], *tmpT = tmpT2[set];
+    LnArgs l; l.x = msa_in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = xln; l.ldy = Cm; l.M = Mi;
     { ProfScope ps_("Opm.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     EpiStore e; e.out = lr; e.ldo = 64; e.bias = b.blr; e.rowscale = msa_mask; e.M = Mi; e.N = 64;
-    { ProfScope ps_("Opm.forward.gemm.g_lr", st); run_gemm(b.g_lr, e, st); }
+    { ProfScope ps_("Opm.forward.gemm.g_lr", st); run_gemm(b.g_lr2[set], e, st); }
     { ProfScope ps_("Opm.forward.opm_pack_left_kernel", st); launch_counter()++; opm_pack_left_kernel<<<cdiv(n * S_ * 16, 256), 256, 0, st>>>(lr, leftT, S_, n); }
     EpiOpmTmp et; et.out = tmpT; et.S = S_; et.Nres = n; et.M = Mi; et.N = OPM_F * OPM_C;
-    { ProfScope ps_("Opm.forward.gemm.g_tmp", st); run_gemm(b.g_tmp, et, st); }
+    { ProfScope ps_("Opm.forward.gemm.g_tmp", st); run_gemm(b.g_tmp2[set], et, st); }
   }
   void forward(int blk, const float* msa_in, const float* pair_in, float* pair_out, cudaStream_t st) {
     W& b = w[blk];
-    products(b, msa_in, st);
+    products(b, blk & 1, msa_in, st);
     EpiOpmOut eo; eo.res_in = pair_in; eo.res_out = pair_out; eo.bias = b.ob; eo.msa_mask = msa_mask; eo.S = S_; eo.Nres = n;
     eo.M = n; eo.N = n * OPM_F;
-    { ProfScope ps_("Opm.forward.gemm.g_out", st); run_gemm(g_out, eo, st); }
+    { ProfScope ps_("Opm.forward.gemm.g_out", st); run_gemm(g_out2[blk & 1], eo, st); }
   }
   // g_pair: cotangent of the pair stream after the module (read only: the module adds to the pair stream, so the
   // cotangent of its pair input is g_pair itself); g_msa accumulates.  lr / leftT / tmpT must hold this block's
@@ -695,9 +707,9 @@ struct Opm {
     const int Mi = (int)Mm, K = 32 * S_;
     { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_counter()++; opm_dout_kernel<<<cdiv(n * n, 8), 256, 0, st>>>(g_pair, msa_mask, dout, S_, n); }
     EpiPartial ep; ep.out = partial; ep.ld = K; ep.bs = (long)n * K; ep.M = n; ep.N = K;
-    { ProfScope ps_("Opm.backward.gemm.g_dleft", st); run_gemm(g_dleft, ep, st); }
+    { ProfScope ps_("Opm.backward.gemm.g_dleft", st); run_gemm(g_dleft2[blk & 1], ep, st); }
     EpiStore ed; ed.out = dtmpT; ed.ldo = K; ed.M = n * OPM_F; ed.N = K;
-    { ProfScope ps_("Opm.backward.gemm.g_dtmp", st); run_gemm(g_dtmp, ed, st); }
+    { ProfScope ps_("Opm.backward.gemm.g_dtmp", st); run_gemm(g_dtmp2[blk & 1], ed, st); }
     { ProfScope ps_("Opm.backward.opm_dleft_reduce_kernel", st); launch_counter()++; opm_dleft_reduce_kernel<<<cdiv(n * K, 256), 256, 0, st>>>(partial, kSplit, msa_mask, dlr_b, S_, n); }
     { ProfScope ps_("Opm.backward.opm_dright_tc_kernel", st); launch_counter()++; opm_dright_tc_kernel<<<cdiv(Mi, OPM_DR_ROWS), 256, 0, st>>>(dtmpT, b.wq, msa_mask, dlr_b, S_, n); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;

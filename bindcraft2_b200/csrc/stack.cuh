@@ -50,13 +50,15 @@ struct EvoStack {
   Transition mtrans, ptrans;
   TriMul tmo, tmi;
   TriAttn tas, tae;
-  float* P[7] = {nullptr};   // pair stream after each pair-side step (P[0] = block input)
+  float* P[7] = {nullptr};   // pair stream after each pair-side step (P[0] = block input; P[1] is P1[block & 1])
+  float* P1[2] = {nullptr, nullptr};  // pair stream after the outer product mean, one per block parity (see backward())
   float* Mx[4] = {nullptr};  // msa stream: input, after row, after col, after transition
   float *pair_mask = nullptr, *msa_mask = nullptr;  // stack-owned copies (stable pointers for the kernels' arguments)
   float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};  // ping-pong block outputs
   std::vector<float*> opm_const;  // pair_only: per-block constant the outer product mean collapses to
   cudaStream_t side = nullptr;  // MSA-track stream (null: everything on the caller's stream)
-  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  bool tail_pending = false;  // a backward tail (row attention + outer product mean of a block) is in flight on `side`
   std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
   size_t weight_bytes = 0;
 
@@ -76,8 +78,10 @@ struct EvoStack {
     // the MSA row attention runs heads narrower than 16 zero-padded to 16: its buffers are msa_heads*16 wide then
     const int cms = std::max(c.Cm, c.msa_heads * 16);
     Sm.init(A, Mm, cms, 4 * cms, false, N, c.msa_heads);
-    for (int i = 1; i < 7; ++i) P[i] = A.alloc<float>(Mp * c.Cz);
+    for (int i = 2; i < 7; ++i) P[i] = A.alloc<float>(Mp * c.Cz);
     P[0] = A.alloc<float>(Mp * c.Cz);
+    for (int i = 0; i < 2; ++i) P1[i] = A.alloc<float>(Mp * c.Cz);
+    P[1] = P1[0];
     for (int i = 0; i < 4; ++i) Mx[i] = A.alloc<float>(Mm * c.Cm);
     for (int i = 0; i < 2; ++i) {
       pp[i] = A.alloc<float>(Mp * c.Cz);
@@ -140,10 +144,11 @@ struct EvoStack {
   // One block.  p_in/m_in are read only; the block output goes to p_out/m_out.  `tail` = false skips the two
   // final GEMMs whose results only the next block would read (the replay before a backward does not need them).
   void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st,
-                     bool tail = true) {
+                     bool tail = true, bool replay = false) {
     const unsigned en = cfg.pair_only ? (module_mask() & 0x1f0u) : module_mask();
     const size_t bp = (size_t)Mp * cfg.Cz * 4, bm = (size_t)Mm * cfg.Cm * 4;
     cudaStream_t ms = side ? side : st;
+    P[1] = P1[b & 1];
     if (cfg.pair_only) {
       // The reference's extra-MSA path (native/block.cuh `pair_only`; bindcraft/af/native.py:1131-1193): the MSA side is
       // not run (its mask is all zeros in a design run) and only the constant of the outer product mean reaches the pair.
@@ -161,9 +166,18 @@ struct EvoStack {
     }
     auto idp = [&](const float* a, float* o, cudaStream_t s_) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, s_)); };
     auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, ms)); };
-    if (side) fork(st, side, ev[0]);
-    if (en & 1) opm.forward(b, m_in, p_in, P[1], ms); else idp(p_in, P[1], ms);
-    if (side) fork(side, st, ev[1]);  // the pair track may start once the outer product mean has produced P[1]
+    if (replay && side) {
+      // Replay before a backward: the side stream may still be busy with the previous block's backward tail (which reads
+      // that block's outer-product operands and its P1 buffer: both exist per block parity).  The outer product mean of
+      // THIS block therefore runs here, on the caller's stream, so that the pair track does not queue behind that tail;
+      // the rest of the MSA track follows the tail on the side stream.
+      if (en & 1) opm.forward(b, m_in, p_in, P[1], st); else idp(p_in, P[1], st);
+      fork(st, side, ev[0]);
+    } else {
+      if (side) fork(st, side, ev[0]);
+      if (en & 1) opm.forward(b, m_in, p_in, P[1], ms); else idp(p_in, P[1], ms);
+      if (side) fork(side, st, ev[1]);  // the pair track may start once the outer product mean has produced P[1]
+    }
     if (en & 2) row.forward(b, m_in, Mx[1], P[1], ms); else idm(m_in, Mx[1]);
     if (en & 4) { if (cfg.extra) colg.forward(b, Mx[1], Mx[2], ms); else col.forward(b, Mx[1], Mx[2], ms); } else idm(Mx[1], Mx[2]);
     if (tail || !(en & 8)) {
@@ -176,14 +190,22 @@ struct EvoStack {
     if (en & 64) tas.forward(b, P[3], P[4], st); else idp(P[3], P[4], st);
     if (en & 128) tae.forward(b, P[4], P[5], st); else idp(P[4], P[5], st);
     if (en & 256) ptrans.forward(b, P[5], p_out, st, tail); else if (tail) idp(P[5], p_out, st);
-    if (side) fork(side, st, ev[2]);  // join
+    // join; after a replay the backward orders itself against the side stream, and waiting here would put the previous
+    // block's tail back on the critical path
+    if (side && !replay) fork(side, st, ev[2]);
   }
   // Needs the module buffers of block b as left by block_forward(b, p_in, m_in, ...).  g_pair/g_msa: cotangents of the
   // block outputs on entry, of the block inputs on return.
   void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
     const unsigned en = cfg.pair_only ? (module_mask() & 0x1f0u) : module_mask();
-    cudaStream_t ms = (side && !cfg.pair_only) ? side : st;
-    if (side && !cfg.pair_only) fork(st, side, ev[0]);
+    const bool two = side && !cfg.pair_only;
+    cudaStream_t ms = two ? side : st;
+    P[1] = P1[b & 1];
+    if (two) {
+      // the pair track needs the cotangents the previous block's tail (on the side stream) finished
+      if (tail_pending) BC2_CUDA(cudaStreamWaitEvent(st, ev[4], 0));
+      fork(st, side, ev[0]);
+    }
     if (en & 8) mtrans.backward(b, Mx[2], g_msa, ms);
     if (en & 4) { if (cfg.extra) colg.backward(b, Mx[1], g_msa, ms); else col.backward(b, Mx[1], g_msa, ms); }
     if (en & 256) ptrans.backward(b, P[5], g_pair, st);
@@ -191,9 +213,15 @@ struct EvoStack {
     if (en & 64) tas.backward(b, P[3], g_pair, st);
     if (en & 32) tmi.backward(b, P[2], g_pair, pair_mask, st);
     if (en & 16) tmo.backward(b, P[1], g_pair, pair_mask, st);
-    if (side && !cfg.pair_only) fork(side, st, ev[1]);  // the row attention needs both cotangents; from here on one stream
-    if (en & 2) row.backward(b, m_in, P[1], g_msa, g_pair, st);
-    if (en & 1) opm.backward(b, m_in, g_pair, g_msa, st);
+    // Tail: the row attention (needs both cotangents) and the outer product mean.  They are a few dozen small kernels;
+    // on the side stream they overlap the NEXT block's replayed pair track instead of leaving the GPU idle.
+    if (two) fork(st, side, ev[3]);
+    if (en & 2) row.backward(b, m_in, P[1], g_msa, g_pair, ms);
+    if (en & 1) opm.backward(b, m_in, g_pair, g_msa, ms);
+    if (two) {
+      BC2_CUDA(cudaEventRecord(ev[4], side));
+      tail_pending = true;
+    }
   }
 
   void set_masks(const float* pm, const float* mm, cudaStream_t st) {
@@ -243,8 +271,12 @@ struct EvoStack {
           (!own_save || keep32.empty()) ? nullptr : reinterpret_cast<const float4*>(keep32[i]),
           reinterpret_cast<float4*>(P[0]), np / 4);
       const float* m_in = msave + (long)i * nm;
-      block_forward(i, P[0], m_in, pp[0], mp[0], st, /*tail=*/false);
+      block_forward(i, P[0], m_in, pp[0], mp[0], st, /*tail=*/false, /*replay=*/true);
       block_backward(i, m_in, dpair, dmsa, st);
+    }
+    if (tail_pending) {  // the last tail writes the results
+      BC2_CUDA(cudaStreamWaitEvent(st, ev[4], 0));
+      tail_pending = false;
     }
   }
 };
