@@ -692,9 +692,12 @@ struct Opm {
     EpiOpmTmp et; et.out = tmpT; et.S = S_; et.Nres = n; et.M = Mi; et.N = OPM_F * OPM_C;
     { ProfScope ps_("Opm.forward.gemm.g_tmp", st); run_gemm(b.g_tmp2[set], et, st); }
   }
-  void forward(int blk, const float* msa_in, const float* pair_in, float* pair_out, cudaStream_t st) {
+  // The msa-only part of the forward of block `blk` (LayerNorm, projections, first product): may be issued ahead of time.
+  void prepare(int blk, const float* msa_in, cudaStream_t st) { products(w[blk], blk & 1, msa_in, st); }
+  // prepared: prepare(blk, msa_in) has already been issued (and ordered before `st`)
+  void forward(int blk, const float* msa_in, const float* pair_in, float* pair_out, cudaStream_t st, bool prepared = false) {
     W& b = w[blk];
-    products(b, blk & 1, msa_in, st);
+    if (!prepared) products(b, blk & 1, msa_in, st);
     EpiOpmOut eo; eo.res_in = pair_in; eo.res_out = pair_out; eo.bias = b.ob; eo.msa_mask = msa_mask; eo.S = S_; eo.Nres = n;
     eo.M = n; eo.N = n * OPM_F;
     { ProfScope ps_("Opm.forward.gemm.g_out", st); run_gemm(g_out2[blk & 1], eo, st); }

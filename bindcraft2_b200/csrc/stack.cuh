@@ -57,7 +57,8 @@ struct EvoStack {
   float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};  // ping-pong block outputs
   std::vector<float*> opm_const;  // pair_only: per-block constant the outer product mean collapses to
   cudaStream_t side = nullptr;  // MSA-track stream (null: everything on the caller's stream)
-  cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int opm_prepared = -1;  // block whose outer-product operands were issued ahead on the side stream (ev[5] marks them done)
   bool tail_pending = false;  // a backward tail (row attention + outer product mean of a block) is in flight on `side`
   std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
   size_t weight_bytes = 0;
@@ -166,7 +167,16 @@ struct EvoStack {
     }
     auto idp = [&](const float* a, float* o, cudaStream_t s_) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, s_)); };
     auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, ms)); };
-    if (replay && side) {
+    // The msa-only operands of this block's outer product mean may already have been issued on the side stream (by the
+    // previous block's forward, or by the backward of the block after this one): then only its last product, a
+    // machine-filling GEMM over the pair tensor, is left, and it runs on the caller's stream.
+    const bool prepared = side && opm_prepared == b && (en & 1);
+    opm_prepared = -1;
+    if (prepared) {
+      BC2_CUDA(cudaStreamWaitEvent(st, ev[5], 0));
+      opm.forward(b, m_in, p_in, P[1], st, /*prepared=*/true);
+      fork(st, side, ev[0]);
+    } else if (replay && side) {
       // Replay before a backward: the side stream may still be busy with the previous block's backward tail (which reads
       // that block's outer-product operands and its P1 buffer: both exist per block parity).  The outer product mean of
       // THIS block therefore runs here, on the caller's stream, so that the pair track does not queue behind that tail;
@@ -185,6 +195,11 @@ struct EvoStack {
     } else {
       mtrans.forward(b, Mx[2], m_out, ms, /*tail=*/false);
     }
+    if (side && !replay && tail && (en & 1) && b + 1 < cfg.depth) {  // next block's msa-only operands, under this pair track
+      opm.prepare(b + 1, m_out, side);
+      BC2_CUDA(cudaEventRecord(ev[5], side));
+      opm_prepared = b + 1;
+    }
     if (en & 16) tmo.forward(b, P[1], P[2], pair_mask, st); else idp(P[1], P[2], st);
     if (en & 32) tmi.forward(b, P[2], P[3], pair_mask, st); else idp(P[2], P[3], st);
     if (en & 64) tas.forward(b, P[3], P[4], st); else idp(P[3], P[4], st);
@@ -196,7 +211,8 @@ struct EvoStack {
   }
   // Needs the module buffers of block b as left by block_forward(b, p_in, m_in, ...).  g_pair/g_msa: cotangents of the
   // block outputs on entry, of the block inputs on return.
-  void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
+  // m_prev: msa input of block b-1 (from the save-set), or null for the first block
+  void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st, const float* m_prev = nullptr) {
     const unsigned en = cfg.pair_only ? (module_mask() & 0x1f0u) : module_mask();
     const bool two = side && !cfg.pair_only;
     cudaStream_t ms = two ? side : st;
@@ -208,6 +224,13 @@ struct EvoStack {
     }
     if (en & 8) mtrans.backward(b, Mx[2], g_msa, ms);
     if (en & 4) { if (cfg.extra) colg.backward(b, Mx[1], g_msa, ms); else col.backward(b, Mx[1], g_msa, ms); }
+    if (two && m_prev && (en & 1)) {
+      // The side stream now waits for the pair track; the msa-only operands of block b-1's replayed outer product mean
+      // fit in that gap.  Their buffer set (parity of b-1) was last read by the tail of block b+1, earlier on this stream.
+      opm.prepare(b - 1, m_prev, side);
+      BC2_CUDA(cudaEventRecord(ev[5], side));
+      opm_prepared = b - 1;
+    }
     if (en & 256) ptrans.backward(b, P[5], g_pair, st);
     if (en & 128) tae.backward(b, P[4], g_pair, st);
     if (en & 64) tas.backward(b, P[3], g_pair, st);
@@ -272,8 +295,9 @@ struct EvoStack {
           reinterpret_cast<float4*>(P[0]), np / 4);
       const float* m_in = msave + (long)i * nm;
       block_forward(i, P[0], m_in, pp[0], mp[0], st, /*tail=*/false, /*replay=*/true);
-      block_backward(i, m_in, dpair, dmsa, st);
+      block_backward(i, m_in, dpair, dmsa, st, i > 0 ? msave + (long)(i - 1) * nm : nullptr);
     }
+    opm_prepared = -1;
     if (tail_pending) {  // the last tail writes the results
       BC2_CUDA(cudaStreamWaitEvent(st, ev[4], 0));
       tail_pending = false;

@@ -244,3 +244,21 @@ def test_extra_msa_modules_alone(lib, tmp_path, step):
 def test_extra_msa_stack_general_path(lib, tmp_path):
     """Configuration 3's extra-MSA part: 4 blocks, c_e = 64, 8 rows, global column attention, at N_res = 224."""
     _extra_case(lib, tmp_path, 153, 154, 224, 8, 4, tag='extra stack N=224 S=8 depth=4')
+
+
+def test_single_stream_mode_gives_the_same_result(lib, tmp_path, monkeypatch):
+    """BC2_NO_SIDE_STREAM=1 (read when a stack object is built) runs both tracks on the caller's stream: same parity, and
+    the two modes agree with each other to the repeat noise of the atomically accumulated bias gradient."""
+    params = synthetic.make_evoformer_params(161, 3)
+    inp = synthetic.make_block_inputs(162, 64, 2, masked=5)
+    lib.bc2_test_set_module_mask(0x1ff)
+    two, _ = _run_cuda(lib, params, inp, 3, tmp_path / 'a', own_save=0)
+    monkeypatch.setenv('BC2_NO_SIDE_STREAM', '1')
+    one, _ = _run_cuda(lib, params, inp, 3, tmp_path / 'b', own_save=0)
+    want = O.stack_fwd_bwd(params, inp, 3)
+    with O.bf16_operands():
+        floor = O.stack_fwd_bwd(params, inp, 3)
+    _check(_crop(one, 59), _crop(want, 59), _crop(floor, 59), 'single stream')
+    assert torch.equal(one['pair'], two['pair']) and torch.equal(one['msa'], two['msa'])
+    for k in ('d_pair', 'd_msa'):
+        assert O.rel_l2(one[k], two[k]) < 1e-2, k
