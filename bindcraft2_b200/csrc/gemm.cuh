@@ -281,6 +281,50 @@ struct EpiOpmOut {
   }
 };
 
+// Attention backward, output side, fused into the GEMM that brings the cotangent back through the output projection:
+// acc = d_og (gradient wrt the gated attention output, [rows][H*D]).  With o the ungated output and g the gate:
+//   d_o = d_og * g -> d_o (bf16);   d(gate pre-activation) = d_og * o * g (1 - g) -> columns [3HD, 4HD) of d_qkvg;
+//   delta[b][h][q] = sum_d d_o * o   (a head's D columns lie inside one 32-column chunk, so no cross-thread sum).
+struct EpiAttnPrep {
+  const bf16* o = nullptr;
+  const bf16* qkvg = nullptr;
+  long ld = 0;  // row length of qkvg / d_qkvg (4*H*D)
+  bf16* d_o = nullptr;
+  bf16* d_qkvg = nullptr;
+  float* delta = nullptr;
+  long row_b = 0, row_p = 0;
+  int Nres = 0, H = 0, D = 0;
+  int M = 0, N = 0;  // N = H*D
+  static constexpr bool kPaired = false;
+  __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
+    if (m >= M || n0 >= N) return;
+    uint32_t ow[16], gw[16], dow[16], dgw[16];
+    ld_global_v8(o + (long)m * N + n0, *reinterpret_cast<uint32_t(*)[8]>(&ow[0]));
+    ld_global_v8(o + (long)m * N + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&ow[8]));
+    ld_global_v8(qkvg + (long)m * ld + 3 * N + n0, *reinterpret_cast<uint32_t(*)[8]>(&gw[0]));
+    ld_global_v8(qkvg + (long)m * ld + 3 * N + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&gw[8]));
+    float part[2] = {0.f, 0.f};  // D = 32: one head per chunk (part[0]); D = 16: two
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 ov = unpack_bf16(ow[j]), gv = unpack_bf16(gw[j]);
+      const float d0 = v[2 * j] * gv.x, d1 = v[2 * j + 1] * gv.y;
+      part[(D == 16 && j >= 8) ? 1 : 0] += d0 * ov.x + d1 * ov.y;
+      dow[j] = pack_bf16(d0, d1);
+      dgw[j] = pack_bf16(d0 * ov.x * (1.f - gv.x), d1 * ov.y * (1.f - gv.y));
+    }
+    st_global_v8(d_o + (long)m * N + n0, *reinterpret_cast<uint32_t(*)[8]>(&dow[0]));
+    st_global_v8(d_o + (long)m * N + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&dow[8]));
+    st_global_v8(d_qkvg + (long)m * ld + 3 * N + n0, *reinterpret_cast<uint32_t(*)[8]>(&dgw[0]));
+    st_global_v8(d_qkvg + (long)m * ld + 3 * N + n0 + 16, *reinterpret_cast<uint32_t(*)[8]>(&dgw[8]));
+    long b, q;
+    if (row_b > row_p) { b = m / row_b; q = (m % row_b) / row_p; }
+    else { q = m / row_p; b = (m % row_p) / row_b; }
+    const int h0 = n0 / D;
+    delta[(b * H + h0) * Nres + q] = part[0];
+    if (D == 16) delta[(b * H + h0 + 1) * Nres + q] = part[1];
+  }
+};
+
 // Triangle-multiplication projection+gate.  The packed weight puts, for each 128-channel group t, the 128
 // projection columns followed by the matching 128 gate columns, so one 256-wide accumulator tile holds both:
 //   g  = sigmoid(gate + bg)            -> gate_out [M, CH] row-major (kept for the backward)

@@ -390,10 +390,10 @@ struct TriAttn {
     W& b = w[blk];
     const int Mi = (int)M, HD = H * D;
     { ProfScope ps_("TriAttn.backward.cvt_f32_bf16", st); cvt_f32_bf16(g, S->dy, M * C, st); }
-    EpiStore e; e.out = S->y; e.ldo = HD; e.M = Mi; e.N = HD;
+    // back through the output projection, with the gating adjoint and delta = rowsum(dO * O) in the epilogue
+    EpiAttnPrep e; e.o = o; e.qkvg = qkvg; e.ld = 4L * HD; e.d_o = S->d_o; e.d_qkvg = S->big; e.delta = S->delta;
+    e.row_b = plan.args.row_b; e.row_p = plan.args.row_p; e.Nres = n; e.H = H; e.D = D; e.M = Mi; e.N = HD;
     { ProfScope ps_("TriAttn.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
-    AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, M, plan.args.row_b, plan.args.row_p, n, H, D};
-    { ProfScope ps_("TriAttn.backward.attn_bwd_prep", st); attn_bwd_prep(p, st); }
     if (!plan.args.ds_store) { ProfScope ps_("TriAttn.backward.memset", st); BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st)); }
     { ProfScope ps_("TriAttn.backward.attn_bwd", st); attn_bwd(plan, st); }
     if (plan.args.ds_store) { ProfScope ps_("TriAttn.backward.attn_dbias_reduce", st); attn_dbias_reduce(plan.args, st); }
@@ -471,10 +471,9 @@ struct MsaRow {
     W& b = w[blk];
     const int Mi = (int)Mm, HD = H * D;
     { ProfScope ps_("MsaRow.backward.cvt_f32_bf16", st); cvt_f32_bf16(g_msa, S->dy, Mm * Cm, st); }
-    EpiStore e; e.out = S->y; e.ldo = HD; e.M = Mi; e.N = HD;
+    EpiAttnPrep e; e.o = o; e.qkvg = qkvg; e.ld = 4L * HD; e.d_o = S->d_o; e.d_qkvg = S->big; e.delta = S->delta;
+    e.row_b = n; e.row_p = 1; e.Nres = n; e.H = H; e.D = D; e.M = Mi; e.N = HD;
     { ProfScope ps_("MsaRow.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
-    AttnBwdPrepArgs p{S->y, o, qkvg, 4L * HD, S->d_o, S->big, S->delta, Mm, (long)n, 1L, n, H, D};
-    { ProfScope ps_("MsaRow.backward.attn_bwd_prep", st); attn_bwd_prep(p, st); }
     { ProfScope ps_("MsaRow.backward.memset", st); BC2_CUDA(cudaMemsetAsync(dnb, 0, (size_t)H * Mp * 4, st)); }
     { ProfScope ps_("MsaRow.backward.attn_bwd", st); attn_bwd(plan, st); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
