@@ -164,24 +164,41 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
   }
 }
 // Same contract on 32x32 tiles (one output row, four columns per thread): with a few hundred rows the 64x64 tiling
-// leaves most SMs idle (M = 400, N = 384 is 42 blocks), this one gives four times as many.
+// leaves most SMs idle (M = 400, N = 384 is 42 blocks), this one gives four times as many.  K advances 64 at a time and
+// the next chunk's global loads are issued into registers before the current chunk is multiplied, so that with one
+// block per SM the load latency hides behind the arithmetic.
 __global__ void __launch_bounds__(256) linear_f32_small_kernel(LinArgs a) {
-  __shared__ float sX[16][32 + 1];
-  __shared__ __align__(16) float sW[16][32];
+  constexpr int KC = 64;
+  __shared__ float sX[KC][32 + 1];
+  __shared__ __align__(16) float sW[KC][32];
   const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
   const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+  // staging: X element (row xr + 4*i, k xk) for i < 8; W element (k wk + 8*i, col wc) for i < 8
+  const int xk = threadIdx.x & 63, xr = threadIdx.x >> 6;
+  const int wc = threadIdx.x & 31, wk = threadIdx.x >> 5;
+  float rx[8], rw[8];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int r = m0 + xr + 4 * i, k = k0 + xk;
+      float xv = (r < a.M && k < a.K) ? a.X[(long)r * a.K + k] : 0.f;
+      rx[i] = a.relu_in ? fmaxf(xv, 0.f) : xv;
+      const int kk = k0 + wk + 8 * i, c = n0 + wc;
+      rw[i] = (kk < a.K && c < a.N) ? a.W[(long)kk * a.N + c] : 0.f;
+    }
+  };
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int k0 = 0; k0 < a.K; k0 += 16) {
-    for (int t = threadIdx.x; t < 32 * 16; t += 256) {
-      const int r = t >> 4, k = t & 15;
-      float xv = (m0 + r < a.M && k0 + k < a.K) ? a.X[(long)(m0 + r) * a.K + k0 + k] : 0.f;
-      sX[k][r] = a.relu_in ? fmaxf(xv, 0.f) : xv;
-      const int kk = t >> 5, c = t & 31;
-      sW[kk][c] = (k0 + kk < a.K && n0 + c < a.N) ? a.W[(long)(k0 + kk) * a.N + n0 + c] : 0.f;
+  fetch(0);
+  for (int k0 = 0; k0 < a.K; k0 += KC) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sX[xk][xr + 4 * i] = rx[i];
+      sW[wk + 8 * i][wc] = rw[i];
     }
     __syncthreads();
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
+    if (k0 + KC < a.K) fetch(k0 + KC);
+#pragma unroll 16
+    for (int k = 0; k < KC; ++k) {
       const float xv = sX[k][ty];
       const float4 w = *reinterpret_cast<const float4*>(&sW[k][tx * 4]);
       acc[0] += xv * w.x; acc[1] += xv * w.y; acc[2] += xv * w.z; acc[3] += xv * w.w;
