@@ -691,7 +691,6 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = *tslot;
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
-  const int nsteps = nqb * nkb;
 
   if (warp == 0) {
     if (lane == 0) {

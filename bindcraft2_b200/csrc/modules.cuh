@@ -159,8 +159,6 @@ struct TriMul {
     ob = A.alloc<bf16>(M * C);
     g2 = A.alloc<bf16>(M * C);
     const bf16 *a = ab, *bq = ab + (long)Hc * M;           // left planes, right planes
-    const bf16 *da = S->dab, *db = S->dab + (long)Hc * M;  // their gradients
-    (void)da; (void)db;
     auto K = [&](const bf16* p) { return Operand{p, n, M, false}; };
     auto T = [&](const bf16* p) { return Operand{p, n, M, true}; };
     if (outgoing) {
