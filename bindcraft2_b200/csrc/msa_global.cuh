@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(64)
 global_col_bwd_kernel(GlobalColW W, const bf16* __restrict__ x, const float* __restrict__ mask, const float* __restrict__ g,
                       bf16* __restrict__ dx, int S, int N) {
   __shared__ float sx[GS][GC], sq[GC], sqa[GC], sk[GS][GD], sv[GS][GD], sw[GH][GS], savg[GC], sgate[GS][GC], sm[GS];
-  __shared__ float sg[GS][GC], sdy[GS][GC], sdavg[GC], sdl[GH][GS], sdq[GC], sdk[GS][GD], sdv[GS][GD], sdgp[GS][GC];
+  __shared__ float sg[GS][GC], sdavg[GC], sdl[GH][GS], sdq[GC], sdk[GS][GD], sdv[GS][GD], sdgp[GS][GC];
   const int n = blockIdx.x, t = threadIdx.x;
   float msum = 0.f;
   for (int s = 0; s < S; ++s) {
@@ -152,7 +152,6 @@ global_col_bwd_kernel(GlobalColW W, const bf16* __restrict__ x, const float* __r
   for (int s = 0; s < S; ++s) {  // thread = hd
     float dy = 0.f;
     for (int o = 0; o < GC; ++o) dy += sg[s][o] * W.wo_t[o * GC + t];
-    sdy[s][t] = dy;
     davg += dy * sgate[s][t];
     const float gt = sgate[s][t];
     sdgp[s][t] = dy * savg[t] * gt * (1.f - gt);  // cotangent of the gate pre-activation
