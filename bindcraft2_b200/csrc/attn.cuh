@@ -104,6 +104,10 @@ __device__ __forceinline__ uint64_t desc_p_mnmajor(uint32_t saddr, int k16) {
 // [half*D/2, (half+1)*D/2).  The S block is read once into registers (one pass), the two partial row maxima meet in
 // shared memory behind a named barrier, and both threads then use the same running max, so their partial sums and
 // partial outputs simply add at the end.
+// K and V blocks pass through a ring of ATTN_KV_STAGES (K, V) tile pairs (a stage is handed back to the producer by a
+// tcgen05.commit after the P V product that read it), so shared memory does not grow with N and two CTAs share an SM at
+// any length: one CTA's serial S -> softmax -> P V chain hides behind the other's.
+constexpr int ATTN_KV_STAGES = 3;
 template <int D>
 __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -111,19 +115,23 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
   const int nkb = cdiv(a.N, 128);
   constexpr int TILE = 128 * D * 2;  // bytes of a [128][D] tile
   constexpr int DH = D / 2;
+  constexpr int KV = ATTN_KV_STAGES;
+  const int nst = nkb < KV ? nkb : KV;
   uint8_t* sP = smem;                 // 32 KB
   uint8_t* sQ = sP + 32768;
   uint8_t* sK = sQ + TILE;
-  uint8_t* sV = sK + nkb * TILE;
-  float* sMask = reinterpret_cast<float*>(sV + nkb * TILE);  // [nkb*128] additive key mask (natural-log units)
+  uint8_t* sV = sK + nst * TILE;
+  float* sMask = reinterpret_cast<float*>(sV + nst * TILE);  // [nkb*128] additive key mask (natural-log units)
   float* sX = sMask + nkb * 128;                              // [2][2][128] partial row maxima, double buffered
   float* sL = sX + 512;                                       // [2][128] partial row sums
   uint64_t* bars = reinterpret_cast<uint64_t*>(sL + 256);
-  uint64_t* b_load = bars;       // Q, K, V landed
+  uint64_t* b_load = bars;       // Q landed
   uint64_t* b_s = bars + 1;      // S block ready in TMEM
   uint64_t* b_p = bars + 2;      // P block written to smem (256 arrivals)
   uint64_t* b_o = bars + 3;      // O block ready in TMEM
-  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 4);
+  uint64_t* b_full = bars + 4;   // [KV] K and V of a key block landed in the stage
+  uint64_t* b_empty = bars + 4 + KV;  // [KV] the stage's P V product has finished
+  uint32_t* tslot = reinterpret_cast<uint32_t*>(bars + 4 + 2 * KV);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q0 = blockIdx.x * 128, h = blockIdx.y, b = blockIdx.z;
@@ -134,6 +142,10 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
     mbar_init(b_s, 1);
     mbar_init(b_p, 256);
     mbar_init(b_o, 1);
+    for (int i = 0; i < KV; ++i) {
+      mbar_init(b_full + i, 1);
+      mbar_init(b_empty + i, 1);
+    }
     fence_barrier_init();
     tma_prefetch_desc(&tm);
   }
@@ -151,11 +163,14 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(b_load, TILE * (1 + 2 * nkb));
+      mbar_expect_tx(b_load, TILE);
       tma_load_3d(sQ, &tm, b_load, h * D, q0, b);
       for (int j = 0; j < nkb; ++j) {
-        tma_load_3d(sK + j * TILE, &tm, b_load, HD + h * D, j * 128, b);
-        tma_load_3d(sV + j * TILE, &tm, b_load, 2 * HD + h * D, j * 128, b);
+        const int stg = j % KV;
+        if (j >= KV && !mbar_wait(b_empty + stg, (j / KV - 1) & 1, SITE_ATTN)) break;
+        mbar_expect_tx(b_full + stg, 2 * TILE);
+        tma_load_3d(sK + stg * TILE, &tm, b_full + stg, HD + h * D, j * 128, b);
+        tma_load_3d(sV + stg * TILE, &tm, b_full + stg, 2 * HD + h * D, j * 128, b);
       }
     }
   } else if (warp == 1) {
@@ -165,23 +180,28 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
       bool ok = mbar_wait(b_load, 0, SITE_ATTN);
       tc_fence_after();
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
-      auto issue_s = [&](int j) {
-        const uint32_t aK = smem_u32(sK + j * TILE);
+      auto issue_s = [&](int j) -> bool {
+        const int stg = j % KV;
+        if (!mbar_wait(b_full + stg, (j / KV) & 1, SITE_ATTN)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + stg * TILE);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
           umma_ss(tS, desc_rows_kmajor<D>(aQ, k), desc_rows_kmajor<D>(aK, k), idS, k > 0 ? 1u : 0u);
         umma_commit(b_s);
+        return true;
       };
-      if (ok) issue_s(0);
+      if (ok) ok = issue_s(0);
       for (int j = 0; j < nkb && ok; ++j) {
         ok = mbar_wait(b_p, j & 1, SITE_ATTN);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t aV = smem_u32(sV + j * TILE);
+        const uint32_t aV = smem_u32(sV + (j % KV) * TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_ss(tO, desc_p_kmajor(aP, k), desc_rows_mnmajor<D>(aV, k), idO, k > 0 ? 1u : 0u);
         umma_commit(b_o);
-        if (j + 1 < nkb) issue_s(j + 1);
+        umma_commit(b_empty + (j % KV));  // K and V of this stage are free once this product (and all before it) is done
+        if (j + 1 < nkb) ok = issue_s(j + 1);
       }
     }
   } else {
@@ -192,6 +212,8 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
     const uint32_t lane_off = (uint32_t)(qd * 32) << 16;
     // bias is stored [h][key][query]: the 32 query rows of a warp read 32 consecutive floats per key
     const float* bq = (a.bias && qin) ? a.bias + (long)h * a.N * a.N + q : nullptr;
+    // the half-precision copy, when there is one: 8 keys of this query row per 128-bit load, octets N uint4 apart
+    const uint4* bq16 = (a.bias16 && qin) ? reinterpret_cast<const uint4*>(a.bias16 + ((long)h * (a.N >> 3) * a.N + q) * 8) : nullptr;
     float mrun = -INFINITY, lsum = 0.f;
     float acc[DH];
 #pragma unroll
@@ -225,7 +247,20 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
             const float4 mk = mk4[i >> 2];
             t[i] += mk.x; t[i + 1] += mk.y; t[i + 2] += mk.z; t[i + 3] += mk.w;
           }
-          if (bp) {
+          if (bq16) {
+            const uint4* b8 = bq16 + (long)(k0 >> 3) * a.N;
+#pragma unroll
+            for (int o = 0; o < 4; ++o) {
+              const uint4 v = b8[(long)o * a.N];
+              const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                t[o * 8 + 2 * e] += f.x;
+                t[o * 8 + 2 * e + 1] += f.y;
+              }
+            }
+          } else if (bp) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) t[i] += bp[(long)i * a.N];
           }
@@ -320,8 +355,8 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
 }
 
 inline int attn_fwd_smem(int N, int D) {
-  const int nkb = cdiv(N, 128);
-  return 1024 + 32768 + 128 * D * 2 * (1 + 2 * nkb) + nkb * 128 * 4 + 768 * 4 + 128;
+  const int nkb = cdiv(N, 128), nst = std::min(nkb, ATTN_KV_STAGES);
+  return 1024 + 32768 + 128 * D * 2 * (1 + 2 * nst) + nkb * 128 * 4 + 768 * 4 + 128;
 }
 
 // ------------------------------------------------------------------------------------------- forward, persistent

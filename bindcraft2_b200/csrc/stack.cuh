@@ -1,9 +1,13 @@
 // Evoformer block and the depth-deep stack with its save-set.
 //
-// Block order is the multimer one (bindcraft/af/alphafold/model/modules.py:1266-1391 with
-// outer_product_mean.first = True, config.py:411-418):
+// Block order (bindcraft/af/alphafold/model/modules.py:1266-1391).  With outer_product_mean.first = True (the multimer
+// model, config.py:411-418):
 //   pair += OPM(msa); msa += RowAttn(msa, pair); msa += ColAttn(msa); msa += Transition(msa);
 //   pair += TriMulOut; pair += TriMulIn; pair += TriAttnStart; pair += TriAttnEnd; pair += Transition(pair)
+// With opm_first = false (the monomer model) the MSA track runs first, on the block's input pair, and the outer product
+// mean reads the UPDATED msa:
+//   msa += RowAttn(msa, pair); msa += ColAttn(msa); msa += Transition(msa); pair += OPM(msa); pair += TriMulOut; ...
+// That order has no independent MSA and pair tracks, so it runs on the caller's stream alone.
 //
 // The stack keeps the reference's purity contract (native/ffi.cu:17-25): the forward writes every block's input into
 // the caller's save-set (pair as bf16, msa as fp32; slot layout native/stack.cuh:795-829) and the backward needs only
@@ -59,6 +63,7 @@ struct EvoStack {
   cudaStream_t side = nullptr;  // MSA-track stream (null: everything on the caller's stream)
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int opm_prepared = -1;  // block whose outer-product operands were issued ahead on the side stream (ev[5] marks them done)
+  const float *blk_p_in = nullptr, *blk_m_out = nullptr;  // opm_first = false: operands the block's backward reads again
   bool tail_pending = false;  // a backward tail (row attention + outer product mean of a block) is in flight on `side`
   std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
   size_t weight_bytes = 0;
@@ -67,7 +72,7 @@ struct EvoStack {
     BC2_CHECK(c.N > 0 && c.N % 32 == 0, "N must be a positive multiple of 32 (the caller pads and masks)");
     BC2_CHECK(c.S >= 1 && c.S <= 8, "alignment depth S must be in 1..8");
     BC2_CHECK(c.depth >= 1, "depth must be positive");
-    BC2_CHECK(c.opm_first, "only the multimer block order (outer product mean first) is built");
+    BC2_CHECK(c.opm_first || !c.extra, "the extra-MSA stack is built in the multimer block order only");
     const int N = c.N, S = c.S;
     Mp = (long)N * N;
     Mm = (long)S * N;
@@ -123,7 +128,7 @@ struct EvoStack {
     }
     weight_bytes = A.bytes - before;
     const char* ns = getenv("BC2_NO_SIDE_STREAM");
-    if (!(ns && ns[0] == '1')) {
+    if (!(ns && ns[0] == '1') && (c.opm_first || c.pair_only)) {
       BC2_CUDA(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
       for (auto& e : ev) BC2_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
@@ -167,6 +172,20 @@ struct EvoStack {
     }
     auto idp = [&](const float* a, float* o, cudaStream_t s_) { BC2_CUDA(cudaMemcpyAsync(o, a, bp, cudaMemcpyDeviceToDevice, s_)); };
     auto idm = [&](const float* a, float* o) { BC2_CUDA(cudaMemcpyAsync(o, a, bm, cudaMemcpyDeviceToDevice, ms)); };
+    if (!cfg.opm_first) {  // monomer order: MSA track on the input pair, then the outer product mean of the new msa
+      blk_p_in = p_in;
+      blk_m_out = m_out;
+      if (en & 2) row.forward(b, m_in, Mx[1], p_in, st); else idm(m_in, Mx[1]);
+      if (en & 4) col.forward(b, Mx[1], Mx[2], st); else idm(Mx[1], Mx[2]);
+      if (en & 8) mtrans.forward(b, Mx[2], m_out, st); else idm(Mx[2], m_out);
+      if (en & 1) opm.forward(b, m_out, p_in, P[1], st); else idp(p_in, P[1], st);
+      if (en & 16) tmo.forward(b, P[1], P[2], pair_mask, st); else idp(P[1], P[2], st);
+      if (en & 32) tmi.forward(b, P[2], P[3], pair_mask, st); else idp(P[2], P[3], st);
+      if (en & 64) tas.forward(b, P[3], P[4], st); else idp(P[3], P[4], st);
+      if (en & 128) tae.forward(b, P[4], P[5], st); else idp(P[4], P[5], st);
+      if (en & 256) ptrans.forward(b, P[5], p_out, st, tail); else if (tail) idp(P[5], p_out, st);
+      return;
+    }
     // The msa-only operands of this block's outer product mean may already have been issued on the side stream (by the
     // previous block's forward, or by the backward of the block after this one): then only its last product, a
     // machine-filling GEMM over the pair tensor, is left, and it runs on the caller's stream.
@@ -217,6 +236,18 @@ struct EvoStack {
     const bool two = side && !cfg.pair_only;
     cudaStream_t ms = two ? side : st;
     P[1] = P1[b & 1];
+    if (!cfg.opm_first && !cfg.pair_only) {  // reverse of the monomer order, on the caller's stream
+      if (en & 256) ptrans.backward(b, P[5], g_pair, st);
+      if (en & 128) tae.backward(b, P[4], g_pair, st);
+      if (en & 64) tas.backward(b, P[3], g_pair, st);
+      if (en & 32) tmi.backward(b, P[2], g_pair, pair_mask, st);
+      if (en & 16) tmo.backward(b, P[1], g_pair, pair_mask, st);
+      if (en & 1) opm.backward(b, blk_m_out, g_pair, g_msa, st);
+      if (en & 8) mtrans.backward(b, Mx[2], g_msa, st);
+      if (en & 4) col.backward(b, Mx[1], g_msa, st);
+      if (en & 2) row.backward(b, m_in, blk_p_in, g_msa, g_pair, st);
+      return;
+    }
     if (two) {
       // the pair track needs the cotangents the previous block's tail (on the side stream) finished
       if (tail_pending) BC2_CUDA(cudaStreamWaitEvent(st, ev[4], 0));

@@ -19,16 +19,16 @@ REL_L2 = 2e-2
 COSINE = 0.999
 
 
-def _run_cuda(lib, params, inp, depth, tmp_path, own_save=1):
+def _run_cuda(lib, params, inp, depth, tmp_path, own_save=1, opm_first=1):
     from bindcraft2_b200 import native
     wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
     dev = 'cuda:0'
     t = {k: v.to(dev).contiguous() for k, v in inp.items()}
     seed = torch.zeros(2, dtype=torch.int32, device=dev)
     p, m, psave, msave = native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, depth=depth, save=1,
-                                              weights_dir=wdir, own_save=own_save)
+                                              weights_dir=wdir, own_save=own_save, opm_first=opm_first)
     dp, dm = native.evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, seed, depth=depth,
-                                  weights_dir=wdir, own_save=own_save)
+                                  weights_dir=wdir, own_save=own_save, opm_first=opm_first)
     torch.cuda.synchronize()
     assert lib.bc2_device_status() == 0
     return dict(pair=p.cpu(), msa=m.cpu(), d_pair=dp.cpu(), d_msa=dm.cpu()), (psave, msave, wdir, t, seed)
@@ -53,18 +53,19 @@ def _check(got, want, floor, tag=''):
     return rep
 
 
-def _case(lib, tmp_path, wseed, iseed, n, s, depth, masked=0, scale=1.0, shift=0.0, steps=None, own_save=1, tag=''):
+def _case(lib, tmp_path, wseed, iseed, n, s, depth, masked=0, scale=1.0, shift=0.0, steps=None, own_save=1, tag='',
+          opm_first=1):
     params = synthetic.make_evoformer_params(wseed, depth)
     inp = synthetic.make_block_inputs(iseed, n, s, masked=masked, scale=scale, shift=shift)
     mask = 0x1ff if steps is None else sum(1 << O.STEPS.index(x) for x in steps)
     lib.bc2_test_set_module_mask(mask)
     try:
-        got, extra = _run_cuda(lib, params, inp, depth, tmp_path, own_save=own_save)
+        got, extra = _run_cuda(lib, params, inp, depth, tmp_path, own_save=own_save, opm_first=opm_first)
     finally:
         lib.bc2_test_set_module_mask(0x1ff)
-    want = O.stack_fwd_bwd(params, inp, depth, steps=steps)
+    want = O.stack_fwd_bwd(params, inp, depth, steps=steps, opm_first=bool(opm_first))
     with O.bf16_operands():
-        floor = O.stack_fwd_bwd(params, inp, depth, steps=steps)
+        floor = O.stack_fwd_bwd(params, inp, depth, steps=steps, opm_first=bool(opm_first))
     real = n - masked
     return _check(_crop(got, real), _crop(want, real), _crop(floor, real), tag), extra
 
@@ -99,6 +100,14 @@ def test_scaled_inputs_n96(lib, tmp_path):
 def test_stack_depth3_n64(lib, tmp_path):
     """Independent weights per block, save-set slots and the replay-based backward across blocks."""
     _case(lib, tmp_path, 107, 108, 64, 1, 3, tag='depth3')
+
+
+def test_monomer_block_order_opm_last(lib, tmp_path):
+    """opm_first = 0 (the monomer model's block order, modules.py:1266-1391 with outer_product_mean.first = False): the MSA
+    track runs on the block's input pair and the outer product mean reads the updated msa.  Two blocks, two alignment rows
+    and a masked pad, so that the order matters in both directions (block 1's row attention sees block 0's outer product)."""
+    _case(lib, tmp_path, 151, 152, 64, 2, 2, masked=5, opm_first=0, tag='opm-last')
+    _case(lib, tmp_path, 153, 154, 96, 1, 1, opm_first=0, own_save=0, tag='opm-last own_save=0')
 
 
 def test_save_set_contract_without_own_save(lib, tmp_path):
