@@ -137,6 +137,7 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
   const int q0 = blockIdx.x * 128, h = blockIdx.y, b = blockIdx.z;
   const int HD = a.H * D;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     mbar_init(b_load, 1);
     mbar_init(b_s, 1);
@@ -150,6 +151,7 @@ __global__ void __launch_bounds__(320, 2) attn_fwd_tc_kernel(const __grid_consta
     tma_prefetch_desc(&tm);
   }
   if (warp == 1) tmem_alloc(tslot, 256);
+  pdl_wait();
   for (int k = threadIdx.x; k < nkb * 128; k += blockDim.x) {
     float mk = 0.f;
     if (k < a.N && a.mask) mk = 1e9f * (a.mask[(long)b * a.mask_b + (long)k * a.mask_k] - 1.f);
@@ -412,6 +414,7 @@ attn_fwd_p_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a, int slices
   const int HD = a.H * D;
   const int bstep = 2 * slices;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int g = 0; g < 2; ++g) {
       uint64_t* bg = bars + 7 * g;
@@ -427,6 +430,7 @@ attn_fwd_p_kernel(const __grid_constant__ CUtensorMap tm, AttnArgs a, int slices
     tma_prefetch_desc(&tm);
   }
   if (warp == 2) tmem_alloc(tslot, 512);
+  pdl_wait();
   if (a.bias16) {
     const int nko = a.N / 8;
     const uint4* src = reinterpret_cast<const uint4*>(a.bias16) + (long)h * nko * a.N;
@@ -698,6 +702,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
   const int h = blockIdx.y, b = blockIdx.z;
   const int HD = a.H * D;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     mbar_init(b_kv, 1);
     mbar_init(b_q, 1);
@@ -711,6 +716,7 @@ __global__ void __launch_bounds__(320) attn_bwd_tc_kernel(const __grid_constant_
     tma_prefetch_desc(&tdo);
   }
   if (warp == 1) tmem_alloc(tslot, 512);
+  pdl_wait();
   bool my_masked = false;
   for (int k = threadIdx.x; k < 256; k += blockDim.x) {
     const int kk = kb0 * 128 + k;
@@ -1150,7 +1156,7 @@ inline void attn_fwd_launch(const AttnPlan& p, cudaStream_t st) {
     set_for = smem;
   }
   dim3 grid(cdiv(a.N, 128), a.H, a.B);
-  launch_counter()++; attn_fwd_tc_kernel<D><<<grid, 320, smem, st>>>(p.tm, a);
+  launch_pdl(attn_fwd_tc_kernel<D>, grid, dim3(320), smem, st, p.tm, a);
 }
 
 template <int D>
@@ -1164,7 +1170,7 @@ inline void attn_fwd_p_launch(const AttnPlan& p, cudaStream_t st) {
   }
   const int pairs = cdiv(a.N, 128) * a.H;
   const int slices = std::max(1, std::min(sm_count() / pairs, cdiv(a.B, 2)));
-  launch_counter()++; attn_fwd_p_kernel<D><<<pairs * slices, ATTN_P_THREADS, smem, st>>>(p.tm, a, slices);
+  launch_pdl(attn_fwd_p_kernel<D>, dim3(pairs * slices), dim3(ATTN_P_THREADS), smem, st, p.tm, a, slices);
 }
 
 template <int D>
@@ -1188,7 +1194,7 @@ inline void attn_bwd_launch(const AttnPlan& p, cudaStream_t st) {
   const int groups = cdiv(cdiv(a.N, 128), 2);
   if (groups > 1) BC2_CUDA(cudaMemsetAsync(a.dq_acc, 0, (size_t)p.rows * HD * 4, st));
   dim3 grid(groups, a.H, a.B);
-  launch_counter()++; attn_bwd_tc_kernel<D><<<grid, 320, smem, st>>>(p.tm, p.tdo, a);
+  launch_pdl(attn_bwd_tc_kernel<D>, grid, dim3(320), smem, st, p.tm, p.tdo, a);
   if (groups > 1) {
     const long m = p.rows * HD;
     launch_counter()++; attn_dq_store<<<(unsigned)((m + 255) / 256), 256, 0, st>>>(a.dq_acc, a.d_qkv, a.ld, p.rows, HD);

@@ -13,6 +13,7 @@
 #include <mutex>
 #include <stdexcept>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace bc2 {
@@ -50,6 +51,38 @@ __device__ __forceinline__ void dev_fail(unsigned site, unsigned info) {
 inline std::atomic<long>& launch_counter() {
   static std::atomic<long> c{0};
   return c;
+}
+
+// Programmatic dependent launch.  A kernel launched through launch_pdl() may have its CTAs placed on an SM, and run its
+// prologue (barrier init, TMEM allocation, descriptor prefetch), while the kernel before it in the stream is still
+// draining; it must call pdl_wait() before its first access to global memory (reads AND writes: the wait returns once the
+// preceding kernel has finished and its stores are visible).  pdl_trigger() at the top of a kernel lets the kernel after
+// it start that early; it is a no-op when nothing was launched that way.  BC2_NO_PDL=1 turns the launch attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("BC2_NO_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  launch_counter()++;
+  BC2_CUDA(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
 }
 
 // Optional per-kernel-class timing with CUDA events on the launching stream (the reference has the same idea behind

@@ -6,6 +6,8 @@
 namespace bc2 {
 
 __global__ void __launch_bounds__(256) cvt_f32_bf16_kernel(const float4* __restrict__ in, uint2* __restrict__ out, long n4) {
+  pdl_trigger();
+  pdl_wait();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
     const float4 v = in[i];
     out[i] = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
@@ -34,6 +36,8 @@ save_narrow_kernel(const float4* __restrict__ in, uint2* __restrict__ out, float
 // simply fails the comparison element by element and falls back to the widened bf16 value.
 __global__ void __launch_bounds__(256)
 save_widen_kernel(const uint2* __restrict__ slot, const float4* __restrict__ keep, float4* __restrict__ out, long n4) {
+  pdl_trigger();
+  pdl_wait();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
     const uint2 s = slot[i];
     float4 k = keep ? keep[i] : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -50,7 +54,7 @@ save_widen_kernel(const uint2* __restrict__ slot, const float4* __restrict__ kee
 
 inline int ew_grid(long n, int per_block) { return (int)std::min<long>((n + per_block - 1) / per_block, 148L * 16); }
 inline void cvt_f32_bf16(const float* in, bf16* out, long n, cudaStream_t st) {
-  launch_counter()++; cvt_f32_bf16_kernel<<<ew_grid(n / 4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n / 4);
+  launch_pdl(cvt_f32_bf16_kernel, dim3(ew_grid(n / 4, 256)), dim3(256), 0, st, reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n / 4);
 }
 inline void cvt_bf16_f32(const bf16* in, float* out, long n, cudaStream_t st) {
   launch_counter()++; cvt_bf16_f32_kernel<<<ew_grid(n / 4, 256), 256, 0, st>>>(reinterpret_cast<const uint2*>(in), reinterpret_cast<float4*>(out), n / 4);
@@ -62,6 +66,8 @@ inline void cvt_bf16_f32(const bf16* in, float* out, long n, cudaStream_t st) {
 __global__ void __launch_bounds__(256)
 trimul_bwd_out_kernel(const float4* __restrict__ dz, const uint2* __restrict__ ob, const uint2* __restrict__ g2,
                       uint2* __restrict__ d_o, bf16* __restrict__ dcat, long ldd, int off, long M, int C) {
+  pdl_trigger();
+  pdl_wait();
   const int c4 = C / 4;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < M * c4; i += (long)gridDim.x * blockDim.x) {
     const long m = i / c4;
@@ -90,6 +96,8 @@ trimul_bwd_gate_kernel(const bf16* __restrict__ d_ab, const bf16* __restrict__ a
   __shared__ __align__(16) bf16 sd[64][66], sa[64][66];
   const long p0 = (long)blockIdx.x * 64;
   const int c0 = blockIdx.y * 64;
+  pdl_trigger();
+  pdl_wait();
   {  // planes -> shared memory, 8 positions (one 128-bit load) per thread
     const int pg = threadIdx.x & 7;
 #pragma unroll

@@ -419,6 +419,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ C
   const int nkb = cdiv(K, GEMM_BK);
   constexpr uint32_t TCOLS = 2 * BN < 32 ? 32 : 2 * BN;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
@@ -437,6 +438,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap ta, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tslot;
+  pdl_wait();  // everything above overlaps the tail of the kernel before this one
 
   if (warp == 0) {
     if (lane == 0) {
@@ -643,7 +645,7 @@ inline void launch_tc(const GemmPlan& p, const Epi& epi, cudaStream_t st) {
     attr_set = true;
   }
   const int mt = cdiv(p.M, GEMM_BM), nt = cdiv(p.N, BN), total = mt * nt * p.batch;
-  launch_counter()++; kern<<<std::min(total, sm_count()), GEMM_THREADS, smem, st>>>(p.ta, p.tb, p.K, mt, nt, total, epi);
+  launch_pdl(kern, dim3(std::min(total, sm_count())), dim3(GEMM_THREADS), smem, st, p.ta, p.tb, p.K, mt, nt, total, epi);
 }
 
 template <class Epi>

@@ -220,16 +220,14 @@ struct TriMul {
   }
   void cln_fwd_c(const bf16* tt, const LnW& l, bf16* y, cudaStream_t st) {
     const unsigned grid = (unsigned)(M / 64);
-    launch_counter()++;
-    if (Hc == 128) cln_fwd_kernel<128><<<grid, 256, 0, st>>>(tt, l.scale, l.offset, y, (int)M);
-    else if (Hc == 64) cln_fwd_kernel<64><<<grid, 256, 0, st>>>(tt, l.scale, l.offset, y, (int)M);
+    if (Hc == 128) launch_pdl(cln_fwd_kernel<128>, dim3(grid), dim3(256), 0, st, tt, l.scale, l.offset, y, (int)M);
+    else if (Hc == 64) launch_pdl(cln_fwd_kernel<64>, dim3(grid), dim3(256), 0, st, tt, l.scale, l.offset, y, (int)M);
     else throw Error("centre norm width not instantiated");
   }
   void cln_bwd_c(const bf16* tt, const LnW& l, const bf16* dy, bf16* dtt, cudaStream_t st) {
     const unsigned grid = (unsigned)(M / 64);
-    launch_counter()++;
-    if (Hc == 128) cln_bwd_kernel<128><<<grid, 256, 0, st>>>(tt, l.scale, dy, dtt, (int)M);
-    else if (Hc == 64) cln_bwd_kernel<64><<<grid, 256, 0, st>>>(tt, l.scale, dy, dtt, (int)M);
+    if (Hc == 128) launch_pdl(cln_bwd_kernel<128>, dim3(grid), dim3(256), 0, st, tt, l.scale, dy, dtt, (int)M);
+    else if (Hc == 64) launch_pdl(cln_bwd_kernel<64>, dim3(grid), dim3(256), 0, st, tt, l.scale, dy, dtt, (int)M);
     else throw Error("centre norm width not instantiated");
   }
   void forward(int blk, const float* in, float* out, const float* mask, cudaStream_t st) {
@@ -250,7 +248,7 @@ struct TriMul {
   void backward(int blk, const float* in, float* g, const float* mask, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)M, CH = 2 * Hc, NP = 2 * CH, KC = NP + C;
-    { ProfScope ps_("TriMul.backward.trimul_bwd_out_kernel", st); launch_counter()++; trimul_bwd_out_kernel<<<ew_grid(M * C / 4, 256), 256, 0, st>>>( reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2), reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C); }
+    { ProfScope ps_("TriMul.backward.trimul_bwd_out_kernel", st); launch_pdl(trimul_bwd_out_kernel, dim3(ew_grid(M * C / 4, 256)), dim3(256), 0, st, reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2), reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C); }
     EpiStore ey; ey.out = S->dy; ey.ldo = Hc; ey.M = Mi; ey.N = Hc;
     { ProfScope ps_("TriMul.backward.gemm.gb_o", st); run_gemm(b.gb_o, ey, st); }
     { ProfScope ps_("TriMul.backward.cln_bwd_c", st); cln_bwd_c(t, b.cn, S->dy, S->dt, st); }
@@ -259,7 +257,7 @@ struct TriMul {
     EpiStore eb = ea; eb.out = S->dab + (long)Hc * M;
     { ProfScope ps_("TriMul.backward.gemm.gb_db", st); run_gemm(gb_db, eb, st); }
     dim3 grid((unsigned)(M / 64), CH / 64);
-    { ProfScope ps_("TriMul.backward.trimul_bwd_gate_kernel", st); launch_counter()++; trimul_bwd_gate_kernel<<<grid, 256, 0, st>>>(S->dab, ab, gate, mask, S->big, KC, M, CH); }
+    { ProfScope ps_("TriMul.backward.trimul_bwd_gate_kernel", st); launch_pdl(trimul_bwd_gate_kernel, grid, dim3(256), 0, st, S->dab, ab, gate, mask, S->big, (long)KC, M, CH); }
     EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
     { ProfScope ps_("TriMul.backward.gemm.gb_cat", st); run_gemm(b.gb_cat, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.g_in = g; l.g_out = g; l.M = Mi;

@@ -336,7 +336,8 @@ __global__ void __launch_bounds__(256) ln_fwd_group_kernel(LnArgs a) {
   using R = GroupRow<C>;
   __shared__ float4 s_wb[LN_MAXH * C / 4];  // bias projection, [h][chunk i][group lane]: conflict-free 128-bit reads
   const int lane = threadIdx.x & 31, gl = lane % R::G, sub = lane / R::G;
-  if (a.wb) {
+  pdl_trigger();
+  if (a.wb) {  // weights are constants: staged before the wait on the preceding kernel
     for (int t = threadIdx.x; t < a.H * C / 4; t += blockDim.x) {
       const int h = t / (C / 4), r = t % (C / 4), i = r / R::G, l = r % R::G;
       s_wb[t] = *reinterpret_cast<const float4*>(a.wb + (long)h * C + i * R::STRIDE + 4 * l);
@@ -346,6 +347,7 @@ __global__ void __launch_bounds__(256) ln_fwd_group_kernel(LnArgs a) {
   float sc[16], of[16];
   gload_f32<C>(a.scale, gl, sc);
   gload_f32<C>(a.offset, gl, of);
+  pdl_wait();
   const int step = gridDim.x * 8 * R::RPW;
   // every lane of a warp stays in the loop together (the shuffles below name the full warp); rows past M are clamped
   for (int mb = (blockIdx.x * 8 + (threadIdx.x >> 5)) * R::RPW; mb < a.M; mb += step) {
@@ -392,6 +394,7 @@ __global__ void __launch_bounds__(256) ln_bwd_group_kernel(LnBwdArgs a) {
   using R = GroupRow<C>;
   __shared__ float4 s_wb[LN_MAXH * C / 4];
   const int lane = threadIdx.x & 31, gl = lane % R::G, sub = lane / R::G;
+  pdl_trigger();
   if (a.wb) {
     for (int t = threadIdx.x; t < a.H * C / 4; t += blockDim.x) {
       const int h = t / (C / 4), r = t % (C / 4), i = r / R::G, l = r % R::G;
@@ -401,6 +404,7 @@ __global__ void __launch_bounds__(256) ln_bwd_group_kernel(LnBwdArgs a) {
   }
   float sc[16];
   gload_f32<C>(a.scale, gl, sc);
+  pdl_wait();
   const int step = gridDim.x * 8 * R::RPW;
   // rows are handed out so that every lane of a warp stays in the loop together (shuffles below need the full warp)
   const int m0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * R::RPW;
@@ -454,23 +458,23 @@ __global__ void __launch_bounds__(256) ln_bwd_group_kernel(LnBwdArgs a) {
 
 template <int C>
 inline void ln_fwd(const LnArgs& a, cudaStream_t st) {
-  launch_counter()++;
   if constexpr (C <= 128) {
     constexpr int rows_per_cta = 8 * GroupRow<C>::RPW;
     BC2_CHECK(!a.wb || a.H <= GroupRow<C>::G, "LayerNorm bias projection: more heads than lanes per row");
-    ln_fwd_group_kernel<C><<<std::min(cdiv(a.M, rows_per_cta), 148 * 8), 256, 0, st>>>(a);
+    launch_pdl(ln_fwd_group_kernel<C>, dim3(std::min(cdiv(a.M, rows_per_cta), 148 * 8)), dim3(256), 0, st, a);
   } else {
+    launch_counter()++;
     ln_fwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
   }
 }
 template <int C>
 inline void ln_bwd(const LnBwdArgs& a, cudaStream_t st) {
-  launch_counter()++;
   if constexpr (C <= 128) {
     constexpr int rows_per_cta = 8 * GroupRow<C>::RPW;
     BC2_CHECK(!a.wb || a.H <= LN_MAXH, "LayerNorm bias projection: too many heads");
-    ln_bwd_group_kernel<C><<<std::min(cdiv(a.M, rows_per_cta), 148 * 8), 256, 0, st>>>(a);
+    launch_pdl(ln_bwd_group_kernel<C>, dim3(std::min(cdiv(a.M, rows_per_cta), 148 * 8)), dim3(256), 0, st, a);
   } else {
+    launch_counter()++;
     ln_bwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
   }
 }
@@ -508,6 +512,8 @@ __global__ void __launch_bounds__(256) cln_fwd_kernel(const bf16* __restrict__ t
   __shared__ float tile[C][65];
   const int p0 = blockIdx.x * 64;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  pdl_wait();
   for (int c = warp; c < C; c += 8) {
     const int p = p0 + 2 * lane;
     float2 f = make_float2(0.f, 0.f);
@@ -541,7 +547,9 @@ __global__ void __launch_bounds__(256) cln_bwd_kernel(const bf16* __restrict__ t
   __shared__ __align__(16) bf16 tile[C][T::PITCH];
   __shared__ float ssc[C];
   const long p0 = (long)blockIdx.x * 64;
+  pdl_trigger();
   for (int c = threadIdx.x; c < C; c += 256) ssc[c] = scale[c];
+  pdl_wait();
   cln_load_tile<C>(t, tile, p0, M);
   __syncthreads();
   const int pl = threadIdx.x >> 2, cg = threadIdx.x & 3;

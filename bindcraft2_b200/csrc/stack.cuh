@@ -319,11 +319,10 @@ struct EvoStack {
     if (dpair != ct_pair) BC2_CUDA(cudaMemcpyAsync(dpair, ct_pair, np * 4, cudaMemcpyDeviceToDevice, st));
     if (dmsa != ct_msa) BC2_CUDA(cudaMemcpyAsync(dmsa, ct_msa, nm * 4, cudaMemcpyDeviceToDevice, st));
     for (int i = cfg.depth - 1; i >= 0; --i) {
-      launch_counter()++;
-      save_widen_kernel<<<ew_grid(np / 4, 256), 256, 0, st>>>(
-          reinterpret_cast<const uint2*>(psave + (long)i * np),
-          (!own_save || keep32.empty()) ? nullptr : reinterpret_cast<const float4*>(keep32[i]),
-          reinterpret_cast<float4*>(P[0]), np / 4);
+      launch_pdl(save_widen_kernel, dim3(ew_grid(np / 4, 256)), dim3(256), 0, st,
+                 reinterpret_cast<const uint2*>(psave + (long)i * np),
+                 (!own_save || keep32.empty()) ? nullptr : reinterpret_cast<const float4*>(keep32[i]),
+                 reinterpret_cast<float4*>(P[0]), np / 4);
       const float* m_in = msave + (long)i * nm;
       block_forward(i, P[0], m_in, pp[0], mp[0], st, /*tail=*/false, /*replay=*/true);
       block_backward(i, m_in, dpair, dmsa, st, i > 0 ? msave + (long)(i - 1) * nm : nullptr);
