@@ -990,6 +990,8 @@ constexpr int attn_bwd_smem() {
 // added in a fixed order: the result does not depend on scheduling.
 __global__ void __launch_bounds__(256)
 attn_dbias_reduce_kernel(const bf16* __restrict__ ds, float* __restrict__ d_bias, int B, int H, int N) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float part[8][32][9];
   const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
   const int q = blockIdx.x * 32 + lane, ko = blockIdx.y, h = blockIdx.z;
@@ -1018,7 +1020,7 @@ attn_dbias_reduce_kernel(const bf16* __restrict__ ds, float* __restrict__ d_bias
 }
 inline void attn_dbias_reduce(const AttnArgs& a, cudaStream_t st) {
   dim3 grid(cdiv(a.N, 32), a.N / 8, a.H);
-  launch_counter()++; attn_dbias_reduce_kernel<<<grid, 256, 0, st>>>(a.ds_store, a.d_bias, a.B, a.H, a.N);
+  launch_pdl(attn_dbias_reduce_kernel, dim3(grid), dim3(256), 0, st, a.ds_store, a.d_bias, a.B, a.H, a.N);
 }
 
 // ------------------------------------------------------------------------------------------- CUDA-core reference
@@ -1114,6 +1116,8 @@ __global__ void attn_ref_dkv_store(const float* acc, bf16* d_qkv, long ld, long 
 
 // fp32 dq accumulator -> bf16 dq columns (only when the backward split its keys over several CTAs)
 __global__ void attn_dq_store(const float* acc, bf16* d_qkv, long ld, long rows, int HD) {
+  pdl_trigger();
+  pdl_wait();
   const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= rows * HD) return;
   const long row = t / HD;
@@ -1197,7 +1201,7 @@ inline void attn_bwd_launch(const AttnPlan& p, cudaStream_t st) {
   launch_pdl(attn_bwd_tc_kernel<D>, grid, dim3(320), smem, st, p.tm, p.tdo, a);
   if (groups > 1) {
     const long m = p.rows * HD;
-    launch_counter()++; attn_dq_store<<<(unsigned)((m + 255) / 256), 256, 0, st>>>(a.dq_acc, a.d_qkv, a.ld, p.rows, HD);
+    launch_pdl(attn_dq_store, dim3((unsigned)((m + 255) / 256)), dim3(256), 0, st, a.dq_acc, a.d_qkv, a.ld, p.rows, HD);
   }
 }
 

@@ -61,28 +61,46 @@ inline std::atomic<long>& launch_counter() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-inline bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("BC2_NO_PDL");
-    return !(e && e[0] == '1');
+// Which launch classes get the attribute: bit 0 the machine-filling kernels of the pair track (default), bit 1 the small
+// kernels of the MSA track, bit 2 the structure module.  Measured on a B200: the first set gains 7% of an Evoformer step;
+// the other two chain many kernels of a few CTAs each, whose successors then all become resident and waiting at once, and
+// get slower with it (the structure module by 70%), so they are launched plainly unless BC2_PDL_SET says otherwise.
+inline int pdl_mask() {
+  static const int m = [] {
+    const char* off = getenv("BC2_NO_PDL");
+    if (off && off[0] == '1') return 0;
+    const char* e = getenv("BC2_PDL_SET");
+    return e ? atoi(e) : 1;
   }();
-  return on;
+  return m;
+}
+
+// Streams that carry a side track (the MSA track of an Evoformer stack): every launch on them counts as class bit 1.
+inline std::vector<cudaStream_t>& pdl_side_streams() {
+  static std::vector<cudaStream_t> v;
+  return v;
 }
 
 template <typename... KArgs, typename... Args>
-inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+inline void launch_pdl_c(int cls, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
+  for (cudaStream_t s : pdl_side_streams())
+    if (s == st) cls = 2;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  at[0].val.programmaticStreamSerializationAllowed = (pdl_mask() & cls) ? 1 : 0;
   cfg.attrs = at;
   cfg.numAttrs = 1;
   launch_counter()++;
   BC2_CUDA(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+}
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  launch_pdl_c(1, kernel, grid, block, smem, st, std::forward<Args>(args)...);
 }
 
 // Optional per-kernel-class timing with CUDA events on the launching stream (the reference has the same idea behind

@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256) cvt_bf16_f32_kernel(const uint2* __restri
 // values it narrowed beside it.
 __global__ void __launch_bounds__(256)
 save_narrow_kernel(const float4* __restrict__ in, uint2* __restrict__ out, float4* __restrict__ keep, long n4) {
+  pdl_trigger();
+  pdl_wait();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
     const float4 v = in[i];
     out[i] = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
@@ -190,6 +192,8 @@ inline void attn_bwd_prep(const AttnBwdPrepArgs& a, cudaStream_t st) {
 // out[m][c] = in[m][c] + v[c]  (fp32 rows of c4*4 channels)
 __global__ void __launch_bounds__(256) add_channel_const_kernel(const float4* __restrict__ in, const float4* __restrict__ v,
                                                                 float4* __restrict__ out, long n4, int c4) {
+  pdl_trigger();
+  pdl_wait();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
     const float4 x = in[i], y = v[i % c4];
     out[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);

@@ -519,7 +519,7 @@ struct MsaCol {
     { ProfScope ps_("MsaCol.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * Cm; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * Cm; e.M = Mi; e.N = 4 * Cm;
     { ProfScope ps_("MsaCol.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
-    { ProfScope ps_("MsaCol.forward.msacol_fwd_kernel", st); launch_counter()++; msacol_fwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S_, n, H); }
+    { ProfScope ps_("MsaCol.forward.msacol_fwd_kernel", st); launch_pdl_c(2, msacol_fwd_kernel<8>, dim3(cdiv(n * H, 8)), dim3(256), 0, st, qkvg, msa_mask, S->y, S_, n, H); }
     EpiResidual er; er.res_in = in; er.res_out = out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm;
     { ProfScope ps_("MsaCol.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
@@ -529,7 +529,7 @@ struct MsaCol {
     { ProfScope ps_("MsaCol.backward.cvt_f32_bf16", st); cvt_f32_bf16(g, S->dy, Mm * Cm, st); }
     EpiStore e; e.out = S->y; e.ldo = Cm; e.M = Mi; e.N = Cm;
     { ProfScope ps_("MsaCol.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
-    { ProfScope ps_("MsaCol.backward.msacol_bwd_kernel", st); launch_counter()++; msacol_bwd_kernel<8><<<cdiv(n * H, 8), 256, 0, st>>>(qkvg, msa_mask, S->y, S->big, S_, n, H); }
+    { ProfScope ps_("MsaCol.backward.msacol_bwd_kernel", st); launch_pdl_c(2, msacol_bwd_kernel<8>, dim3(cdiv(n * H, 8)), dim3(256), 0, st, qkvg, msa_mask, S->y, S->big, S_, n, H); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
     { ProfScope ps_("MsaCol.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g; l.g_out = g; l.M = Mi;
@@ -683,7 +683,7 @@ struct Opm {
     { ProfScope ps_("Opm.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
     EpiStore e; e.out = lr; e.ldo = 64; e.bias = b.blr; e.rowscale = msa_mask; e.M = Mi; e.N = 64;
     { ProfScope ps_("Opm.forward.gemm.g_lr", st); run_gemm(b.g_lr2[set], e, st); }
-    { ProfScope ps_("Opm.forward.opm_pack_left_kernel", st); launch_counter()++; opm_pack_left_kernel<<<cdiv(n * S_ * 16, 256), 256, 0, st>>>(lr, leftT, S_, n); }
+    { ProfScope ps_("Opm.forward.opm_pack_left_kernel", st); launch_pdl_c(2, opm_pack_left_kernel, dim3(cdiv(n * S_ * 16, 256)), dim3(256), 0, st, lr, leftT, S_, n); }
     EpiOpmTmp et; et.out = tmpT; et.S = S_; et.Nres = n; et.M = Mi; et.N = OPM_F * OPM_C;
     { ProfScope ps_("Opm.forward.gemm.g_tmp", st); run_gemm(b.g_tmp2[set], et, st); }
   }
@@ -703,13 +703,13 @@ struct Opm {
   void backward(int blk, const float* msa_in, const float* g_pair, float* g_msa, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm, K = 32 * S_;
-    { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_counter()++; opm_dout_kernel<<<cdiv(n * n, 8), 256, 0, st>>>(g_pair, msa_mask, dout, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_pdl_c(2, opm_dout_kernel, dim3(cdiv(n * n, 8)), dim3(256), 0, st, g_pair, msa_mask, dout, S_, n); }
     EpiPartial ep; ep.out = partial; ep.ld = K; ep.bs = (long)n * K; ep.M = n; ep.N = K;
     { ProfScope ps_("Opm.backward.gemm.g_dleft", st); run_gemm(g_dleft2[blk & 1], ep, st); }
     EpiStore ed; ed.out = dtmpT; ed.ldo = K; ed.M = n * OPM_F; ed.N = K;
     { ProfScope ps_("Opm.backward.gemm.g_dtmp", st); run_gemm(g_dtmp2[blk & 1], ed, st); }
-    { ProfScope ps_("Opm.backward.opm_dleft_reduce_kernel", st); launch_counter()++; opm_dleft_reduce_kernel<<<cdiv(n * K, 256), 256, 0, st>>>(partial, kSplit, msa_mask, dlr_b, S_, n); }
-    { ProfScope ps_("Opm.backward.opm_dright_tc_kernel", st); launch_counter()++; opm_dright_tc_kernel<<<cdiv(Mi, OPM_DR_ROWS), 256, 0, st>>>(dtmpT, b.wq, msa_mask, dlr_b, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dleft_reduce_kernel", st); launch_pdl_c(2, opm_dleft_reduce_kernel, dim3(cdiv(n * K, 256)), dim3(256), 0, st, partial, kSplit, msa_mask, dlr_b, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dright_tc_kernel", st); launch_pdl_c(2, opm_dright_tc_kernel, dim3(cdiv(Mi, OPM_DR_ROWS)), dim3(256), 0, st, dtmpT, b.wq, msa_mask, dlr_b, S_, n); }
     EpiStore ex; ex.out = S->dx; ex.ldo = Cm; ex.M = Mi; ex.N = Cm;
     { ProfScope ps_("Opm.backward.gemm.gb_lr", st); run_gemm(b.gb_lr, ex, st); }
     LnBwdArgs l; l.x = msa_in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;

@@ -19,6 +19,8 @@ constexpr int OPM_F = 128;  // pair channels (c_z)
 
 // leftT from lr rows (s*N + i): one thread per (i, s, pair of channels)
 __global__ void opm_pack_left_kernel(const bf16* __restrict__ lr, bf16* __restrict__ leftT, int S, int N) {
+  pdl_trigger();
+  pdl_wait();
   const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= (long)N * S * 16) return;
   const int c2 = (int)(t % 16), s = (int)((t / 16) % S), i = (int)(t / (16L * S));
@@ -29,6 +31,8 @@ __global__ void opm_pack_left_kernel(const bf16* __restrict__ lr, bf16* __restri
 // dout = g * 1/(1e-3 + sum_s m[s,i] m[s,j]): one warp per pair position (i,j), 4 channels per lane
 __global__ void __launch_bounds__(256)
 opm_dout_kernel(const float* __restrict__ g, const float* __restrict__ msa_mask, bf16* __restrict__ dout, int S, int N) {
+  pdl_trigger();
+  pdl_wait();
   const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (m >= (long)N * N) return;
   const int lane = threadIdx.x & 31;
@@ -43,6 +47,8 @@ opm_dout_kernel(const float* __restrict__ g, const float* __restrict__ msa_mask,
 // d(left) from the split-K partial sums: dlr_b[(s*N+i)][c] = mask[s,i] * sum_z partial[z][i][s*32+c]
 __global__ void opm_dleft_reduce_kernel(const float* __restrict__ partial, int nsplit, const float* __restrict__ msa_mask,
                                         bf16* __restrict__ dlr_b, int S, int N) {
+  pdl_trigger();
+  pdl_wait();
   const long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const int K = 32 * S;
   if (t >= (long)N * K) return;
@@ -58,6 +64,8 @@ constexpr int OPM_DR_ROWS = 2;
 __global__ void __launch_bounds__(256)
 opm_dright_tc_kernel(const bf16* __restrict__ dtmpT, const float* __restrict__ Wq, const float* __restrict__ msa_mask,
                      bf16* __restrict__ dlr_b, int S, int N) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sd[OPM_DR_ROWS][OPM_F][OPM_C];  // 32 KB
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long row0 = (long)blockIdx.x * OPM_DR_ROWS;
@@ -101,6 +109,8 @@ template <int MAXS>
 __global__ void __launch_bounds__(256)
 msacol_fwd_kernel(const bf16* __restrict__ qkvg, const float* __restrict__ msa_mask, bf16* __restrict__ og, int S, int N,
                   int H) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long w = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (w >= (long)N * H) return;
@@ -146,6 +156,8 @@ template <int MAXS>
 __global__ void __launch_bounds__(256)
 msacol_bwd_kernel(const bf16* __restrict__ qkvg, const float* __restrict__ msa_mask, const bf16* __restrict__ d_og,
                   bf16* __restrict__ d_qkvg, int S, int N, int H) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long w = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (w >= (long)N * H) return;

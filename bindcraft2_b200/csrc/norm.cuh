@@ -135,6 +135,8 @@ constexpr int LN_MAXH = 8;
 // Persistent: each warp keeps scale, offset and its slice of the bias projection in registers and strides over rows.
 template <int C>
 __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
+  pdl_trigger();
+  pdl_wait();
   using R = RowVec<C>;
   const int lane = threadIdx.x & 31;
   const int nwarp = gridDim.x * 8;
@@ -202,6 +204,8 @@ struct LnBwdArgs {
 
 template <int C>
 __global__ void __launch_bounds__(256) ln_bwd_kernel(LnBwdArgs a) {
+  pdl_trigger();
+  pdl_wait();
   using R = RowVec<C>;
   const int lane = threadIdx.x & 31;
   const int nwarp = gridDim.x * 8;
@@ -463,8 +467,7 @@ inline void ln_fwd(const LnArgs& a, cudaStream_t st) {
     BC2_CHECK(!a.wb || a.H <= GroupRow<C>::G, "LayerNorm bias projection: more heads than lanes per row");
     launch_pdl(ln_fwd_group_kernel<C>, dim3(std::min(cdiv(a.M, rows_per_cta), 148 * 8)), dim3(256), 0, st, a);
   } else {
-    launch_counter()++;
-    ln_fwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
+    launch_pdl_c(2, ln_fwd_kernel<C>, dim3(std::min(cdiv(a.M, 8), 148 * 8)), dim3(256), 0, st, a);
   }
 }
 template <int C>
@@ -474,8 +477,7 @@ inline void ln_bwd(const LnBwdArgs& a, cudaStream_t st) {
     BC2_CHECK(!a.wb || a.H <= LN_MAXH, "LayerNorm bias projection: too many heads");
     launch_pdl(ln_bwd_group_kernel<C>, dim3(std::min(cdiv(a.M, rows_per_cta), 148 * 8)), dim3(256), 0, st, a);
   } else {
-    launch_counter()++;
-    ln_bwd_kernel<C><<<std::min(cdiv(a.M, 8), 148 * 8), 256, 0, st>>>(a);
+    launch_pdl_c(2, ln_bwd_kernel<C>, dim3(std::min(cdiv(a.M, 8), 148 * 8)), dim3(256), 0, st, a);
   }
 }
 

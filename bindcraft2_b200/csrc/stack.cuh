@@ -20,6 +20,7 @@
 // own_save has too: the result then depends on state inside the stack object (within rounding), so callers that
 // interleave states use own_save = 0.
 #pragma once
+#include <algorithm>
 #include <memory>
 
 #include "modules.cuh"
@@ -130,6 +131,7 @@ struct EvoStack {
     const char* ns = getenv("BC2_NO_SIDE_STREAM");
     if (!(ns && ns[0] == '1') && (c.opm_first || c.pair_only)) {
       BC2_CUDA(cudaStreamCreateWithFlags(&side, cudaStreamNonBlocking));
+      pdl_side_streams().push_back(side);
       for (auto& e : ev) BC2_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     }
     BC2_CUDA(cudaDeviceSynchronize());
@@ -137,7 +139,11 @@ struct EvoStack {
   ~EvoStack() {
     for (auto& e : ev)
       if (e) cudaEventDestroy(e);
-    if (side) cudaStreamDestroy(side);
+    if (side) {
+      auto& v = pdl_side_streams();
+      v.erase(std::remove(v.begin(), v.end(), side), v.end());
+      cudaStreamDestroy(side);
+    }
   }
 
   // Fork/join helpers.  The MSA track (a few dozen kernels over S*N rows, each a handful of CTAs) runs on a side stream
@@ -158,8 +164,7 @@ struct EvoStack {
     if (cfg.pair_only) {
       // The reference's extra-MSA path (native/block.cuh `pair_only`; bindcraft/af/native.py:1131-1193): the MSA side is
       // not run (its mask is all zeros in a design run) and only the constant of the outer product mean reaches the pair.
-      launch_counter()++;
-      add_channel_const_kernel<<<ew_grid(Mp * cfg.Cz / 4, 256), 256, 0, st>>>(
+      launch_pdl(add_channel_const_kernel, dim3(ew_grid(Mp * cfg.Cz / 4, 256)), dim3(256), 0, st,
           reinterpret_cast<const float4*>(p_in), reinterpret_cast<const float4*>(opm_const[b]),
           reinterpret_cast<float4*>(P[1]), Mp * cfg.Cz / 4, cfg.Cz / 4);
       if (tail && m_out != m_in) BC2_CUDA(cudaMemcpyAsync(m_out, m_in, bm, cudaMemcpyDeviceToDevice, st));
@@ -294,10 +299,10 @@ struct EvoStack {
         if (own_save) {
           if (keep32.empty())
             for (int d = 0; d < cfg.depth; ++d) keep32.push_back(A.alloc<float>(np));
-          launch_counter()++;
-          save_narrow_kernel<<<ew_grid(np / 4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(pc),
-                                                                  reinterpret_cast<uint2*>(psave + (long)i * np),
-                                                                  reinterpret_cast<float4*>(keep32[i]), np / 4);
+          launch_pdl(save_narrow_kernel, dim3(ew_grid(np / 4, 256)), dim3(256), 0, st,
+                     reinterpret_cast<const float4*>(pc),
+                     reinterpret_cast<uint2*>(psave + (long)i * np),
+                     reinterpret_cast<float4*>(keep32[i]), np / 4);
         } else {
           cvt_f32_bf16(pc, psave + (long)i * np, np, st);
         }

@@ -35,6 +35,8 @@ __global__ void __launch_bounds__(256)
 ln_f32_kernel(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ offset,
               float* __restrict__ y, long M, const float* __restrict__ w2d /*[C][H]*/, const float* __restrict__ b2d_bias,
               float* __restrict__ b2d /*[M][H]*/) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int V = C / 32;
   const int lane = threadIdx.x & 31;
   const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -70,6 +72,8 @@ template <int C>
 __global__ void __launch_bounds__(256)
 ln_f32_bwd_kernel(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ dy, float* __restrict__ dx,
                   long M, const float* __restrict__ w2d, const float* __restrict__ db2d) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int V = C / 32;
   const int lane = threadIdx.x & 31;
   const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -115,6 +119,8 @@ struct LinArgs {
   int relu_in = 0;                                    // the input is max(X, 0)
 };
 __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sX[16][64 + 1], sW[16][64];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
@@ -168,6 +174,8 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
 // the next chunk's global loads are issued into registers before the current chunk is multiplied, so that with one
 // block per SM the load latency hides behind the arithmetic.
 __global__ void __launch_bounds__(256) linear_f32_small_kernel(LinArgs a) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int KC = 64;
   __shared__ float sX[KC][32 + 1];
   __shared__ __align__(16) float sW[KC][32];
@@ -220,13 +228,12 @@ __global__ void __launch_bounds__(256) linear_f32_small_kernel(LinArgs a) {
   }
 }
 inline void linear_f32(const LinArgs& a, cudaStream_t st) {
-  launch_counter()++;
   if (a.M <= 2048) {
     dim3 grid(cdiv(a.N, 32), cdiv(a.M, 32));
-    linear_f32_small_kernel<<<grid, 256, 0, st>>>(a);
+    launch_pdl_c(4, linear_f32_small_kernel, dim3(grid), dim3(256), 0, st, a);
   } else {
     dim3 grid(cdiv(a.N, 64), cdiv(a.M, 64));
-    linear_f32_kernel<<<grid, 256, 0, st>>>(a);
+    launch_pdl_c(4, linear_f32_kernel, dim3(grid), dim3(256), 0, st, a);
   }
 }
 
@@ -269,6 +276,8 @@ __device__ __forceinline__ void quat_rot_bwd(float x0, float y0, float z0, const
 constexpr int GP = 16;
 __global__ void __launch_bounds__(192)
 ipa_points_kernel(const float* __restrict__ proj, const float* __restrict__ rig, float* __restrict__ gpts) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x, t = threadIdx.x;  // t = h*16 + slot
   const int h = t >> 4, slot = t & 15;
   const float* R = rig + (long)n * 12;
@@ -291,6 +300,8 @@ ipa_attn_fwd_kernel(const float* __restrict__ proj, const float* __restrict__ gp
                     const float* __restrict__ pair_ln, const float* __restrict__ b2d, const float* __restrict__ mask /*[N][N]*/,
                     const float* __restrict__ pw /*[H] point weights*/, float* __restrict__ attn /*[N][N][H]*/,
                     float* __restrict__ fin /*[N][NFINAL]*/, int N) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sl[];  // [N][H]
   __shared__ float sq[H * SQK], sgq[H * PQK * 3], spg[H * PV * 3], spw[H];
   const int i = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -374,6 +385,8 @@ ipa_attn_fwd_kernel(const float* __restrict__ proj, const float* __restrict__ gp
 
 // rigid_new = rigid o update(upd): R' = R U(q), t' = R u + t      (thread per residue)
 __global__ void rigid_update_kernel(const float* __restrict__ rig, const float* __restrict__ upd, float* __restrict__ out, int N) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   const float* R = rig + (long)n * 12;
@@ -391,6 +404,8 @@ __global__ void rigid_update_kernel(const float* __restrict__ rig, const float* 
 // Given the cotangent g_out of the new frame: cotangent of the old frame (ACCUMULATED into g_in) and of upd (written).
 __global__ void rigid_update_bwd_kernel(const float* __restrict__ rig, const float* __restrict__ upd, const float* __restrict__ g_out,
                                         float* __restrict__ g_in, float* __restrict__ d_upd, int N) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x * blockDim.x + threadIdx.x;
   if (n >= N) return;
   const float* R = rig + (long)n * 12;

@@ -18,6 +18,8 @@ inline std::vector<float> transpose2d(const std::vector<float>& w, int rows, int
 }
 
 __global__ void scale_translation_kernel(const float* __restrict__ in, float* __restrict__ out, float s, int n) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t < n) out[t] = (t % 12 >= 9) ? in[t] * s : in[t];
 }
@@ -141,12 +143,12 @@ struct StructureCore {
   template <int C>
   void ln(const float* x, const float* sc, const float* of, float* y, long M, cudaStream_t st, const float* w = nullptr,
           const float* bb = nullptr, float* bo = nullptr) {
-    launch_counter()++; ln_f32_kernel<C><<<(unsigned)cdiv(M, 8L), 256, 0, st>>>(x, sc, of, y, M, w, bb, bo);
+    launch_pdl_c(4, ln_f32_kernel<C>, dim3((unsigned)cdiv(M, 8L)), dim3(256), 0, st, x, sc, of, y, M, w, bb, bo);
   }
   template <int C>
   void ln_bwd(const float* x, const float* sc, const float* dy, float* dx, long M, cudaStream_t st, const float* w = nullptr,
               const float* db = nullptr) {
-    launch_counter()++; ln_f32_bwd_kernel<C><<<(unsigned)cdiv(M, 8L), 256, 0, st>>>(x, sc, dy, dx, M, w, db);
+    launch_pdl_c(4, ln_f32_bwd_kernel<C>, dim3((unsigned)cdiv(M, 8L)), dim3(256), 0, st, x, sc, dy, dx, M, w, db);
   }
   void lin(const float* X, const float* W, const float* b, float* Y, int K, int Nn, cudaStream_t st, int relu = 0,
            const float* R = nullptr, const float* G = nullptr, int accumulate = 0) {
@@ -175,8 +177,8 @@ struct StructureCore {
     }
     for (int l = 0; l < L; ++l) {
       lin(act_in[l], proj.w, proj.b, projv[l], CS, NPROJ, st);
-      launch_counter()++; ipa_points_kernel<<<N, H * GP, 0, st>>>(projv[l], rig[l], gpts[l]);
-      launch_counter()++; ipa_attn_fwd_kernel<<<N, 256, attn_smem / 2, st>>>(projv[l], gpts[l], rig[l], pair_ln, b2d, mask, pw, attn[l], fin[l], N);
+      launch_pdl_c(4, ipa_points_kernel, dim3(N), dim3(H * GP), 0, st, projv[l], rig[l], gpts[l]);
+      launch_pdl_c(4, ipa_attn_fwd_kernel, dim3(N), dim3(256), attn_smem / 2, st, projv[l], gpts[l], rig[l], pair_ln, b2d, mask, pw, attn[l], fin[l], N);
       lin(fin[l], out.w, out.b, act1[l], NFINAL, CS, st, 0, act_in[l]);
       ln<CS>(act1[l], ln_a_scale, ln_a_off, ln1[l], N, st);
       lin(ln1[l], t1.w, t1.b, h1[l], CS, CS, st, 1);
@@ -184,10 +186,10 @@ struct StructureCore {
       lin(h2[l], t3.w, t3.b, act2[l], CS, CS, st, 0, ln1[l]);
       ln<CS>(act2[l], ln_t_scale, ln_t_off, act_in[l + 1], N, st);
       lin(act_in[l + 1], quat.w, quat.b, upd[l], CS, 6, st);
-      launch_counter()++; rigid_update_kernel<<<cdiv(N, 128), 128, 0, st>>>(rig[l], upd[l], rig[l + 1], N);
+      launch_pdl_c(4, rigid_update_kernel, dim3(cdiv(N, 128)), dim3(128), 0, st, rig[l], upd[l], rig[l + 1], N);
     }
     if (act_out) BC2_CUDA(cudaMemcpyAsync(act_out, act_in[L], (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
-    if (rig_out) { launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(rig[L], rig_out, POSITION_SCALE, N * 12); }
+    if (rig_out) { launch_pdl_c(4, scale_translation_kernel, dim3(cdiv(N * 12, 256)), dim3(256), 0, st, rig[L], rig_out, POSITION_SCALE, N * 12); }
   }
 
   // Cotangents d_act [N,384] and d_rig [N,12] (rotation entries, then the SCALED translation) -> d_single, d_pair.
@@ -197,7 +199,7 @@ struct StructureCore {
                 float* d_pair, cudaStream_t st, const float* d_single_ln_extra = nullptr) {
     const long n2 = (long)N * N;
     BC2_CUDA(cudaMemcpyAsync(g_act, d_act, (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
-    launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(d_rig, g_rig[0], POSITION_SCALE, N * 12);
+    launch_pdl_c(4, scale_translation_kernel, dim3(cdiv(N * 12, 256)), dim3(256), 0, st, d_rig, g_rig[0], POSITION_SCALE, N * 12);
     BC2_CUDA(cudaMemsetAsync(db2d, 0, (size_t)n2 * H * 4, st));
     BC2_CUDA(cudaMemsetAsync(dpair_ln, 0, (size_t)n2 * CZ * 4, st));
     int cur = 0;
@@ -205,7 +207,7 @@ struct StructureCore {
       float* g_out = g_rig[cur];
       float* g_in = g_rig[cur ^ 1];
       BC2_CUDA(cudaMemsetAsync(g_in, 0, (size_t)N * 12 * 4, st));
-      launch_counter()++; rigid_update_bwd_kernel<<<cdiv(N, 128), 128, 0, st>>>(rig[l], upd[l], g_out, g_in, d_upd, N);
+      launch_pdl_c(4, rigid_update_bwd_kernel, dim3(cdiv(N, 128)), dim3(128), 0, st, rig[l], upd[l], g_out, g_in, d_upd, N);
       lin(d_upd, quat.wt, nullptr, g_act, 6, CS, st, 0, nullptr, nullptr, 1);         // g_act += d_upd Wq^T
       ln_bwd<CS>(act2[l], ln_t_scale, g_act, dA, N, st);                               // dA = d(act2)
       lin(dA, t3.wt, nullptr, tA, CS, CS, st, 0, nullptr, h2[l]);                      // d(h2 pre-relu)
@@ -213,9 +215,9 @@ struct StructureCore {
       lin(tB, t1.wt, nullptr, tA, CS, CS, st, 0, dA);                                  // d(ln1) = dA + . W1^T
       ln_bwd<CS>(act1[l], ln_a_scale, tA, dB, N, st);                                  // dB = d(act1)
       lin(dB, out.wt, nullptr, d_fin, CS, NFINAL, st);                                 // d(final)
-      launch_counter()++; ipa_bwd_query_kernel<<<N, 256, attn_smem, st>>>(projv[l], gpts[l], rig[l], pair_ln, attn[l], fin[l], d_fin, pw, dlogit,
+      launch_pdl_c(4, ipa_bwd_query_kernel, dim3(N), dim3(256), attn_smem, st, projv[l], gpts[l], rig[l], pair_ln, attn[l], fin[l], d_fin, pw, dlogit,
                                                      db2d, dpair_ln, dopg, d_proj, g_in, N);
-      launch_counter()++; ipa_bwd_key_kernel<<<N, 256, 0, st>>>(projv[l], gpts[l], rig[l], attn[l], dlogit, d_fin, dopg, pw, d_proj, g_in, N);
+      launch_pdl_c(4, ipa_bwd_key_kernel, dim3(N), dim3(256), 0, st, projv[l], gpts[l], rig[l], attn[l], dlogit, d_fin, dopg, pw, d_proj, g_in, N);
       lin(d_proj, proj.wt, nullptr, g_act, NPROJ, CS, st, 0, dB);                      // g_act = dB + d_proj Wproj^T
       cur ^= 1;
     }
