@@ -32,6 +32,7 @@ extern "C" {
  *   results   pair_out f32 [N,N,128], msa_out f32 [S,N,256],
  *             psave bf16 [slots,N,N,128], msave f32 [slots,S,N,256]   (slots = bc2 native_save_slots_probe(depth, N);
  *             both may be null when save == 0: the detached pass)
+ * opm_first = 1 is the multimer block order, 0 the monomer one (outer product mean after the MSA track).
  * N must be a multiple of 32 (the caller pads and masks, bindcraft/af/native.py:927-972). */
 int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
                       const uint32_t* seed, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t pair_only,
