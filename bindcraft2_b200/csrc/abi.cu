@@ -130,16 +130,17 @@ sm::StructureHeads* get_heads(int N, int depth, const std::string& dir) {
 extern "C" {
 
 int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
-                      const uint32_t* /*seed*/, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t pair_only,
-                      int64_t own_save, int64_t opm_first, int64_t /*dropout*/, const char* weights_dir,
+                      const uint32_t* seed, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t pair_only,
+                      int64_t own_save, int64_t opm_first, int64_t dropout, const char* weights_dir,
                       float* pair_out, float* msa_out, uint16_t* psave, float* msave) {
   try {
     BC2_CHECK(pair && msa && pair_mask && msa_mask && pair_out && msa_out && weights_dir, "null operand");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     BC2_CHECK(!save || (psave && msave), "save != 0 needs psave and msave");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
     s->forward(pair, msa, pair_mask, msa_mask, pair_out, msa_out, save ? reinterpret_cast<bf16*>(psave) : nullptr,
-               save ? msave : nullptr, own_save != 0, (cudaStream_t)stream);
+               save ? msave : nullptr, own_save != 0, (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -148,15 +149,16 @@ int bc2_evoformer_fwd(void* stream, const float* pair, const float* msa, const f
 }
 
 int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
-                      const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* /*seed*/,
+                      const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* seed,
                       int64_t N, int64_t S, int64_t depth, int64_t pair_only, int64_t own_save, int64_t opm_first,
-                      int64_t /*dropout*/, const char* weights_dir, float* dpair, float* dmsa) {
+                      int64_t dropout, const char* weights_dir, float* dpair, float* dmsa) {
   try {
     BC2_CHECK(ct_pair && ct_msa && pair_mask && msa_mask && psave && msave && dpair && dmsa && weights_dir, "null operand");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, pair_only != 0, opm_first != 0);
     s->backward(ct_pair, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave), msave, dpair, dmsa,
-                own_save != 0, (cudaStream_t)stream);
+                own_save != 0, (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -165,16 +167,17 @@ int bc2_evoformer_bwd(void* stream, const float* ct_pair, const float* ct_msa, c
 }
 
 int bc2_extra_msa_stack_fwd(void* stream, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
-                            const uint32_t* /*seed*/, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t own_save,
-                            int64_t /*dropout*/, const char* weights_dir, float* pair_out, float* msa_out, uint16_t* psave,
+                            const uint32_t* seed, int64_t N, int64_t S, int64_t depth, int64_t save, int64_t own_save,
+                            int64_t dropout, const char* weights_dir, float* pair_out, float* msa_out, uint16_t* psave,
                             float* msave) {
   try {
     BC2_CHECK(pair && msa && pair_mask && msa_mask && pair_out && msa_out && weights_dir, "null operand");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     BC2_CHECK(!save || (psave && msave), "save != 0 needs psave and msave");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, false, true, true);
     s->forward(pair, msa, pair_mask, msa_mask, pair_out, msa_out, save ? reinterpret_cast<bf16*>(psave) : nullptr,
-               save ? msave : nullptr, own_save != 0, (cudaStream_t)stream);
+               save ? msave : nullptr, own_save != 0, (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -183,15 +186,16 @@ int bc2_extra_msa_stack_fwd(void* stream, const float* pair, const float* msa, c
 }
 
 int bc2_extra_msa_stack_bwd(void* stream, const float* ct_pair, const float* ct_msa, const float* pair_mask,
-                            const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* /*seed*/,
-                            int64_t N, int64_t S, int64_t depth, int64_t own_save, int64_t /*dropout*/,
+                            const float* msa_mask, const uint16_t* psave, const float* msave, const uint32_t* seed,
+                            int64_t N, int64_t S, int64_t depth, int64_t own_save, int64_t dropout,
                             const char* weights_dir, float* dpair, float* dmsa) {
   try {
     BC2_CHECK(ct_pair && ct_msa && pair_mask && msa_mask && psave && msave && dpair && dmsa && weights_dir, "null operand");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     EvoStack* s = get_stack((int)N, (int)S, (int)depth, weights_dir, false, true, true);
     s->backward(ct_pair, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave), msave, dpair, dmsa,
-                own_save != 0, (cudaStream_t)stream);
+                own_save != 0, (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -214,14 +218,14 @@ int native_stack_prealloc(int N, int S, int depth, const char* weights_dir, int 
   }
 }
 
-int bc2_template_pair_stack_fwd(void* stream, const float* pair, const float* pair_mask, const uint32_t* /*seed*/,
-                                int64_t N, int64_t depth, int64_t /*dropout*/, const char* weights_dir, float* out,
+int bc2_template_pair_stack_fwd(void* stream, const float* pair, const float* pair_mask, const uint32_t* seed,
+                                int64_t N, int64_t depth, int64_t dropout, const char* weights_dir, float* out,
                                 uint16_t* save) {
   try {
     BC2_CHECK(pair && pair_mask && out && weights_dir, "null operand");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     TplStack* t = get_tpl((int)N, (int)depth, weights_dir);
-    t->forward(pair, pair_mask, out, reinterpret_cast<bf16*>(save), (cudaStream_t)stream);
+    t->forward(pair, pair_mask, out, reinterpret_cast<bf16*>(save), (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -230,13 +234,13 @@ int bc2_template_pair_stack_fwd(void* stream, const float* pair, const float* pa
 }
 
 int bc2_template_pair_stack_bwd(void* stream, const float* ct, const float* pair_mask, const uint16_t* save,
-                                const uint32_t* /*seed*/, int64_t N, int64_t depth, int64_t /*dropout*/,
+                                const uint32_t* seed, int64_t N, int64_t depth, int64_t dropout,
                                 const char* weights_dir, float* dpair) {
   try {
     BC2_CHECK(ct && pair_mask && save && dpair && weights_dir, "null operand");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     TplStack* t = get_tpl((int)N, (int)depth, weights_dir);
-    t->backward(ct, pair_mask, reinterpret_cast<const bf16*>(save), dpair, (cudaStream_t)stream);
+    t->backward(ct, pair_mask, reinterpret_cast<const bf16*>(save), dpair, (cudaStream_t)stream, nullptr, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -245,13 +249,13 @@ int bc2_template_pair_stack_bwd(void* stream, const float* ct, const float* pair
 }
 
 int bc2_template_embedding_fwd(void* stream, const float* query, const float* act_const, const float* pair_mask,
-                               const uint32_t* /*seed*/, int64_t N, int64_t depth, int64_t /*dropout*/,
+                               const uint32_t* seed, int64_t N, int64_t depth, int64_t dropout,
                                const char* weights_dir, float* out, uint16_t* save) {
   try {
     BC2_CHECK(query && act_const && pair_mask && out && weights_dir, "null operand");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     TplEmbed* t = get_tplembed((int)N, (int)depth, weights_dir);
-    t->forward(query, act_const, pair_mask, out, reinterpret_cast<bf16*>(save), (cudaStream_t)stream);
+    t->forward(query, act_const, pair_mask, out, reinterpret_cast<bf16*>(save), (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -260,13 +264,13 @@ int bc2_template_embedding_fwd(void* stream, const float* query, const float* ac
 }
 
 int bc2_template_embedding_bwd(void* stream, const float* ct, const float* query, const float* act_const,
-                               const float* pair_mask, const uint16_t* /*save*/, const uint32_t* /*seed*/, int64_t N,
-                               int64_t depth, int64_t /*dropout*/, const char* weights_dir, float* dquery) {
+                               const float* pair_mask, const uint16_t* /*save*/, const uint32_t* seed, int64_t N,
+                               int64_t depth, int64_t dropout, const char* weights_dir, float* dquery) {
   try {
     BC2_CHECK(ct && query && act_const && pair_mask && dquery && weights_dir, "null operand");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     TplEmbed* t = get_tplembed((int)N, (int)depth, weights_dir);
-    t->backward(ct, query, act_const, pair_mask, dquery, (cudaStream_t)stream);
+    t->backward(ct, query, act_const, pair_mask, dquery, (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -338,7 +342,7 @@ int bc2_structure_module_bwd(void* stream, const float* single, const float* pai
 }
 
 int bc2_structure_heads_fwd(void* stream, const float* single, const float* pair, const float* mask, const float* aatype,
-                            const uint32_t* /*seed*/, int64_t N, int64_t depth, const char* weights_dir, float* atom14,
+                            const uint32_t* seed, int64_t N, int64_t depth, const char* weights_dir, float* atom14,
                             float* dgram, float* pae, float* plddt, float* expres) {
   try {
     BC2_CHECK(single && pair && mask && aatype && weights_dir, "null operand");
@@ -346,7 +350,7 @@ int bc2_structure_heads_fwd(void* stream, const float* single, const float* pair
     BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     sm::StructureHeads* s = get_heads((int)N, (int)depth, weights_dir);
-    s->forward(single, pair, mask, aatype, atom14, dgram, pae, plddt, expres, (cudaStream_t)stream);
+    s->forward(single, pair, mask, aatype, atom14, dgram, pae, plddt, expres, (cudaStream_t)stream, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -355,7 +359,7 @@ int bc2_structure_heads_fwd(void* stream, const float* single, const float* pair
 }
 
 int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair, const float* mask, const float* aatype,
-                            const uint32_t* /*seed*/, const float* d_atom14, const float* d_dgram, const float* d_pae,
+                            const uint32_t* seed, const float* d_atom14, const float* d_dgram, const float* d_pae,
                             const float* d_plddt, const float* d_expres, int64_t N, int64_t depth, const char* weights_dir,
                             float* dsingle, float* dpair) {
   try {
@@ -364,7 +368,8 @@ int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair
     BC2_CHECK(N > 0 && depth > 0 && depth <= 64, "bad shape");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     sm::StructureHeads* s = get_heads((int)N, (int)depth, weights_dir);
-    s->backward(single, pair, mask, aatype, d_atom14, d_dgram, d_pae, d_plddt, d_expres, dsingle, dpair, (cudaStream_t)stream);
+    s->backward(single, pair, mask, aatype, d_atom14, d_dgram, d_pae, d_plddt, d_expres, dsingle, dpair, (cudaStream_t)stream,
+                seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {

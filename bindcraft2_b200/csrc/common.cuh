@@ -156,6 +156,42 @@ struct ProfScope {
   }
 };
 
+// ------------------------------------------------------------------------------------------- dropout
+// The reference's native masks are not stored: they are a counter hash of (seed, block index, module id, mask index)
+// turned into keep ? 1/keep_rate : 0 (native/common.cuh:944-981); the mask index is (unit * C + channel), where the
+// unit is the COLUMN j of a pair position (i, j) for the masks shared over rows (tri-mul out/in, starting-node
+// attention, MSA row attention: residue index) and the ROW i for the ending-node attention's mask shared over
+// columns (native/common.cuh:983-1030, module ids native/block.cuh:75 and native/tplblock.cuh:66).  This library
+// evaluates the same hash once per call into [unit][C] tables of scales (a few hundred KB per block, read through
+// L1/L2 by the epilogues), from the caller's device-side {seed, enabled} words, so forward and backward of a call
+// pair see the same masks without any state kept between them.
+__host__ __device__ inline uint32_t drop_hash(uint32_t seed, uint32_t depth, uint32_t mod, uint32_t idx) {
+  uint32_t h = seed * 0x9e3779b9u;
+  const uint32_t in[3] = {depth + 0x85ebca6bu, mod + 0xc2b2ae35u, idx + 0x27d4eb2fu};
+  for (int i = 0; i < 3; ++i) h ^= in[i] + (h << 6) + (h >> 2);
+  h ^= h >> 15;
+  h *= 0x2c1b3c6du;
+  h ^= h >> 12;
+  h *= 0x297a2d39u;
+  h ^= h >> 15;
+  return h;
+}
+__host__ __device__ inline float drop_scale(uint32_t seed, uint32_t depth, uint32_t mod, uint32_t idx, float rate) {
+  const float keep = 1.f - rate;
+  const float u = (float)drop_hash(seed, depth, mod, idx) * 2.3283064365386963e-10f;  // hash / 2^32
+  return u < keep ? 1.f / keep : 0.f;
+}
+
+// One dropout site of one block: scale of element (row m, channel c) = tab[unit(m) * C + c].
+struct DropSite {
+  const float* tab = nullptr;  // null: no dropout
+  int n = 1;                   // positions per row of the [n, n] pair grid (or residues per alignment row)
+  int by_row = 0;              // 1: unit = m / n (mask shared over columns), 0: unit = m % n (shared over rows)
+  __device__ __forceinline__ const float* row(long m, int C) const {
+    return tab + (long)(by_row ? m / n : m % n) * C;
+  }
+};
+
 // ------------------------------------------------------------------------------------------- small helpers
 __host__ __device__ constexpr int cdiv(int a, int b) { return (a + b - 1) / b; }
 

@@ -54,9 +54,52 @@ save_widen_kernel(const uint2* __restrict__ slot, const float4* __restrict__ kee
   }
 }
 
+// fp32 -> bf16 with a dropout site's scales applied: the cotangent entering a module whose output was dropped.
+__global__ void __launch_bounds__(256)
+cvt_drop_f32_bf16_kernel(const float4* __restrict__ in, uint2* __restrict__ out, DropSite d, long M, int C) {
+  pdl_trigger();
+  pdl_wait();
+  const int c4 = C / 4;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < M * c4; i += (long)gridDim.x * blockDim.x) {
+    const long m = i / c4;
+    const int c = (int)(i - m * c4) * 4;
+    const float4 v = in[i];
+    const float4 s = *reinterpret_cast<const float4*>(d.row(m, C) + c);
+    out[i] = make_uint2(pack_bf16(v.x * s.x, v.y * s.y), pack_bf16(v.z * s.z, v.w * s.w));
+  }
+}
+
+// Scale tables of every dropout site of a stack, from the device-side {seed, enabled} words.  Table t of block b holds
+// n * widths[t] floats; sites are laid out block after block.  enabled == 0 writes ones (the masks then change nothing).
+struct DropTableArgs {
+  float* tab;
+  const uint32_t* seed;
+  int blocks, n, sites;
+  int width[5], mod[5];
+  float rate[5];
+  long per_block;
+};
+__global__ void __launch_bounds__(256) drop_tables_kernel(DropTableArgs a) {
+  const uint32_t seed = a.seed[0], enabled = a.seed[1];
+  const long total = a.per_block * a.blocks;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int b = (int)(i / a.per_block);
+    long r = i - (long)b * a.per_block;
+    int t = 0;
+    while (t + 1 < a.sites && r >= (long)a.n * a.width[t]) { r -= (long)a.n * a.width[t]; ++t; }
+    a.tab[i] = enabled ? drop_scale(seed, (uint32_t)b, (uint32_t)a.mod[t], (uint32_t)r, a.rate[t]) : 1.f;
+  }
+}
+
 inline int ew_grid(long n, int per_block) { return (int)std::min<long>((n + per_block - 1) / per_block, 148L * 16); }
 inline void cvt_f32_bf16(const float* in, bf16* out, long n, cudaStream_t st) {
   launch_pdl(cvt_f32_bf16_kernel, dim3(ew_grid(n / 4, 256)), dim3(256), 0, st, reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), n / 4);
+}
+// rows of C channels; d.tab == null is the plain conversion
+inline void cvt_drop_f32_bf16(const float* in, bf16* out, long M, int C, const DropSite& d, cudaStream_t st) {
+  if (!d.tab) return cvt_f32_bf16(in, out, M * C, st);
+  launch_pdl(cvt_drop_f32_bf16_kernel, dim3(ew_grid(M * C / 4, 256)), dim3(256), 0, st,
+             reinterpret_cast<const float4*>(in), reinterpret_cast<uint2*>(out), d, M, C);
 }
 inline void cvt_bf16_f32(const bf16* in, float* out, long n, cudaStream_t st) {
   launch_counter()++; cvt_bf16_f32_kernel<<<ew_grid(n / 4, 256), 256, 0, st>>>(reinterpret_cast<const uint2*>(in), reinterpret_cast<float4*>(out), n / 4);
@@ -67,14 +110,18 @@ inline void cvt_bf16_f32(const bf16* in, float* out, long n, cudaStream_t st) {
 // d(gate pre-activation) = dz * ob * g2 * (1 - g2) -> columns [off, off+C) of the concatenated gradient buffer.
 __global__ void __launch_bounds__(256)
 trimul_bwd_out_kernel(const float4* __restrict__ dz, const uint2* __restrict__ ob, const uint2* __restrict__ g2,
-                      uint2* __restrict__ d_o, bf16* __restrict__ dcat, long ldd, int off, long M, int C) {
+                      uint2* __restrict__ d_o, bf16* __restrict__ dcat, long ldd, int off, long M, int C, DropSite drop) {
   pdl_trigger();
   pdl_wait();
   const int c4 = C / 4;
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < M * c4; i += (long)gridDim.x * blockDim.x) {
     const long m = i / c4;
     const int c = (int)(i - m * c4) * 4;
-    const float4 z = dz[i];
+    float4 z = dz[i];
+    if (drop.tab) {  // the module's output was dropped: so is the cotangent that enters it
+      const float4 s = *reinterpret_cast<const float4*>(drop.row(m, C) + c);
+      z.x *= s.x; z.y *= s.y; z.z *= s.z; z.w *= s.w;
+    }
     const uint2 o2 = ob[i], g = g2[i];
     const float2 o01 = unpack_bf16(o2.x), o23 = unpack_bf16(o2.y), g01 = unpack_bf16(g.x), g23 = unpack_bf16(g.y);
     d_o[i] = make_uint2(pack_bf16(z.x * g01.x, z.y * g01.y), pack_bf16(z.z * g23.x, z.w * g23.y));

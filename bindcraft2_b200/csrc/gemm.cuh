@@ -164,6 +164,7 @@ struct EpiResidual {
   bf16* save = nullptr;
   long lds = 0;
   int M = 0, N = 0;
+  DropSite drop;  // dropout scales of the module output (applied last, to what is added to the residual)
   static constexpr bool kPaired = false;
   __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
     if (m >= M || n0 >= N) return;
@@ -203,6 +204,14 @@ struct EpiResidual {
         const float2 mm = unpack_bf16(mw[j]);
         x[2 * j] *= mm.x;
         x[2 * j + 1] *= mm.y;
+      }
+    }
+    if (drop.tab) {
+      const float4* dp = reinterpret_cast<const float4*>(drop.row(m, N) + n0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 d4 = dp[j];
+        x[4 * j] *= d4.x; x[4 * j + 1] *= d4.y; x[4 * j + 2] *= d4.z; x[4 * j + 3] *= d4.w;
       }
     }
 #pragma unroll

@@ -137,6 +137,7 @@ struct Transition {
 // modules.TriangleMultiplication._fused_triangle_multiplication (modules.py:1043-1088).
 struct TriMul {
   int n = 0, C = 0, Hc = 0;
+  DropSite drop;  // dropout scales of this module's output for the block about to run (set by the stack; null: none)
   bool outgoing = true;
   long M = 0;
   struct W {
@@ -242,13 +243,13 @@ struct TriMul {
     { ProfScope ps_("TriMul.forward.cln_fwd_c", st); cln_fwd_c(t, b.cn, S->y, st); }
     EpiStore eg; eg.out = g2; eg.ldo = C; eg.bias = b.bg2; eg.act = 2; eg.act_from = 0; eg.M = Mi; eg.N = C;
     { ProfScope ps_("TriMul.forward.gemm.g_g2", st); run_gemm(b.g_g2, eg, st); }
-    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.bo; er.mul = g2; er.ldm = C; er.save = ob; er.lds = C; er.M = Mi; er.N = C;
+    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.bo; er.mul = g2; er.ldm = C; er.save = ob; er.lds = C; er.M = Mi; er.N = C; er.drop = drop;
     { ProfScope ps_("TriMul.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* in, float* g, const float* mask, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)M, CH = 2 * Hc, NP = 2 * CH, KC = NP + C;
-    { ProfScope ps_("TriMul.backward.trimul_bwd_out_kernel", st); launch_pdl(trimul_bwd_out_kernel, dim3(ew_grid(M * C / 4, 256)), dim3(256), 0, st, reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2), reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C); }
+    { ProfScope ps_("TriMul.backward.trimul_bwd_out_kernel", st); launch_pdl(trimul_bwd_out_kernel, dim3(ew_grid(M * C / 4, 256)), dim3(256), 0, st, reinterpret_cast<const float4*>(g), reinterpret_cast<const uint2*>(ob), reinterpret_cast<const uint2*>(g2), reinterpret_cast<uint2*>(S->d_o), S->big, KC, NP, M, C, drop); }
     EpiStore ey; ey.out = S->dy; ey.ldo = Hc; ey.M = Mi; ey.N = Hc;
     { ProfScope ps_("TriMul.backward.gemm.gb_o", st); run_gemm(b.gb_o, ey, st); }
     { ProfScope ps_("TriMul.backward.cln_bwd_c", st); cln_bwd_c(t, b.cn, S->dy, S->dt, st); }
@@ -313,6 +314,7 @@ struct AttnW {
 // modules.TriangleAttention (modules.py:675-734); `ending` = per_column orientation.
 struct TriAttn {
   int n = 0, C = 0, H = 0, D = 0;
+  DropSite drop;  // dropout scales of this module's output for the block about to run (set by the stack; null: none)
   bool ending = false;
   long M = 0;
   struct W {
@@ -379,13 +381,13 @@ struct TriAttn {
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
     { ProfScope ps_("TriAttn.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
     { ProfScope ps_("TriAttn.forward.attn_fwd", st); attn_fwd(plan, st); }
-    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.a.bo; er.M = Mi; er.N = C;
+    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.a.bo; er.M = Mi; er.N = C; er.drop = drop;
     { ProfScope ps_("TriAttn.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* in, float* g, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)M, HD = H * D;
-    { ProfScope ps_("TriAttn.backward.cvt_f32_bf16", st); cvt_f32_bf16(g, S->dy, M * C, st); }
+    { ProfScope ps_("TriAttn.backward.cvt_f32_bf16", st); cvt_drop_f32_bf16(g, S->dy, M, C, drop, st); }
     // back through the output projection, with the gating adjoint and delta = rowsum(dO * O) in the epilogue
     EpiAttnPrep e; e.o = o; e.qkvg = qkvg; e.ld = 4L * HD; e.d_o = S->d_o; e.d_qkvg = S->big; e.delta = S->delta;
     e.row_b = plan.args.row_b; e.row_p = plan.args.row_p; e.Nres = n; e.H = H; e.D = D; e.M = Mi; e.N = HD;
@@ -405,6 +407,7 @@ struct TriAttn {
 // modules.MSARowAttentionWithPairBias (modules.py:500-563).  The gradient lands on the msa AND the pair stream.
 struct MsaRow {
   int n = 0, S_ = 0, Cm = 0, Cz = 0, H = 0, D = 0, Dreal = 0;  // D: head width the kernels use (>= 16), Dreal: the model's
+  DropSite drop;  // dropout scales of this module's output for the block about to run (set by the stack; null: none)
   long Mm = 0, Mp = 0;
   struct W {
     LnW qn, fn;
@@ -460,13 +463,13 @@ struct MsaRow {
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
     { ProfScope ps_("MsaRow.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
     { ProfScope ps_("MsaRow.forward.attn_fwd", st); attn_fwd(plan, st); }
-    EpiResidual er; er.res_in = msa_in; er.res_out = msa_out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm;
+    EpiResidual er; er.res_in = msa_in; er.res_out = msa_out; er.ld = Cm; er.bias = b.a.bo; er.M = Mi; er.N = Cm; er.drop = drop;
     { ProfScope ps_("MsaRow.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
   void backward(int blk, const float* msa_in, const float* pair, float* g_msa, float* g_pair, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm, HD = H * D;
-    { ProfScope ps_("MsaRow.backward.cvt_f32_bf16", st); cvt_f32_bf16(g_msa, S->dy, Mm * Cm, st); }
+    { ProfScope ps_("MsaRow.backward.cvt_f32_bf16", st); cvt_drop_f32_bf16(g_msa, S->dy, Mm, Cm, drop, st); }
     EpiAttnPrep e; e.o = o; e.qkvg = qkvg; e.ld = 4L * HD; e.d_o = S->d_o; e.d_qkvg = S->big; e.delta = S->delta;
     e.row_b = n; e.row_p = 1; e.Nres = n; e.H = H; e.D = D; e.M = Mi; e.N = HD;
     { ProfScope ps_("MsaRow.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }

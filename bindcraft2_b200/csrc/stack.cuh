@@ -66,6 +66,12 @@ struct EvoStack {
   int opm_prepared = -1;  // block whose outer-product operands were issued ahead on the side stream (ev[5] marks them done)
   const float *blk_p_in = nullptr, *blk_m_out = nullptr;  // opm_first = false: operands the block's backward reads again
   bool tail_pending = false;  // a backward tail (row attention + outer product mean of a block) is in flight on `side`
+  // Dropout (reference sites and rates: native/block.cuh:70-75): per block five tables of scales, [N][Cz] for tri-mul
+  // out / in and the two triangle attentions, [N][Cm] for the MSA row attention; filled at the start of a call from the
+  // caller's {seed, enabled} words, allocated on the first call that asks for dropout.
+  float* drop_tab = nullptr;
+  long drop_per_block = 0;
+  bool dropping = false;  // the call in progress applies the tables
   std::vector<float*> keep32;  // fp32 block inputs beside the caller's bf16 save-set (allocated on the first save)
   size_t weight_bytes = 0;
 
@@ -146,6 +152,39 @@ struct EvoStack {
     }
   }
 
+  void prepare_dropout(bool dropout, const uint32_t* seed, cudaStream_t st) {
+    dropping = dropout && seed != nullptr;
+    if (!dropping) {
+      tmo.drop = tmi.drop = tas.drop = tae.drop = row.drop = DropSite{};
+      return;
+    }
+    DropTableArgs a{};
+    a.blocks = cfg.depth; a.n = cfg.N; a.sites = 5; a.seed = seed;
+    const int widths[5] = {cfg.Cz, cfg.Cz, cfg.Cz, cfg.Cz, cfg.Cm};
+    const int mods[5] = {2, 3, 4, 5, 1};  // tri-mul out, in, attention start, end, MSA row
+    long per = 0;
+    for (int t = 0; t < 5; ++t) {
+      a.width[t] = widths[t]; a.mod[t] = mods[t]; a.rate[t] = t == 4 ? 0.15f : 0.25f;
+      per += (long)cfg.N * widths[t];
+    }
+    a.per_block = drop_per_block = per;
+    if (!drop_tab) drop_tab = A.alloc<float>(per * cfg.depth);
+    a.tab = drop_tab;
+    launch_counter()++;
+    drop_tables_kernel<<<ew_grid(per * cfg.depth, 256), 256, 0, st>>>(a);
+  }
+  // point the modules at block b's tables
+  void set_drop_sites(int b) {
+    if (!dropping) return;
+    float* t = drop_tab + (long)b * drop_per_block;
+    const long np = (long)cfg.N * cfg.Cz;
+    tmo.drop = DropSite{t, cfg.N, 0};
+    tmi.drop = DropSite{t + np, cfg.N, 0};
+    tas.drop = DropSite{t + 2 * np, cfg.N, 0};
+    tae.drop = DropSite{t + 3 * np, cfg.N, 1};
+    row.drop = DropSite{t + 4 * np, cfg.N, 0};
+  }
+
   // Fork/join helpers.  The MSA track (a few dozen kernels over S*N rows, each a handful of CTAs) runs on a side stream
   // beside the pair track, which owns the machine-filling kernels; the two tracks have disjoint scratch sets.
   void fork(cudaStream_t from, cudaStream_t to, cudaEvent_t ev) {
@@ -161,6 +200,7 @@ struct EvoStack {
     const size_t bp = (size_t)Mp * cfg.Cz * 4, bm = (size_t)Mm * cfg.Cm * 4;
     cudaStream_t ms = side ? side : st;
     P[1] = P1[b & 1];
+    set_drop_sites(b);
     if (cfg.pair_only) {
       // The reference's extra-MSA path (native/block.cuh `pair_only`; bindcraft/af/native.py:1131-1193): the MSA side is
       // not run (its mask is all zeros in a design run) and only the constant of the outer product mean reaches the pair.
@@ -241,6 +281,7 @@ struct EvoStack {
     const bool two = side && !cfg.pair_only;
     cudaStream_t ms = two ? side : st;
     P[1] = P1[b & 1];
+    set_drop_sites(b);
     if (!cfg.opm_first && !cfg.pair_only) {  // reverse of the monomer order, on the caller's stream
       if (en & 256) ptrans.backward(b, P[5], g_pair, st);
       if (en & 128) tae.backward(b, P[4], g_pair, st);
@@ -290,8 +331,10 @@ struct EvoStack {
 
   // psave: [depth][N][N][Cz] bf16, msave: [depth][S][N][Cm] fp32 (null when save == false).
   void forward(const float* pair, const float* msa, const float* pm, const float* mm, float* pair_out, float* msa_out,
-               bf16* psave, float* msave, bool own_save, cudaStream_t st) {
+               bf16* psave, float* msave, bool own_save, cudaStream_t st, bool dropout = false,
+               const uint32_t* seed = nullptr) {
     set_masks(pm, mm, st);
+    prepare_dropout(dropout, seed, st);
     const long np = Mp * cfg.Cz, nm = Mm * cfg.Cm;
     const float *pc = pair, *mc = msa;
     for (int i = 0; i < cfg.depth; ++i) {
@@ -318,8 +361,10 @@ struct EvoStack {
   }
 
   void backward(const float* ct_pair, const float* ct_msa, const float* pm, const float* mm, const bf16* psave,
-                const float* msave, float* dpair, float* dmsa, bool own_save, cudaStream_t st) {
+                const float* msave, float* dpair, float* dmsa, bool own_save, cudaStream_t st, bool dropout = false,
+                const uint32_t* seed = nullptr) {
     set_masks(pm, mm, st);
+    prepare_dropout(dropout, seed, st);
     const long np = Mp * cfg.Cz, nm = Mm * cfg.Cm;
     if (dpair != ct_pair) BC2_CUDA(cudaMemcpyAsync(dpair, ct_pair, np * 4, cudaMemcpyDeviceToDevice, st));
     if (dmsa != ct_msa) BC2_CUDA(cudaMemcpyAsync(dmsa, ct_msa, nm * 4, cudaMemcpyDeviceToDevice, st));
@@ -355,6 +400,33 @@ struct TplStack {
   TriAttn tas, tae;
   float* P[6] = {nullptr};  // block input and the stream after each of the first four steps
   float *pair_mask = nullptr, *bo[2] = {nullptr, nullptr};
+  float* drop_tab = nullptr;  // dropout scales, [depth][4 sites][N][C] (reference: native/tplblock.cuh:55-66, ids 11..14, rate 0.25)
+  bool dropping = false;
+
+  void prepare_dropout(bool dropout, const uint32_t* seed, cudaStream_t st) {
+    dropping = dropout && seed != nullptr;
+    if (!dropping) {
+      tmo.drop = tmi.drop = tas.drop = tae.drop = DropSite{};
+      return;
+    }
+    DropTableArgs a{};
+    a.blocks = depth; a.n = N; a.sites = 4; a.seed = seed;
+    for (int t = 0; t < 4; ++t) { a.width[t] = C; a.mod[t] = 11 + t; a.rate[t] = 0.25f; }
+    a.per_block = 4L * N * C;
+    if (!drop_tab) drop_tab = A.alloc<float>(a.per_block * depth);
+    a.tab = drop_tab;
+    launch_counter()++;
+    drop_tables_kernel<<<ew_grid(a.per_block * depth, 256), 256, 0, st>>>(a);
+  }
+  void set_drop_sites(int b) {
+    if (!dropping) return;
+    const long np = (long)N * C;
+    float* t = drop_tab + (long)b * 4 * np;
+    tmo.drop = DropSite{t, N, 0};
+    tmi.drop = DropSite{t + np, N, 0};
+    tas.drop = DropSite{t + 2 * np, N, 0};
+    tae.drop = DropSite{t + 3 * np, N, 1};
+  }
 
   TplStack(int n, int depth_, const std::string& weights_dir) : N(n), depth(depth_) {
     BC2_CHECK(n > 0 && n % 32 == 0, "N must be a positive multiple of 32 (the caller pads and masks)");
@@ -381,6 +453,7 @@ struct TplStack {
     BC2_CUDA(cudaDeviceSynchronize());
   }
   void block_forward(int b, const float* in, float* out, cudaStream_t st, bool tail = true) {
+    set_drop_sites(b);
     tmo.forward(b, in, P[1], pair_mask, st);
     tmi.forward(b, P[1], P[2], pair_mask, st);
     tas.forward(b, P[2], P[3], st);
@@ -388,13 +461,16 @@ struct TplStack {
     ptrans.forward(b, P[4], out, st, tail);
   }
   void block_backward(int b, const float* in, float* g, cudaStream_t st) {
+    set_drop_sites(b);
     ptrans.backward(b, P[4], g, st);
     tae.backward(b, P[3], g, st);
     tas.backward(b, P[2], g, st);
     tmi.backward(b, P[1], g, pair_mask, st);
     tmo.backward(b, in, g, pair_mask, st);
   }
-  void forward(const float* pair, const float* pm, float* out, bf16* save, cudaStream_t st) {
+  void forward(const float* pair, const float* pm, float* out, bf16* save, cudaStream_t st, bool dropout = false,
+               const uint32_t* seed = nullptr) {
+    prepare_dropout(dropout, seed, st);
     BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, Mp * 4, cudaMemcpyDeviceToDevice, st));
     const long np = Mp * C;
     if (save) cvt_f32_bf16(pair, save, np, st);
@@ -407,7 +483,8 @@ struct TplStack {
   }
   // in32: the stack input in fp32 when the caller still has it (then `save` is not read)
   void backward(const float* ct, const float* pm, const bf16* save, float* dpair, cudaStream_t st,
-                const float* in32 = nullptr) {
+                const float* in32 = nullptr, bool dropout = false, const uint32_t* seed = nullptr) {
+    prepare_dropout(dropout, seed, st);
     BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, Mp * 4, cudaMemcpyDeviceToDevice, st));
     const long np = Mp * C;
     if (dpair != ct) BC2_CUDA(cudaMemcpyAsync(dpair, ct, np * 4, cudaMemcpyDeviceToDevice, st));
@@ -478,9 +555,10 @@ struct TplEmbed {
     EpiResidual e; e.res_in = act_const; e.res_out = act0; e.ld = C; e.bias = b8; e.M = (int)M; e.N = C;
     run_gemm(g_8, e, st);
   }
-  void forward(const float* query, const float* act_const, const float* pm, float* out, bf16* save, cudaStream_t st) {
+  void forward(const float* query, const float* act_const, const float* pm, float* out, bf16* save, cudaStream_t st,
+               bool dropout = false, const uint32_t* seed = nullptr) {
     embed_input(query, act_const, st);
-    stack.forward(act0, pm, act1, save, st);
+    stack.forward(act0, pm, act1, save, st, dropout, seed);
     LnArgs l; l.x = act1; l.scale = on.scale; l.offset = on.offset; l.y = y64; l.ldy = C; l.relu = 1; l.M = (int)M;
     ln_fwd<64>(l, st);
     EpiResidual e; e.res_in = nullptr; e.res_out = out; e.ld = CQ; e.bias = bout; e.M = (int)M; e.N = CQ;
@@ -488,9 +566,9 @@ struct TplEmbed {
   }
   // Pure: everything is rebuilt from the operands (query, act_const); `save` is accepted for the boundary's sake.
   void backward(const float* ct, const float* query, const float* act_const, const float* pm, float* dquery,
-                cudaStream_t st) {
+                cudaStream_t st, bool dropout = false, const uint32_t* seed = nullptr) {
     embed_input(query, act_const, st);
-    stack.forward(act0, pm, act1, nullptr, st);
+    stack.forward(act0, pm, act1, nullptr, st, dropout, seed);
     LnArgs l; l.x = act1; l.scale = on.scale; l.offset = on.offset; l.y = y64; l.ldy = C; l.relu = 1; l.M = (int)M;
     ln_fwd<64>(l, st);
     cvt_f32_bf16(ct, ctb, M * CQ, st);
@@ -498,7 +576,7 @@ struct TplEmbed {
     run_gemm(gb_out, e, st);
     LnBwdArgs lb; lb.x = act1; lb.scale = on.scale; lb.dy = d64; lb.ldy = C; lb.g_in = nullptr; lb.g_out = g64; lb.M = (int)M;
     ln_bwd<64>(lb, st);
-    stack.backward(g64, pm, nullptr, g64, st, act0);
+    stack.backward(g64, pm, nullptr, g64, st, act0, dropout, seed);
     cvt_f32_bf16(g64, d64, M * C, st);
     EpiStore e2; e2.out = x128; e2.ldo = CQ; e2.M = (int)M; e2.N = CQ;
     run_gemm(gb_8, e2, st);

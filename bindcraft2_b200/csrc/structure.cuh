@@ -71,7 +71,7 @@ ln_f32_kernel(const float* __restrict__ x, const float* __restrict__ scale, cons
 template <int C>
 __global__ void __launch_bounds__(256)
 ln_f32_bwd_kernel(const float* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ dy, float* __restrict__ dx,
-                  long M, const float* __restrict__ w2d, const float* __restrict__ db2d) {
+                  long M, const float* __restrict__ w2d, const float* __restrict__ db2d, const float* __restrict__ drop) {
   pdl_trigger();
   pdl_wait();
   constexpr int V = C / 32;
@@ -105,7 +105,11 @@ ln_f32_bwd_kernel(const float* __restrict__ x, const float* __restrict__ scale, 
   s1 = warp_sum(s1) * (1.f / C);
   s2 = warp_sum(s2) * (1.f / C);
 #pragma unroll
-  for (int i = 0; i < V; ++i) dx[m * C + i * 32 + lane] = rstd * (d[i] - s1 - v[i] * s2);
+  for (int i = 0; i < V; ++i) {
+    const long idx = m * C + i * 32 + lane;
+    const float g = rstd * (d[i] - s1 - v[i] * s2);
+    dx[idx] = drop ? g * drop[idx] : g;  // the normalised tensor was a dropped one: its cotangent takes the same scales
+  }
 }
 
 // ------------------------------------------------------------------------------------------- Linear (fp32)
@@ -114,6 +118,7 @@ struct LinArgs {
   const float* X = nullptr; const float* W = nullptr; const float* bias = nullptr;
   const float* R = nullptr;     // residual added after the activation, or null
   const float* G = nullptr;     // ReLU gate of the backward: output multiplied by (G > 0), or null
+  const float* D = nullptr;     // elementwise dropout scales applied to (result + residual), or null
   float* Y = nullptr;
   int M = 0, N = 0, K = 0, relu = 0, accumulate = 0;  // accumulate: Y += result
   int relu_in = 0;                                    // the input is max(X, 0)
@@ -165,6 +170,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(LinArgs a) {
       const long idx = (long)m * a.N + n;
       if (a.R) v += a.R[idx];
       if (a.G) v = a.G[idx] > 0.f ? v : 0.f;
+      if (a.D) v *= a.D[idx];
       a.Y[idx] = a.accumulate ? a.Y[idx] + v : v;
     }
   }
@@ -224,6 +230,7 @@ __global__ void __launch_bounds__(256) linear_f32_small_kernel(LinArgs a) {
     const long idx = (long)m * a.N + n;
     if (a.R) v += a.R[idx];
     if (a.G) v = a.G[idx] > 0.f ? v : 0.f;
+    if (a.D) v *= a.D[idx];
     a.Y[idx] = a.accumulate ? a.Y[idx] + v : v;
   }
 }

@@ -5,6 +5,7 @@
 #include <string>
 #include <vector>
 
+#include "ew.cuh"
 #include "structure_bwd.cuh"
 
 namespace bc2 {
@@ -147,15 +148,34 @@ struct StructureCore {
   }
   template <int C>
   void ln_bwd(const float* x, const float* sc, const float* dy, float* dx, long M, cudaStream_t st, const float* w = nullptr,
-              const float* db = nullptr) {
-    launch_pdl_c(4, ln_f32_bwd_kernel<C>, dim3((unsigned)cdiv(M, 8L)), dim3(256), 0, st, x, sc, dy, dx, M, w, db);
+              const float* db = nullptr, const float* drop = nullptr) {
+    launch_pdl_c(4, ln_f32_bwd_kernel<C>, dim3((unsigned)cdiv(M, 8L)), dim3(256), 0, st, x, sc, dy, dx, M, w, db, drop);
   }
   void lin(const float* X, const float* W, const float* b, float* Y, int K, int Nn, cudaStream_t st, int relu = 0,
-           const float* R = nullptr, const float* G = nullptr, int accumulate = 0) {
+           const float* R = nullptr, const float* G = nullptr, int accumulate = 0, const float* D = nullptr) {
     LinArgs a; a.X = X; a.W = W; a.bias = b; a.Y = Y; a.M = N; a.N = Nn; a.K = K; a.relu = relu; a.R = R; a.G = G;
-    a.accumulate = accumulate;
+    a.accumulate = accumulate; a.D = D;
     linear_f32(a, st);
   }
+  // Dropout of the fold iterations (reference: folding_multimer.py:408-412,428,449; native masks native/foldit.cuh:152-166,
+  // 308-326): the WHOLE activation is dropped after the attention residual (module id 21) and after the transition
+  // residual (id 22), elementwise (mask index = flat [N, 384] index), rate 0.1, iteration l drawing with depth index l.
+  // Tables [L][2][N*384] of scales are filled per call from the caller's {seed, enabled} words; null seed: no dropout.
+  float* drop_tab = nullptr;
+  bool dropping = false;
+  void prepare_dropout(const uint32_t* seed, cudaStream_t st) {
+    dropping = seed != nullptr;
+    if (!dropping) return;
+    DropTableArgs a{};
+    a.blocks = L; a.n = N; a.sites = 2; a.seed = seed;
+    for (int t = 0; t < 2; ++t) { a.width[t] = CS; a.mod[t] = 21 + t; a.rate[t] = 0.1f; }
+    a.per_block = 2L * N * CS;
+    if (!drop_tab) drop_tab = A.alloc<float>(a.per_block * L);
+    a.tab = drop_tab;
+    launch_counter()++;
+    drop_tables_kernel<<<ew_grid(a.per_block * L, 256), 256, 0, st>>>(a);
+  }
+  const float* drop_site(int l, int site) const { return dropping ? drop_tab + ((long)l * 2 + site) * N * CS : nullptr; }
 
   // seq_mask [N] -> m_i m_j [N][N] in this object's buffer (the reference's caller passes that product)
   const float* outer_mask(const float* seq_mask, cudaStream_t st) {
@@ -164,8 +184,10 @@ struct StructureCore {
   }
 
   // mask: [N][N] pair mask (m_i m_j)
-  void forward(const float* single, const float* pair, const float* mask, float* act_out, float* rig_out, cudaStream_t st) {
+  void forward(const float* single, const float* pair, const float* mask, float* act_out, float* rig_out, cudaStream_t st,
+               const uint32_t* seed = nullptr) {
     const long n2 = (long)N * N;
+    prepare_dropout(seed, st);
     ln<CS>(single, ln_s_scale, ln_s_off, single_ln, N, st);
     lin(single_ln, init.w, init.b, act_in[0], CS, CS, st);
     ln<CZ>(pair, ln_p_scale, ln_p_off, pair_ln, n2, st, w2d, b2d_bias, b2d);
@@ -179,11 +201,11 @@ struct StructureCore {
       lin(act_in[l], proj.w, proj.b, projv[l], CS, NPROJ, st);
       launch_pdl_c(4, ipa_points_kernel, dim3(N), dim3(H * GP), 0, st, projv[l], rig[l], gpts[l]);
       launch_pdl_c(4, ipa_attn_fwd_kernel, dim3(N), dim3(256), attn_smem / 2, st, projv[l], gpts[l], rig[l], pair_ln, b2d, mask, pw, attn[l], fin[l], N);
-      lin(fin[l], out.w, out.b, act1[l], NFINAL, CS, st, 0, act_in[l]);
+      lin(fin[l], out.w, out.b, act1[l], NFINAL, CS, st, 0, act_in[l], nullptr, 0, drop_site(l, 0));
       ln<CS>(act1[l], ln_a_scale, ln_a_off, ln1[l], N, st);
       lin(ln1[l], t1.w, t1.b, h1[l], CS, CS, st, 1);
       lin(h1[l], t2.w, t2.b, h2[l], CS, CS, st, 1);
-      lin(h2[l], t3.w, t3.b, act2[l], CS, CS, st, 0, ln1[l]);
+      lin(h2[l], t3.w, t3.b, act2[l], CS, CS, st, 0, ln1[l], nullptr, 0, drop_site(l, 1));
       ln<CS>(act2[l], ln_t_scale, ln_t_off, act_in[l + 1], N, st);
       lin(act_in[l + 1], quat.w, quat.b, upd[l], CS, 6, st);
       launch_pdl_c(4, rigid_update_kernel, dim3(cdiv(N, 128)), dim3(128), 0, st, rig[l], upd[l], rig[l + 1], N);
@@ -209,11 +231,11 @@ struct StructureCore {
       BC2_CUDA(cudaMemsetAsync(g_in, 0, (size_t)N * 12 * 4, st));
       launch_pdl_c(4, rigid_update_bwd_kernel, dim3(cdiv(N, 128)), dim3(128), 0, st, rig[l], upd[l], g_out, g_in, d_upd, N);
       lin(d_upd, quat.wt, nullptr, g_act, 6, CS, st, 0, nullptr, nullptr, 1);         // g_act += d_upd Wq^T
-      ln_bwd<CS>(act2[l], ln_t_scale, g_act, dA, N, st);                               // dA = d(act2)
+      ln_bwd<CS>(act2[l], ln_t_scale, g_act, dA, N, st, nullptr, nullptr, drop_site(l, 1));  // dA = d(act2 before its dropout)
       lin(dA, t3.wt, nullptr, tA, CS, CS, st, 0, nullptr, h2[l]);                      // d(h2 pre-relu)
       lin(tA, t2.wt, nullptr, tB, CS, CS, st, 0, nullptr, h1[l]);                      // d(h1 pre-relu)
       lin(tB, t1.wt, nullptr, tA, CS, CS, st, 0, dA);                                  // d(ln1) = dA + . W1^T
-      ln_bwd<CS>(act1[l], ln_a_scale, tA, dB, N, st);                                  // dB = d(act1)
+      ln_bwd<CS>(act1[l], ln_a_scale, tA, dB, N, st, nullptr, nullptr, drop_site(l, 0));   // dB = d(act1 before its dropout)
       lin(dB, out.wt, nullptr, d_fin, CS, NFINAL, st);                                 // d(final)
       launch_pdl_c(4, ipa_bwd_query_kernel, dim3(N), dim3(256), attn_smem, st, projv[l], gpts[l], rig[l], pair_ln, attn[l], fin[l], d_fin, pw, dlogit,
                                                      db2d, dpair_ln, dopg, d_proj, g_in, N);

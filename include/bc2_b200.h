@@ -27,7 +27,10 @@ extern "C" {
  * `native_evoformer_fwd`.
  *   pair      f32 [N,N,128]      msa      f32 [S,N,256]
  *   pair_mask f32 [N,N]          msa_mask f32 [S,N]
- *   seed      u32 [2] = {seed, dropout_enabled} (device; accepted, dropout itself is not applied)
+ *   seed      u32 [2] = {seed, dropout_enabled} (device).  With the attribute dropout != 0 and the enable word set, the
+ *             five dropout sites of each block scale their module output by the reference's counter-hash masks
+ *             (native/common.cuh:944-1030, ids and rates native/block.cuh:70-75), forward and backward alike; the enable
+ *             word is read on the device, so flipping it costs nothing.
  *   attrs     depth, save, pair_only, own_save, opm_first, dropout, weights_dir
  *   results   pair_out f32 [N,N,128], msa_out f32 [S,N,256],
  *             psave bf16 [slots,N,N,128], msave f32 [slots,S,N,256]   (slots = bc2 native_save_slots_probe(depth, N);
@@ -124,8 +127,10 @@ int bc2_extra_msa_stack_bwd(void* stream, const float* ct_pair, const float* ct_
 /* Replaces StructureHeadsFwd (native/ffi.cu:1009-1025, FFI target `native_post_trunk_fwd`): the structure module with
  * its side-chain atoms, and the four output heads.
  *   single f32 [N,384], pair f32 [N,N,128], mask f32 [N,N] (seq_mask (x) seq_mask, the IPA reads mask[q*N+k]),
- *   aatype f32 [N] (residue type 0..20 as float, as the reference passes it), seed u32 [2] (accepted, unused: no dropout
- *   in this call), depth = 8 fold iterations, weights_dir = the post-trunk manifest including const/default_frame,
+ *   aatype f32 [N] (residue type 0..20 as float, as the reference passes it), seed u32 [2] = {seed, enabled} or null:
+ *   with the enable word set, each fold iteration drops its activation after the attention residual and after the
+ *   transition residual (elementwise, rate 0.1, the reference's hash masks: native/foldit.cuh:152-166,308-326),
+ *   depth = 8 fold iterations, weights_dir = the post-trunk manifest including const/default_frame,
  *   const/atom14_to_group, const/atom14_lit_pos, const/atom14_mask (bindcraft/af/native.py:339-444).
  *   -> atom14 f32 [N,14,3] (Angstrom), dgram f32 [N,N,64] (symmetrised distogram logits), pae f32 [N,N,64],
  *      plddt f32 [N,50], expres f32 [N,37].  No padding requirement on N. */

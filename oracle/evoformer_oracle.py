@@ -163,20 +163,72 @@ def triangle_attention(p: Params, pair, pair_mask, per_column: bool):
     return out
 
 
+# ----------------------------------------------------------------------------- dropout masks
+# The reference's native path does not reproduce JAX's threefry masks; it regenerates, in forward and backward alike, a
+# counter hash of (seed, block index, module id, mask index) -- native/common.cuh:944-981 (dropHash, dropScale) -- with
+# the mask index (unit * C + channel): unit = the column j of pair position (i, j), or the residue of an msa position,
+# for the sites whose mask is shared over rows (tri-mul out / in, starting-node attention, MSA row attention;
+# modules.py:61-72 broadcast_dim 0), and the row i for the ending-node attention (shared over columns);
+# native/common.cuh:983-1030.  Rates and module ids: native/block.cuh:70-75 (0.15 for the MSA row attention = id 1,
+# 0.25 for tri-mul out/in = 2/3 and the attentions start/end = 4/5); template stack ids 11..14, native/tplblock.cuh:65-66.
+DROP_SITES = {'msa_row_attention_with_pair_bias': (1, 0.15), 'triangle_multiplication_outgoing': (2, 0.25),
+              'triangle_multiplication_incoming': (3, 0.25), 'triangle_attention_starting_node': (4, 0.25),
+              'triangle_attention_ending_node': (5, 0.25)}
+
+
+def dropout_hash(seed, depth, mod, idx):
+    """uint32 counter hash of native/common.cuh:944-955; ``idx`` may be an array."""
+    import numpy as np
+    u = np.uint32
+    with np.errstate(over='ignore'):
+        h = np.asarray(u(seed) * u(0x9e3779b9), dtype=np.uint32) + np.zeros_like(np.asarray(idx, dtype=np.uint32))
+        for v, k in ((u(depth), u(0x85ebca6b)), (u(mod), u(0xc2b2ae35)), (np.asarray(idx, dtype=np.uint32), u(0x27d4eb2f))):
+            h = h ^ (v + k + (h << u(6)) + (h >> u(2)))
+        h = h ^ (h >> u(15))
+        h = h * u(0x2c1b3c6d)
+        h = h ^ (h >> u(12))
+        h = h * u(0x297a2d39)
+        h = h ^ (h >> u(15))
+    return h
+
+
+def dropout_scale_table(seed, depth, mod, units, channels, rate):
+    """[units, channels] float32 table of keep ? 1/keep_rate : 0 (native/common.cuh:971-981), fp32 arithmetic as there."""
+    import numpy as np
+    idx = np.arange(units * channels, dtype=np.uint32)
+    keep = np.float32(1.0) - np.float32(rate)
+    uu = dropout_hash(seed, depth, mod, idx).astype(np.float32) * np.float32(2.3283064365386963e-10)
+    tab = np.where(uu < keep, np.float32(1.0) / keep, np.float32(0.0)).astype(np.float32)
+    return torch.from_numpy(tab.reshape(units, channels))
+
+
+def block_dropout_masks(seed, depth_index, n, cz, cm, ids=DROP_SITES):
+    """Broadcastable mask tensors of one block: [1,N,C] for the row-shared sites, [N,1,C] for the ending node."""
+    out = {}
+    for name, (mod, rate) in ids.items():
+        c = cm if name.startswith('msa_row') else cz
+        t = dropout_scale_table(seed, depth_index, mod, n, c, rate)
+        out[name] = t[:, None, :] if name.endswith('ending_node') else t[None, :, :]
+    return out
+
+
 STEPS = ('outer_product_mean', 'msa_row_attention_with_pair_bias', 'msa_column_attention', 'msa_transition',
          'triangle_multiplication_outgoing', 'triangle_multiplication_incoming', 'triangle_attention_starting_node',
          'triangle_attention_ending_node', 'pair_transition')
 
 
-def evoformer_iteration(p: Params, msa, pair, msa_mask, pair_mask, is_extra_msa=False, opm_first=True, steps=None):
+def evoformer_iteration(p: Params, msa, pair, msa_mask, pair_mask, is_extra_msa=False, opm_first=True, steps=None,
+                        drop=None):
     """modules.EvoformerIteration.__call__ (modules.py:1266-1391), dropout off, so dropout_wrapper
     (modules.py:46-76) reduces to ``act + module(act)``.  Multimer order: OPM first (config.py:411-418)."""
     on = (lambda name: True) if steps is None else (lambda name: name in steps)
+    dm = (lambda name: 1.0) if drop is None else (lambda name: drop[name].to(pair.dtype))  # dropout_wrapper, modules.py:46-76
     opm = lambda: outer_product_mean(sub(p, 'outer_product_mean'), msa, msa_mask)
     if opm_first and on('outer_product_mean'):
         pair = pair + opm()
     if on('msa_row_attention_with_pair_bias'):
-        msa = msa + msa_row_attention_with_pair_bias(sub(p, 'msa_row_attention_with_pair_bias'), msa, msa_mask, pair)
+        msa = msa + dm('msa_row_attention_with_pair_bias') * msa_row_attention_with_pair_bias(
+            sub(p, 'msa_row_attention_with_pair_bias'), msa, msa_mask, pair)
     if on('msa_column_attention'):
         if is_extra_msa:
             msa = msa + msa_column_global_attention(sub(p, 'msa_column_global_attention'), msa, msa_mask)
@@ -187,79 +239,101 @@ def evoformer_iteration(p: Params, msa, pair, msa_mask, pair_mask, is_extra_msa=
     if not opm_first and on('outer_product_mean'):
         pair = pair + opm()
     if on('triangle_multiplication_outgoing'):
-        pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_outgoing'), pair, pair_mask, True)
+        pair = pair + dm('triangle_multiplication_outgoing') * triangle_multiplication(
+            sub(p, 'triangle_multiplication_outgoing'), pair, pair_mask, True)
     if on('triangle_multiplication_incoming'):
-        pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_incoming'), pair, pair_mask, False)
+        pair = pair + dm('triangle_multiplication_incoming') * triangle_multiplication(
+            sub(p, 'triangle_multiplication_incoming'), pair, pair_mask, False)
     if on('triangle_attention_starting_node'):
-        pair = pair + triangle_attention(sub(p, 'triangle_attention_starting_node'), pair, pair_mask, False)
+        pair = pair + dm('triangle_attention_starting_node') * triangle_attention(
+            sub(p, 'triangle_attention_starting_node'), pair, pair_mask, False)
     if on('triangle_attention_ending_node'):
-        pair = pair + triangle_attention(sub(p, 'triangle_attention_ending_node'), pair, pair_mask, True)
+        pair = pair + dm('triangle_attention_ending_node') * triangle_attention(
+            sub(p, 'triangle_attention_ending_node'), pair, pair_mask, True)
     if on('pair_transition'):
         pair = pair + transition(sub(p, 'pair_transition'), pair)
     return msa, pair
 
 
-def evoformer_stack(p: Params, msa, pair, msa_mask, pair_mask, depth, is_extra_msa=False, opm_first=True, steps=None):
+def evoformer_stack(p: Params, msa, pair, msa_mask, pair_mask, depth, is_extra_msa=False, opm_first=True, steps=None,
+                    dropout_seed=None):
     """The layer_stack of EvoformerIteration (modules_multimer.py:619-679; extra stack :547-603).
-    ``p`` holds ``block{b}/...`` entries, one independent weight set per block."""
+    ``p`` holds ``block{b}/...`` entries, one independent weight set per block.  ``dropout_seed``: apply the native
+    path's hash masks of that seed (block b draws with depth index b, native/stack.cuh:877)."""
     for b in range(depth):
+        drop = None if dropout_seed is None else block_dropout_masks(dropout_seed, b, pair.shape[0], pair.shape[-1],
+                                                                      msa.shape[-1])
         msa, pair = evoformer_iteration(sub(p, f'block{b}'), msa, pair, msa_mask, pair_mask,
-                                        is_extra_msa=is_extra_msa, opm_first=opm_first, steps=steps)
+                                        is_extra_msa=is_extra_msa, opm_first=opm_first, steps=steps, drop=drop)
     return msa, pair
 
 
-def template_pair_iteration(p: Params, pair, pair_mask):
+TPL_DROP_SITES = {'triangle_multiplication_outgoing': (11, 0.25), 'triangle_multiplication_incoming': (12, 0.25),
+                  'triangle_attention_starting_node': (13, 0.25), 'triangle_attention_ending_node': (14, 0.25)}
+
+
+def template_pair_iteration(p: Params, pair, pair_mask, drop=None):
     """modules_multimer.TemplateEmbeddingIteration.__call__ (modules_multimer.py:1008-1077): tri-mul out,
-    tri-mul in, tri-attn start, tri-attn end, pair transition, each residual, dropout off."""
-    pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_outgoing'), pair, pair_mask, True)
-    pair = pair + triangle_multiplication(sub(p, 'triangle_multiplication_incoming'), pair, pair_mask, False)
-    pair = pair + triangle_attention(sub(p, 'triangle_attention_starting_node'), pair, pair_mask, False)
-    pair = pair + triangle_attention(sub(p, 'triangle_attention_ending_node'), pair, pair_mask, True)
+    tri-mul in, tri-attn start, tri-attn end, pair transition, each residual; ``drop``: dropout scale masks per site."""
+    dm = (lambda name: 1.0) if drop is None else (lambda name: drop[name].to(pair.dtype))
+    pair = pair + dm('triangle_multiplication_outgoing') * triangle_multiplication(
+        sub(p, 'triangle_multiplication_outgoing'), pair, pair_mask, True)
+    pair = pair + dm('triangle_multiplication_incoming') * triangle_multiplication(
+        sub(p, 'triangle_multiplication_incoming'), pair, pair_mask, False)
+    pair = pair + dm('triangle_attention_starting_node') * triangle_attention(
+        sub(p, 'triangle_attention_starting_node'), pair, pair_mask, False)
+    pair = pair + dm('triangle_attention_ending_node') * triangle_attention(
+        sub(p, 'triangle_attention_ending_node'), pair, pair_mask, True)
     pair = pair + transition(sub(p, 'pair_transition'), pair)
     return pair
 
 
-def template_pair_stack(p: Params, pair, pair_mask, depth):
+def template_pair_stack(p: Params, pair, pair_mask, depth, dropout_seed=None):
+    """``dropout_seed``: the native path's hash masks with the template stack's module ids (native/tplblock.cuh:55-66)."""
     for b in range(depth):
-        pair = template_pair_iteration(sub(p, f'block{b}'), pair, pair_mask)
+        drop = None if dropout_seed is None else block_dropout_masks(dropout_seed, b, pair.shape[0], pair.shape[-1], 0,
+                                                                      ids=TPL_DROP_SITES)
+        pair = template_pair_iteration(sub(p, f'block{b}'), pair, pair_mask, drop)
     return pair
 
 
-def stack_fwd_bwd(p: Params, inp, depth, is_extra_msa=False, opm_first=True, dtype=torch.float32, steps=None):
+def stack_fwd_bwd(p: Params, inp, depth, is_extra_msa=False, opm_first=True, dtype=torch.float32, steps=None,
+                  dropout_seed=None):
     """Forward and input gradients (weights frozen) of the stack for cotangents ``ct_msa``/``ct_pair``."""
     pp = {k: v.to(dtype) for k, v in p.items()}
     msa = inp['msa'].to(dtype).clone().requires_grad_(True)
     pair = inp['pair'].to(dtype).clone().requires_grad_(True)
     m_out, p_out = evoformer_stack(pp, msa, pair, inp['msa_mask'].to(dtype), inp['pair_mask'].to(dtype), depth,
-                                   is_extra_msa=is_extra_msa, opm_first=opm_first, steps=steps)
+                                   is_extra_msa=is_extra_msa, opm_first=opm_first, steps=steps,
+                                   dropout_seed=dropout_seed)
     loss = (m_out * inp['ct_msa'].to(dtype)).sum() + (p_out * inp['ct_pair'].to(dtype)).sum()
     d_msa, d_pair = torch.autograd.grad(loss, [msa, pair])
     return dict(msa=m_out.detach(), pair=p_out.detach(), d_msa=d_msa, d_pair=d_pair)
 
 
-def template_embedding(p: Params, query, act_const, pair_mask, depth):
+def template_embedding(p: Params, query, act_const, pair_mask, depth, dropout_seed=None):
     """One-template TemplateEmbedding with the eight template-only projections given as ``act_const``
     (modules_multimer.py:930-956 query_projection, :958-1006 stack + output_layer_norm, :796-809 relu + output_linear)."""
     q = layer_norm(query, p['query_embedding_norm/scale'], p['query_embedding_norm/offset'])
     act = act_const + linear(q, p['template_pair_embedding_8/weights'], p['template_pair_embedding_8/bias'])
-    act = template_pair_stack(p, act, pair_mask, depth)
+    act = template_pair_stack(p, act, pair_mask, depth, dropout_seed=dropout_seed)
     act = layer_norm(act, p['output_layer_norm/scale'], p['output_layer_norm/offset'])
     return linear(torch.relu(act), p['output_linear/weights'], p['output_linear/bias'])
 
 
-def template_embedding_fwd_bwd(p: Params, query, act_const, pair_mask, ct, depth, dtype=torch.float32):
+def template_embedding_fwd_bwd(p: Params, query, act_const, pair_mask, ct, depth, dtype=torch.float32, dropout_seed=None):
     pp = {k: v.to(dtype) for k, v in p.items()}
     x = query.to(dtype).clone().requires_grad_(True)
-    out = template_embedding(pp, x, act_const.to(dtype), pair_mask.to(dtype), depth)
+    out = template_embedding(pp, x, act_const.to(dtype), pair_mask.to(dtype), depth, dropout_seed=dropout_seed)
     (g,) = torch.autograd.grad((out * ct.to(dtype)).sum(), [x])
     return dict(out=out.detach(), d_query=g)
 
 
-def template_stack_fwd_bwd(p: Params, pair, pair_mask, ct, depth, dtype=torch.float32):
+def template_stack_fwd_bwd(p: Params, pair, pair_mask, ct, depth, dtype=torch.float32, dropout_seed=None):
     """Forward and input gradient of the template pair stack for cotangent ``ct``."""
     pp = {k: v.to(dtype) for k, v in p.items()}
     x = pair.to(dtype).clone().requires_grad_(True)
-    out = template_pair_stack(pp, x, pair_mask.to(dtype), depth)
+    out = template_pair_stack(pp, x, pair_mask.to(dtype), depth, dropout_seed=dropout_seed)
     (g,) = torch.autograd.grad((out * ct.to(dtype)).sum(), [x])
     return dict(pair=out.detach(), d_pair=g)
 

@@ -89,17 +89,31 @@ def invariant_point_attention(p: Params, act, pair_ln, mask, rot, trans):
     return final @ p[f'{IPA}/output_projection/weights'] + p[f'{IPA}/output_projection/bias']
 
 
-def fold_iteration(p: Params, act, rot, trans, pair_ln, mask):
-    """FoldIteration.__call__ without the side-chain branch (folding_multimer.py:397-474), dropout off."""
+def fold_dropout_masks(seed, iteration, n, channels=384):
+    """The two elementwise masks of one fold iteration as the reference's native path draws them (native/foldit.cuh:152-166:
+    module ids 21 and 22, rate 0.1, depth index = iteration, mask index = flat [N, C] index)."""
+    from evoformer_oracle import dropout_scale_table
+    return tuple(dropout_scale_table(seed, iteration, mod, n, channels, 0.1) for mod in (21, 22))
+
+
+def fold_iteration(p: Params, act, rot, trans, pair_ln, mask, drop=None):
+    """FoldIteration.__call__ without the side-chain branch (folding_multimer.py:397-474).  ``drop``: the two dropout
+    scale masks [N,384]; the reference drops the WHOLE activation after each residual add (folding_multimer.py:408-412,
+    428, 449: safe_dropout with broadcast_dim None), not a module delta as the Evoformer does."""
     f = 'fold_iteration'
     act = act + invariant_point_attention(p, act, pair_ln, mask, rot, trans)
+    if drop is not None:
+        act = act * drop[0].to(act.dtype)
     act = layer_norm(act, p[f'{f}/attention_layer_norm/scale'], p[f'{f}/attention_layer_norm/offset'])
     x = act
     for i, nm in enumerate(('transition', 'transition_1', 'transition_2')):
         x = x @ p[f'{f}/{nm}/weights'] + p[f'{f}/{nm}/bias']
         if i < 2:
             x = torch.relu(x)
-    act = layer_norm(act + x, p[f'{f}/transition_layer_norm/scale'], p[f'{f}/transition_layer_norm/offset'])
+    act = act + x
+    if drop is not None:
+        act = act * drop[1].to(act.dtype)
+    act = layer_norm(act, p[f'{f}/transition_layer_norm/scale'], p[f'{f}/transition_layer_norm/offset'])
     upd = act @ p[f'{f}/quat_rigid/rigid/weights'] + p[f'{f}/quat_rigid/rigid/bias']   # [N, 6]: qx qy qz tx ty tz
     u_rot = quat_to_rot(upd[:, 0], upd[:, 1], upd[:, 2])
     new_trans = torch.einsum('nab,nb->na', rot, upd[:, 3:6]) + trans                   # rigid @ update
@@ -107,7 +121,7 @@ def fold_iteration(p: Params, act, rot, trans, pair_ln, mask):
     return act, new_rot, new_trans
 
 
-def structure_core(p: Params, single, pair, seq_mask, depth=NUM_LAYER):
+def structure_core(p: Params, single, pair, seq_mask, depth=NUM_LAYER, dropout_seed=None):
     """generate_monomer_rigids (folding_multimer.py:477-556) with identity initial frames.
     Returns the final activations [N,384], rotations [N,3,3] and translations [N,3] (scaled by position_scale, as the
     reference's 'final_rigids')."""
@@ -117,8 +131,9 @@ def structure_core(p: Params, single, pair, seq_mask, depth=NUM_LAYER):
     pair_ln = layer_norm(pair, p['pair_layer_norm/scale'], p['pair_layer_norm/offset'])
     rot = torch.eye(3, dtype=single.dtype).expand(n, 3, 3).contiguous()
     trans = torch.zeros(n, 3, dtype=single.dtype)
-    for _ in range(depth):
-        act, rot, trans = fold_iteration(p, act, rot, trans, pair_ln, seq_mask)
+    for it in range(depth):
+        drop = None if dropout_seed is None else fold_dropout_masks(dropout_seed, it, n, act.shape[-1])
+        act, rot, trans = fold_iteration(p, act, rot, trans, pair_ln, seq_mask, drop)
     return act, rot, trans * POSITION_SCALE
 
 
@@ -194,10 +209,10 @@ def heads(p: Params, single, pair, act):
     return dgram, pae, plddt, expres
 
 
-def structure_heads(p: Params, tables, single, pair, seq_mask, aatype, depth=NUM_LAYER):
+def structure_heads(p: Params, tables, single, pair, seq_mask, aatype, depth=NUM_LAYER, dropout_seed=None):
     """What the reference's post-trunk call returns (native/ffi.cu:1009-1025): atom14 [N,14,3], distogram logits
     [N,N,64], aligned-error logits [N,N,64], pLDDT logits [N,50], experimentally-resolved logits [N,37]."""
-    act, rot, trans = structure_core(p, single, pair, seq_mask, depth)
+    act, rot, trans = structure_core(p, single, pair, seq_mask, depth, dropout_seed=dropout_seed)
     initial_act = layer_norm(single, p['single_layer_norm/scale'], p['single_layer_norm/offset'])
     atom14 = sidechain_atoms(p, tables, act, initial_act, rot, trans, aatype)
     return (atom14,) + heads(p, single, pair, act)
@@ -206,11 +221,12 @@ def structure_heads(p: Params, tables, single, pair, seq_mask, aatype, depth=NUM
 HEAD_OUTS = ('atom14', 'dgram', 'pae', 'plddt', 'expres')
 
 
-def structure_heads_fwd_bwd(p: Params, tables, inp, depth=NUM_LAYER, dtype=torch.float32):
+def structure_heads_fwd_bwd(p: Params, tables, inp, depth=NUM_LAYER, dtype=torch.float32, dropout_seed=None):
     pp = {k: v.to(dtype) for k, v in p.items()}
     single = inp['single'].to(dtype).clone().requires_grad_(True)
     pair = inp['pair'].to(dtype).clone().requires_grad_(True)
-    outs = structure_heads(pp, tables, single, pair, inp['seq_mask'].to(dtype), inp['aatype'], depth)
+    outs = structure_heads(pp, tables, single, pair, inp['seq_mask'].to(dtype), inp['aatype'], depth,
+                           dropout_seed=dropout_seed)
     loss = sum((o * inp['ct_' + k].to(dtype)).sum() for k, o in zip(HEAD_OUTS, outs))
     d_single, d_pair = torch.autograd.grad(loss, [single, pair])
     res = {k: o.detach() for k, o in zip(HEAD_OUTS, outs)}

@@ -19,16 +19,16 @@ REL_L2 = 2e-2
 COSINE = 0.999
 
 
-def _run_cuda(lib, params, inp, depth, tmp_path, own_save=1, opm_first=1):
+def _run_cuda(lib, params, inp, depth, tmp_path, own_save=1, opm_first=1, dropout=0, seed_words=(0, 0)):
     from bindcraft2_b200 import native
     wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
     dev = 'cuda:0'
     t = {k: v.to(dev).contiguous() for k, v in inp.items()}
-    seed = torch.zeros(2, dtype=torch.int32, device=dev)
+    seed = torch.tensor(list(seed_words), dtype=torch.int32, device=dev)
     p, m, psave, msave = native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, depth=depth, save=1,
-                                              weights_dir=wdir, own_save=own_save, opm_first=opm_first)
+                                              weights_dir=wdir, own_save=own_save, opm_first=opm_first, dropout=dropout)
     dp, dm = native.evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, seed, depth=depth,
-                                  weights_dir=wdir, own_save=own_save, opm_first=opm_first)
+                                  weights_dir=wdir, own_save=own_save, opm_first=opm_first, dropout=dropout)
     torch.cuda.synchronize()
     assert lib.bc2_device_status() == 0
     return dict(pair=p.cpu(), msa=m.cpu(), d_pair=dp.cpu(), d_msa=dm.cpu()), (psave, msave, wdir, t, seed)
@@ -108,6 +108,34 @@ def test_monomer_block_order_opm_last(lib, tmp_path):
     and a masked pad, so that the order matters in both directions (block 1's row attention sees block 0's outer product)."""
     _case(lib, tmp_path, 151, 152, 64, 2, 2, masked=5, opm_first=0, tag='opm-last')
     _case(lib, tmp_path, 153, 154, 96, 1, 1, opm_first=0, own_save=0, tag='opm-last own_save=0')
+
+
+def test_dropout_masks_of_the_native_hash(lib, tmp_path):
+    """dropout = 1 and seed words {seed, 1}: the five dropout sites of every block scale their module output by the
+    reference's counter-hash masks (native/common.cuh:944-1030; the oracle restates the hash in numpy), in the forward
+    and, from the seed operand alone, in the backward.  With the enable word 0 the same call must give exactly what
+    dropout = 0 gives: BindCraft2 flips that word between design stages without rebuilding anything."""
+    n, s_, depth, seed = 64, 2, 2, 20261125
+    params = synthetic.make_evoformer_params(161, depth)
+    inp = synthetic.make_block_inputs(162, n, s_)
+    got, _ = _run_cuda(lib, params, inp, depth, tmp_path, dropout=1, seed_words=(seed, 1))
+    want = O.stack_fwd_bwd(params, inp, depth, dropout_seed=seed)
+    with O.bf16_operands():
+        floor = O.stack_fwd_bwd(params, inp, depth, dropout_seed=seed)
+    _check(got, want, floor, 'dropout')
+    plain = O.stack_fwd_bwd(params, inp, depth)
+    assert O.rel_l2(want['pair'], plain['pair']) > 0.05  # the masks do change the result: the test is not vacuous
+    off, _ = _run_cuda(lib, params, inp, depth, tmp_path, dropout=1, seed_words=(seed, 0))
+    base, _ = _run_cuda(lib, params, inp, depth, tmp_path, dropout=0)
+    for k in ('pair', 'msa'):
+        assert torch.equal(off[k], base[k]), k
+    # The bias gradient is summed with fp32 atomics, and bf16 roundings downstream amplify the summation order: two
+    # identical calls differ by a few 1e-3 in the gradients.  The disabled masks must stay within that noise.
+    again, _ = _run_cuda(lib, params, inp, depth, tmp_path, dropout=0)
+    for k in ('d_pair', 'd_msa'):
+        noise = O.rel_l2(again[k], base[k])
+        print(k, 'masks disabled vs dropout=0', O.rel_l2(off[k], base[k]), 'run-to-run', noise)
+        assert O.rel_l2(off[k], base[k]) <= max(3 * noise, 2e-3), k
 
 
 def test_save_set_contract_without_own_save(lib, tmp_path):

@@ -95,13 +95,13 @@ def test_bad_arguments_return_errors(lib, tmp_path):
 
 
 # ----------------------------------------------------------------------------- post-trunk call (side chains + heads)
-def _run_heads(lib, params, tables, inp, depth, tmp_path):
+def _run_heads(lib, params, tables, inp, depth, tmp_path, seed_words=(0, 0)):
     from bindcraft2_b200 import native
     wdir = native.post_trunk_weights(params, tables, str(tmp_path / 'w'))
     t = {k: v.cuda().contiguous() for k, v in inp.items()}
     mask2d = (t['seq_mask'][:, None] * t['seq_mask'][None, :]).contiguous()
     aatype = t['aatype'].float()
-    seed = torch.zeros(2, dtype=torch.int32, device='cuda')
+    seed = torch.tensor(list(seed_words), dtype=torch.int32, device='cuda')
     outs = native.post_trunk_fwd(t['single'], t['pair'], mask2d, aatype, seed, depth=depth, weights_dir=wdir)
     cts = [t['ct_' + k] for k in SO.HEAD_OUTS]
     ds, dp = native.post_trunk_bwd(t['single'], t['pair'], mask2d, aatype, seed, *cts, depth=depth, weights_dir=wdir)
@@ -120,6 +120,25 @@ def test_post_trunk_matches_oracle(lib, tmp_path, n, depth, masked):
     got, _ = _run_heads(lib, params, tables, inp, depth, tmp_path)
     want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth)
     _check(got, want, f'post-trunk N={n} depth={depth}')
+
+
+def test_post_trunk_dropout_masks(lib, tmp_path):
+    """Enable word set: every fold iteration drops its activation twice with the reference's hash masks (elementwise,
+    rate 0.1, native/foldit.cuh:152-166), in the forward and in the replayed backward.  Enable word clear: exactly the
+    plain result."""
+    n, depth, seed = 48, 3, 424242
+    params = synthetic.add_structure_head_params(synthetic.make_structure_params(431), 432)
+    tables = synthetic.make_structure_tables(433)
+    inp = synthetic.add_structure_head_inputs(synthetic.make_structure_inputs(434, n), 435)
+    got, _ = _run_heads(lib, params, tables, inp, depth, tmp_path, seed_words=(seed, 1))
+    want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth, dropout_seed=seed)
+    _check(got, want, 'post-trunk dropout')
+    plain = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth)
+    assert SO.rel_l2(want['plddt'], plain['plddt']) > 0.02
+    off, _ = _run_heads(lib, params, tables, inp, depth, tmp_path, seed_words=(seed, 0))
+    base, _ = _run_heads(lib, params, tables, inp, depth, tmp_path)
+    for k in base:
+        assert torch.equal(off[k], base[k]), k
 
 
 def test_post_trunk_each_cotangent_alone(lib, tmp_path):

@@ -57,9 +57,10 @@ def test_template_stack_autograd(lib, tmp_path):
     assert O.cosine(x.grad.cpu(), want['d_pair']) >= 0.998
 
 
-@pytest.mark.parametrize('n,masked', [(64, 0), (96, 11)])
-def test_template_embedding_matches_oracle(lib, tmp_path, n, masked):
-    """Whole template embedding (query norm + projection + act_const, stack, output norm, ReLU, output Linear)."""
+@pytest.mark.parametrize('n,masked,drop_seed', [(64, 0, None), (96, 11, None), (64, 0, 77001)])
+def test_template_embedding_matches_oracle(lib, tmp_path, n, masked, drop_seed):
+    """Whole template embedding (query norm + projection + act_const, stack, output norm, ReLU, output Linear); the last
+    case with dropout on: the template stack's four sites draw the reference's hash masks (module ids 11..14)."""
     from bindcraft2_b200 import native
     depth = 2
     params = synthetic.make_template_embed_params(320 + n, depth)
@@ -72,15 +73,20 @@ def test_template_embedding_matches_oracle(lib, tmp_path, n, masked):
         res[n - masked:] = 0
     mask = res[:, None] * res[None, :]
     wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
-    seed = torch.zeros(2, dtype=torch.int32, device='cuda')
-    out, sv = native.template_embedding_fwd(query.cuda(), act_const.cuda(), mask.cuda(), seed, depth=depth, weights_dir=wdir)
+    seed = torch.tensor([drop_seed or 0, 1 if drop_seed else 0], dtype=torch.int32, device='cuda')
+    dropout = 1 if drop_seed else 0
+    out, sv = native.template_embedding_fwd(query.cuda(), act_const.cuda(), mask.cuda(), seed, depth=depth, weights_dir=wdir,
+                                            dropout=dropout)
     dq = native.template_embedding_bwd(ct.cuda(), query.cuda(), act_const.cuda(), mask.cuda(), sv, seed, depth=depth,
-                                       weights_dir=wdir)
+                                       weights_dir=wdir, dropout=dropout)
     torch.cuda.synchronize()
     assert lib.bc2_device_status() == 0
-    want = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth)
+    want = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth, dropout_seed=drop_seed)
     with O.bf16_operands():
-        floor = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth)
+        floor = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth, dropout_seed=drop_seed)
+    if drop_seed:
+        plain = O.template_embedding_fwd_bwd(params, query, act_const, mask, ct, depth)
+        assert O.rel_l2(want['out'], plain['out']) > 0.05
     r = n - masked
     c = lambda t: t[:r, :r]
     fwd = O.rel_l2(c(out.cpu()), c(want['out']))

@@ -110,3 +110,35 @@ def test_opm_matches_reference_einsum_order():
     ref = torch.einsum('dceb,cef->dbf', act, w).permute(1, 0, 2)
     mine = torch.einsum('bdce,cef->bdf', torch.einsum('abc,ade->bdce', left, right), w)
     assert O.rel_l2(mine, ref) < 1e-12
+
+
+def test_dropout_hash_restatement_is_self_consistent():
+    """The numpy statement of the reference's mask hash (native/common.cuh:944-981) against a scalar Python statement
+    of the same recurrence, plus the keep rates it has to produce (0.75 for the pair sites, 0.85 for the MSA rows)."""
+    import numpy as np
+
+    def scalar(a, b, c, d):
+        m = 0xffffffff
+        h = (a * 0x9e3779b9) & m
+        for v, k in ((b, 0x85ebca6b), (c, 0xc2b2ae35), (d, 0x27d4eb2f)):
+            h ^= (v + k + ((h << 6) & m) + (h >> 2)) & m
+        h ^= h >> 15
+        h = (h * 0x2c1b3c6d) & m
+        h ^= h >> 12
+        h = (h * 0x297a2d39) & m
+        h ^= h >> 15
+        return h
+
+    idx = np.arange(0, 5000, 7)
+    got = O.dropout_hash(987654321, 47, 5, idx)
+    assert got.dtype == np.uint32
+    assert (got == np.array([scalar(987654321, 47, 5, int(i)) for i in idx], dtype=np.uint32)).all()
+    for mod, rate in ((2, 0.25), (1, 0.15)):
+        t = O.dropout_scale_table(11, 3, mod, 224, 128, rate)
+        vals = sorted(set(t.flatten().tolist()))
+        assert len(vals) == 2 and vals[0] == 0.0 and abs(vals[1] - 1.0 / (1.0 - rate)) < 1e-6
+        assert abs(float((t > 0).float().mean()) - (1.0 - rate)) < 0.01
+    m = O.block_dropout_masks(5, 0, 32, 128, 256)
+    assert m['triangle_attention_ending_node'].shape == (32, 1, 128)
+    assert m['triangle_multiplication_outgoing'].shape == (1, 32, 128)
+    assert m['msa_row_attention_with_pair_bias'].shape == (1, 32, 256)
