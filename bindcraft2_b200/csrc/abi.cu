@@ -394,14 +394,14 @@ int bc2_embedder_fwd(void* stream, const float* target_feat, const float* msa_fe
   }
 }
 
-int bc2_embedder_bwd(void* stream, const float* d_msa, const float* d_pair, const float* /*target_feat*/, int64_t N,
+int bc2_embedder_bwd(void* stream, const float* d_msa, const float* d_pair, const float* target_feat, int64_t N,
                      int64_t S, const char* weights_dir, float* d_target_feat, float* d_msa_feat) {
   try {
     BC2_CHECK(d_msa && d_pair && d_target_feat && d_msa_feat && weights_dir, "null operand");
     BC2_CHECK(N > 0 && S > 0, "bad shape");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     emb::Embedder* e = get_embedder((int)N, (int)S, weights_dir);
-    e->backward(d_msa, d_pair, d_target_feat, d_msa_feat, (cudaStream_t)stream);
+    e->backward(d_msa, d_pair, target_feat, d_target_feat, d_msa_feat, (cudaStream_t)stream);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {

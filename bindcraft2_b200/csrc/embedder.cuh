@@ -6,6 +6,14 @@
 // a 6-bin chain offset clipped at +-2 with one extra bin for "other entity"; the one-hots select rows of the
 // [73,128] position_activations weight, so the Linear is a gather of three rows).
 // fp32 throughout (the reference's native call works in fp32 as well).
+//
+// Two details of the reference's NATIVE embedder (native/embed.cuh) that its Python fallback does not have:
+//  * rows whose target_feat is all zero (padding) get preprocess_1d = 0 AFTER the Linear, bias included
+//    (featMaskK, native/embed.cuh:189-197,313; the same rows are cleared in the backward, :363);
+//  * the monomer model (alphafold2_ptm) is a different embedder, not the same one on other weights
+//    (native/embed.cuh:43-62): target_feat is 22 wide (padded on both sides), the relative encoding is ONE one-hot of
+//    65 clipped offset bins through the Linear named `pair_activiations`, with no chain/entity terms and no feature
+//    mask.  It is selected here by the manifest holding `pair_activiations/weights`.
 #pragma once
 #include "structure_host.cuh"
 
@@ -36,6 +44,28 @@ __global__ void pair_init_kernel(const float* __restrict__ left, const float* __
   pair[ij * CZ + c] = v;
 }
 
+// monomer: pair[i,j,:] = left[i,:] + right[j,:] + W[clip(ri - rj + 32, 0, 64)] + b
+__global__ void pair_init_monomer_kernel(const float* __restrict__ left, const float* __restrict__ right,
+                                         const float* __restrict__ wpos, const float* __restrict__ bpos,
+                                         const float* __restrict__ residue_index, float* __restrict__ pair, int N) {
+  const long ij = (long)blockIdx.x * 2 + (threadIdx.x >> 7);
+  if (ij >= (long)N * N) return;
+  const int c = threadIdx.x & 127;
+  const int j = (int)(ij % N), i = (int)(ij / N);
+  const int off = (int)residue_index[i] - (int)residue_index[j];
+  const int bin = min(max(off + MAX_REL, 0), 2 * MAX_REL);
+  pair[ij * CZ + c] = left[(long)i * CZ + c] + right[(long)j * CZ + c] + wpos[(long)bin * CZ + c] + bpos[c];
+}
+
+// x[n,:] = 0 for rows n whose target_feat sums to exactly zero (block = row)
+__global__ void feat_mask_kernel(float* __restrict__ x, const float* __restrict__ tf, int naa, int width) {
+  const int n = blockIdx.x;
+  float s = 0.f;
+  for (int k = 0; k < naa; ++k) s += tf[(long)n * naa + k];
+  if (s != 0.f) return;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) x[(long)n * width + c] = 0.f;
+}
+
 // rows[i,c] = sum_j d[i,j,c]   (block = i, thread = channel)
 __global__ void pair_rowsum_kernel(const float* __restrict__ d, float* __restrict__ rows, int N) {
   const int i = blockIdx.x, c = threadIdx.x;
@@ -60,7 +90,8 @@ __global__ void sum_over_rows_kernel(const float* __restrict__ d, float* __restr
 }
 
 struct Embedder {
-  int N = 0, S = 0;
+  int N = 0, S = 0, naa = NAA;
+  bool monomer = false;
   DeviceArena A;
   sm::Lin pre1d, premsa, left, right;
   float *wpos, *bpos;
@@ -70,13 +101,18 @@ struct Embedder {
     N = n; S = s;
     const Manifest m = Manifest::load(dir);
     auto v = [&](const std::string& k) { return m.get("param/" + k).data; };
-    pre1d.set(A, v("preprocess_1d/weights"), v("preprocess_1d/bias"), NAA, CM);
+    monomer = m.has("param/pair_activiations/weights");
+    naa = monomer ? NAA + 1 : NAA;
+    BC2_CHECK(v("preprocess_1d/weights").size() == (size_t)naa * CM, "preprocess_1d: weight rows do not match the embedder variant");
+    pre1d.set(A, v("preprocess_1d/weights"), v("preprocess_1d/bias"), naa, CM);
     premsa.set(A, v("preprocess_msa/weights"), v("preprocess_msa/bias"), NMSAF, CM);
-    left.set(A, v("left_single/weights"), v("left_single/bias"), NAA, CZ);
-    right.set(A, v("right_single/weights"), v("right_single/bias"), NAA, CZ);
-    BC2_CHECK(v("position_activations/weights").size() == (size_t)REL_TOT * CZ, "position_activations: expected [73,128]");
-    wpos = A.upload(v("position_activations/weights"));
-    bpos = A.upload(v("position_activations/bias"));
+    left.set(A, v("left_single/weights"), v("left_single/bias"), naa, CZ);
+    right.set(A, v("right_single/weights"), v("right_single/bias"), naa, CZ);
+    const std::string pos = monomer ? "pair_activiations" : "position_activations";
+    BC2_CHECK(v(pos + "/weights").size() == (size_t)(monomer ? 2 * MAX_REL + 1 : REL_TOT) * CZ,
+              pos + ": expected [" + std::to_string(monomer ? 2 * MAX_REL + 1 : REL_TOT) + ",128]");
+    wpos = A.upload(v(pos + "/weights"));
+    bpos = A.upload(v(pos + "/bias"));
     p1 = A.alloc<float>((size_t)N * CM);
     l = A.alloc<float>((size_t)N * CZ); r = A.alloc<float>((size_t)N * CZ);
     rows = A.alloc<float>((size_t)N * CZ); cols = A.alloc<float>((size_t)N * CZ);
@@ -89,21 +125,29 @@ struct Embedder {
   }
   void forward(const float* tf, const float* msa_feat, const float* residue_index, const float* asym_id, const float* entity_id,
                const float* sym_id, float* msa, float* pair, cudaStream_t st) {
-    lin(tf, pre1d.w, pre1d.b, p1, N, NAA, CM, st);
+    lin(tf, pre1d.w, pre1d.b, p1, N, naa, CM, st);
+    if (!monomer) { launch_counter()++; feat_mask_kernel<<<N, 256, 0, st>>>(p1, tf, naa, CM); }
     for (int s = 0; s < S; ++s)  // msa[s] = preprocess_msa(msa_feat[s]) + preprocess_1d(target_feat)
       lin(msa_feat + (long)s * N * NMSAF, premsa.w, premsa.b, msa + (long)s * N * CM, N, NMSAF, CM, st, p1);
-    lin(tf, left.w, left.b, l, N, NAA, CZ, st);
-    lin(tf, right.w, right.b, r, N, NAA, CZ, st);
-    launch_counter()++; pair_init_kernel<<<(unsigned)cdiv((long)N * N, 2L), 256, 0, st>>>(l, r, wpos, bpos, residue_index, asym_id, entity_id, sym_id, pair, N);
+    lin(tf, left.w, left.b, l, N, naa, CZ, st);
+    lin(tf, right.w, right.b, r, N, naa, CZ, st);
+    launch_counter()++;
+    if (monomer) pair_init_monomer_kernel<<<(unsigned)cdiv((long)N * N, 2L), 256, 0, st>>>(l, r, wpos, bpos, residue_index, pair, N);
+    else pair_init_kernel<<<(unsigned)cdiv((long)N * N, 2L), 256, 0, st>>>(l, r, wpos, bpos, residue_index, asym_id, entity_id, sym_id, pair, N);
   }
-  void backward(const float* d_msa, const float* d_pair, float* d_tf, float* d_msa_feat, cudaStream_t st) {
+  // tf: the forward's target_feat (its all-zero rows take no gradient through preprocess_1d; may be null for the monomer)
+  void backward(const float* d_msa, const float* d_pair, const float* tf, float* d_tf, float* d_msa_feat, cudaStream_t st) {
     lin(d_msa, premsa.wt, nullptr, d_msa_feat, (long)S * N, CM, NMSAF, st);
     launch_counter()++; sum_over_rows_kernel<<<(unsigned)cdiv((long)N * CM, 256L), 256, 0, st>>>(d_msa, dsum, S, (long)N * CM);
+    if (!monomer) {
+      BC2_CHECK(tf != nullptr, "embedder backward: target_feat is needed for the feature mask");
+      launch_counter()++; feat_mask_kernel<<<N, 256, 0, st>>>(dsum, tf, naa, CM);
+    }
     launch_counter()++; pair_rowsum_kernel<<<N, CZ, 0, st>>>(d_pair, rows, N);
     launch_counter()++; pair_colsum_kernel<<<N, CZ, 0, st>>>(d_pair, cols, N);
-    lin(dsum, pre1d.wt, nullptr, d_tf, N, CM, NAA, st);
-    lin(rows, left.wt, nullptr, d_tf, N, CZ, NAA, st, nullptr, 1);
-    lin(cols, right.wt, nullptr, d_tf, N, CZ, NAA, st, nullptr, 1);
+    lin(dsum, pre1d.wt, nullptr, d_tf, N, CM, naa, st);
+    lin(rows, left.wt, nullptr, d_tf, N, CZ, naa, st, nullptr, 1);
+    lin(cols, right.wt, nullptr, d_tf, N, CZ, naa, st, nullptr, 1);
   }
 };
 

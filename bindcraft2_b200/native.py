@@ -17,6 +17,7 @@ results of a custom call.
 from __future__ import annotations
 
 import hashlib
+import functools
 import os
 import tempfile
 from typing import Dict, Optional
@@ -336,11 +337,20 @@ def make_post_trunk(weights_dir: str, depth: int = 8):
     return _Post.apply
 
 
+@functools.lru_cache(maxsize=None)
+def embedder_target_width(weights_dir: str) -> int:
+    """21 for the multimer embedder, 22 for the monomer (``alphafold2_ptm``) one, which the library selects when the
+    manifest holds ``pair_activiations/weights`` (reference: native/embed.cuh:43-62)."""
+    with open(os.path.join(weights_dir, 'manifest.txt')) as f:
+        return 22 if any(line.split()[:1] == ['param/pair_activiations/weights'] for line in f) else 21
+
+
 def embedder_fwd(target_feat, msa_feat, residue_index, asym_id, entity_id, sym_id, *, weights_dir):
-    """FFI target ``native_embed_fwd`` (reference handler native/ffi.cu:1045-1057): (msa [S,N,256], pair [N,N,128])."""
+    """FFI target ``native_embed_fwd`` (reference handler native/ffi.cu:1045-1057): (msa [S,N,256], pair [N,N,128]).
+    ``target_feat`` is [N,21] (multimer) or [N,22] (monomer weights; asym/entity/sym ids are then ignored)."""
     lib = _lib.load()
     n, s = int(target_feat.shape[0]), int(msa_feat.shape[0])
-    _check_f32('target_feat', target_feat, (n, 21))
+    _check_f32('target_feat', target_feat, (n, embedder_target_width(weights_dir)))
     _check_f32('msa_feat', msa_feat, (s, n, 49))
     for name, t in (('residue_index', residue_index), ('asym_id', asym_id), ('entity_id', entity_id), ('sym_id', sym_id)):
         _check_f32(name, t, (n,))
@@ -360,7 +370,9 @@ def embedder_bwd(d_msa, d_pair, target_feat, *, weights_dir):
     s, n = int(d_msa.shape[0]), int(d_msa.shape[1])
     _check_f32('d_msa', d_msa, (s, n, CM))
     _check_f32('d_pair', d_pair, (n, n, CZ))
-    d_tf = torch.empty(n, 21, dtype=torch.float32, device=d_msa.device)
+    width = embedder_target_width(weights_dir)
+    _check_f32('target_feat', target_feat, (n, width))
+    d_tf = torch.empty(n, width, dtype=torch.float32, device=d_msa.device)
     d_mf = torch.empty(s, n, 49, dtype=torch.float32, device=d_msa.device)
     stream = torch.cuda.current_stream(d_msa.device).cuda_stream
     with torch.cuda.device(d_msa.device):

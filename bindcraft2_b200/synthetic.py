@@ -290,18 +290,21 @@ def add_structure_head_inputs(inp, seed: int):
 
 
 # ----------------------------------------------------------------------------- input embedder
-def make_embedder_params(seed: int, cm=256, cz=128) -> Params:
-    """The five Linears of the multimer input embedder under their haiku names (embedder manifest keys)."""
+def make_embedder_params(seed: int, cm=256, cz=128, monomer=False) -> Params:
+    """The five Linears of the input embedder under their haiku names (embedder manifest keys): the multimer model's, or
+    with ``monomer`` the monomer model's (22-wide target features, 65-bin ``pair_activiations``)."""
     g = torch.Generator().manual_seed(seed)
     p: Params = {}
-    for nm, cin, cout in (('preprocess_1d', 21, cm), ('preprocess_msa', 49, cm), ('left_single', 21, cz),
-                          ('right_single', 21, cz), ('position_activations', 73, cz)):
+    naa = 22 if monomer else 21
+    pos = ('pair_activiations', 65, cz) if monomer else ('position_activations', 73, cz)
+    for nm, cin, cout in (('preprocess_1d', naa, cm), ('preprocess_msa', 49, cm), ('left_single', naa, cz),
+                          ('right_single', naa, cz), pos):
         p[f'{nm}/weights'] = _lin(g, cin, (cin, cout))
         p[f'{nm}/bias'] = 0.02 * torch.randn(cout, generator=g)
     return p
 
 
-def make_embedder_inputs(seed: int, n_binder: int, n_target: int, s: int = 1):
+def make_embedder_inputs(seed: int, n_binder: int, n_target: int, s: int = 1, monomer=False, n_pad: int = 0):
     """A two-chain complex as in a design step: binder target_feat = softmax of seeded N(0,1) logits over 20 types,
     target = one-hot of a seeded random sequence (both padded to 21 columns); residue_index restarts per chain with a
     gap inside the target so that the clip at +-32 is exercised; cotangents for both outputs."""
@@ -312,6 +315,10 @@ def make_embedder_inputs(seed: int, n_binder: int, n_target: int, s: int = 1):
     tf[n_binder:, :20] = torch.nn.functional.one_hot(torch.randint(0, 20, (n_target,), generator=g), 20).float()
     ri = torch.cat([torch.arange(n_binder), torch.arange(n_target) + (torch.arange(n_target) >= n_target // 2) * 50]).float()
     asym = torch.cat([torch.zeros(n_binder), torch.ones(n_target)])
+    if n_pad:  # trailing padding rows: all-zero target features
+        tf[n - n_pad:] = 0
+    if monomer:  # the monomer pads one column on BOTH sides: the 20 sequence columns start at 1
+        tf = torch.cat([torch.zeros(n, 1), tf], 1)
     return dict(target_feat=tf, msa_feat=torch.randn(s, n, 49, generator=g), residue_index=ri, asym_id=asym,
                 entity_id=asym.clone(), sym_id=torch.zeros(n), ct_msa=torch.randn(s, n, 256, generator=g),
                 ct_pair=torch.randn(n, n, 128, generator=g))

@@ -28,10 +28,26 @@ def relative_features(residue_index, asym_id, entity_id, sym_id, dtype):
 
 
 def embedder(p, target_feat, msa_feat, residue_index, asym_id, entity_id, sym_id):
-    """msa [S,N,256], pair [N,N,128]."""
+    """msa [S,N,256], pair [N,N,128].
+
+    Multimer weights (``position_activations``): as modules_multimer.py:447-510 + :358-433, plus the one thing the
+    reference's NATIVE embedder adds to that: rows whose target_feat is all zero (padding) get preprocess_1d = 0 after
+    the Linear, bias included (native/embed.cuh:189-197,313).
+    Monomer weights (``pair_activiations``, the monomer model's own spelling): target_feat is 22 wide, the relative
+    encoding is one 65-bin one-hot of the clipped residue offset (modules.py:1471-1485), no chain terms, no feature mask
+    (native/embed.cuh:43-62)."""
     lin = lambda name, x: x @ p[f'{name}/weights'] + p[f'{name}/bias']
-    msa = lin('preprocess_1d', target_feat)[None] + lin('preprocess_msa', msa_feat)
+    monomer = 'pair_activiations/weights' in p
+    pre1d = lin('preprocess_1d', target_feat)
+    if not monomer:
+        pre1d = pre1d * (target_feat.sum(-1, keepdim=True) != 0).to(pre1d.dtype)
+    msa = pre1d[None] + lin('preprocess_msa', msa_feat)
     pair = lin('left_single', target_feat)[:, None] + lin('right_single', target_feat)[None]
+    if monomer:
+        ri = residue_index.long()
+        rel = torch.nn.functional.one_hot(torch.clamp(ri[:, None] - ri[None, :] + MAX_REL, 0, 2 * MAX_REL),
+                                          2 * MAX_REL + 1).to(target_feat.dtype)
+        return msa, pair + lin('pair_activiations', rel)
     rel = relative_features(residue_index, asym_id, entity_id, sym_id, target_feat.dtype)
     return msa, pair + lin('position_activations', rel)
 

@@ -33,3 +33,30 @@ def test_gradient_matches_finite_differences():
     fd = (loss(tf0 + eps * dt, mf0 + eps * dm) - loss(tf0 - eps * dt, mf0 - eps * dm)) / (2 * eps)
     an = float((out['d_target_feat'] * dt).sum() + (out['d_msa_feat'] * dm).sum())
     assert abs(fd - an) <= 1e-6 * max(1.0, abs(an))
+
+
+def test_feature_mask_and_monomer_variant():
+    """Padding rows (all-zero target features) get preprocess_1d = 0 in the multimer embedder (the reference's native
+    embedder, native/embed.cuh:189-197) but not in the monomer one, whose pair term is a single 65-bin one-hot of the
+    clipped residue offset."""
+    import torch
+    from bindcraft2_b200 import synthetic
+    p = synthetic.make_embedder_params(31)
+    inp = synthetic.make_embedder_inputs(32, 6, 10, 1, n_pad=3)
+    msa, pair = EO.embedder(p, inp['target_feat'], inp['msa_feat'], inp['residue_index'], inp['asym_id'], inp['entity_id'],
+                            inp['sym_id'])
+    only_msa = inp['msa_feat'] @ p['preprocess_msa/weights'] + p['preprocess_msa/bias']
+    assert torch.allclose(msa[:, -3:], only_msa[:, -3:])            # padding rows: no preprocess_1d term, not even its bias
+    assert not torch.allclose(msa[:, :3], only_msa[:, :3])
+    pm = synthetic.make_embedder_params(33, monomer=True)
+    im = synthetic.make_embedder_inputs(34, 6, 10, 1, monomer=True, n_pad=3)
+    assert im['target_feat'].shape[1] == 22 and float(im['target_feat'][:, 0].abs().sum()) == 0
+    msa_m, pair_m = EO.embedder(pm, im['target_feat'], im['msa_feat'], im['residue_index'], im['asym_id'], im['entity_id'],
+                                im['sym_id'])
+    only = im['msa_feat'] @ pm['preprocess_msa/weights'] + pm['preprocess_msa/bias']
+    assert torch.allclose(msa_m[:, -3:] - only[:, -3:], pm['preprocess_1d/bias'].expand(1, 3, -1), atol=1e-6)  # bias kept
+    i, j = 2, 5
+    off = int(im['residue_index'][i] - im['residue_index'][j])
+    want = (im['target_feat'][i] @ pm['left_single/weights'] + pm['left_single/bias'] + im['target_feat'][j] @ pm['right_single/weights']
+            + pm['right_single/bias'] + pm['pair_activiations/weights'][min(max(off + 32, 0), 64)] + pm['pair_activiations/bias'])
+    assert torch.allclose(pair_m[i, j], want, atol=1e-5)

@@ -8,11 +8,15 @@ from bindcraft2_b200 import synthetic
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize('nb,nt,s', [(8, 24, 1), (80, 144, 2)])
-def test_embedder_matches_oracle(lib, tmp_path, nb, nt, s):
+@pytest.mark.parametrize('nb,nt,s,monomer,n_pad', [(8, 24, 1, False, 0), (80, 144, 2, False, 0), (20, 44, 1, False, 9),
+                                                  (16, 48, 1, True, 0), (40, 88, 2, True, 5)])
+def test_embedder_matches_oracle(lib, tmp_path, nb, nt, s, monomer, n_pad):
+    """Multimer embedder, the same with trailing padding rows (all-zero target features: the reference's native embedder
+    zeroes preprocess_1d there, forward and backward), and the monomer model's embedder (22-wide target features, 65-bin
+    ``pair_activiations``, no chain terms, no feature mask), selected by the manifest."""
     from bindcraft2_b200 import native
-    p = synthetic.make_embedder_params(501 + nb)
-    inp = synthetic.make_embedder_inputs(502 + nb, nb, nt, s)
+    p = synthetic.make_embedder_params(501 + nb, monomer=monomer)
+    inp = synthetic.make_embedder_inputs(502 + nb, nb, nt, s, monomer=monomer, n_pad=n_pad)
     wdir = native.weights_from_flat(p, str(tmp_path / 'w'))
     t = {k: v.cuda().contiguous() for k, v in inp.items()}
     msa, pair = native.embedder_fwd(t['target_feat'], t['msa_feat'], t['residue_index'], t['asym_id'], t['entity_id'],
