@@ -150,15 +150,20 @@ int bc2_structure_heads_bwd(void* stream, const float* single, const float* pair
  *   target_feat f32 [N,21] (already padded to 21), msa_feat f32 [S,N,49], residue_index / asym_id / entity_id / sym_id as
  *   f32 [N] -> msa f32 [S,N,256] = preprocess_1d(target_feat)[None] + preprocess_msa(msa_feat),
  *   pair f32 [N,N,128] = left_single[:,None] + right_single[None] + position_activations(relative encoding).
+ * Rows whose target_feat is all zero (padding) get preprocess_1d = 0 after the Linear, as in the reference's native
+ * embedder (native/embed.cuh:189-197).
  * weights_dir: the embedder manifest (param/preprocess_1d, preprocess_msa, left_single, right_single,
- * position_activations; bindcraft/af/native.py:516-570). */
+ * position_activations; bindcraft/af/native.py:516-570).  A manifest that holds param/pair_activiations instead selects
+ * the monomer model's embedder (native/embed.cuh:43-62): target_feat is then f32 [N,22], the pair term is the 65-bin
+ * one-hot of the clipped residue offset, the three chain id operands are not read and there is no feature mask. */
 int bc2_embedder_fwd(void* stream, const float* target_feat, const float* msa_feat, const float* residue_index,
                      const float* asym_id, const float* entity_id, const float* sym_id, int64_t N, int64_t S,
                      const char* weights_dir, float* msa, float* pair);
 
 /* Replaces EmbedderBwd (native/ffi.cu:1059-1069, FFI target `native_embed_bwd`): d_msa f32 [S,N,256], d_pair f32
- * [N,N,128], target_feat (accepted as in the reference; the gradient here does not depend on it) ->
- * d_target_feat f32 [N,21], d_msa_feat f32 [S,N,49].  This is where a design step's gradient reaches the sequence. */
+ * [N,N,128], target_feat (the forward's: its all-zero rows take no gradient through preprocess_1d) ->
+ * d_target_feat f32 [N,21] ([N,22] with monomer weights), d_msa_feat f32 [S,N,49].  This is where a design step's
+ * gradient reaches the sequence. */
 int bc2_embedder_bwd(void* stream, const float* d_msa, const float* d_pair, const float* target_feat, int64_t N, int64_t S,
                      const char* weights_dir, float* d_target_feat, float* d_msa_feat);
 
