@@ -4,6 +4,7 @@ accumulation, dropout off, random-init weights, synthetic seeded inputs.
 
     python bench.py --gpus N --steps K --warmup W            # this library (one process per GPU under torchrun)
     python bench.py --impl reference --steps K --warmup W    # CPU arm: the oracle restatement of the JAX trunk
+    torchrun ... bench.py --shard --gpus N --n-res 768       # ONE long complex, pair rows sharded over the N GPUs
 
 One JSON line is printed by rank 0.  `value` is design steps per second over all GPUs (independent trajectories, one
 per GPU, no collectives: the reference's own multi-GPU model); `ms_per_step` is the per-trajectory latency.
@@ -395,6 +396,100 @@ def run_ours(args):
         torch.distributed.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------- one complex over N GPUs
+def run_sharded(args):
+    """The long-complex mode: ONE Evoformer stack forward(save) + backward at N_res = --n-res, the pair representation
+    split by rows over all ranks (exchange steps over NCCL inside the library).  Strong scaling: the work is fixed and
+    `value` is steps per second of that one complex; time = max over ranks of the device-timed region."""
+    from bindcraft2_b200 import _lib, native
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)  # keep stdout for the one JSON line (the communicator prints its version there)
+    try:
+        if world > 1:
+            torch.distributed.init_process_group('nccl', device_id=dev)
+        else:
+            os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+            os.environ.setdefault('MASTER_PORT', '29533')
+            torch.distributed.init_process_group('gloo', rank=0, world_size=1)
+        torch.distributed.barrier()
+        lib = _lib.load()
+        native.shard_init()
+        torch.cuda.synchronize()
+    finally:
+        os.dup2(saved, 1)
+        os.close(saved)
+    n, s, depth = args.n_res, args.msa_rows, args.depth
+    nb = n * 120 // 768
+    wdir = weights_dir_for(depth, rank, world)
+    host = make_inputs(100, nb, n - nb, s)  # the same complex on every rank
+    lo, hi = native.band_of(n, world, rank)
+    t = {k: (v[lo:hi] if k in ('pair', 'ct_pair') else v).contiguous().to(dev) for k, v in host.items()}
+    kw = dict(depth=depth, weights_dir=wdir)
+
+    def step():
+        p, m, psave, msave = native.sharded_evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], save=1, **kw)
+        return native.sharded_evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, **kw)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    step()
+    torch.cuda.synchronize()
+    lib.bc2_profile_mode(1, None)
+    step()
+    classes = profile_report(lib)
+    lib.bc2_profile_mode(0, None)
+    for _ in range(max(args.warmup - 2, 1)):
+        step()
+    sampler = ClockSampler(local)
+    sync_all()
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.bc2_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        dp, dm = step()
+    e1.record()
+    sync_all()
+    launches = lib.bc2_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms_step = e0.elapsed_time(e1) / args.steps
+    status = lib.bc2_device_status()
+    checksum = float(dp.double().abs().sum())
+    (ms_step,) = max_over_ranks([ms_step], dev)
+    native.shard_finalize()
+    if rank == 0:
+        peaks = measured_peaks()
+        total_ms = sum(ms for _, ms in classes.values())
+        table = sorted(((k, c, ms) for k, (c, ms) in classes.items()), key=lambda r: -r[2])
+        exch = sum(ms for k, (c, ms) in classes.items() if k.endswith('.exchange'))
+        step_flops = fwd_bwd_flops(n, s) * depth
+        print(json.dumps({
+            'metric': f'long-complex steps/sec, Evoformer trunk fwd+bwd ({depth} blocks, N_res={n}), pair rows sharded',
+            'value': 1e3 / ms_step, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+            'ms_per_step': ms_step, 'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'bf16',
+            'data': 'synthetic',
+            'config': {'workload': f'ONE Evoformer stack fwd(save)+bwd, depth {depth}, N_res {n} ({nb}+{n - nb}), S {s}, '
+                                   f'pair rows in {world} bands of {n // world}', 'parallelism': f'axial sharding x{world}',
+                       'l2': 'per-rank working set exceeds the 126 MB L2'},
+            'gpu_launches': int(launches), 'clocks': clocks,
+            'step_tflops': step_flops / (ms_step * 1e-3) / 1e12,
+            'step_frac_of_tensor_peak': step_flops / (ms_step * 1e-3) / 1e12 / (peaks['tensor'] * world),
+            'exchange_share_rank0': exch / total_ms if total_ms else None,
+            'kernel_classes_top': [{'name': k, 'launches': c, 'ms': round(ms, 4), 'share': round(ms / total_ms, 4)} for k, c, ms in table[:30]],
+            'dpair_band_abs_sum_rank0': checksum, 'device_status': status}))
+    torch.distributed.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -407,9 +502,12 @@ def main():
     ap.add_argument('--own-save', type=int, default=0)
     ap.add_argument('--cpu-reps', type=int, default=5)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--shard', action='store_true', help='one complex, pair rows sharded over the ranks (strong scaling)')
     args = ap.parse_args()
     if args.impl == 'reference':
         run_reference(args)
+    elif args.shard:
+        run_sharded(args)
     else:
         run_ours(args)
 

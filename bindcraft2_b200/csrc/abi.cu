@@ -7,7 +7,10 @@
 #include <tuple>
 
 #include "../../include/bc2_b200.h"
+#include <thread>
+
 #include "stack.cuh"
+#include "sharded.cuh"
 #include "structure_heads.cuh"
 #include "embedder.cuh"
 
@@ -122,6 +125,30 @@ sm::StructureHeads* get_heads(int N, int depth, const std::string& dir) {
   sm::StructureHeads* p = s.get();
   g_heads.emplace(k, std::move(s));
   fprintf(stderr, "native: post-trunk N=%d depth=%d (%.1f MB)\n", N, depth, (p->A.bytes + p->core.A.bytes) / 1e6);
+  return p;
+}
+
+// Sharded stack: one exchange object per process (set by bc2_shard_init) and stacks cached like the others.
+std::unique_ptr<NcclComm> g_shard_comm;
+using ShardKey = std::tuple<int, int, int, int, std::string>;
+std::map<ShardKey, std::unique_ptr<ShardedEvoStack>> g_sharded;
+
+ShardedEvoStack* get_sharded(int N, int S, int depth, const std::string& dir) {
+  BC2_CHECK(g_shard_comm, "bc2_shard_init has not been called in this process");
+  int dev = 0;
+  BC2_CUDA(cudaGetDevice(&dev));
+  ShardKey k{dev, N, S, depth, dir};
+  auto it = g_sharded.find(k);
+  if (it != g_sharded.end()) return it->second.get();
+  StackConfig c;
+  c.N = N;
+  c.S = S;
+  c.depth = depth;
+  auto s = std::make_unique<ShardedEvoStack>(c, dir, g_shard_comm.get());
+  ShardedEvoStack* p = s.get();
+  g_sharded.emplace(k, std::move(s));
+  fprintf(stderr, "native: sharded stack rank %d/%d N=%d (band of %d rows) S=%d depth=%d (%.2f GB)\n", p->rank, p->P, N, p->R, S,
+          depth, p->A.bytes / 1e9);
   return p;
 }
 
@@ -419,6 +446,141 @@ int native_sm_prealloc(int N, int depth, const char* weights_dir) {
   }
 }
 
+// ---- one complex over several GPUs (no counterpart in the reference, which shards over trajectories only) ----------
+
+int bc2_shard_unique_id(uint8_t* id128) {
+  try {
+    BC2_CHECK(id128, "null operand");
+    static_assert(sizeof(ncclUniqueId) == 128, "NCCL unique id size");
+    ncclUniqueId id;
+    BC2_NCCL(NcclApi::get().GetUniqueId(&id));
+    memcpy(id128, &id, 128);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_shard_init(int world, int rank, const uint8_t* id128) {
+  try {
+    BC2_CHECK(id128 && world >= 1 && rank >= 0 && rank < world, "bad world / rank / id");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    g_sharded.clear();
+    g_shard_comm.reset();
+    ncclUniqueId id;
+    memcpy(&id, id128, 128);
+    g_shard_comm = std::make_unique<NcclComm>(world, rank, id);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+void bc2_shard_finalize(void) {
+  std::lock_guard<std::recursive_mutex> lock(g_mu);
+  g_sharded.clear();
+  g_shard_comm.reset();
+}
+
+int bc2_evoformer_sharded_fwd(void* stream, const float* pair_band, const float* msa, const float* pair_mask,
+                              const float* msa_mask, int64_t N, int64_t S, int64_t depth, int64_t save,
+                              const char* weights_dir, float* pair_out_band, float* msa_out, uint16_t* psave_band,
+                              float* msave) {
+  try {
+    BC2_CHECK(pair_band && msa && pair_mask && msa_mask && pair_out_band && msa_out && weights_dir, "null operand");
+    BC2_CHECK(!save || (psave_band && msave), "save != 0 needs psave and msave");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    ShardedEvoStack* s = get_sharded((int)N, (int)S, (int)depth, weights_dir);
+    s->forward(pair_band, msa, pair_mask, msa_mask, pair_out_band, msa_out,
+               save ? reinterpret_cast<bf16*>(psave_band) : nullptr, save ? msave : nullptr, (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_evoformer_sharded_bwd(void* stream, const float* ct_pair_band, const float* ct_msa, const float* pair_mask,
+                              const float* msa_mask, const uint16_t* psave_band, const float* msave, int64_t N, int64_t S,
+                              int64_t depth, const char* weights_dir, float* dpair_band, float* dmsa) {
+  try {
+    BC2_CHECK(ct_pair_band && ct_msa && pair_mask && msa_mask && psave_band && msave && dpair_band && dmsa && weights_dir,
+              "null operand");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    ShardedEvoStack* s = get_sharded((int)N, (int)S, (int)depth, weights_dir);
+    s->backward(ct_pair_band, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave_band), msave, dpair_band, dmsa,
+                (cudaStream_t)stream);
+    BC2_CUDA(cudaGetLastError());
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
+int bc2_test_sharded_local(int P, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
+                           const float* ct_pair, const float* ct_msa, int64_t N, int64_t S, int64_t depth,
+                           const char* weights_dir, float* pair_out, float* msa_out, float* dpair, float* dmsa) {
+  try {
+    BC2_CHECK(pair && msa && pair_mask && msa_mask && ct_pair && ct_msa && pair_out && msa_out && dpair && dmsa && weights_dir,
+              "null operand");
+    BC2_CHECK(P >= 1 && P <= kMaxLocalRanks, "1 to 8 local ranks");
+    std::lock_guard<std::recursive_mutex> lock(g_mu);
+    int dev = 0;
+    BC2_CUDA(cudaGetDevice(&dev));
+    LocalWorld world(P);
+    DeviceArena extra;
+    std::vector<std::unique_ptr<LocalComm>> comms;
+    std::vector<std::unique_ptr<ShardedEvoStack>> stacks;
+    std::vector<cudaStream_t> streams(P);
+    StackConfig c;
+    c.N = (int)N;
+    c.S = (int)S;
+    c.depth = (int)depth;
+    for (int r = 0; r < P; ++r) {
+      comms.push_back(std::make_unique<LocalComm>(&world, r, &extra));
+      stacks.push_back(std::make_unique<ShardedEvoStack>(c, weights_dir, comms.back().get()));
+      BC2_CUDA(cudaStreamCreateWithFlags(&streams[r], cudaStreamNonBlocking));
+    }
+    const long band = (long)(N / P) * N * c.Cz, nm = (long)S * N * c.Cm;
+    std::vector<bf16*> psave(P);
+    std::vector<float*> msave(P), mo(P), dm(P);
+    for (int r = 0; r < P; ++r) {
+      psave[r] = extra.alloc<bf16>(band * depth);
+      msave[r] = extra.alloc<float>(nm * depth);
+      mo[r] = r == 0 ? msa_out : extra.alloc<float>(nm);
+      dm[r] = r == 0 ? dmsa : extra.alloc<float>(nm);
+    }
+    BC2_CUDA(cudaDeviceSynchronize());
+    std::vector<std::string> errs(P);
+    std::vector<std::thread> threads;
+    for (int r = 0; r < P; ++r) {
+      threads.emplace_back([&, r] {
+        std::unique_lock<std::mutex> held(world.issue);
+        comms[r]->held = &held;
+        try {
+          BC2_CUDA(cudaSetDevice(dev));
+          ShardedEvoStack* s = stacks[r].get();
+          cudaStream_t st = streams[r];
+          s->forward(pair + r * band, msa, pair_mask, msa_mask, pair_out + r * band, mo[r], psave[r], msave[r], st);
+          s->backward(ct_pair + r * band, ct_msa, pair_mask, msa_mask, psave[r], msave[r], dpair + r * band, dm[r], st);
+          BC2_CUDA(cudaStreamSynchronize(st));
+          BC2_CUDA(cudaGetLastError());
+        } catch (const std::exception& e) {
+          errs[r] = e.what();
+          world.fail();
+        }
+      });
+    }
+    for (auto& t : threads) t.join();
+    for (auto& st : streams) cudaStreamDestroy(st);
+    for (int r = 0; r < P; ++r)
+      BC2_CHECK(errs[r].empty(), "local rank " + std::to_string(r) + ": " + errs[r]);
+    return 0;
+  } catch (const std::exception& e) {
+    return fail(e);
+  }
+}
+
 void bc2_release_all(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
   g_heads.clear();
@@ -427,6 +589,7 @@ void bc2_release_all(void) {
   g_stacks.clear();
   g_tpl.clear();
   g_tplembed.clear();
+  g_sharded.clear();
 }
 
 const char* bc2_last_error(void) { return t_error.c_str(); }

@@ -265,6 +265,7 @@ struct EpiOpmOut {
   const float* msa_mask = nullptr;  // [S][Nres]
   int S = 0, Nres = 0;
   int M = 0, N = 0;
+  int row0 = 0;  // residue index of output row 0 (a band of rows i of the pair tensor computes rows row0 .. row0+M-1)
   static constexpr bool kPaired = false;
   __device__ __forceinline__ void operator()(int, int m, int n0, const float (&v)[32]) const {
     if (m >= M || n0 >= N) return;
@@ -274,7 +275,7 @@ struct EpiOpmOut {
 #pragma unroll
     for (int q = 0; q < 4; ++q) ld_global_v8(res_in + off + q * 8, *reinterpret_cast<uint32_t(*)[8]>(&r[q * 8]));
     float nrm = 1e-3f;
-    for (int s = 0; s < S; ++s) nrm += msa_mask[(long)s * Nres + m] * msa_mask[(long)s * Nres + j];
+    for (int s = 0; s < S; ++s) nrm += msa_mask[(long)s * Nres + m + row0] * msa_mask[(long)s * Nres + j];
     const float inv = 1.f / nrm;
     const float4* bp = reinterpret_cast<const float4*>(bias + f0);
 #pragma unroll

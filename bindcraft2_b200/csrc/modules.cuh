@@ -13,6 +13,7 @@
 #include "msa.cuh"
 #include "msa_global.cuh"
 #include "norm.cuh"
+#include "shard_comm.cuh"
 #include "weights.cuh"
 
 namespace bc2 {
@@ -48,6 +49,7 @@ struct Scratch {
   bf16 *dt = nullptr, *dab = nullptr;  // channel-major planes (pair stream only)
   float *delta = nullptr, *dnb = nullptr, *dq_acc = nullptr, *ref_dkv = nullptr;
   bf16* ds_store = nullptr;  // triangle attention backward: dS of every batch row (see AttnArgs::ds_store)
+  bf16* stage = nullptr;     // sharded tri-mul: staging block of the plane exchanges (allocated by the first user)
   void init(DeviceArena& A, long rows_, int C_, int wide_, bool pair, int n_res, int max_heads) {
     rows = rows_; C = C_; wide = wide_;
     x = A.alloc<bf16>(rows * C); y = A.alloc<bf16>(rows * C); dx = A.alloc<bf16>(rows * C);
@@ -60,6 +62,22 @@ struct Scratch {
     if (kUseRefKernels) ref_dkv = A.alloc<float>(rows * 2 * C);
   }
 };
+
+// Sharded stack: every rank has produced the attention pair bias of its band of R query rows into a compact block
+// [H][n][R] floats followed by [H][n/8][R][8] halves (`mine`, H*n*R*6 bytes).  Gather all bands (`all`, P such blocks)
+// and spread them into the whole [H][n][n] / [H][n/8][n][8] arrays the attention kernels read.
+inline void gather_bias(ShardComm* comm, const char* mine, char* all, float* nb, __half* nb16, int H, int n, int R,
+                        cudaStream_t st) {
+  const size_t cnt = (size_t)H * n * R, blk = cnt * 6;
+  comm->all_gather(mine, all, blk, st);
+  for (int r = 0; r < comm->P; ++r) {
+    const char* src = all + (size_t)r * blk;
+    BC2_CUDA(cudaMemcpy2DAsync(nb + (size_t)r * R, (size_t)n * 4, src, (size_t)R * 4, (size_t)R * 4, (size_t)H * n,
+                               cudaMemcpyDeviceToDevice, st));
+    BC2_CUDA(cudaMemcpy2DAsync(nb16 + (size_t)r * R * 8, (size_t)n * 16, src + cnt * 4, (size_t)R * 16, (size_t)R * 16,
+                               (size_t)H * n / 8, cudaMemcpyDeviceToDevice, st));
+  }
+}
 
 struct LnW {
   float *scale = nullptr, *offset = nullptr;
@@ -150,29 +168,69 @@ struct TriMul {
   GemmPlan g_con, gb_da, gb_db;  // activation x activation: shared by all blocks
   bf16 *gate = nullptr, *ab = nullptr, *t = nullptr, *ob = nullptr, *g2 = nullptr;
   Scratch* S = nullptr;
+  // Sharded stack (comm != null): this rank holds a band of R pair rows, M = R*n positions.  Everything per position
+  // (norms, projections, gates) runs on the band.  The contraction mixes all rows, so it runs per CHANNEL instead: an
+  // all-to-all turns the band's planes of all Hc channels into whole n x n planes of Hc/P channels (abF), the
+  // contraction and its two gradients run on those with the unchanged plans (batch = Hc/P), and a second all-to-all
+  // brings the result planes (tF, dabF) back to bands.
+  ShardComm* comm = nullptr;
+  int Hl = 0;  // channels contracted on this rank
+  bf16 *abF = nullptr, *tF = nullptr, *dtF = nullptr, *dabF = nullptr;
 
-  void init(DeviceArena& A, Scratch* s, int n_, int C_, int Hc_, bool outgoing_) {
-    S = s; n = n_; C = C_; Hc = Hc_; outgoing = outgoing_;
-    M = (long)n * n;
+  void init(DeviceArena& A, Scratch* s, int n_, int C_, int Hc_, bool outgoing_, int R = 0, ShardComm* comm_ = nullptr) {
+    S = s; n = n_; C = C_; Hc = Hc_; outgoing = outgoing_; comm = comm_;
+    if (R <= 0) R = n;
+    M = (long)R * n;
+    BC2_CHECK(comm || R == n, "a band of pair rows needs an exchange object");
     gate = A.alloc<bf16>(M * 2 * Hc);
     ab = A.alloc<bf16>(M * 2 * Hc);
     t = A.alloc<bf16>(M * Hc);
     ob = A.alloc<bf16>(M * C);
     g2 = A.alloc<bf16>(M * C);
-    const bf16 *a = ab, *bq = ab + (long)Hc * M;           // left planes, right planes
-    auto K = [&](const bf16* p) { return Operand{p, n, M, false}; };
-    auto T = [&](const bf16* p) { return Operand{p, n, M, true}; };
+    const long MF = (long)n * n;  // positions of one whole plane
+    Hl = Hc;
+    const bf16 *a = ab, *bq = ab + (long)Hc * M, *dt = S->dt;  // left planes, right planes, d(t) planes
+    if (comm) {
+      BC2_CHECK(Hc % comm->P == 0 && M % 128 == 0, "sharded tri-mul: hidden channels and band size must divide evenly");
+      Hl = Hc / comm->P;
+      abF = A.alloc<bf16>(2L * Hl * MF);
+      tF = A.alloc<bf16>((long)Hl * MF);
+      dtF = A.alloc<bf16>((long)Hl * MF);
+      dabF = A.alloc<bf16>(2L * Hl * MF);
+      if (!S->stage) S->stage = A.alloc<bf16>(M * Hc);
+      a = abF; bq = abF + (long)Hl * MF; dt = dtF;
+    }
+    auto K = [&](const bf16* p) { return Operand{p, n, MF, false}; };
+    auto T = [&](const bf16* p) { return Operand{p, n, MF, true}; };
     if (outgoing) {
       // t[i,j] = sum_k a[i,k] b[j,k];  da[i,k] = sum_j dt[i,j] b[j,k];  db[j,k] = sum_i dt[i,j] a[i,k]
-      g_con = make_gemm(K(a), K(bq), n, n, n, Hc, 128);
-      gb_da = make_gemm(K(S->dt), T(bq), n, n, n, Hc, 128);
-      gb_db = make_gemm(T(S->dt), T(a), n, n, n, Hc, 128);
+      g_con = make_gemm(K(a), K(bq), n, n, n, Hl, 128);
+      gb_da = make_gemm(K(dt), T(bq), n, n, n, Hl, 128);
+      gb_db = make_gemm(T(dt), T(a), n, n, n, Hl, 128);
     } else {
       // t[i,j] = sum_k r[k,i] l[k,j];  dr[k,i] = sum_j l[k,j] dt[i,j];  dl[k,j] = sum_i r[k,i] dt[i,j]   (l = a, r = b)
-      g_con = make_gemm(T(bq), T(a), n, n, n, Hc, 128);
-      gb_db = make_gemm(K(a), K(S->dt), n, n, n, Hc, 128);
-      gb_da = make_gemm(K(bq), T(S->dt), n, n, n, Hc, 128);
+      g_con = make_gemm(T(bq), T(a), n, n, n, Hl, 128);
+      gb_db = make_gemm(K(a), K(dt), n, n, n, Hl, 128);
+      gb_da = make_gemm(K(bq), T(dt), n, n, n, Hl, 128);
     }
+  }
+  // band planes [npl][M] -> whole planes [npl/P][n*n] of this rank's channel group
+  void planes_to_channels(const bf16* src, bf16* dst, int npl, cudaStream_t st) {
+    const int P = comm->P, per = npl / P;
+    const size_t MF = (size_t)n * n;
+    comm->all_to_all(src, S->stage, (size_t)per * M * 2, st);
+    for (int r = 0; r < P; ++r)
+      BC2_CUDA(cudaMemcpy2DAsync(dst + (size_t)r * M, MF * 2, S->stage + (size_t)r * per * M, (size_t)M * 2, (size_t)M * 2, per,
+                                 cudaMemcpyDeviceToDevice, st));
+  }
+  // whole planes [npl/P][n*n] of this rank's channel group -> band planes [npl][M]
+  void channels_to_planes(const bf16* src, bf16* dst, int npl, cudaStream_t st) {
+    const int P = comm->P, per = npl / P;
+    const size_t MF = (size_t)n * n;
+    for (int q = 0; q < P; ++q)
+      BC2_CUDA(cudaMemcpy2DAsync(S->stage + (size_t)q * per * M, (size_t)M * 2, src + (size_t)q * M, MF * 2, (size_t)M * 2, per,
+                                 cudaMemcpyDeviceToDevice, st));
+    comm->all_to_all(S->stage, dst, (size_t)per * M * 2, st);
   }
   void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
     W b;
@@ -238,8 +296,15 @@ struct TriMul {
     { ProfScope ps_("TriMul.forward.ln_fwd_c", st); ln_fwd_c(C, l, st); }
     EpiProjGate ep; ep.bias_p = b.bp; ep.bias_g = b.bg; ep.mask = mask; ep.gate_out = gate; ep.ab_out = ab; ep.M = Mi; ep.CH = CH;
     { ProfScope ps_("TriMul.forward.gemm.g_pg", st); run_gemm(b.g_pg, ep, st); }
-    EpiStore ec; ec.out = t; ec.ldo = n; ec.bso = M; ec.M = n; ec.N = n;
-    { ProfScope ps_("TriMul.forward.gemm.g_con", st); run_gemm(g_con, ec, st); }
+    if (comm) {
+      { ProfScope ps_("TriMul.forward.exchange", st); planes_to_channels(ab, abF, Hc, st); planes_to_channels(ab + (long)Hc * M, abF + (long)Hl * n * n, Hc, st); }
+      EpiStore ec; ec.out = tF; ec.ldo = n; ec.bso = (long)n * n; ec.M = n; ec.N = n;
+      { ProfScope ps_("TriMul.forward.gemm.g_con", st); run_gemm(g_con, ec, st); }
+      { ProfScope ps_("TriMul.forward.exchange", st); channels_to_planes(tF, t, Hc, st); }
+    } else {
+      EpiStore ec; ec.out = t; ec.ldo = n; ec.bso = M; ec.M = n; ec.N = n;
+      { ProfScope ps_("TriMul.forward.gemm.g_con", st); run_gemm(g_con, ec, st); }
+    }
     { ProfScope ps_("TriMul.forward.cln_fwd_c", st); cln_fwd_c(t, b.cn, S->y, st); }
     EpiStore eg; eg.out = g2; eg.ldo = C; eg.bias = b.bg2; eg.act = 2; eg.act_from = 0; eg.M = Mi; eg.N = C;
     { ProfScope ps_("TriMul.forward.gemm.g_g2", st); run_gemm(b.g_g2, eg, st); }
@@ -253,10 +318,20 @@ struct TriMul {
     EpiStore ey; ey.out = S->dy; ey.ldo = Hc; ey.M = Mi; ey.N = Hc;
     { ProfScope ps_("TriMul.backward.gemm.gb_o", st); run_gemm(b.gb_o, ey, st); }
     { ProfScope ps_("TriMul.backward.cln_bwd_c", st); cln_bwd_c(t, b.cn, S->dy, S->dt, st); }
-    EpiStore ea; ea.out = S->dab; ea.ldo = n; ea.bso = M; ea.M = n; ea.N = n;
-    { ProfScope ps_("TriMul.backward.gemm.gb_da", st); run_gemm(gb_da, ea, st); }
-    EpiStore eb = ea; eb.out = S->dab + (long)Hc * M;
-    { ProfScope ps_("TriMul.backward.gemm.gb_db", st); run_gemm(gb_db, eb, st); }
+    if (comm) {
+      const long MF = (long)n * n;
+      { ProfScope ps_("TriMul.backward.exchange", st); planes_to_channels(S->dt, dtF, Hc, st); }
+      EpiStore ea; ea.out = dabF; ea.ldo = n; ea.bso = MF; ea.M = n; ea.N = n;
+      { ProfScope ps_("TriMul.backward.gemm.gb_da", st); run_gemm(gb_da, ea, st); }
+      EpiStore eb = ea; eb.out = dabF + (long)Hl * MF;
+      { ProfScope ps_("TriMul.backward.gemm.gb_db", st); run_gemm(gb_db, eb, st); }
+      { ProfScope ps_("TriMul.backward.exchange", st); channels_to_planes(dabF, S->dab, Hc, st); channels_to_planes(dabF + (long)Hl * MF, S->dab + (long)Hc * M, Hc, st); }
+    } else {
+      EpiStore ea; ea.out = S->dab; ea.ldo = n; ea.bso = M; ea.M = n; ea.N = n;
+      { ProfScope ps_("TriMul.backward.gemm.gb_da", st); run_gemm(gb_da, ea, st); }
+      EpiStore eb = ea; eb.out = S->dab + (long)Hc * M;
+      { ProfScope ps_("TriMul.backward.gemm.gb_db", st); run_gemm(gb_db, eb, st); }
+    }
     dim3 grid((unsigned)(M / 64), CH / 64);
     { ProfScope ps_("TriMul.backward.trimul_bwd_gate_kernel", st); launch_pdl(trimul_bwd_gate_kernel, grid, dim3(256), 0, st, S->dab, ab, gate, mask, S->big, (long)KC, M, CH); }
     EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
@@ -330,20 +405,38 @@ struct TriAttn {
   AttnPlan plan;
   Scratch* S = nullptr;
 
-  void init(DeviceArena& A, Scratch* s, int n_, int C_, int H_, int D_, bool ending_, const float* pair_mask) {
-    S = s; n = n_; C = C_; H = H_; D = D_; ending = ending_;
-    M = (long)n * n;
+  // Sharded stack (comm != null): this rank holds a band of R batch rows starting at row0 (M = R*n positions).  The
+  // attention itself is local to a batch row; only the pair bias b[h][q][k] = Linear(LN(x[q][k])) needs every row, so
+  // each rank produces the bias of its band of QUERY rows and the bands are all-gathered; in the backward the bias
+  // gradient is summed over ranks and each rank takes the rows of its band.  (The ending-node orientation is run by the
+  // sharded stack as this module on the transposed pair stream, so `ending` stays false there.)
+  ShardComm* comm = nullptr;
+  int R = 0, row0 = 0;
+  char *bias_mine = nullptr, *bias_all = nullptr;
+
+  void init(DeviceArena& A, Scratch* s, int n_, int C_, int H_, int D_, bool ending_, const float* pair_mask, int R_ = 0,
+            int row0_ = 0, ShardComm* comm_ = nullptr) {
+    S = s; n = n_; C = C_; H = H_; D = D_; ending = ending_; comm = comm_;
+    R = R_ > 0 ? R_ : n; row0 = row0_;
+    BC2_CHECK(comm || R == n, "a band of pair rows needs an exchange object");
+    BC2_CHECK(!comm || !ending, "sharded triangle attention runs in the row orientation");
+    M = (long)R * n;
+    const long MF = (long)n * n;
     const int HD = H * D;
     BC2_CHECK(HD == C, "triangle attention: heads x width must equal the channel count");
     qkvg = A.alloc<bf16>(M * 4 * HD);
     o = A.alloc<bf16>(M * HD);
-    nb = A.alloc<float>((long)H * M);
-    nb16 = A.alloc<__half>((long)H * M);
-    lse = A.alloc<float>(2L * n * H * n);
+    nb = A.alloc<float>((long)H * MF);
+    nb16 = A.alloc<__half>((long)H * MF);
+    lse = A.alloc<float>(2L * R * H * n);
+    if (comm) {
+      bias_mine = A.alloc<char>((size_t)H * n * R * 6);
+      bias_all = A.alloc<char>((size_t)H * n * R * 6 * comm->P);
+    }
     AttnArgs& a = plan.args;
     a.qkvg = qkvg; a.ld = 4 * HD;
     a.row_b = ending ? 1 : n; a.row_p = ending ? n : 1;
-    a.B = n; a.N = n; a.H = H; a.D = D;
+    a.B = R; a.N = n; a.H = H; a.D = D;
     a.bias = nb; a.bias16 = nb16; a.mask = pair_mask; a.mask_b = ending ? 1 : n; a.mask_k = ending ? n : 1;
     a.o = o; a.og = S->y; a.lse = lse;
     a.d_o = S->d_o; a.delta = S->delta; a.d_qkv = S->big; a.d_bias = S->dnb; a.dq_acc = S->dq_acc;
@@ -352,7 +445,7 @@ struct TriAttn {
     // BC2_DETERMINISTIC=1: the bias gradient is summed over batch rows in a fixed order from a bf16 copy of dS
     // (n*H*n*n elements, shared by every triangle attention of the stack; at most 1 GiB, n <= ~500) instead of with
     // fp32 atomics.  Bit-reproducible from run to run, about 1 % slower at n = 224 (the copy is written and read once).
-    const long ds_elems = (long)n * H * n * n;
+    const long ds_elems = (long)R * H * n * n;
     const char* det = getenv("BC2_DETERMINISTIC");
     if (det && det[0] == '1' && plan.tc && ds_elems * 2 <= (1L << 30)) {
       if (!S->ds_store) S->ds_store = A.alloc<bf16>(ds_elems);
@@ -372,19 +465,27 @@ struct TriAttn {
     b.gb_qkvg = make_gemm(kmaj(S->big, 4 * HD), kmaj(b.a.wqkvg_b, 4 * HD), Mi, C, 4 * HD);
     w.push_back(b);
   }
-  void forward(int blk, const float* in, float* out, cudaStream_t st) {
+  // residual = false: out = module(in) alone (the sharded stack adds it to the stream after transposing it back)
+  void forward(int blk, const float* in, float* out, cudaStream_t st, bool residual = true) {
     W& b = w[blk];
     const int Mi = (int)M, HD = H * D;
     LnArgs l; l.x = in; l.scale = b.ln.scale; l.offset = b.ln.offset; l.y = S->x; l.ldy = C; l.M = Mi;
     l.wb = b.wb; l.nb = nb; l.nb16 = nb16; l.H = H; l.n = n; l.transposed = ending ? 1 : 0;
+    if (comm) {  // compact [H][n][R] block of this band's query rows
+      l.nb = reinterpret_cast<float*>(bias_mine);
+      l.nb16 = reinterpret_cast<__half*>(bias_mine + (size_t)H * n * R * 4);
+      l.qs = R;
+    }
     { ProfScope ps_("TriAttn.forward.ln_fwd_c", st); ln_fwd_c(C, l, st); }
+    if (comm) { ProfScope ps_("TriAttn.forward.exchange", st); gather_bias(comm, bias_mine, bias_all, nb, nb16, H, n, R, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
     { ProfScope ps_("TriAttn.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
     { ProfScope ps_("TriAttn.forward.attn_fwd", st); attn_fwd(plan, st); }
-    EpiResidual er; er.res_in = in; er.res_out = out; er.ld = C; er.bias = b.a.bo; er.M = Mi; er.N = C; er.drop = drop;
+    EpiResidual er; er.res_in = residual ? in : nullptr; er.res_out = out; er.ld = C; er.bias = b.a.bo; er.M = Mi; er.N = C; er.drop = drop;
     { ProfScope ps_("TriAttn.forward.gemm.g_o", st); run_gemm(b.g_o, er, st); }
   }
-  void backward(int blk, const float* in, float* g, cudaStream_t st) {
+  // g_branch != null: the module's own contribution J(in)^T g goes there and g is left as it is
+  void backward(int blk, const float* in, float* g, cudaStream_t st, float* g_branch = nullptr) {
     W& b = w[blk];
     const int Mi = (int)M, HD = H * D;
     { ProfScope ps_("TriAttn.backward.cvt_f32_bf16", st); cvt_drop_f32_bf16(g, S->dy, M, C, drop, st); }
@@ -392,13 +493,15 @@ struct TriAttn {
     EpiAttnPrep e; e.o = o; e.qkvg = qkvg; e.ld = 4L * HD; e.d_o = S->d_o; e.d_qkvg = S->big; e.delta = S->delta;
     e.row_b = plan.args.row_b; e.row_p = plan.args.row_p; e.Nres = n; e.H = H; e.D = D; e.M = Mi; e.N = HD;
     { ProfScope ps_("TriAttn.backward.gemm.gb_o", st); run_gemm(b.gb_o, e, st); }
-    if (!plan.args.ds_store) { ProfScope ps_("TriAttn.backward.memset", st); BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * M * 4, st)); }
+    if (!plan.args.ds_store) { ProfScope ps_("TriAttn.backward.memset", st); BC2_CUDA(cudaMemsetAsync(S->dnb, 0, (size_t)H * n * n * 4, st)); }
     { ProfScope ps_("TriAttn.backward.attn_bwd", st); attn_bwd(plan, st); }
     if (plan.args.ds_store) { ProfScope ps_("TriAttn.backward.attn_dbias_reduce", st); attn_dbias_reduce(plan.args, st); }
+    if (comm) { ProfScope ps_("TriAttn.backward.exchange", st); comm->all_reduce_f32(S->dnb, (size_t)H * n * n, st); }
     EpiStore ex; ex.out = S->dx; ex.ldo = C; ex.M = Mi; ex.N = C;
     { ProfScope ps_("TriAttn.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
-    LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.wb = b.wb; l.dnb = S->dnb; l.H = H; l.n = n;
-    l.transposed = ending ? 1 : 0; l.g_in = g; l.g_out = g; l.M = Mi;
+    LnBwdArgs l; l.x = in; l.scale = b.ln.scale; l.dy = S->dx; l.ldy = C; l.wb = b.wb; l.dnb = S->dnb + row0; l.H = H; l.n = n;
+    l.hs = (long)n * n;  // the band reads its query rows of the whole [H][n][n] gradient
+    l.transposed = ending ? 1 : 0; l.g_in = g_branch ? nullptr : g; l.g_out = g_branch ? g_branch : g; l.M = Mi;
     { ProfScope ps_("TriAttn.backward.ln_bwd_c", st); ln_bwd_c(C, l, st); }
   }
 };
@@ -421,9 +524,22 @@ struct MsaRow {
   __half* nb16 = nullptr;
   AttnPlan plan;
   Scratch* S = nullptr;
+  // Sharded stack (comm != null): the msa is replicated, the pair stream is a band of R rows starting at row0.  The pair
+  // bias of the band's query rows is all-gathered (as in TriAttn); the bias gradient is computed whole on every rank
+  // (the msa side is replicated) and each rank back-propagates the rows of its band into its pair cotangent.
+  ShardComm* comm = nullptr;
+  int R = 0, row0 = 0;
+  char *bias_mine = nullptr, *bias_all = nullptr;
 
-  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, int Cz_, int H_, const float* msa_mask) {
+  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, int Cz_, int H_, const float* msa_mask, int R_ = 0,
+            int row0_ = 0, ShardComm* comm_ = nullptr) {
     S = s; n = n_; S_ = S__; Cm = Cm_; Cz = Cz_; H = H_; Dreal = Cm / H; D = std::max(Dreal, 16);
+    comm = comm_; R = R_ > 0 ? R_ : n; row0 = row0_;
+    BC2_CHECK(comm || R == n, "a band of pair rows needs an exchange object");
+    if (comm) {
+      bias_mine = A.alloc<char>((size_t)H * n * R * 6);
+      bias_all = A.alloc<char>((size_t)H * n * R * 6 * comm->P);
+    }
     Mm = (long)S_ * n; Mp = (long)n * n;
     const int HD = H * D;
     qkvg = A.alloc<bf16>(Mm * 4 * HD);
@@ -458,8 +574,14 @@ struct MsaRow {
     const int Mi = (int)Mm, HD = H * D;
     LnArgs l; l.x = msa_in; l.scale = b.qn.scale; l.offset = b.qn.offset; l.y = S->x; l.ldy = Cm; l.M = Mi;
     { ProfScope ps_("MsaRow.forward.ln_fwd_c", st); ln_fwd_c(Cm, l, st); }
-    LnArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.offset = b.fn.offset; lp.wb = b.wb; lp.nb = nb; lp.nb16 = nb16; lp.H = H; lp.n = n; lp.M = (int)Mp;
+    LnArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.offset = b.fn.offset; lp.wb = b.wb; lp.nb = nb; lp.nb16 = nb16; lp.H = H; lp.n = n; lp.M = (int)((long)R * n);
+    if (comm) {
+      lp.nb = reinterpret_cast<float*>(bias_mine);
+      lp.nb16 = reinterpret_cast<__half*>(bias_mine + (size_t)H * n * R * 4);
+      lp.qs = R;
+    }
     { ProfScope ps_("MsaRow.forward.ln_fwd_c", st); ln_fwd_c(Cz, lp, st); }
+    if (comm) { ProfScope ps_("MsaRow.forward.exchange", st); gather_bias(comm, bias_mine, bias_all, nb, nb16, H, n, R, st); }
     EpiStore e; e.out = qkvg; e.ldo = 4 * HD; e.bias = b.a.bqkvg; e.act = 2; e.act_from = 3 * HD; e.M = Mi; e.N = 4 * HD;
     { ProfScope ps_("MsaRow.forward.gemm.g_qkvg", st); run_gemm(b.g_qkvg, e, st); }
     { ProfScope ps_("MsaRow.forward.attn_fwd", st); attn_fwd(plan, st); }
@@ -479,7 +601,7 @@ struct MsaRow {
     { ProfScope ps_("MsaRow.backward.gemm.gb_qkvg", st); run_gemm(b.gb_qkvg, ex, st); }
     LnBwdArgs l; l.x = msa_in; l.scale = b.qn.scale; l.dy = S->dx; l.ldy = Cm; l.g_in = g_msa; l.g_out = g_msa; l.M = Mi;
     { ProfScope ps_("MsaRow.backward.ln_bwd_c", st); ln_bwd_c(Cm, l, st); }
-    LnBwdArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.wb = b.wb; lp.dnb = dnb; lp.H = H; lp.n = n; lp.g_in = g_pair; lp.g_out = g_pair; lp.M = (int)Mp;
+    LnBwdArgs lp; lp.x = pair; lp.scale = b.fn.scale; lp.wb = b.wb; lp.dnb = dnb + row0; lp.hs = Mp; lp.H = H; lp.n = n; lp.g_in = g_pair; lp.g_out = g_pair; lp.M = (int)((long)R * n);
     { ProfScope ps_("MsaRow.backward.ln_bwd_c", st); ln_bwd_c(Cz, lp, st); }
   }
 };
@@ -615,8 +737,16 @@ struct Opm {
   GemmPlan g_out2[2], g_dleft2[2], g_dtmp2[2];
   const float* msa_mask = nullptr;
   Scratch* S = nullptr;
-  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, const float* mask) {
+  // Sharded stack (comm != null): the msa-side products are replicated; the last product writes only the band of R pair
+  // rows this rank holds, and in the backward the bands of the scaled pair cotangent are all-gathered so that the
+  // msa-side gradient (a sum over all pair positions) is again computed whole on every rank.
+  ShardComm* comm = nullptr;
+  int R = 0, row0 = 0;
+  void init(DeviceArena& A, Scratch* s, int n_, int S__, int Cm_, const float* mask, int R_ = 0, int row0_ = 0,
+            ShardComm* comm_ = nullptr) {
     S = s; n = n_; S_ = S__; Cm = Cm_; Mm = (long)S_ * n; msa_mask = mask;
+    comm = comm_; R = R_ > 0 ? R_ : n; row0 = row0_;
+    BC2_CHECK(comm || R == n, "a band of pair rows needs an exchange object");
     const int K = 32 * S_;
     const long NF = (long)n * OPM_F;
     for (int i = 0; i < 2; ++i) {
@@ -633,7 +763,7 @@ struct Opm {
     BC2_CHECK(NF % (kSplit * 64) == 0, "outer product mean: n must be a multiple of 32");
     for (int i = 0; i < 2; ++i) {
       // second product: D[i][(j,f)] = leftT . tmpT^T
-      g_out2[i] = make_gemm(kmaj(leftT2[i], K), kmaj(tmpT2[i], K), n, (int)NF, K, 1, 256);
+      g_out2[i] = make_gemm(kmaj(leftT2[i] + (long)row0 * K, K), kmaj(tmpT2[i], K), R, (int)NF, K, 1, 256);
       // d(left)[i][k] = sum_{(j,f)} dout[i][(j,f)] tmpT[(j,f)][k], the (j,f) range cut into kSplit batches
       g_dleft2[i] = make_gemm(Operand{dout, NF, Kc, false}, Operand{tmpT2[i], K, Kc * K, true}, n, K, (int)Kc, kSplit, 128);
       // d(tmpT)[(j,f)][k] = sum_i dout[i][(j,f)] leftT[i][k]: both operands read through their MN-major views
@@ -697,7 +827,7 @@ struct Opm {
     W& b = w[blk];
     if (!prepared) products(b, blk & 1, msa_in, st);
     EpiOpmOut eo; eo.res_in = pair_in; eo.res_out = pair_out; eo.bias = b.ob; eo.msa_mask = msa_mask; eo.S = S_; eo.Nres = n;
-    eo.M = n; eo.N = n * OPM_F;
+    eo.M = R; eo.N = n * OPM_F; eo.row0 = row0;
     { ProfScope ps_("Opm.forward.gemm.g_out", st); run_gemm(g_out2[blk & 1], eo, st); }
   }
   // g_pair: cotangent of the pair stream after the module (read only: the module adds to the pair stream, so the
@@ -706,7 +836,8 @@ struct Opm {
   void backward(int blk, const float* msa_in, const float* g_pair, float* g_msa, cudaStream_t st) {
     W& b = w[blk];
     const int Mi = (int)Mm, K = 32 * S_;
-    { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_pdl_c(2, opm_dout_kernel, dim3(cdiv(n * n, 8)), dim3(256), 0, st, g_pair, msa_mask, dout, S_, n); }
+    { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_pdl_c(2, opm_dout_kernel, dim3(cdiv(R * n, 8)), dim3(256), 0, st, g_pair, msa_mask, dout + (long)row0 * n * OPM_F, S_, n, R, row0); }
+    if (comm) { ProfScope ps_("Opm.backward.exchange", st); comm->all_gather(dout + (long)row0 * n * OPM_F, dout, (size_t)R * n * OPM_F * 2, st); }
     EpiPartial ep; ep.out = partial; ep.ld = K; ep.bs = (long)n * K; ep.M = n; ep.N = K;
     { ProfScope ps_("Opm.backward.gemm.g_dleft", st); run_gemm(g_dleft2[blk & 1], ep, st); }
     EpiStore ed; ed.out = dtmpT; ed.ldo = K; ed.M = n * OPM_F; ed.N = K;

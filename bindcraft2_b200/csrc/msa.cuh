@@ -30,15 +30,17 @@ __global__ void opm_pack_left_kernel(const bf16* __restrict__ lr, bf16* __restri
 
 // dout = g * 1/(1e-3 + sum_s m[s,i] m[s,j]): one warp per pair position (i,j), 4 channels per lane
 __global__ void __launch_bounds__(256)
-opm_dout_kernel(const float* __restrict__ g, const float* __restrict__ msa_mask, bf16* __restrict__ dout, int S, int N) {
+opm_dout_kernel(const float* __restrict__ g, const float* __restrict__ msa_mask, bf16* __restrict__ dout, int S, int N,
+                int rows, int row0) {
+  // rows / row0: g and dout hold the band of `rows` pair rows starting at residue row0 (the whole tensor: N, 0)
   pdl_trigger();
   pdl_wait();
   const long m = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (m >= (long)N * N) return;
+  if (m >= (long)rows * N) return;
   const int lane = threadIdx.x & 31;
   const int i = (int)(m / N), j = (int)(m - (long)i * N);
   float nrm = 1e-3f;
-  for (int s = 0; s < S; ++s) nrm += msa_mask[(long)s * N + i] * msa_mask[(long)s * N + j];
+  for (int s = 0; s < S; ++s) nrm += msa_mask[(long)s * N + i + row0] * msa_mask[(long)s * N + j];
   const float inv = 1.f / nrm;
   const float4 v = *reinterpret_cast<const float4*>(g + m * OPM_F + lane * 4);
   *reinterpret_cast<uint2*>(dout + m * OPM_F + lane * 4) = make_uint2(pack_bf16(v.x * inv, v.y * inv), pack_bf16(v.z * inv, v.w * inv));

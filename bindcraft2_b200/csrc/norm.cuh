@@ -98,17 +98,19 @@ __device__ __forceinline__ void row_stats(const float (&v)[C / 32], float& mean,
 // the bias as [head][KEY][query] (a warp's 32 query rows then read consecutive floats).  Row-wise attention uses
 // bias(q = i, k = j), stored at j*n + i; the ending-node attention is built from the transposed activations
 // (modules.py:696-720), bias(q = j, k = i), stored at i*n + j = m.
-__device__ __forceinline__ long bias_pos(int m, int n, int transposed) {
+// qs = distance between consecutive keys (n for a whole pair tensor; the slab height when only a band of query rows is
+// produced into a compact [key][local query] array).
+__device__ __forceinline__ long bias_pos(int m, int n, int transposed, int qs) {
   if (transposed) return m;
   const int i = m / n, j = m - i * n;
-  return (long)j * n + i;
+  return (long)j * qs + i;
 }
 
 // Offset (within one head) of the same entry in the half-precision copy [key/8][query][8 keys].
-__device__ __forceinline__ long bias16_pos(int m, int n, int transposed) {
+__device__ __forceinline__ long bias16_pos(int m, int n, int transposed, int qs) {
   const int i = m / n, j = m - i * n;
   const int q = transposed ? j : i, k = transposed ? i : j;
-  return ((long)(k >> 3) * n + q) * 8 + (k & 7);
+  return ((long)(k >> 3) * qs + q) * 8 + (k & 7);
 }
 // Value kept for the attention bias: rounded to half precision (clamped to its finite range) when a half copy is kept,
 // so that every kernel reading either array sees the same number.
@@ -126,6 +128,8 @@ struct LnArgs {
   float* nb = nullptr;          // [H][M]
   __half* nb16 = nullptr;       // optional half copy, [H][n/8][n][8] (see bias16_pos); nb then holds the rounded values
   int H = 0, n = 0, transposed = 0;
+  int qs = 0;   // key stride of nb / nb16 in queries (0: n); a slab of query rows writes a compact array with qs = slab height
+  long hs = 0;  // head stride of nb / nb16 (0: M)
   int relu = 0;  // y = max(LN(x), 0)
   int M = 0;
 };
@@ -167,7 +171,7 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
     }
     if (a.y) store_row_bf16<C>(a.y + (long)m * a.ldy, lane, v);
     if (a.wb) {
-      const long pos = bias_pos(m, a.n, a.transposed);
+      const long pos = bias_pos(m, a.n, a.transposed, a.qs);
       float mine = 0.f;  // lane h ends up holding head h's dot product
 #pragma unroll
       for (int h = 0; h < LN_MAXH; ++h)
@@ -181,9 +185,9 @@ __global__ void __launch_bounds__(256) ln_fwd_kernel(LnArgs a) {
       if (lane < a.H) {
         if (a.nb16) {
           mine = bias_round16(mine);
-          a.nb16[(long)lane * a.M + bias16_pos(m, a.n, a.transposed)] = __float2half_rn(mine);
+          a.nb16[(long)lane * a.hs + bias16_pos(m, a.n, a.transposed, a.qs)] = __float2half_rn(mine);
         }
-        a.nb[(long)lane * a.M + pos] = mine;
+        a.nb[(long)lane * a.hs + pos] = mine;
       }
     }
   }
@@ -197,6 +201,8 @@ struct LnBwdArgs {
   const float* wb = nullptr;     // [H, C]
   const float* dnb = nullptr;    // [H][M] gradient wrt the bias
   int H = 0, n = 0, transposed = 0;
+  int qs = 0;   // key stride of dnb in queries (0: n)
+  long hs = 0;  // head stride of dnb (0: M); a slab of query rows reads a whole [H][n][n] array with hs = n*n
   const float* g_in = nullptr;   // [M, C] running cotangent or null
   float* g_out = nullptr;        // [M, C]
   int M = 0;
@@ -237,8 +243,8 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(LnBwdArgs a) {
     }
     if (m + nwarp < a.M) load_next(m + nwarp);
     if (a.wb) {
-      const long pos = bias_pos(m, a.n, a.transposed);
-      const float mine = lane < a.H ? a.dnb[(long)lane * a.M + pos] : 0.f;
+      const long pos = bias_pos(m, a.n, a.transposed, a.qs);
+      const float mine = lane < a.H ? a.dnb[(long)lane * a.hs + pos] : 0.f;
 #pragma unroll
       for (int h = 0; h < LN_MAXH; ++h)
         if (h < a.H) {
@@ -370,7 +376,7 @@ __global__ void __launch_bounds__(256) ln_fwd_group_kernel(LnArgs a) {
     }
     if (a.y && live) gstore_bf16<C>(a.y + (long)m * a.ldy, gl, v);
     if (a.wb) {
-      const long pos = bias_pos(mr, a.n, a.transposed);
+      const long pos = bias_pos(mr, a.n, a.transposed, a.qs);
       float mine = 0.f;  // group lane h ends up holding head h's dot product (H <= G, checked by the launcher)
       for (int h = 0; h < a.H; ++h) {
         float s = 0.f;
@@ -385,9 +391,9 @@ __global__ void __launch_bounds__(256) ln_fwd_group_kernel(LnArgs a) {
       if (gl < a.H && live) {
         if (a.nb16) {
           mine = bias_round16(mine);
-          a.nb16[(long)gl * a.M + bias16_pos(m, a.n, a.transposed)] = __float2half_rn(mine);
+          a.nb16[(long)gl * a.hs + bias16_pos(m, a.n, a.transposed, a.qs)] = __float2half_rn(mine);
         }
-        a.nb[(long)gl * a.M + pos] = mine;
+        a.nb[(long)gl * a.hs + pos] = mine;
       }
     }
   }
@@ -424,9 +430,9 @@ __global__ void __launch_bounds__(256) ln_bwd_group_kernel(LnBwdArgs a) {
       for (int i = 0; i < 16; ++i) d[i] = 0.f;
     }
     if (a.wb) {
-      const long pos = bias_pos(mr, a.n, a.transposed);
+      const long pos = bias_pos(mr, a.n, a.transposed, a.qs);
       for (int h = 0; h < a.H; ++h) {
-        const float gb = a.dnb[(long)h * a.M + pos];  // same address across the group: one broadcast transaction
+        const float gb = a.dnb[(long)h * a.hs + pos];  // same address across the group: one broadcast transaction
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float4 w = s_wb[h * (C / 4) + i * R::G + gl];
@@ -461,7 +467,10 @@ __global__ void __launch_bounds__(256) ln_bwd_group_kernel(LnBwdArgs a) {
 }
 
 template <int C>
-inline void ln_fwd(const LnArgs& a, cudaStream_t st) {
+inline void ln_fwd(const LnArgs& a_, cudaStream_t st) {
+  LnArgs a = a_;
+  if (!a.qs) a.qs = a.n;
+  if (!a.hs) a.hs = a.M;
   if constexpr (C <= 128) {
     constexpr int rows_per_cta = 8 * GroupRow<C>::RPW;
     BC2_CHECK(!a.wb || a.H <= GroupRow<C>::G, "LayerNorm bias projection: more heads than lanes per row");
@@ -471,7 +480,10 @@ inline void ln_fwd(const LnArgs& a, cudaStream_t st) {
   }
 }
 template <int C>
-inline void ln_bwd(const LnBwdArgs& a, cudaStream_t st) {
+inline void ln_bwd(const LnBwdArgs& a_, cudaStream_t st) {
+  LnBwdArgs a = a_;
+  if (!a.qs) a.qs = a.n;
+  if (!a.hs) a.hs = a.M;
   if constexpr (C <= 128) {
     constexpr int rows_per_cta = 8 * GroupRow<C>::RPW;
     BC2_CHECK(!a.wb || a.H <= LN_MAXH, "LayerNorm bias projection: too many heads");

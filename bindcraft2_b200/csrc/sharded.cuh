@@ -1,0 +1,227 @@
+// One long complex over P GPUs: the Evoformer stack with the pair representation sharded by rows.
+//
+// The reference runs a complex on one GPU (bindcraft/af/native.py:906-975 pads and masks a single [N,N,128] tensor) and
+// parallelises over trajectories only (bindcraft/design_workers.py); this layer exists for complexes whose pair track
+// is too slow on one device.  Block order and arithmetic are those of EvoStack (modules.py:1266-1391, multimer order).
+//
+// Layout.  Rank r of P holds the band of R = N/P pair rows starting at r*R, [R][N][Cz] fp32, for the residual stream,
+// its cotangent, the save-set and every per-position buffer.  The msa track (S <= 8 rows) is replicated: every rank
+// computes it whole from identical operands.  What crosses ranks, per block and direction:
+//   outer product mean      forward none (each rank forms its band from the replicated msa); backward one all-gather of
+//                           the scaled pair cotangent (bf16), after which the msa-side gradient is computed whole
+//   MSA row attention       all-gather of the pair bias [8][N][N] (fp32 + half copy); its gradient is computed whole on
+//                           every rank and each rank back-propagates its band
+//   tri-mul out / in        all-to-all band planes -> channel planes (a, b), contraction over whole N x N planes of
+//                           Hc/P channels, all-to-all back (t); backward: dt out, (da, db) back
+//   tri-attn starting node  all-gather of the pair bias [4][N][N]; backward: float sum of the bias gradient
+//   tri-attn ending node    the module is the starting-node module applied to the TRANSPOSED stream, so the band is
+//                           transposed across ranks (all-to-all of R x R x Cz blocks), the module runs on it with the
+//                           transposed mask, and its output is transposed back and added; backward mirrors that
+//   transitions             none
+// Exchange objects: shard_comm.cuh.  Everything runs on the caller's stream in program order (no side stream yet).
+// Dropout is not supported here (the sites' tables are indexed by whole-tensor residue numbers).
+#pragma once
+#include "stack.cuh"
+
+namespace bc2 {
+
+// stage[q][jj][ii][:] = x[ii][q*R + jj][:]   (x: [R][n][C] fp32 band; C4 = C/4 float4 per position)
+__global__ void __launch_bounds__(256)
+band_pack_transposed_kernel(const float4* __restrict__ x, float4* __restrict__ stage, int R, int n, int C4, long total) {
+  pdl_trigger();
+  pdl_wait();
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int c4 = (int)(idx % C4);
+    long t = idx / C4;
+    const int ii = (int)(t % R);
+    t /= R;
+    const int jj = (int)(t % R), q = (int)(t / R);
+    stage[idx] = x[((long)ii * n + (long)q * R + jj) * C4 + c4];
+  }
+}
+
+__global__ void transpose_mask_kernel(const float* __restrict__ m, float* __restrict__ mt, int n) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long)n * n) return;
+  const int i = (int)(idx / n), j = (int)(idx - (long)i * n);
+  mt[idx] = m[(long)j * n + i];
+}
+
+struct ShardedEvoStack {
+  StackConfig cfg;
+  ShardComm* comm = nullptr;
+  int P = 1, rank = 0, R = 0, row0 = 0;
+  DeviceArena A;
+  long Mb = 0, Mm = 0;  // pair positions of the band, msa positions
+  Scratch Sp, Sm;
+  Opm opm;
+  MsaRow row;
+  MsaCol col;
+  Transition mtrans, ptrans;
+  TriMul tmo, tmi;
+  TriAttn tas, tae;
+  float* Pb[6] = {nullptr};  // band of the pair stream: block input and after each of the first five pair-side steps
+  float* Mx[3] = {nullptr};  // msa stream after row attention and after column attention (index 1, 2)
+  float *pair_mask = nullptr, *mask_t = nullptr, *msa_mask = nullptr;  // whole [N][N] mask, its transpose, [S][N]
+  float *XT = nullptr, *UT = nullptr, *VT = nullptr, *Ub = nullptr;   // transposed band, module output / cotangent there
+  float* tstage[2] = {nullptr, nullptr};
+  float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};
+  size_t weight_bytes = 0;
+
+  ShardedEvoStack(const StackConfig& c, const std::string& weights_dir, ShardComm* comm_) : cfg(c), comm(comm_) {
+    BC2_CHECK(comm_, "the sharded stack needs an exchange object");
+    P = comm->P;
+    rank = comm->rank;
+    BC2_CHECK(c.N > 0 && c.N % 32 == 0, "N must be a positive multiple of 32 (the caller pads and masks)");
+    BC2_CHECK(c.N % P == 0 && (c.N / P) % 8 == 0, "N must split into P bands of a multiple of 8 rows");
+    BC2_CHECK(c.S >= 1 && c.S <= 8, "alignment depth S must be in 1..8");
+    BC2_CHECK(c.depth >= 1, "depth must be positive");
+    BC2_CHECK(c.opm_first && !c.pair_only && !c.extra, "the sharded stack runs the main stack in the multimer block order");
+    const int N = c.N, S = c.S;
+    R = N / P;
+    row0 = rank * R;
+    Mb = (long)R * N;
+    Mm = (long)S * N;
+    BC2_CHECK(Mb % 128 == 0, "band size must be a multiple of 128 positions");
+    Manifest man = Manifest::load(weights_dir);
+    pair_mask = A.alloc<float>((long)N * N);
+    mask_t = A.alloc<float>((long)N * N);
+    msa_mask = A.alloc<float>(Mm);
+    const int wide_p = std::max(4 * c.tri_hidden + c.Cz, std::max(4 * c.Cz, c.trans_factor * c.Cz));
+    Sp.init(A, Mb, c.Cz, wide_p, true, N, c.tri_heads);
+    const int cms = std::max(c.Cm, c.msa_heads * 16);
+    Sm.init(A, Mm, cms, 4 * cms, false, N, c.msa_heads);
+    for (auto& p : Pb) p = A.alloc<float>(Mb * c.Cz);
+    for (int i = 1; i < 3; ++i) Mx[i] = A.alloc<float>(Mm * c.Cm);
+    XT = A.alloc<float>(Mb * c.Cz);
+    UT = A.alloc<float>(Mb * c.Cz);
+    VT = A.alloc<float>(Mb * c.Cz);
+    Ub = A.alloc<float>(Mb * c.Cz);
+    for (auto& p : tstage) p = A.alloc<float>(Mb * c.Cz);
+    for (int i = 0; i < 2; ++i) {
+      pp[i] = A.alloc<float>(Mb * c.Cz);
+      mp[i] = A.alloc<float>(Mm * c.Cm);
+    }
+    const float* mask_band = pair_mask + (long)row0 * N;
+    opm.init(A, &Sm, N, S, c.Cm, msa_mask, R, row0, comm);
+    row.init(A, &Sm, N, S, c.Cm, c.Cz, c.msa_heads, msa_mask, R, row0, comm);
+    col.init(A, &Sm, N, S, c.Cm, c.msa_heads, msa_mask);
+    mtrans.init(A, &Sm, Mm, c.Cm, c.trans_factor);
+    tmo.init(A, &Sp, N, c.Cz, c.tri_hidden, true, R, comm);
+    tmi.init(A, &Sp, N, c.Cz, c.tri_hidden, false, R, comm);
+    tas.init(A, &Sp, N, c.Cz, c.tri_heads, c.Cz / c.tri_heads, false, mask_band, R, row0, comm);
+    // ending node: the same module on the transposed stream, key mask = rows of the transposed mask
+    tae.init(A, &Sp, N, c.Cz, c.tri_heads, c.Cz / c.tri_heads, false, mask_t + (long)row0 * N, R, row0, comm);
+    ptrans.init(A, &Sp, Mb, c.Cz, c.trans_factor);
+    const size_t before = A.bytes;
+    for (int b = 0; b < c.depth; ++b) {
+      const std::string p = "param/block" + std::to_string(b) + "/";
+      opm.add_block(A, man, p + "outer_product_mean");
+      row.add_block(A, man, p + "msa_row_attention_with_pair_bias");
+      col.add_block(A, man, p + "msa_column_attention");
+      mtrans.add_block(A, man, p + "msa_transition");
+      tmo.add_block(A, man, p + "triangle_multiplication_outgoing");
+      tmi.add_block(A, man, p + "triangle_multiplication_incoming");
+      tas.add_block(A, man, p + "triangle_attention_starting_node");
+      tae.add_block(A, man, p + "triangle_attention_ending_node");
+      ptrans.add_block(A, man, p + "pair_transition");
+    }
+    weight_bytes = A.bytes - before;
+    BC2_CUDA(cudaDeviceSynchronize());
+  }
+
+  // dst = band of the transposed tensor held by this rank, given every rank's band `src` of the tensor itself
+  void transpose_bands(const float* src, float* dst, cudaStream_t st) {
+    const int C = cfg.Cz, N = cfg.N;
+    const long total = Mb * C / 4;
+    launch_pdl(band_pack_transposed_kernel, dim3(ew_grid(total, 256)), dim3(256), 0, st,
+               reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(tstage[0]), R, N, C / 4, total);
+    const size_t blk = (size_t)R * R * C * 4;
+    comm->all_to_all(tstage[0], tstage[1], blk, st);
+    for (int r = 0; r < P; ++r)
+      BC2_CUDA(cudaMemcpy2DAsync(dst + (size_t)r * R * C, (size_t)N * C * 4, tstage[1] + (size_t)r * R * R * C, (size_t)R * C * 4,
+                                 (size_t)R * C * 4, R, cudaMemcpyDeviceToDevice, st));
+  }
+  void add(const float* a, const float* b, float* o, cudaStream_t st) {
+    const long n4 = Mb * cfg.Cz / 4;
+    launch_counter()++;
+    add_f32_kernel<<<ew_grid(n4, 256), 256, 0, st>>>(reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
+                                                     reinterpret_cast<float4*>(o), n4);
+  }
+
+  void set_masks(const float* pm, const float* mm, cudaStream_t st) {
+    const long nn = (long)cfg.N * cfg.N;
+    BC2_CUDA(cudaMemcpyAsync(pair_mask, pm, nn * 4, cudaMemcpyDeviceToDevice, st));
+    BC2_CUDA(cudaMemcpyAsync(msa_mask, mm, Mm * 4, cudaMemcpyDeviceToDevice, st));
+    launch_counter()++;
+    transpose_mask_kernel<<<(unsigned)((nn + 255) / 256), 256, 0, st>>>(pair_mask, mask_t, cfg.N);
+  }
+
+  // p_in / p_out: bands; m_in / m_out: whole msa.  tail = false skips the two GEMMs only the next block would read.
+  void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st, bool tail = true) {
+    const float* mask_band = pair_mask + (long)row0 * cfg.N;
+    opm.forward(b, m_in, p_in, Pb[1], st);
+    row.forward(b, m_in, Mx[1], Pb[1], st);
+    col.forward(b, Mx[1], Mx[2], st);
+    mtrans.forward(b, Mx[2], m_out, st, tail);
+    tmo.forward(b, Pb[1], Pb[2], mask_band, st);
+    tmi.forward(b, Pb[2], Pb[3], mask_band, st);
+    tas.forward(b, Pb[3], Pb[4], st);
+    transpose_bands(Pb[4], XT, st);
+    tae.forward(b, XT, UT, st, /*residual=*/false);
+    transpose_bands(UT, Ub, st);
+    add(Pb[4], Ub, Pb[5], st);
+    ptrans.forward(b, Pb[5], p_out, st, tail);
+  }
+  // needs the module buffers (and XT) as block_forward(b, ...) left them; cotangents are updated in place
+  void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
+    const float* mask_band = pair_mask + (long)row0 * cfg.N;
+    mtrans.backward(b, Mx[2], g_msa, st);
+    col.backward(b, Mx[1], g_msa, st);
+    ptrans.backward(b, Pb[5], g_pair, st);
+    transpose_bands(g_pair, UT, st);
+    tae.backward(b, XT, UT, st, /*g_branch=*/VT);
+    transpose_bands(VT, Ub, st);
+    add(g_pair, Ub, g_pair, st);
+    tas.backward(b, Pb[3], g_pair, st);
+    tmi.backward(b, Pb[2], g_pair, mask_band, st);
+    tmo.backward(b, Pb[1], g_pair, mask_band, st);
+    row.backward(b, m_in, Pb[1], g_msa, g_pair, st);
+    opm.backward(b, m_in, g_pair, g_msa, st);
+  }
+
+  // pair / pair_out / psave: this rank's band ([R][N][Cz]; psave [depth] of them in bf16); msa, masks, msave: whole.
+  void forward(const float* pair, const float* msa, const float* pm, const float* mm, float* pair_out, float* msa_out,
+               bf16* psave, float* msave, cudaStream_t st) {
+    set_masks(pm, mm, st);
+    const long np = Mb * cfg.Cz, nm = Mm * cfg.Cm;
+    const float *pc = pair, *mc = msa;
+    for (int i = 0; i < cfg.depth; ++i) {
+      if (psave) {
+        cvt_f32_bf16(pc, psave + (long)i * np, np, st);
+        BC2_CUDA(cudaMemcpyAsync(msave + (long)i * nm, mc, nm * 4, cudaMemcpyDeviceToDevice, st));
+      }
+      const bool last = i == cfg.depth - 1;
+      float* po = last ? pair_out : pp[i & 1];
+      float* mo = last ? msa_out : mp[i & 1];
+      block_forward(i, pc, mc, po, mo, st);
+      pc = po;
+      mc = mo;
+    }
+  }
+  void backward(const float* ct_pair, const float* ct_msa, const float* pm, const float* mm, const bf16* psave,
+                const float* msave, float* dpair, float* dmsa, cudaStream_t st) {
+    set_masks(pm, mm, st);
+    const long np = Mb * cfg.Cz, nm = Mm * cfg.Cm;
+    if (dpair != ct_pair) BC2_CUDA(cudaMemcpyAsync(dpair, ct_pair, np * 4, cudaMemcpyDeviceToDevice, st));
+    if (dmsa != ct_msa) BC2_CUDA(cudaMemcpyAsync(dmsa, ct_msa, nm * 4, cudaMemcpyDeviceToDevice, st));
+    for (int i = cfg.depth - 1; i >= 0; --i) {
+      cvt_bf16_f32(psave + (long)i * np, Pb[0], np, st);
+      const float* m_in = msave + (long)i * nm;
+      block_forward(i, Pb[0], m_in, pp[0], mp[0], st, /*tail=*/false);
+      block_backward(i, m_in, dpair, dmsa, st);
+    }
+  }
+};
+
+}  // namespace bc2

@@ -16,6 +16,7 @@ results of a custom call.
 """
 from __future__ import annotations
 
+import ctypes
 import hashlib
 import functools
 import os
@@ -173,6 +174,102 @@ def evoformer_bwd(ct_pair, ct_msa, pair_mask, msa_mask, psave, msave, seed, *, d
                                          int(own_save), int(opm_first), int(dropout), os.fsencode(weights_dir),
                                          _ptr(dpair), _ptr(dmsa)))
     return dpair, dmsa
+
+
+
+# ----------------------------------------------------------------------------------------- one complex over several GPUs
+def shard_init(group=None) -> None:
+    """Joins this process (one per GPU, ``torch.distributed`` already initialised, its device current) to the library's
+    exchange group.  Rank 0 creates the id; it travels through ``torch.distributed``.  The reference has no such mode
+    (one complex = one GPU, bindcraft/af/native.py:906-975); the band layout is described at ``sharded_evoformer_fwd``."""
+    import torch.distributed as dist
+    lib = _lib.load()
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ident = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = (ctypes.c_uint8 * 128)()
+        _lib.check(lib.bc2_shard_unique_id(ctypes.addressof(buf)))
+        ident = torch.tensor(list(buf), dtype=torch.uint8)
+    if world > 1:
+        dev = torch.device('cuda', torch.cuda.current_device()) if dist.get_backend(group) == 'nccl' else torch.device('cpu')
+        ident = ident.to(dev)
+        dist.broadcast(ident, src=0, group=group)
+        ident = ident.cpu()
+    buf = (ctypes.c_uint8 * 128)(*ident.tolist())
+    _lib.check(lib.bc2_shard_init(world, rank, ctypes.addressof(buf)))
+
+
+def shard_finalize() -> None:
+    _lib.load().bc2_shard_finalize()
+
+
+def band_of(n: int, world: int, rank: int):
+    """Rows [lo, hi) of the pair representation that ``rank`` of ``world`` holds."""
+    if n % world or (n // world) % 8 or n % 32:
+        raise ValueError('N must be a multiple of 32 and of 8 * world')
+    r = n // world
+    return rank * r, (rank + 1) * r
+
+
+def sharded_evoformer_fwd(pair_band, msa, pair_mask, msa_mask, *, depth, save, weights_dir):
+    """Forward of the main stack on this rank's band of pair rows (collective: every rank of the group calls it).
+
+    pair_band f32 [N/world, N, 128]; msa [S, N, 256], pair_mask [N, N], msa_mask [S, N] whole and identical on all
+    ranks.  Returns (pair_out_band, msa_out, psave_band bf16 [depth, N/world, N, 128], msave f32 [depth, S, N, 256])."""
+    lib = _lib.load()
+    r, n, s = int(pair_band.shape[0]), int(pair_band.shape[1]), int(msa.shape[0])
+    _check_f32('pair_band', pair_band, (r, n, CZ))
+    _check_f32('msa', msa, (s, n, CM))
+    _check_f32('pair_mask', pair_mask, (n, n))
+    _check_f32('msa_mask', msa_mask, (s, n))
+    slots = int(depth) if save else 0
+    pair_out = torch.empty_like(pair_band)
+    msa_out = torch.empty_like(msa)
+    psave = torch.empty((slots, r, n, CZ), dtype=torch.bfloat16, device=pair_band.device)
+    msave = torch.empty((slots, s, n, CM), dtype=torch.float32, device=pair_band.device)
+    stream = torch.cuda.current_stream(pair_band.device).cuda_stream
+    with torch.cuda.device(pair_band.device):
+        _lib.check(lib.bc2_evoformer_sharded_fwd(stream, _ptr(pair_band), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask), n, s,
+                                                 int(depth), int(save), os.fsencode(weights_dir), _ptr(pair_out),
+                                                 _ptr(msa_out), _ptr(psave) if save else 0, _ptr(msave) if save else 0))
+    return pair_out, msa_out, psave, msave
+
+
+def sharded_evoformer_bwd(ct_pair_band, ct_msa, pair_mask, msa_mask, psave, msave, *, depth, weights_dir):
+    """Backward of ``sharded_evoformer_fwd``: (dpair_band, dmsa).  Pure: reads only its operands."""
+    lib = _lib.load()
+    r, n, s = int(ct_pair_band.shape[0]), int(ct_pair_band.shape[1]), int(ct_msa.shape[0])
+    _check_f32('ct_pair_band', ct_pair_band, (r, n, CZ))
+    _check_f32('ct_msa', ct_msa, (s, n, CM))
+    if psave.dtype != torch.bfloat16 or tuple(psave.shape) != (int(depth), r, n, CZ):
+        raise ValueError('psave does not have the shape the forward declared')
+    dpair = torch.empty_like(ct_pair_band)
+    dmsa = torch.empty_like(ct_msa)
+    stream = torch.cuda.current_stream(ct_pair_band.device).cuda_stream
+    with torch.cuda.device(ct_pair_band.device):
+        _lib.check(lib.bc2_evoformer_sharded_bwd(stream, _ptr(ct_pair_band), _ptr(ct_msa), _ptr(pair_mask), _ptr(msa_mask),
+                                                 _ptr(psave), _ptr(msave), n, s, int(depth), os.fsencode(weights_dir),
+                                                 _ptr(dpair), _ptr(dmsa)))
+    return dpair, dmsa
+
+
+def sharded_local_step(world, pair, msa, pair_mask, msa_mask, ct_pair, ct_msa, *, depth, weights_dir):
+    """Test helper: the sharded stack with its ``world`` ranks as host threads on the current GPU, forward + backward on
+    whole tensors.  Returns (pair_out, msa_out, dpair, dmsa) laid out like ``evoformer_fwd`` / ``evoformer_bwd``."""
+    lib = _lib.load()
+    n, s = int(pair.shape[0]), int(msa.shape[0])
+    band_of(n, world, 0)
+    _check_f32('pair', pair, (n, n, CZ))
+    _check_f32('msa', msa, (s, n, CM))
+    _check_f32('ct_pair', ct_pair, (n, n, CZ))
+    _check_f32('ct_msa', ct_msa, (s, n, CM))
+    outs = [torch.empty_like(pair), torch.empty_like(msa), torch.empty_like(pair), torch.empty_like(msa)]
+    torch.cuda.synchronize(pair.device)
+    with torch.cuda.device(pair.device):
+        _lib.check(lib.bc2_test_sharded_local(int(world), _ptr(pair), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask),
+                                              _ptr(ct_pair), _ptr(ct_msa), n, s, int(depth), os.fsencode(weights_dir),
+                                              *[_ptr(o) for o in outs]))
+    return tuple(outs)
 
 
 def template_pair_stack_fwd(pair, pair_mask, seed, *, depth, weights_dir, dropout=0, save=1):

@@ -203,6 +203,36 @@ int64_t bc2_launch_count(void);
 void bc2_profile_mode(int mode, const char* only);
 int64_t bc2_profile_report(char* buf, int64_t cap);
 
+/* ---- one long complex over several GPUs: the pair representation sharded by rows ------------------------------ */
+/* No counterpart in the reference (it runs a complex on one GPU, bindcraft/af/native.py:906-975, and parallelises over
+ * trajectories, bindcraft/design_workers.py).  One process per GPU; rank r of `world` holds the band of N/world pair
+ * rows starting at r*N/world.  Block arithmetic is that of bc2_evoformer_fwd/bwd (multimer block order, dropout off).
+ * Exchange steps (NCCL, bound at run time from libnccl.so.2): all-to-all for the row <-> column transposes of the
+ * ending-node attention and for the row-band <-> channel-group relayout of the triangle-multiplication planes,
+ * all-gather for the attention pair biases and the outer-product cotangent, a float sum for the bias gradients. */
+
+/* Rank 0 creates a 128-byte id and hands it to the other ranks through the host framework's own process group. */
+int bc2_shard_unique_id(uint8_t* id128);
+/* Every rank, with its device current: joins the exchange group.  Collective: returns when all `world` ranks called. */
+int bc2_shard_init(int world, int rank, const uint8_t* id128);
+/* Drops the sharded stacks and leaves the group. */
+void bc2_shard_finalize(void);
+
+/* Operands as bc2_evoformer_fwd with pair / pair_out / psave replaced by this rank's band:
+ * pair_band f32 [N/world][N][128], msa f32 [S][N][256] (whole, identical on every rank), pair_mask f32 [N][N] (whole),
+ * msa_mask f32 [S][N] -> pair_out_band, msa_out (whole, computed on every rank), psave_band bf16
+ * [depth][N/world][N][128], msave f32 [depth][S][N][256].  Collective over the group: every rank calls it with the same
+ * N, S, depth and weights.  N must be a multiple of 32 and of 8*world. */
+int bc2_evoformer_sharded_fwd(void* stream, const float* pair_band, const float* msa, const float* pair_mask,
+                              const float* msa_mask, int64_t N, int64_t S, int64_t depth, int64_t save,
+                              const char* weights_dir, float* pair_out_band, float* msa_out, uint16_t* psave_band,
+                              float* msave);
+/* Pure like bc2_evoformer_bwd: reads only its operands.  dpair_band f32 [N/world][N][128], dmsa f32 [S][N][256] (whole;
+ * equal on every rank up to the order of floating-point sums). */
+int bc2_evoformer_sharded_bwd(void* stream, const float* ct_pair_band, const float* ct_msa, const float* pair_mask,
+                              const float* msa_mask, const uint16_t* psave_band, const float* msave, int64_t N, int64_t S,
+                              int64_t depth, const char* weights_dir, float* dpair_band, float* dmsa);
+
 /* ---- bring-up / unit-test entry points (not part of the reference surface) ------------------------------------ */
 
 /* Enables a subset of the nine residual steps of every block (bit i = step i in block order: outer product mean, MSA
@@ -225,6 +255,13 @@ int bc2_test_gemm(void* stream, const uint16_t* a, int64_t lda, int64_t a_bs, in
 int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, const float* mask, const uint16_t* d_og,
                        int64_t B, int64_t N, int64_t H, int64_t D, int transposed, uint16_t* og, uint16_t* d_qkvg,
                        float* d_bias, int use_ref);
+
+/* The sharded stack with its P ranks run as P host threads on the CURRENT device (exchanges become device copies behind
+ * host barriers): forward + backward of whole tensors, for checking the partitioned path against bc2_evoformer_fwd/bwd
+ * on a single GPU.  Operands and results are whole tensors laid out as in bc2_evoformer_fwd/bwd. */
+int bc2_test_sharded_local(int P, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
+                           const float* ct_pair, const float* ct_msa, int64_t N, int64_t S, int64_t depth,
+                           const char* weights_dir, float* pair_out, float* msa_out, float* dpair, float* dmsa);
 
 /* Gated attention forward that allocates nothing.  No counterpart in the reference.
  * For hosts that cannot allocate device memory when the call is made (inside a stream capture they do not own, after
