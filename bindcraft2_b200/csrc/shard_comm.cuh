@@ -99,8 +99,13 @@ struct NcclComm : ShardComm {
   }
   void all_to_all(const void* send, void* recv, size_t bytes, cudaStream_t st) override {
     NcclApi& n = NcclApi::get();
+    // this rank's own chunk never leaves the device: a plain copy instead of a send/receive pair with itself
+    BC2_CUDA(cudaMemcpyAsync(static_cast<char*>(recv) + (size_t)rank * bytes, static_cast<const char*>(send) + (size_t)rank * bytes,
+                             bytes, cudaMemcpyDeviceToDevice, st));
+    if (P == 1) return;
     BC2_NCCL(n.GroupStart());
     for (int r = 0; r < P; ++r) {
+      if (r == rank) continue;
       BC2_NCCL(n.Send(static_cast<const char*>(send) + (size_t)r * bytes, bytes, ncclChar, r, comm, st));
       BC2_NCCL(n.Recv(static_cast<char*>(recv) + (size_t)r * bytes, bytes, ncclChar, r, comm, st));
     }

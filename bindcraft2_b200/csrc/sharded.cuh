@@ -134,6 +134,7 @@ struct ShardedEvoStack {
   void transpose_bands(const float* src, float* dst, cudaStream_t st) {
     const int C = cfg.Cz, N = cfg.N;
     const long total = Mb * C / 4;
+    ProfScope ps_("TriAttn.transpose.exchange", st);
     launch_pdl(band_pack_transposed_kernel, dim3(ew_grid(total, 256)), dim3(256), 0, st,
                reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(tstage[0]), R, N, C / 4, total);
     const size_t blk = (size_t)R * R * C * 4;
