@@ -466,6 +466,7 @@ int bc2_shard_init(int world, int rank, const uint8_t* id128) {
     BC2_CHECK(id128 && world >= 1 && rank >= 0 && rank < world, "bad world / rank / id");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     g_sharded.clear();
+    if (g_shard_comm) g_shard_comm->shutdown();
     g_shard_comm.reset();
     ncclUniqueId id;
     memcpy(&id, id128, 128);
@@ -479,6 +480,7 @@ int bc2_shard_init(int world, int rank, const uint8_t* id128) {
 void bc2_shard_finalize(void) {
   std::lock_guard<std::recursive_mutex> lock(g_mu);
   g_sharded.clear();
+  if (g_shard_comm) g_shard_comm->shutdown();
   g_shard_comm.reset();
 }
 

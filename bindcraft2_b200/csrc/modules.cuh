@@ -68,15 +68,12 @@ struct Scratch {
 // and spread them into the whole [H][n][n] / [H][n/8][n][8] arrays the attention kernels read.
 inline void gather_bias(ShardComm* comm, const char* mine, char* all, float* nb, __half* nb16, int H, int n, int R,
                         cudaStream_t st) {
-  const size_t cnt = (size_t)H * n * R, blk = cnt * 6;
-  comm->all_gather(mine, all, blk, st);
-  for (int r = 0; r < comm->P; ++r) {
-    const char* src = all + (size_t)r * blk;
-    BC2_CUDA(cudaMemcpy2DAsync(nb + (size_t)r * R, (size_t)n * 4, src, (size_t)R * 4, (size_t)R * 4, (size_t)H * n,
-                               cudaMemcpyDeviceToDevice, st));
-    BC2_CUDA(cudaMemcpy2DAsync(nb16 + (size_t)r * R * 8, (size_t)n * 16, src + cnt * 4, (size_t)R * 16, (size_t)R * 16,
-                               (size_t)H * n / 8, cudaMemcpyDeviceToDevice, st));
-  }
+  const size_t cnt = (size_t)H * n * R;
+  // fp32 part: H*n rows of R floats into columns [r*R, (r+1)*R) of the [H*n][n] array
+  comm->exchange_2d(mine, 0, 0, (size_t)R * 4, nb, (size_t)R * 4, (size_t)n * 4, (size_t)R * 4, (size_t)H * n, all, st);
+  // half part: H*n/8 rows of R*8 halves
+  comm->exchange_2d(mine + cnt * 4, 0, 0, (size_t)R * 16, nb16, (size_t)R * 16, (size_t)n * 16, (size_t)R * 16, (size_t)H * n / 8,
+                    all, st);
 }
 
 struct LnW {
@@ -183,7 +180,7 @@ struct TriMul {
     M = (long)R * n;
     BC2_CHECK(comm || R == n, "a band of pair rows needs an exchange object");
     gate = A.alloc<bf16>(M * 2 * Hc);
-    ab = A.alloc<bf16>(M * 2 * Hc);
+    ab = comm ? static_cast<bf16*>(comm->alloc_exchange(A, (size_t)M * 2 * Hc * 2)) : A.alloc<bf16>(M * 2 * Hc);
     t = A.alloc<bf16>(M * Hc);
     ob = A.alloc<bf16>(M * C);
     g2 = A.alloc<bf16>(M * C);
@@ -194,9 +191,9 @@ struct TriMul {
       BC2_CHECK(Hc % comm->P == 0 && M % 128 == 0, "sharded tri-mul: hidden channels and band size must divide evenly");
       Hl = Hc / comm->P;
       abF = A.alloc<bf16>(2L * Hl * MF);
-      tF = A.alloc<bf16>((long)Hl * MF);
+      tF = static_cast<bf16*>(comm->alloc_exchange(A, (size_t)Hl * MF * 2));
       dtF = A.alloc<bf16>((long)Hl * MF);
-      dabF = A.alloc<bf16>(2L * Hl * MF);
+      dabF = static_cast<bf16*>(comm->alloc_exchange(A, 2 * (size_t)Hl * MF * 2));
       if (!S->stage) S->stage = A.alloc<bf16>(M * Hc);
       a = abF; bq = abF + (long)Hl * MF; dt = dtF;
     }
@@ -214,23 +211,17 @@ struct TriMul {
       gb_da = make_gemm(K(bq), T(dt), n, n, n, Hl, 128);
     }
   }
-  // band planes [npl][M] -> whole planes [npl/P][n*n] of this rank's channel group
+  // band planes [npl][M] -> whole planes [npl/P][n*n] of this rank's channel group: from rank r come its band's planes
+  // of my channels, `per` rows of M values, into columns [r*M, (r+1)*M) of my whole planes
   void planes_to_channels(const bf16* src, bf16* dst, int npl, cudaStream_t st) {
-    const int P = comm->P, per = npl / P;
-    const size_t MF = (size_t)n * n;
-    comm->all_to_all(src, S->stage, (size_t)per * M * 2, st);
-    for (int r = 0; r < P; ++r)
-      BC2_CUDA(cudaMemcpy2DAsync(dst + (size_t)r * M, MF * 2, S->stage + (size_t)r * per * M, (size_t)M * 2, (size_t)M * 2, per,
-                                 cudaMemcpyDeviceToDevice, st));
+    const size_t per = npl / comm->P, MF = (size_t)n * n, Mb = (size_t)M;
+    comm->exchange_2d(src, 0, per * Mb * 2, Mb * 2, dst, Mb * 2, MF * 2, Mb * 2, per, S->stage, st);
   }
-  // whole planes [npl/P][n*n] of this rank's channel group -> band planes [npl][M]
+  // whole planes [npl/P][n*n] of this rank's channel group -> band planes [npl][M]: from rank r come columns
+  // [me*M, (me+1)*M) of its `per` whole planes, which are planes [r*per, (r+1)*per) of my band
   void channels_to_planes(const bf16* src, bf16* dst, int npl, cudaStream_t st) {
-    const int P = comm->P, per = npl / P;
-    const size_t MF = (size_t)n * n;
-    for (int q = 0; q < P; ++q)
-      BC2_CUDA(cudaMemcpy2DAsync(S->stage + (size_t)q * per * M, (size_t)M * 2, src + (size_t)q * M, MF * 2, (size_t)M * 2, per,
-                                 cudaMemcpyDeviceToDevice, st));
-    comm->all_to_all(S->stage, dst, (size_t)per * M * 2, st);
+    const size_t per = npl / comm->P, MF = (size_t)n * n, Mb = (size_t)M;
+    comm->exchange_2d(src, 0, Mb * 2, MF * 2, dst, per * Mb * 2, Mb * 2, Mb * 2, per, S->stage, st);
   }
   void add_block(DeviceArena& A, const Manifest& m, const std::string& p) {
     W b;
@@ -430,8 +421,8 @@ struct TriAttn {
     nb16 = A.alloc<__half>((long)H * MF);
     lse = A.alloc<float>(2L * R * H * n);
     if (comm) {
-      bias_mine = A.alloc<char>((size_t)H * n * R * 6);
-      bias_all = A.alloc<char>((size_t)H * n * R * 6 * comm->P);
+      bias_mine = static_cast<char*>(comm->alloc_exchange(A, (size_t)H * n * R * 6));
+      bias_all = A.alloc<char>((size_t)H * n * R * 4 * comm->P);
     }
     AttnArgs& a = plan.args;
     a.qkvg = qkvg; a.ld = 4 * HD;
@@ -537,8 +528,8 @@ struct MsaRow {
     comm = comm_; R = R_ > 0 ? R_ : n; row0 = row0_;
     BC2_CHECK(comm || R == n, "a band of pair rows needs an exchange object");
     if (comm) {
-      bias_mine = A.alloc<char>((size_t)H * n * R * 6);
-      bias_all = A.alloc<char>((size_t)H * n * R * 6 * comm->P);
+      bias_mine = static_cast<char*>(comm->alloc_exchange(A, (size_t)H * n * R * 6));
+      bias_all = A.alloc<char>((size_t)H * n * R * 4 * comm->P);
     }
     Mm = (long)S_ * n; Mp = (long)n * n;
     const int HD = H * D;
@@ -757,7 +748,7 @@ struct Opm {
     xln = A.alloc<bf16>(Mm * Cm);
     dlr_b = A.alloc<bf16>(Mm * 64);
     dtmpT = A.alloc<bf16>(NF * K);
-    dout = A.alloc<bf16>((long)n * NF);
+    dout = comm ? static_cast<bf16*>(comm->alloc_exchange(A, (size_t)n * NF * 2)) : A.alloc<bf16>((long)n * NF);
     partial = A.alloc<float>((long)kSplit * n * K);
     const long Kc = NF / kSplit;
     BC2_CHECK(NF % (kSplit * 64) == 0, "outer product mean: n must be a multiple of 32");
@@ -837,7 +828,7 @@ struct Opm {
     W& b = w[blk];
     const int Mi = (int)Mm, K = 32 * S_;
     { ProfScope ps_("Opm.backward.opm_dout_kernel", st); launch_pdl_c(2, opm_dout_kernel, dim3(cdiv(R * n, 8)), dim3(256), 0, st, g_pair, msa_mask, dout + (long)row0 * n * OPM_F, S_, n, R, row0); }
-    if (comm) { ProfScope ps_("Opm.backward.exchange", st); comm->all_gather(dout + (long)row0 * n * OPM_F, dout, (size_t)R * n * OPM_F * 2, st); }
+    if (comm) { ProfScope ps_("Opm.backward.exchange", st); const size_t band = (size_t)R * n * OPM_F * 2; comm->exchange_2d(dout, band, 0, band, dout, band, band, band, 1, nullptr, st); }
     EpiPartial ep; ep.out = partial; ep.ld = K; ep.bs = (long)n * K; ep.M = n; ep.N = K;
     { ProfScope ps_("Opm.backward.gemm.g_dleft", st); run_gemm(g_dleft2[blk & 1], ep, st); }
     EpiStore ed; ed.out = dtmpT; ed.ldo = K; ed.M = n * OPM_F; ed.N = K;

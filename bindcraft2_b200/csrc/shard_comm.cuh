@@ -33,6 +33,41 @@ struct ShardComm {
   virtual void all_gather(const void* send, void* recv, size_t bytes, cudaStream_t st) = 0;
   // buf <- sum over ranks of buf
   virtual void all_reduce_f32(float* buf, size_t count, cudaStream_t st) = 0;
+
+  // Memory that exchange_2d may read from other ranks.  Collective: every rank asks for the same sizes in the same order.
+  virtual void* alloc_exchange(DeviceArena& A, size_t bytes) { return A.alloc<char>(bytes); }
+
+  // The one exchange pattern of the sharded stack.  `src` names the same buffer on every rank.  For every rank r, the
+  // 2-D block (`height` rows of `width` bytes, row pitch spitch) that starts at byte r*ostride + me*sstride of rank r's
+  // `src` lands at dst + r*dstride with row pitch dpitch.  sstride = 0: every rank reads the same block of r (an
+  // all-gather); with ostride = dstride and src = dst it is an in-place gather of bands.
+  // `stage` (P*width*height bytes) is used by carriers that move contiguous chunks only, on whichever side is strided
+  // (never both in this library).  This default packs, runs the equal-chunk collective and unpacks.
+  virtual void exchange_2d(const void* src, size_t ostride, size_t sstride, size_t spitch, void* dst, size_t dstride,
+                           size_t dpitch, size_t width, size_t height, void* stage, cudaStream_t st) {
+    const size_t blk = width * height;
+    const bool src_dense = height == 1 || spitch == width, dst_dense = (height == 1 || dpitch == width) && dstride == blk;
+    const char* send = static_cast<const char*>(src) + (size_t)rank * ostride;
+    char* recv = static_cast<char*>(dst);
+    BC2_CHECK(src_dense || dst_dense, "exchange_2d: one staging block cannot serve both sides");
+    if (sstride != 0 && !(src_dense && sstride == blk)) {
+      BC2_CHECK(stage && dst_dense, "exchange_2d: strided source needs the staging block");
+      for (int q = 0; q < P; ++q)
+        BC2_CUDA(cudaMemcpy2DAsync(static_cast<char*>(stage) + (size_t)q * blk, width, send + (size_t)q * sstride, spitch, width,
+                                   height, cudaMemcpyDeviceToDevice, st));
+      send = static_cast<const char*>(stage);
+    }
+    if (!dst_dense) {
+      BC2_CHECK(stage, "exchange_2d: strided destination needs the staging block");
+      recv = static_cast<char*>(stage);
+    }
+    if (sstride != 0) all_to_all(send, recv, blk, st);
+    else all_gather(send, recv, blk, st);
+    if (!dst_dense)
+      for (int r = 0; r < P; ++r)
+        BC2_CUDA(cudaMemcpy2DAsync(static_cast<char*>(dst) + (size_t)r * dstride, dpitch, recv + (size_t)r * blk, width, width,
+                                   height, cudaMemcpyDeviceToDevice, st));
+  }
 };
 
 // ------------------------------------------------------------------------------------------- NCCL, bound at run time
@@ -87,15 +122,103 @@ struct NcclApi {
     }                                                                                                        \
   } while (0)
 
+// One process per GPU.  Small collectives (bias-gradient sum, barriers) go through NCCL.  The bulk exchanges read the
+// other ranks' memory directly: buffers from alloc_exchange() are shared between the processes (CUDA IPC handles,
+// gathered through NCCL when the buffer is made), and exchange_2d() is one stream-ordered barrier followed by one 2-D
+// peer copy per source rank, straight from the peer's buffer into its final strided place here: no staging hop, and
+// copy-engine peer copies run at the NVLink rate where NCCL's send/receive pairs reach about a third of it.
+// BC2_SHARD_IPC=0 (or a failing handle exchange) falls back to the packed NCCL path of the base class.
+//
+// Why one barrier per exchange is enough: a rank writes into its OWN memory only (it pulls), so the only hazard is a
+// rank overwriting a source buffer while a slower peer still reads it.  Every source buffer of the sharded stack is next
+// written at least one exchange later, and that later exchange's barrier completes on the writer only after every peer
+// has reached it, i.e. after the peer's earlier pulls (stream-ordered before its barrier) have finished.
 struct NcclComm : ShardComm {
   ncclComm_t comm = nullptr;
+  bool use_ipc = true;
+  struct Shared {
+    char* mine = nullptr;
+    size_t bytes = 0;
+    std::vector<char*> peer;  // peer[r]: rank r's buffer as mapped into this process (peer[rank] = mine)
+  };
+  std::vector<Shared> shared;
+  float* flag = nullptr;              // barrier operand
+  char* handles_dev = nullptr;        // P IPC handles
+
   NcclComm(int world, int rank_, const ncclUniqueId& id) {
     P = world;
     rank = rank_;
     BC2_NCCL(NcclApi::get().CommInitRank(&comm, world, id, rank_));
+    const char* e = getenv("BC2_SHARD_IPC");
+    use_ipc = !(e && e[0] == '0') && world > 1;
+    BC2_CUDA(cudaMalloc(&flag, 256));
+    BC2_CUDA(cudaMemset(flag, 0, 256));
+    BC2_CUDA(cudaMalloc(&handles_dev, sizeof(cudaIpcMemHandle_t) * (size_t)world));
   }
-  ~NcclComm() override {
-    if (comm && NcclApi::get().CommDestroy) NcclApi::get().CommDestroy(comm);
+  // Orderly, collective teardown (every rank calls it): nobody frees a buffer a peer still has mapped.  A process that
+  // ends without it leaves the memory to the driver's process cleanup; the destructor makes no collective call.
+  void shutdown() {
+    if (!comm) return;
+    cudaDeviceSynchronize();
+    for (auto& sh : shared)
+      for (int r = 0; r < (int)sh.peer.size(); ++r)
+        if (r != rank && sh.peer[r]) cudaIpcCloseMemHandle(sh.peer[r]);
+    if (NcclApi::get().AllReduce(flag, flag, 1, ncclFloat, ncclSum, comm, nullptr) == ncclSuccess) cudaStreamSynchronize(nullptr);
+    for (auto& sh : shared) cudaFree(sh.mine);
+    shared.clear();
+    cudaFree(flag);
+    cudaFree(handles_dev);
+    if (NcclApi::get().CommDestroy) NcclApi::get().CommDestroy(comm);
+    comm = nullptr;
+  }
+  ~NcclComm() override {}
+  void barrier(cudaStream_t st) { BC2_NCCL(NcclApi::get().AllReduce(flag, flag, 1, ncclFloat, ncclSum, comm, st)); }
+
+  void* alloc_exchange(DeviceArena& A, size_t bytes) override {
+    if (!use_ipc) return A.alloc<char>(bytes);
+    Shared sh;
+    sh.bytes = ((bytes + 255) / 256) * 256;
+    BC2_CUDA(cudaMalloc(reinterpret_cast<void**>(&sh.mine), sh.bytes));
+    A.bytes += sh.bytes;  // accounted with the stack, owned (and freed) by the exchange object
+    cudaIpcMemHandle_t h;
+    BC2_CUDA(cudaIpcGetMemHandle(&h, sh.mine));
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    BC2_CUDA(cudaMemcpy(handles_dev + (size_t)rank * hb, &h, hb, cudaMemcpyHostToDevice));
+    BC2_NCCL(NcclApi::get().AllGather(handles_dev + (size_t)rank * hb, handles_dev, hb, ncclChar, comm, nullptr));
+    BC2_CUDA(cudaStreamSynchronize(nullptr));
+    std::vector<cudaIpcMemHandle_t> all(P);
+    BC2_CUDA(cudaMemcpy(all.data(), handles_dev, hb * P, cudaMemcpyDeviceToHost));
+    sh.peer.assign(P, nullptr);
+    for (int r = 0; r < P; ++r) {
+      if (r == rank) { sh.peer[r] = sh.mine; continue; }
+      void* p = nullptr;
+      BC2_CUDA(cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess));
+      sh.peer[r] = static_cast<char*>(p);
+    }
+    shared.push_back(sh);
+    return sh.mine;
+  }
+  const Shared* find(const void* p, size_t& off) const {
+    const char* c = static_cast<const char*>(p);
+    for (const auto& sh : shared)
+      if (c >= sh.mine && c < sh.mine + sh.bytes) { off = (size_t)(c - sh.mine); return &sh; }
+    return nullptr;
+  }
+  void exchange_2d(const void* src, size_t ostride, size_t sstride, size_t spitch, void* dst, size_t dstride, size_t dpitch,
+                   size_t width, size_t height, void* stage, cudaStream_t st) override {
+    size_t off = 0;
+    const Shared* sh = use_ipc ? find(src, off) : nullptr;
+    if (!sh) return ShardComm::exchange_2d(src, ostride, sstride, spitch, dst, dstride, dpitch, width, height, stage, st);
+    BC2_CHECK(off + (size_t)(P - 1) * (sstride + ostride) + (height - 1) * spitch + width <= sh->bytes, "exchange_2d: source range");
+    barrier(st);
+    for (int i = 0; i < P; ++i) {
+      const int r = (rank + i) % P;  // start with the local block, then walk the peers from different starting points
+      char* d = static_cast<char*>(dst) + (size_t)r * dstride;
+      const char* s_ = sh->peer[r] + off + (size_t)r * ostride + (size_t)rank * sstride;
+      if (d == s_) continue;  // in-place all-gather: the local block is already there
+      BC2_CUDA(cudaMemcpy2DAsync(d, height == 1 ? width : dpitch, s_, height == 1 ? width : spitch, width, height,
+                                 cudaMemcpyDefault, st));
+    }
   }
   void all_to_all(const void* send, void* recv, size_t bytes, cudaStream_t st) override {
     NcclApi& n = NcclApi::get();

@@ -97,7 +97,9 @@ struct ShardedEvoStack {
     UT = A.alloc<float>(Mb * c.Cz);
     VT = A.alloc<float>(Mb * c.Cz);
     Ub = A.alloc<float>(Mb * c.Cz);
-    for (auto& p : tstage) p = A.alloc<float>(Mb * c.Cz);
+    tstage[0] = static_cast<float*>(comm->alloc_exchange(A, (size_t)Mb * c.Cz * 4));
+    tstage[1] = A.alloc<float>(Mb * c.Cz);
+    Sp.dt = static_cast<bf16*>(comm->alloc_exchange(A, (size_t)Mb * c.Cz * 2));  // tri-mul backward sends it
     for (int i = 0; i < 2; ++i) {
       pp[i] = A.alloc<float>(Mb * c.Cz);
       mp[i] = A.alloc<float>(Mm * c.Cm);
@@ -137,11 +139,10 @@ struct ShardedEvoStack {
     ProfScope ps_("TriAttn.transpose.exchange", st);
     launch_pdl(band_pack_transposed_kernel, dim3(ew_grid(total, 256)), dim3(256), 0, st,
                reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(tstage[0]), R, N, C / 4, total);
-    const size_t blk = (size_t)R * R * C * 4;
-    comm->all_to_all(tstage[0], tstage[1], blk, st);
-    for (int r = 0; r < P; ++r)
-      BC2_CUDA(cudaMemcpy2DAsync(dst + (size_t)r * R * C, (size_t)N * C * 4, tstage[1] + (size_t)r * R * R * C, (size_t)R * C * 4,
-                                 (size_t)R * C * 4, R, cudaMemcpyDeviceToDevice, st));
+    // from rank r comes the R x R block (its rows, my columns), already transposed: R rows of R*C values into columns
+    // [r*R, (r+1)*R) of my band
+    const size_t row = (size_t)R * C * 4;
+    comm->exchange_2d(tstage[0], 0, (size_t)R * row, row, dst, row, (size_t)N * C * 4, row, R, tstage[1], st);
   }
   void add(const float* a, const float* b, float* o, cudaStream_t st) {
     const long n4 = Mb * cfg.Cz / 4;

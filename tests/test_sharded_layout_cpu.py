@@ -110,3 +110,15 @@ def test_band_of_rejects_uneven_splits():
         native.band_of(224, 8, 0)   # 28 rows per band: not a multiple of 8
     with pytest.raises(ValueError):
         native.band_of(100, 2, 0)   # not a multiple of 32
+
+
+def test_unique_id_and_uninitialised_call(lib):
+    """Host-side paths that need no GPU: rank 0 can create the exchange-group id (NCCL is bound at run time), and a
+    sharded call before bc2_shard_init comes back as a status code with a message, not a crash."""
+    import ctypes
+    buf = (ctypes.c_uint8 * 128)()
+    assert lib.bc2_shard_unique_id(ctypes.addressof(buf)) == 0
+    assert any(buf)
+    rc = lib.bc2_evoformer_sharded_fwd(None, 1, 1, 1, 1, 64, 1, 1, 0, b'/nonexistent', 1, 1, None, None)
+    assert rc != 0
+    assert lib.bc2_last_error()
