@@ -261,7 +261,7 @@ struct StructureHeads {
   void sidechain_forward(const float* aatype, float* atom14, cudaStream_t st) {
     const int L = core.L;
     const float* act = core.act_in[L];
-    launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(core.rig[L], rig_s, POSITION_SCALE, N * 12);
+    launch_counter()++; scale_translation_kernel<<<cdiv(N * 12, 256), 256, 0, st>>>(core.rig[L], rig_s, core.pos_scale, N * 12);
     lin(act, ip.w, ip.b, x0, N, CS, SCC, st, 0, 1);
     lin(core.single_ln, ip1.w, ip1.b, x0, N, CS, SCC, st, 0, 1, nullptr, nullptr, 1);
     lin(x0, rb1.w, rb1.b, r1, N, SCC, SCC, st, 0, 1);

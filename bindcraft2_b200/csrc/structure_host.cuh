@@ -58,9 +58,17 @@ struct StructureCore {
 
   static std::vector<float> vec(const Manifest& m, const std::string& k) { return m.get(k).data; }
 
+  // Units of the frames' translation: 20 in the multimer model (config.py:595), 10 in the monomer model (config.py:357);
+  // the reference's native fold iteration keeps it as a member for the same reason (native/foldit.cuh `pos_scale`).
+  // The manifest selects it with an optional scalar `const/position_scale`.
+  float pos_scale = POSITION_SCALE;
   void build(int n, int depth, const std::string& dir) {
     N = n; L = depth;
     const Manifest m = Manifest::load(dir);
+    if (m.has("const/position_scale")) {
+      pos_scale = m.get("const/position_scale").data.at(0);
+      BC2_CHECK(pos_scale > 0.f, "const/position_scale must be positive");
+    }
     const std::string P = "param/", I = P + "fold_iteration/invariant_point_attention/", F = P + "fold_iteration/";
     auto up = [&](const std::string& k, size_t expect) {
       const auto& t = m.get(k);
@@ -93,10 +101,11 @@ struct StructureCore {
         BC2_CHECK((int)w.size() == CS * p.width, p.key + ": unexpected weight size");
         for (int c = 0; c < CS; ++c)
           for (int o = 0; o < p.width; ++o) W[(size_t)c * NPROJ + p.off + o] = p.scale * w[(size_t)c * p.width + o];
-        if (p.bias) {
+        // the scalar projections carry a bias only in the monomer checkpoint (optional entry; zero otherwise)
+        if (p.bias || m.has(I + p.key + "/bias")) {
           const auto& b = m.get(I + p.key + "/bias").data;
           BC2_CHECK((int)b.size() == p.width, p.key + ": unexpected bias size");
-          for (int o = 0; o < p.width; ++o) B[p.off + o] = b[o];
+          for (int o = 0; o < p.width; ++o) B[p.off + o] = p.scale * b[o];
         }
       }
       proj.set(A, W, B, CS, NPROJ);
@@ -211,7 +220,7 @@ struct StructureCore {
       launch_pdl_c(4, rigid_update_kernel, dim3(cdiv(N, 128)), dim3(128), 0, st, rig[l], upd[l], rig[l + 1], N);
     }
     if (act_out) BC2_CUDA(cudaMemcpyAsync(act_out, act_in[L], (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
-    if (rig_out) { launch_pdl_c(4, scale_translation_kernel, dim3(cdiv(N * 12, 256)), dim3(256), 0, st, rig[L], rig_out, POSITION_SCALE, N * 12); }
+    if (rig_out) { launch_pdl_c(4, scale_translation_kernel, dim3(cdiv(N * 12, 256)), dim3(256), 0, st, rig[L], rig_out, pos_scale, N * 12); }
   }
 
   // Cotangents d_act [N,384] and d_rig [N,12] (rotation entries, then the SCALED translation) -> d_single, d_pair.
@@ -221,7 +230,7 @@ struct StructureCore {
                 float* d_pair, cudaStream_t st, const float* d_single_ln_extra = nullptr) {
     const long n2 = (long)N * N;
     BC2_CUDA(cudaMemcpyAsync(g_act, d_act, (size_t)N * CS * 4, cudaMemcpyDeviceToDevice, st));
-    launch_pdl_c(4, scale_translation_kernel, dim3(cdiv(N * 12, 256)), dim3(256), 0, st, d_rig, g_rig[0], POSITION_SCALE, N * 12);
+    launch_pdl_c(4, scale_translation_kernel, dim3(cdiv(N * 12, 256)), dim3(256), 0, st, d_rig, g_rig[0], pos_scale, N * 12);
     BC2_CUDA(cudaMemsetAsync(db2d, 0, (size_t)n2 * H * 4, st));
     BC2_CUDA(cudaMemsetAsync(dpair_ln, 0, (size_t)n2 * CZ * 4, st));
     int cur = 0;

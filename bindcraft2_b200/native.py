@@ -370,12 +370,73 @@ def structure_module_bwd(single, pair, seq_mask, d_act, d_rigids, *, depth=8, we
     return d_single, d_pair
 
 
-def post_trunk_weights(params: Dict[str, torch.Tensor], tables: Dict[str, torch.Tensor], out_dir: Optional[str] = None) -> str:
+def monomer_structure_params_to_multimer(flat: Dict[str, np.ndarray], heads: int = 12) -> Dict[str, np.ndarray]:
+    """Monomer (``alphafold2_ptm``) structure-module parameters in the layout the kernels read.
+
+    The monomer checkpoint fuses the IPA projections (``q_scalar``, ``kv_scalar``, ``q_point_local``,
+    ``kv_point_local``) and calls the backbone update ``affine_update``; the multimer model, and this library, have one
+    Linear per role with a per-head layout.  The reference converts while writing its post-trunk manifest
+    (bindcraft/af/native.py:365-411); this is the same mapping on a flat ``{'param/...': array}`` dict:
+
+    * scalar projections ``[in, heads*w]`` -> ``[in, heads, w]``, split along w into q (16) or k (16) | v (16);
+    * point projections ``[in, 3*heads*p]`` stored coordinate-major (x of all heads and points, then y, then z) ->
+      ``[in, heads, 3*p]`` (per head: x of its points, y, z), split along p into q (4) or k (4) | v (8);
+    * ``affine_update`` -> ``quat_rigid/rigid``.
+
+    Entries that are already in the multimer layout are left alone."""
+    out = dict(flat)
+    ipa = 'param/fold_iteration/invariant_point_attention/'
+    for fused, roles in (('q_scalar', (('q_scalar_projection', 16),)),
+                         ('kv_scalar', (('k_scalar_projection', 16), ('v_scalar_projection', 16)))):
+        if ipa + fused + '/weights' not in out:
+            continue
+        w = np.asarray(out.pop(ipa + fused + '/weights'), np.float32)
+        b = np.asarray(out.pop(ipa + fused + '/bias'), np.float32)
+        w = w.reshape(w.shape[0], heads, -1)
+        b = b.reshape(heads, -1)
+        lo = 0
+        for role, width in roles:
+            out[f'{ipa}{role}/weights'] = np.ascontiguousarray(w[:, :, lo:lo + width])
+            out[f'{ipa}{role}/bias'] = np.ascontiguousarray(b[:, lo:lo + width])
+            lo += width
+    for fused, roles in (('q_point_local', (('q_point_projection/point_projection', 4),)),
+                         ('kv_point_local', (('k_point_projection/point_projection', 4),
+                                             ('v_point_projection/point_projection', 8)))):
+        if ipa + fused + '/weights' not in out:
+            continue
+        w = np.asarray(out.pop(ipa + fused + '/weights'), np.float32)
+        b = np.asarray(out.pop(ipa + fused + '/bias'), np.float32)
+        n_in = w.shape[0]
+        w = w.reshape(n_in, 3, heads, -1).transpose(0, 2, 1, 3)   # [in, head, coordinate, point]
+        b = b.reshape(3, heads, -1).transpose(1, 0, 2)
+        lo = 0
+        for role, pts in roles:
+            out[f'{ipa}{role}/weights'] = np.ascontiguousarray(w[:, :, :, lo:lo + pts].reshape(n_in, heads, 3 * pts))
+            out[f'{ipa}{role}/bias'] = np.ascontiguousarray(b[:, :, lo:lo + pts].reshape(heads, 3 * pts))
+            lo += pts
+    old, new = 'param/fold_iteration/affine_update/', 'param/fold_iteration/quat_rigid/rigid/'
+    if old + 'weights' in out:
+        out[new + 'weights'] = out.pop(old + 'weights')
+        out[new + 'bias'] = out.pop(old + 'bias')
+    return out
+
+
+def post_trunk_weights(params: Dict[str, torch.Tensor], tables: Dict[str, torch.Tensor], out_dir: Optional[str] = None,
+                       position_scale: Optional[float] = None) -> str:
     """Post-trunk manifest: ``param/...`` weights plus the ``const/...`` residue tables, the layout of the reference's
-    ``post_weights_from_params`` (bindcraft/af/native.py:339-444)."""
+    ``post_weights_from_params`` (bindcraft/af/native.py:339-444).  ``position_scale`` (or a ``position_scale`` entry of
+    ``params``) selects the units of the frames: 20 for the multimer model (the default when absent), 10 for the
+    monomer model (config.py:595 / :357; the reference's native fold iteration keeps it as ``pos_scale``).  Monomer
+    parameters in their fused layout are converted with ``monomer_structure_params_to_multimer``."""
     out = out_dir or tempfile.mkdtemp(prefix='bc2_native_')
+    params = dict(params)
+    if 'position_scale' in params:
+        position_scale = float(params.pop('position_scale'))
     arrays = {'param/' + k: v.detach().cpu().numpy() for k, v in params.items()}
+    arrays = monomer_structure_params_to_multimer(arrays)
     arrays.update({'const/' + k: v.detach().cpu().float().numpy() for k, v in tables.items()})
+    if position_scale is not None:
+        arrays['const/position_scale'] = np.asarray([position_scale], np.float32)
     return write_manifest(arrays, out)
 
 

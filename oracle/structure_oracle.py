@@ -68,8 +68,13 @@ def invariant_point_attention(p: Params, act, pair_ln, mask, rot, trans):
     k_pt, _ = point_projection(p, 'k_point_projection', act, rot, trans, POINT_QK)
     d2 = ((q_pt[:, None] - k_pt[None, :]) ** 2).sum(-1)                      # [q, k, H, P]
     logits = -0.5 * (point_w[:, None] * d2).sum(-1)                          # [q, k, H]
-    q_s = (act @ p[f'{IPA}/q_scalar_projection/weights'].reshape(C_S, -1)).reshape(n, HEADS, SCALAR_QK)
-    k_s = (act @ p[f'{IPA}/k_scalar_projection/weights'].reshape(C_S, -1)).reshape(n, HEADS, SCALAR_QK)
+    def scalar(name, width):
+        # no bias in the multimer model (folding_multimer.py:236-247); the monomer checkpoint carries one (optional entry)
+        y = (act @ p[f'{IPA}/{name}/weights'].reshape(C_S, -1)).reshape(n, HEADS, width)
+        b = p.get(f'{IPA}/{name}/bias')
+        return y if b is None else y + b.reshape(HEADS, width)
+    q_s = scalar('q_scalar_projection', SCALAR_QK)
+    k_s = scalar('k_scalar_projection', SCALAR_QK)
     q_s = q_s * math.sqrt(1.0 / SCALAR_QK)
     logits = logits + torch.einsum('qhc,khc->qkh', q_s, k_s)
     logits = logits + pair_ln @ p[f'{IPA}/attention_2d/weights'] + p[f'{IPA}/attention_2d/bias']
@@ -77,7 +82,7 @@ def invariant_point_attention(p: Params, act, pair_ln, mask, rot, trans):
     logits = logits - 1e5 * (1.0 - m2[..., None])
     logits = logits * math.sqrt(1.0 / 3)
     attn = torch.softmax(logits, dim=1)                                      # over keys
-    v_s = (act @ p[f'{IPA}/v_scalar_projection/weights'].reshape(C_S, -1)).reshape(n, HEADS, SCALAR_V)
+    v_s = scalar('v_scalar_projection', SCALAR_V)
     res_scalar = torch.einsum('qkh,khc->qhc', attn, v_s).reshape(n, -1)
     v_pt, _ = point_projection(p, 'v_point_projection', act, rot, trans, POINT_V)
     res_pt_glob = torch.einsum('qkh,khpa->qhpa', attn, v_pt)                 # [N, H, P, 3]
@@ -134,7 +139,9 @@ def structure_core(p: Params, single, pair, seq_mask, depth=NUM_LAYER, dropout_s
     for it in range(depth):
         drop = None if dropout_seed is None else fold_dropout_masks(dropout_seed, it, n, act.shape[-1])
         act, rot, trans = fold_iteration(p, act, rot, trans, pair_ln, seq_mask, drop)
-    return act, rot, trans * POSITION_SCALE
+    # 20 in the multimer model, 10 in the monomer model (config.py:595 / :357); an optional entry of the parameter dict
+    scale = float(p['position_scale']) if 'position_scale' in p else POSITION_SCALE
+    return act, rot, trans * scale
 
 
 def structure_core_fwd_bwd(p: Params, inp, depth=NUM_LAYER, dtype=torch.float32):

@@ -122,6 +122,25 @@ def test_post_trunk_matches_oracle(lib, tmp_path, n, depth, masked):
     _check(got, want, f'post-trunk N={n} depth={depth}')
 
 
+def test_post_trunk_monomer_position_scale(lib, tmp_path):
+    """The monomer model's structure module: frame units of 10 instead of 20 (selected through the manifest) and biases
+    on the scalar q/k/v projections of the point attention (present in that checkpoint only)."""
+    n, depth = 40, 2
+    params = synthetic.add_structure_head_params(synthetic.make_structure_params(451), 452)
+    params['position_scale'] = torch.tensor(10.0)
+    g = torch.Generator().manual_seed(456)
+    for role in 'qkv':
+        params[f'fold_iteration/invariant_point_attention/{role}_scalar_projection/bias'] = 0.3 * torch.randn(12, 16, generator=g)
+    tables = synthetic.make_structure_tables(453)
+    inp = synthetic.add_structure_head_inputs(synthetic.make_structure_inputs(454, n, masked=3), 455)
+    got, _ = _run_heads(lib, params, tables, inp, depth, tmp_path)
+    want = SO.structure_heads_fwd_bwd(params, tables, inp, depth=depth)
+    _check(got, want, 'post-trunk position_scale 10')
+    params20 = {k: v for k, v in params.items() if k != 'position_scale'}
+    other = SO.structure_heads_fwd_bwd(params20, tables, inp, depth=depth)
+    assert SO.rel_l2(other['atom14'], want['atom14']) > 1e-2  # the two settings give different atoms
+
+
 def test_post_trunk_dropout_masks(lib, tmp_path):
     """Enable word set: every fold iteration drops its activation twice with the reference's hash masks (elementwise,
     rate 0.1, native/foldit.cuh:152-166), in the forward and in the replayed backward.  Enable word clear: exactly the

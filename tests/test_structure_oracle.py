@@ -113,3 +113,49 @@ def test_sidechain_atoms_follow_the_backbone_frame():
     moved = SO.sidechain_atoms(p, tables, act, ini, G @ rot, trans @ G.T + t, aatype)
     mask = tables['atom14_mask'].double()[aatype][..., None]
     assert torch.allclose(moved, (base @ G.T + t) * mask, atol=1e-9)
+
+
+def test_monomer_ipa_layout_conversion_roundtrip():
+    """``native.monomer_structure_params_to_multimer`` (reference: bindcraft/af/native.py:365-411): fuse the per-role
+    projections of a synthetic multimer-layout parameter set into the monomer checkpoint layout with an independently
+    written inverse, convert, and get the originals back."""
+    import numpy as np
+    from bindcraft2_b200 import native, synthetic
+    heads = 12
+    src = {'param/' + k: v.numpy() for k, v in synthetic.make_structure_params(77).items()}
+    ipa = 'param/fold_iteration/invariant_point_attention/'
+    rng = np.random.default_rng(5)
+    for role, width in (('q', 16), ('k', 16), ('v', 16)):  # the monomer checkpoint has biases on the scalar projections
+        src[f'{ipa}{role}_scalar_projection/bias'] = rng.standard_normal((heads, width)).astype(np.float32)
+    fused = {k: v for k, v in src.items() if 'scalar_projection' not in k and 'point_projection' not in k and 'quat_rigid' not in k}
+    n_in = src[ipa + 'q_scalar_projection/weights'].shape[0]
+
+    def scal(names):
+        w = np.concatenate([src[ipa + n + '/weights'].reshape(n_in, heads, -1) for n in names], -1)
+        b = np.concatenate([src[ipa + n + '/bias'].reshape(heads, -1) for n in names], -1)
+        return w.reshape(n_in, -1), b.reshape(-1)
+
+    def pts(names):
+        ws, bs = [], []
+        for n in names:
+            w = src[ipa + n + '/point_projection/weights']           # [in, heads, 3*p]: per head x.., y.., z..
+            b = src[ipa + n + '/point_projection/bias']
+            ws.append(w.reshape(n_in, heads, 3, -1))
+            bs.append(b.reshape(heads, 3, -1))
+        w = np.concatenate(ws, -1).transpose(0, 2, 1, 3)             # [in, 3, heads, points of all roles]
+        b = np.concatenate(bs, -1).transpose(1, 0, 2)
+        return w.reshape(n_in, -1), b.reshape(-1)
+
+    fused[ipa + 'q_scalar/weights'], fused[ipa + 'q_scalar/bias'] = scal(['q_scalar_projection'])
+    fused[ipa + 'kv_scalar/weights'], fused[ipa + 'kv_scalar/bias'] = scal(['k_scalar_projection', 'v_scalar_projection'])
+    fused[ipa + 'q_point_local/weights'], fused[ipa + 'q_point_local/bias'] = pts(['q_point_projection'])
+    fused[ipa + 'kv_point_local/weights'], fused[ipa + 'kv_point_local/bias'] = pts(['k_point_projection', 'v_point_projection'])
+    for nm in ('weights', 'bias'):
+        fused['param/fold_iteration/affine_update/' + nm] = src['param/fold_iteration/quat_rigid/rigid/' + nm]
+    back = native.monomer_structure_params_to_multimer(fused, heads)
+    assert sorted(back) == sorted(src)
+    for k in src:
+        np.testing.assert_array_equal(back[k].reshape(src[k].shape), src[k], err_msg=k)
+    # a set already in the multimer layout passes through untouched
+    same = native.monomer_structure_params_to_multimer(src, heads)
+    assert all(same[k] is src[k] for k in src)
