@@ -34,9 +34,9 @@ PROTOTYPES = {
     'bc2_shard_unique_id': (_i32, [_vp]),
     'bc2_shard_init': (_i32, [_i32, _i32, _vp]),
     'bc2_shard_finalize': (None, []),
-    'bc2_evoformer_sharded_fwd': (_i32, [_vp] * 5 + [_i64] * 4 + [_cp] + [_vp] * 4),
-    'bc2_evoformer_sharded_bwd': (_i32, [_vp] * 7 + [_i64] * 3 + [_cp] + [_vp] * 2),
-    'bc2_test_sharded_local': (_i32, [_i32] + [_vp] * 6 + [_i64] * 3 + [_cp] + [_vp] * 4),
+    'bc2_evoformer_sharded_fwd': (_i32, [_vp] * 6 + [_i64] * 5 + [_cp] + [_vp] * 4),
+    'bc2_evoformer_sharded_bwd': (_i32, [_vp] * 8 + [_i64] * 4 + [_cp] + [_vp] * 2),
+    'bc2_test_sharded_local': (_i32, [_i32] + [_vp] * 7 + [_i64] * 4 + [_cp] + [_vp] * 4),
     'bc2_release_all': (None, []),
     'bc2_last_error': (_cp, []),
     'bc2_device_status': (_i32, []),

@@ -485,16 +485,18 @@ void bc2_shard_finalize(void) {
 }
 
 int bc2_evoformer_sharded_fwd(void* stream, const float* pair_band, const float* msa, const float* pair_mask,
-                              const float* msa_mask, int64_t N, int64_t S, int64_t depth, int64_t save,
-                              const char* weights_dir, float* pair_out_band, float* msa_out, uint16_t* psave_band,
-                              float* msave) {
+                              const float* msa_mask, const uint32_t* seed, int64_t N, int64_t S, int64_t depth,
+                              int64_t save, int64_t dropout, const char* weights_dir, float* pair_out_band,
+                              float* msa_out, uint16_t* psave_band, float* msave) {
   try {
     BC2_CHECK(pair_band && msa && pair_mask && msa_mask && pair_out_band && msa_out && weights_dir, "null operand");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     BC2_CHECK(!save || (psave_band && msave), "save != 0 needs psave and msave");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     ShardedEvoStack* s = get_sharded((int)N, (int)S, (int)depth, weights_dir);
     s->forward(pair_band, msa, pair_mask, msa_mask, pair_out_band, msa_out,
-               save ? reinterpret_cast<bf16*>(psave_band) : nullptr, save ? msave : nullptr, (cudaStream_t)stream);
+               save ? reinterpret_cast<bf16*>(psave_band) : nullptr, save ? msave : nullptr, (cudaStream_t)stream,
+               dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -503,15 +505,17 @@ int bc2_evoformer_sharded_fwd(void* stream, const float* pair_band, const float*
 }
 
 int bc2_evoformer_sharded_bwd(void* stream, const float* ct_pair_band, const float* ct_msa, const float* pair_mask,
-                              const float* msa_mask, const uint16_t* psave_band, const float* msave, int64_t N, int64_t S,
-                              int64_t depth, const char* weights_dir, float* dpair_band, float* dmsa) {
+                              const float* msa_mask, const uint16_t* psave_band, const float* msave, const uint32_t* seed,
+                              int64_t N, int64_t S, int64_t depth, int64_t dropout, const char* weights_dir,
+                              float* dpair_band, float* dmsa) {
   try {
     BC2_CHECK(ct_pair_band && ct_msa && pair_mask && msa_mask && psave_band && msave && dpair_band && dmsa && weights_dir,
               "null operand");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     ShardedEvoStack* s = get_sharded((int)N, (int)S, (int)depth, weights_dir);
     s->backward(ct_pair_band, ct_msa, pair_mask, msa_mask, reinterpret_cast<const bf16*>(psave_band), msave, dpair_band, dmsa,
-                (cudaStream_t)stream);
+                (cudaStream_t)stream, dropout != 0, seed);
     BC2_CUDA(cudaGetLastError());
     return 0;
   } catch (const std::exception& e) {
@@ -520,12 +524,14 @@ int bc2_evoformer_sharded_bwd(void* stream, const float* ct_pair_band, const flo
 }
 
 int bc2_test_sharded_local(int P, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
-                           const float* ct_pair, const float* ct_msa, int64_t N, int64_t S, int64_t depth,
-                           const char* weights_dir, float* pair_out, float* msa_out, float* dpair, float* dmsa) {
+                           const float* ct_pair, const float* ct_msa, const uint32_t* seed, int64_t N, int64_t S,
+                           int64_t depth, int64_t dropout, const char* weights_dir, float* pair_out, float* msa_out,
+                           float* dpair, float* dmsa) {
   try {
     BC2_CHECK(pair && msa && pair_mask && msa_mask && ct_pair && ct_msa && pair_out && msa_out && dpair && dmsa && weights_dir,
               "null operand");
     BC2_CHECK(P >= 1 && P <= kMaxLocalRanks, "1 to 8 local ranks");
+    BC2_CHECK(!dropout || seed, "dropout != 0 needs the {seed, enabled} words");
     std::lock_guard<std::recursive_mutex> lock(g_mu);
     int dev = 0;
     BC2_CUDA(cudaGetDevice(&dev));
@@ -563,8 +569,10 @@ int bc2_test_sharded_local(int P, const float* pair, const float* msa, const flo
           BC2_CUDA(cudaSetDevice(dev));
           ShardedEvoStack* s = stacks[r].get();
           cudaStream_t st = streams[r];
-          s->forward(pair + r * band, msa, pair_mask, msa_mask, pair_out + r * band, mo[r], psave[r], msave[r], st);
-          s->backward(ct_pair + r * band, ct_msa, pair_mask, msa_mask, psave[r], msave[r], dpair + r * band, dm[r], st);
+          s->forward(pair + r * band, msa, pair_mask, msa_mask, pair_out + r * band, mo[r], psave[r], msave[r], st,
+                     dropout != 0, seed);
+          s->backward(ct_pair + r * band, ct_msa, pair_mask, msa_mask, psave[r], msave[r], dpair + r * band, dm[r], st,
+                      dropout != 0, seed);
           BC2_CUDA(cudaStreamSynchronize(st));
           BC2_CUDA(cudaGetLastError());
         } catch (const std::exception& e) {

@@ -19,7 +19,9 @@
 //                           transposed mask, and its output is transposed back and added; backward mirrors that
 //   transitions             none
 // Exchange objects: shard_comm.cuh.  Everything runs on the caller's stream in program order (no side stream yet).
-// Dropout is not supported here (the sites' tables are indexed by whole-tensor residue numbers).
+// Dropout: the same counter-hash tables as EvoStack.  The masks shared over rows are indexed by the column of a
+// position, which a band of whole rows keeps; the ending-node mask is shared over columns, i.e. indexed by the ROW of
+// the original position, which is the column of the transposed band the module runs on: the same indexing again.
 #pragma once
 #include "stack.cuh"
 
@@ -67,6 +69,41 @@ struct ShardedEvoStack {
   float* tstage[2] = {nullptr, nullptr};
   float *pp[2] = {nullptr, nullptr}, *mp[2] = {nullptr, nullptr};
   size_t weight_bytes = 0;
+  float* drop_tab = nullptr;  // [depth][5 sites] tables of scales, as in EvoStack
+  long drop_per_block = 0;
+  bool dropping = false;
+
+  void prepare_dropout(bool dropout, const uint32_t* seed, cudaStream_t st) {
+    dropping = dropout && seed != nullptr;
+    if (!dropping) {
+      tmo.drop = tmi.drop = tas.drop = tae.drop = row.drop = DropSite{};
+      return;
+    }
+    DropTableArgs a{};
+    a.blocks = cfg.depth; a.n = cfg.N; a.sites = 5; a.seed = seed;
+    const int widths[5] = {cfg.Cz, cfg.Cz, cfg.Cz, cfg.Cz, cfg.Cm};
+    const int mods[5] = {2, 3, 4, 5, 1};  // tri-mul out, in, attention start, end, MSA row (native/block.cuh:70-75)
+    long per = 0;
+    for (int t = 0; t < 5; ++t) {
+      a.width[t] = widths[t]; a.mod[t] = mods[t]; a.rate[t] = t == 4 ? 0.15f : 0.25f;
+      per += (long)cfg.N * widths[t];
+    }
+    a.per_block = drop_per_block = per;
+    if (!drop_tab) drop_tab = A.alloc<float>(per * cfg.depth);
+    a.tab = drop_tab;
+    launch_counter()++;
+    drop_tables_kernel<<<ew_grid(per * cfg.depth, 256), 256, 0, st>>>(a);
+  }
+  void set_drop_sites(int b) {
+    if (!dropping) return;
+    float* t = drop_tab + (long)b * drop_per_block;
+    const long np = (long)cfg.N * cfg.Cz;
+    tmo.drop = DropSite{t, cfg.N, 0};
+    tmi.drop = DropSite{t + np, cfg.N, 0};
+    tas.drop = DropSite{t + 2 * np, cfg.N, 0};
+    tae.drop = DropSite{t + 3 * np, cfg.N, 0};  // on the transposed band: unit = column there = row of the original
+    row.drop = DropSite{t + 4 * np, cfg.N, 0};
+  }
 
   ShardedEvoStack(const StackConfig& c, const std::string& weights_dir, ShardComm* comm_) : cfg(c), comm(comm_) {
     BC2_CHECK(comm_, "the sharded stack needs an exchange object");
@@ -162,6 +199,7 @@ struct ShardedEvoStack {
   // p_in / p_out: bands; m_in / m_out: whole msa.  tail = false skips the two GEMMs only the next block would read.
   void block_forward(int b, const float* p_in, const float* m_in, float* p_out, float* m_out, cudaStream_t st, bool tail = true) {
     const float* mask_band = pair_mask + (long)row0 * cfg.N;
+    set_drop_sites(b);
     opm.forward(b, m_in, p_in, Pb[1], st);
     row.forward(b, m_in, Mx[1], Pb[1], st);
     col.forward(b, Mx[1], Mx[2], st);
@@ -178,6 +216,7 @@ struct ShardedEvoStack {
   // needs the module buffers (and XT) as block_forward(b, ...) left them; cotangents are updated in place
   void block_backward(int b, const float* m_in, float* g_pair, float* g_msa, cudaStream_t st) {
     const float* mask_band = pair_mask + (long)row0 * cfg.N;
+    set_drop_sites(b);
     mtrans.backward(b, Mx[2], g_msa, st);
     col.backward(b, Mx[1], g_msa, st);
     ptrans.backward(b, Pb[5], g_pair, st);
@@ -194,8 +233,9 @@ struct ShardedEvoStack {
 
   // pair / pair_out / psave: this rank's band ([R][N][Cz]; psave [depth] of them in bf16); msa, masks, msave: whole.
   void forward(const float* pair, const float* msa, const float* pm, const float* mm, float* pair_out, float* msa_out,
-               bf16* psave, float* msave, cudaStream_t st) {
+               bf16* psave, float* msave, cudaStream_t st, bool dropout = false, const uint32_t* seed = nullptr) {
     set_masks(pm, mm, st);
+    prepare_dropout(dropout, seed, st);
     const long np = Mb * cfg.Cz, nm = Mm * cfg.Cm;
     const float *pc = pair, *mc = msa;
     for (int i = 0; i < cfg.depth; ++i) {
@@ -212,8 +252,10 @@ struct ShardedEvoStack {
     }
   }
   void backward(const float* ct_pair, const float* ct_msa, const float* pm, const float* mm, const bf16* psave,
-                const float* msave, float* dpair, float* dmsa, cudaStream_t st) {
+                const float* msave, float* dpair, float* dmsa, cudaStream_t st, bool dropout = false,
+                const uint32_t* seed = nullptr) {
     set_masks(pm, mm, st);
+    prepare_dropout(dropout, seed, st);
     const long np = Mb * cfg.Cz, nm = Mm * cfg.Cm;
     if (dpair != ct_pair) BC2_CUDA(cudaMemcpyAsync(dpair, ct_pair, np * 4, cudaMemcpyDeviceToDevice, st));
     if (dmsa != ct_msa) BC2_CUDA(cudaMemcpyAsync(dmsa, ct_msa, nm * 4, cudaMemcpyDeviceToDevice, st));

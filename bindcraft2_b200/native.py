@@ -211,11 +211,12 @@ def band_of(n: int, world: int, rank: int):
     return rank * r, (rank + 1) * r
 
 
-def sharded_evoformer_fwd(pair_band, msa, pair_mask, msa_mask, *, depth, save, weights_dir):
+def sharded_evoformer_fwd(pair_band, msa, pair_mask, msa_mask, *, depth, save, weights_dir, seed=None, dropout=0):
     """Forward of the main stack on this rank's band of pair rows (collective: every rank of the group calls it).
 
     pair_band f32 [N/world, N, 128]; msa [S, N, 256], pair_mask [N, N], msa_mask [S, N] whole and identical on all
-    ranks.  Returns (pair_out_band, msa_out, psave_band bf16 [depth, N/world, N, 128], msave f32 [depth, S, N, 256])."""
+    ranks.  ``seed`` / ``dropout`` as in ``evoformer_fwd`` (identical on every rank).  Returns (pair_out_band, msa_out,
+    psave_band bf16 [depth, N/world, N, 128], msave f32 [depth, S, N, 256])."""
     lib = _lib.load()
     r, n, s = int(pair_band.shape[0]), int(pair_band.shape[1]), int(msa.shape[0])
     _check_f32('pair_band', pair_band, (r, n, CZ))
@@ -229,13 +230,15 @@ def sharded_evoformer_fwd(pair_band, msa, pair_mask, msa_mask, *, depth, save, w
     msave = torch.empty((slots, s, n, CM), dtype=torch.float32, device=pair_band.device)
     stream = torch.cuda.current_stream(pair_band.device).cuda_stream
     with torch.cuda.device(pair_band.device):
-        _lib.check(lib.bc2_evoformer_sharded_fwd(stream, _ptr(pair_band), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask), n, s,
-                                                 int(depth), int(save), os.fsencode(weights_dir), _ptr(pair_out),
+        _lib.check(lib.bc2_evoformer_sharded_fwd(stream, _ptr(pair_band), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask),
+                                                 _ptr(seed), n, s, int(depth), int(save), int(dropout),
+                                                 os.fsencode(weights_dir), _ptr(pair_out),
                                                  _ptr(msa_out), _ptr(psave) if save else 0, _ptr(msave) if save else 0))
     return pair_out, msa_out, psave, msave
 
 
-def sharded_evoformer_bwd(ct_pair_band, ct_msa, pair_mask, msa_mask, psave, msave, *, depth, weights_dir):
+def sharded_evoformer_bwd(ct_pair_band, ct_msa, pair_mask, msa_mask, psave, msave, *, depth, weights_dir, seed=None,
+                          dropout=0):
     """Backward of ``sharded_evoformer_fwd``: (dpair_band, dmsa).  Pure: reads only its operands."""
     lib = _lib.load()
     r, n, s = int(ct_pair_band.shape[0]), int(ct_pair_band.shape[1]), int(ct_msa.shape[0])
@@ -248,12 +251,13 @@ def sharded_evoformer_bwd(ct_pair_band, ct_msa, pair_mask, msa_mask, psave, msav
     stream = torch.cuda.current_stream(ct_pair_band.device).cuda_stream
     with torch.cuda.device(ct_pair_band.device):
         _lib.check(lib.bc2_evoformer_sharded_bwd(stream, _ptr(ct_pair_band), _ptr(ct_msa), _ptr(pair_mask), _ptr(msa_mask),
-                                                 _ptr(psave), _ptr(msave), n, s, int(depth), os.fsencode(weights_dir),
-                                                 _ptr(dpair), _ptr(dmsa)))
+                                                 _ptr(psave), _ptr(msave), _ptr(seed), n, s, int(depth), int(dropout),
+                                                 os.fsencode(weights_dir), _ptr(dpair), _ptr(dmsa)))
     return dpair, dmsa
 
 
-def sharded_local_step(world, pair, msa, pair_mask, msa_mask, ct_pair, ct_msa, *, depth, weights_dir):
+def sharded_local_step(world, pair, msa, pair_mask, msa_mask, ct_pair, ct_msa, *, depth, weights_dir, seed=None,
+                       dropout=0):
     """Test helper: the sharded stack with its ``world`` ranks as host threads on the current GPU, forward + backward on
     whole tensors.  Returns (pair_out, msa_out, dpair, dmsa) laid out like ``evoformer_fwd`` / ``evoformer_bwd``."""
     lib = _lib.load()
@@ -267,7 +271,8 @@ def sharded_local_step(world, pair, msa, pair_mask, msa_mask, ct_pair, ct_msa, *
     torch.cuda.synchronize(pair.device)
     with torch.cuda.device(pair.device):
         _lib.check(lib.bc2_test_sharded_local(int(world), _ptr(pair), _ptr(msa), _ptr(pair_mask), _ptr(msa_mask),
-                                              _ptr(ct_pair), _ptr(ct_msa), n, s, int(depth), os.fsencode(weights_dir),
+                                              _ptr(ct_pair), _ptr(ct_msa), _ptr(seed), n, s, int(depth), int(dropout),
+                                              os.fsencode(weights_dir),
                                               *[_ptr(o) for o in outs]))
     return tuple(outs)
 

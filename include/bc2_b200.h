@@ -206,7 +206,8 @@ int64_t bc2_profile_report(char* buf, int64_t cap);
 /* ---- one long complex over several GPUs: the pair representation sharded by rows ------------------------------ */
 /* No counterpart in the reference (it runs a complex on one GPU, bindcraft/af/native.py:906-975, and parallelises over
  * trajectories, bindcraft/design_workers.py).  One process per GPU; rank r of `world` holds the band of N/world pair
- * rows starting at r*N/world.  Block arithmetic is that of bc2_evoformer_fwd/bwd (multimer block order, dropout off).
+ * rows starting at r*N/world.  Block arithmetic is that of bc2_evoformer_fwd/bwd (multimer block order; seed / dropout
+ * as there: seed u32 {seed, enabled} on the device, identical on every rank).
  * Exchange steps (NCCL, bound at run time from libnccl.so.2): all-to-all for the row <-> column transposes of the
  * ending-node attention and for the row-band <-> channel-group relayout of the triangle-multiplication planes,
  * all-gather for the attention pair biases and the outer-product cotangent, a float sum for the bias gradients. */
@@ -224,14 +225,15 @@ void bc2_shard_finalize(void);
  * [depth][N/world][N][128], msave f32 [depth][S][N][256].  Collective over the group: every rank calls it with the same
  * N, S, depth and weights.  N must be a multiple of 32 and of 8*world. */
 int bc2_evoformer_sharded_fwd(void* stream, const float* pair_band, const float* msa, const float* pair_mask,
-                              const float* msa_mask, int64_t N, int64_t S, int64_t depth, int64_t save,
-                              const char* weights_dir, float* pair_out_band, float* msa_out, uint16_t* psave_band,
-                              float* msave);
+                              const float* msa_mask, const uint32_t* seed, int64_t N, int64_t S, int64_t depth,
+                              int64_t save, int64_t dropout, const char* weights_dir, float* pair_out_band,
+                              float* msa_out, uint16_t* psave_band, float* msave);
 /* Pure like bc2_evoformer_bwd: reads only its operands.  dpair_band f32 [N/world][N][128], dmsa f32 [S][N][256] (whole;
  * equal on every rank up to the order of floating-point sums). */
 int bc2_evoformer_sharded_bwd(void* stream, const float* ct_pair_band, const float* ct_msa, const float* pair_mask,
-                              const float* msa_mask, const uint16_t* psave_band, const float* msave, int64_t N, int64_t S,
-                              int64_t depth, const char* weights_dir, float* dpair_band, float* dmsa);
+                              const float* msa_mask, const uint16_t* psave_band, const float* msave, const uint32_t* seed,
+                              int64_t N, int64_t S, int64_t depth, int64_t dropout, const char* weights_dir,
+                              float* dpair_band, float* dmsa);
 
 /* ---- bring-up / unit-test entry points (not part of the reference surface) ------------------------------------ */
 
@@ -260,8 +262,9 @@ int bc2_test_attention(void* stream, const uint16_t* qkvg, const float* bias, co
  * host barriers): forward + backward of whole tensors, for checking the partitioned path against bc2_evoformer_fwd/bwd
  * on a single GPU.  Operands and results are whole tensors laid out as in bc2_evoformer_fwd/bwd. */
 int bc2_test_sharded_local(int P, const float* pair, const float* msa, const float* pair_mask, const float* msa_mask,
-                           const float* ct_pair, const float* ct_msa, int64_t N, int64_t S, int64_t depth,
-                           const char* weights_dir, float* pair_out, float* msa_out, float* dpair, float* dmsa);
+                           const float* ct_pair, const float* ct_msa, const uint32_t* seed, int64_t N, int64_t S,
+                           int64_t depth, int64_t dropout, const char* weights_dir, float* pair_out, float* msa_out,
+                           float* dpair, float* dmsa);
 
 /* Gated attention forward that allocates nothing.  No counterpart in the reference.
  * For hosts that cannot allocate device memory when the call is made (inside a stream capture they do not own, after

@@ -90,3 +90,34 @@ def test_sharded_general_attention_kernels_n288(lib, tmp_path):
         assert rep[k][0] <= 1e-3, rep
     for k in ('d_pair', 'd_msa'):
         assert rep[k][0] <= REL_L2 and rep[k][1] >= COSINE, rep
+
+
+def test_sharded_dropout_uses_the_same_masks(lib, tmp_path):
+    """Dropout on (the native counter-hash masks): the sharded stack over two ranks and the unsharded stack get the same
+    {seed, enabled} words and must drop the same elements, including the ending-node mask, which the sharded stack
+    applies on the transposed band."""
+    n, s, depth = 128, 1, 2
+    params = synthetic.make_evoformer_params(611, depth)
+    inp = synthetic.make_block_inputs(612, n, s)
+    wdir = native.weights_from_flat(params, str(tmp_path / 'w'))
+    dev = 'cuda:0'
+    t = {k: v.to(dev).contiguous() for k, v in inp.items()}
+    seed = torch.tensor([1234, 1], dtype=torch.int32, device=dev)
+    kw = dict(depth=depth, weights_dir=wdir, dropout=1)
+    p, m, psave, msave = native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, save=1, own_save=0, **kw)
+    dp, dm = native.evoformer_bwd(t['ct_pair'], t['ct_msa'], t['pair_mask'], t['msa_mask'], psave, msave, seed, own_save=0, **kw)
+    p0, _, _, _ = native.evoformer_fwd(t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], seed, save=0, depth=depth,
+                                       weights_dir=wdir, dropout=0)
+    torch.cuda.synchronize()
+    one = dict(pair=p.cpu(), msa=m.cpu(), d_pair=dp.cpu(), d_msa=dm.cpu())
+    sp, sm, sdp, sdm = native.sharded_local_step(2, t['pair'], t['msa'], t['pair_mask'], t['msa_mask'], t['ct_pair'],
+                                                 t['ct_msa'], seed=seed, **kw)
+    torch.cuda.synchronize()
+    assert lib.bc2_device_status() == 0
+    many = dict(pair=sp.cpu(), msa=sm.cpu(), d_pair=sdp.cpu(), d_msa=sdm.cpu())
+    rep = _report('P=2 sharded vs one GPU, dropout on', many, one)
+    assert O.rel_l2(p.cpu(), p0.cpu()) > 1e-2  # the masks did something
+    for k in ('pair', 'msa'):
+        assert rep[k][0] <= 1e-3, rep
+    for k in ('d_pair', 'd_msa'):
+        assert rep[k][0] <= REL_L2 and rep[k][1] >= COSINE, rep

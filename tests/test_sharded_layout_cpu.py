@@ -119,6 +119,6 @@ def test_unique_id_and_uninitialised_call(lib):
     buf = (ctypes.c_uint8 * 128)()
     assert lib.bc2_shard_unique_id(ctypes.addressof(buf)) == 0
     assert any(buf)
-    rc = lib.bc2_evoformer_sharded_fwd(None, 1, 1, 1, 1, 64, 1, 1, 0, b'/nonexistent', 1, 1, None, None)
+    rc = lib.bc2_evoformer_sharded_fwd(None, 1, 1, 1, 1, None, 64, 1, 1, 0, 0, b'/nonexistent', 1, 1, None, None)
     assert rc != 0
     assert lib.bc2_last_error()
