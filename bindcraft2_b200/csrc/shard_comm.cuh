@@ -15,6 +15,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <condition_variable>
 #include <mutex>
 #include <vector>
@@ -144,6 +145,13 @@ struct NcclComm : ShardComm {
   std::vector<Shared> shared;
   float* flag = nullptr;              // barrier operand
   char* handles_dev = nullptr;        // P IPC handles
+  // The per-rank copies of one exchange are independent: they go round-robin onto a few side streams so that several
+  // copy engines (and the local and the remote paths) work at once; the caller's stream forks before and joins after.
+  // BC2_SHARD_COPY_STREAMS=k (k <= 8) turns that on; the default, 1, keeps them inline on the caller's stream.
+  static constexpr int kMaxCopyStreams = 8;
+  int n_copy = 1;
+  cudaStream_t copy_st[kMaxCopyStreams] = {nullptr};
+  cudaEvent_t ev_fork = nullptr, ev_join[kMaxCopyStreams] = {nullptr};
 
   NcclComm(int world, int rank_, const ncclUniqueId& id) {
     P = world;
@@ -154,6 +162,15 @@ struct NcclComm : ShardComm {
     BC2_CUDA(cudaMalloc(&flag, 256));
     BC2_CUDA(cudaMemset(flag, 0, 256));
     BC2_CUDA(cudaMalloc(&handles_dev, sizeof(cudaIpcMemHandle_t) * (size_t)world));
+    if (const char* c = getenv("BC2_SHARD_COPY_STREAMS")) n_copy = std::max(1, std::min(atoi(c), (int)kMaxCopyStreams));
+    n_copy = std::min(n_copy, std::max(world, 1));
+    if (n_copy > 1) {
+      BC2_CUDA(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+      for (int i = 0; i < n_copy; ++i) {
+        BC2_CUDA(cudaStreamCreateWithFlags(&copy_st[i], cudaStreamNonBlocking));
+        BC2_CUDA(cudaEventCreateWithFlags(&ev_join[i], cudaEventDisableTiming));
+      }
+    }
   }
   // Orderly, collective teardown (every rank calls it): nobody frees a buffer a peer still has mapped.  A process that
   // ends without it leaves the memory to the driver's process cleanup; the destructor makes no collective call.
@@ -166,6 +183,13 @@ struct NcclComm : ShardComm {
     if (NcclApi::get().AllReduce(flag, flag, 1, ncclFloat, ncclSum, comm, nullptr) == ncclSuccess) cudaStreamSynchronize(nullptr);
     for (auto& sh : shared) cudaFree(sh.mine);
     shared.clear();
+    for (int i = 0; i < kMaxCopyStreams; ++i) {
+      if (copy_st[i]) cudaStreamDestroy(copy_st[i]);
+      if (ev_join[i]) cudaEventDestroy(ev_join[i]);
+      copy_st[i] = nullptr; ev_join[i] = nullptr;
+    }
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    ev_fork = nullptr;
     cudaFree(flag);
     cudaFree(handles_dev);
     if (NcclApi::get().CommDestroy) NcclApi::get().CommDestroy(comm);
@@ -211,14 +235,24 @@ struct NcclComm : ShardComm {
     if (!sh) return ShardComm::exchange_2d(src, ostride, sstride, spitch, dst, dstride, dpitch, width, height, stage, st);
     BC2_CHECK(off + (size_t)(P - 1) * (sstride + ostride) + (height - 1) * spitch + width <= sh->bytes, "exchange_2d: source range");
     barrier(st);
+    const bool fan = n_copy > 1;
+    if (fan) {
+      BC2_CUDA(cudaEventRecord(ev_fork, st));
+      for (int i = 0; i < n_copy; ++i) BC2_CUDA(cudaStreamWaitEvent(copy_st[i], ev_fork, 0));
+    }
     for (int i = 0; i < P; ++i) {
       const int r = (rank + i) % P;  // start with the local block, then walk the peers from different starting points
       char* d = static_cast<char*>(dst) + (size_t)r * dstride;
       const char* s_ = sh->peer[r] + off + (size_t)r * ostride + (size_t)rank * sstride;
       if (d == s_) continue;  // in-place all-gather: the local block is already there
       BC2_CUDA(cudaMemcpy2DAsync(d, height == 1 ? width : dpitch, s_, height == 1 ? width : spitch, width, height,
-                                 cudaMemcpyDefault, st));
+                                 cudaMemcpyDefault, fan ? copy_st[i % n_copy] : st));
     }
+    if (fan)
+      for (int i = 0; i < n_copy; ++i) {
+        BC2_CUDA(cudaEventRecord(ev_join[i], copy_st[i]));
+        BC2_CUDA(cudaStreamWaitEvent(st, ev_join[i], 0));
+      }
   }
   void all_to_all(const void* send, void* recv, size_t bytes, cudaStream_t st) override {
     NcclApi& n = NcclApi::get();
