@@ -2,12 +2,16 @@
 // N/P pair rows starting at r*N/P; the reference runs one complex on one GPU, bindcraft/af/native.py:906-975, so this
 // has no counterpart there).
 //
-// Three collectives are all the sharded stack needs: an all-to-all of equal chunks (row band <-> channel group of the
-// triangle-multiplication planes, row band <-> column band of the pair stream), an all-gather (attention pair bias,
-// outer-product cotangent) and a float sum (attention bias gradient).  Two carriers:
-//   NcclComm   one process per GPU; NCCL is bound at run time (dlopen of libnccl.so.2: the library keeps no link-time
+// All bulk traffic has one shape, exchange_2d(): from every rank a 2-D block (rows of a band, or of a group of planes)
+// lands at a strided place on this rank.  It covers the row band <-> channel group relayout of the triangle-
+// multiplication planes, the row band <-> column band transposes of the pair stream (both all-to-alls), and the
+// gathers of the attention pair bias and of the outer-product cotangent.  Besides it there is one float sum (attention
+// bias gradient).  Carriers:
+//   NcclComm   one process per GPU.  NCCL is bound at run time (dlopen of libnccl.so.2: the library keeps no link-time
 //              dependency on it and still loads where NCCL is absent); the unique id travels through the host
-//              framework's own process group.
+//              framework's own process group.  Bulk blocks are pulled from the peers' memory (CUDA IPC buffers) with
+//              copy-engine peer copies after one NCCL barrier; the packed send/receive path of the base class remains
+//              as the fallback.
 //   LocalComm  P ranks as P host threads of ONE process on ONE GPU, for tests on a single device: exchanges are
 //              device-to-device copies between the ranks' buffers behind host barriers.  No kernel ever waits on
 //              another kernel; only host threads wait, after synchronising their own stream.
