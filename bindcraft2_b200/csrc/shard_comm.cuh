@@ -151,9 +151,9 @@ struct NcclComm : ShardComm {
   char* handles_dev = nullptr;        // P IPC handles
   // The per-rank copies of one exchange are independent: they go round-robin onto a few side streams so that several
   // copy engines (and the local and the remote paths) work at once; the caller's stream forks before and joins after.
-  // BC2_SHARD_COPY_STREAMS=k (k <= 8) turns that on; the default, 1, keeps them inline on the caller's stream.
+  // BC2_SHARD_COPY_STREAMS=k sets their number (default 4, at most 8); 1 keeps the copies inline on the caller's stream.
   static constexpr int kMaxCopyStreams = 8;
-  int n_copy = 1;
+  int n_copy = 4;
   cudaStream_t copy_st[kMaxCopyStreams] = {nullptr};
   cudaEvent_t ev_fork = nullptr, ev_join[kMaxCopyStreams] = {nullptr};
 
