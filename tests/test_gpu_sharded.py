@@ -121,3 +121,13 @@ def test_sharded_dropout_uses_the_same_masks(lib, tmp_path):
         assert rep[k][0] <= 1e-3, rep
     for k in ('d_pair', 'd_msa'):
         assert rep[k][0] <= REL_L2 and rep[k][1] >= COSINE, rep
+
+
+def test_sharded_eight_ranks_n256(lib, tmp_path):
+    """The full box's partition on one GPU: eight ranks, bands of 32 rows, 16 tri-mul channels per rank."""
+    one, many, _, _ = _both(lib, tmp_path, 8, 256, 1, 1, wseed=701, iseed=702)
+    rep = _report('P=8 N=256 sharded vs one GPU', many, one)
+    for k in ('pair', 'msa'):
+        assert rep[k][0] <= 1e-3, rep
+    for k in ('d_pair', 'd_msa'):
+        assert rep[k][0] <= REL_L2 and rep[k][1] >= COSINE, rep
